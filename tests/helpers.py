@@ -1,0 +1,64 @@
+"""Shared helpers of the test-suite: fixture loading, spec construction, comparison metrics."""
+
+from __future__ import annotations
+
+import os
+
+import torch
+
+from oracle.kvm_oracle import KvmSpec
+
+GOLDEN = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
+SMALL_FIXTURES = ["fixed_gqa_fp32", "powerlaw_bf16", "plusone_bf16", "short_prompt_fp32", "saturation_bf16"]
+
+# stated bf16 tolerance of the activation / state comparison (max-abs, mean-relative)
+MAX_ABS_TOL = 2e-2
+MEAN_REL_TOL = 1e-3
+
+
+def load_fixture(name: str):
+    return torch.load(os.path.join(GOLDEN, f"{name}.pt"), weights_only=False)
+
+
+def spec_from_fixture(fix, device="cpu", dtype=None) -> KvmSpec:
+    cfg = fix["case"]["cfg"]
+    sd = fix["state_dict"]
+    H = cfg["num_attention_heads"]
+    Hkv = cfg.get("num_key_value_heads") or H
+    d = cfg["d_head"]
+
+    def p(name):
+        t = sd[name].to(device)
+        return t.to(dtype) if dtype is not None else t
+
+    return KvmSpec(
+        num_attention_heads=H, num_key_value_heads=Hkv, d_qk_head=d, d_v_head=d,
+        rope_partial_dim=cfg["rope_partial_dim"] if cfg["rope_partial_dim"] > 0 else d,
+        chunk_len=cfg["chunk_len"], n_bswa_chunks=cfg["n_bswa_chunks"], n_max_d_chunks=cfg["n_max_d_chunks"],
+        sink_len=cfg["sink_len"],
+        state_budget_mode="plus_one" if fix["case"].get("plus_one") else cfg["state_budget_mode"],
+        state_growth_factor=cfg.get("state_growth_factor", 1.0),
+        state_growth_exponent=cfg.get("state_growth_exponent", 0.5),
+        state_round_down=cfg.get("state_round_down", 1), state_min_len=cfg.get("state_min_len", -1),
+        state_saturation_n=cfg.get("state_saturation_n"),
+        kvm_apply_merge_gate_to_initial_state=cfg.get("kvm_apply_merge_gate_to_initial_state", 0),
+        kvm_apply_merge_gate_to_appends=cfg.get("kvm_apply_merge_gate_to_appends", 0),
+        ln_weight=p("ln_s_k.weight"), ln_bias=p("ln_s_k.bias"),
+        front_head_temp=p("front_head_temp"), state_head_temp=p("state_head_temp"),
+    )
+
+
+def max_abs(a: torch.Tensor, b: torch.Tensor) -> float:
+    return float((a.float() - b.float()).abs().max()) if a.numel() else 0.0
+
+
+def mean_rel(a: torch.Tensor, b: torch.Tensor) -> float:
+    """mean |a-b| / mean |b| (b is the reference side)."""
+    if not a.numel():
+        return 0.0
+    return float((a.float() - b.float()).abs().mean() / b.float().abs().mean().clamp_min(1e-12))
+
+
+def assert_close_bf16(a, b, what="", max_abs_tol=MAX_ABS_TOL, mean_rel_tol=MEAN_REL_TOL):
+    ma, mr = max_abs(a, b), mean_rel(a, b)
+    assert ma <= max_abs_tol and mr <= mean_rel_tol, f"{what}: max-abs {ma:.3e} (tol {max_abs_tol}), mean-rel {mr:.3e} (tol {mean_rel_tol})"
