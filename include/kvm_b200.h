@@ -1,0 +1,159 @@
+/*
+ * kvm_b200 -- C ABI of the B200 (sm_100a) Key-Value-Means sequence-mixer kernels.
+ *
+ * The reference project (SmerkyG/KVM-paper) has no FFI: its mixer is a Python class and its device
+ * code is Triton-in-Python.  The entry points below are what a binding for that hot path binds
+ * instead; each one cites the reference interface it replaces (path inside the reference project).
+ *
+ * Conventions
+ *   - every pointer named *_dev / documented "device" is a CUDA device pointer owned by the caller;
+ *     the library allocates nothing and keeps no state between calls;
+ *   - all activations and memory rows are bfloat16, lengths/norms fp32, indices int32;
+ *   - `stream` is a cudaStream_t passed as void* (NULL = default stream); calls only enqueue work;
+ *   - return value 0 = ok, otherwise one of KVM_ERR_*; kvm_last_error_string() describes the last
+ *     failure of the calling thread.  Argument errors are detected before anything is launched.
+ *   - "kv row" = one (batch, kv-head) pair, index b*Hkv + h;  "q row" = b*Hq + h.
+ */
+#ifndef KVM_B200_H_
+#define KVM_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define KVM_OK 0
+#define KVM_ERR_BAD_ARGUMENT 1
+#define KVM_ERR_CAPACITY 2
+#define KVM_ERR_DEVICE_TIMEOUT 3
+#define KVM_ERR_CUDA 4
+#define KVM_ERR_UNSUPPORTED 5
+
+/* Static description of one mixer layer: the fields the reference mixer reads from its config and
+ * parameters (model/kvm_mixer.py:79-118).  Device arrays are read by the kernels. */
+typedef struct kvm_layer {
+  int32_t n_q_heads;      /* Hq */
+  int32_t n_kv_heads;     /* Hkv, divides Hq */
+  int32_t head_dim;       /* D == Dv, one of 32, 64, 128 */
+  int32_t chunk_len;      /* C, block length; multiple of 16, <= 512 */
+  int32_t n_bswa_chunks;  /* W, blocks in the sliding window (>= 1) */
+  int32_t rope_dim;       /* leading key dims zeroed before the memory LayerNorm */
+  int32_t sink_len;       /* protected leading memory rows */
+  int32_t gate_keys;      /* kvm_use_merge_gate_keys */
+  int32_t gate_values;    /* kvm_use_merge_gate_values */
+  int32_t gate_appends;   /* kvm_apply_merge_gate_to_appends */
+  int32_t gate_initial;   /* kvm_apply_merge_gate_to_initial_state */
+  float ln_eps;           /* eps of ln_s_k */
+  const float* ln_weight_dev;   /* [D] fp32 copy of ln_s_k.weight */
+  const float* ln_bias_dev;     /* [D] */
+  const float* front_temp_dev;  /* [Hq] front_head_temp (ones if head temps are off) */
+  const float* state_temp_dev;  /* [Hq] state_head_temp */
+} kvm_layer;
+
+/* A strided bf16 tensor [B, H, T, D] with the last dimension contiguous (strides in elements).
+ * The reference hands the mixer transposed views of [B,T,H,D] projections (model/kvm_mixer.py:397-399). */
+typedef struct kvm_tensor4 {
+  const void* ptr;
+  int64_t stride_b, stride_h, stride_t;
+} kvm_tensor4;
+
+/* The compressed memory of one layer for `n_rows` kv rows, `capacity` rows each (device). */
+typedef struct kvm_memory {
+  void* k_sum;    /* [n_rows, capacity, D] bf16  sums of prepared keys  (reference cache entry kvm_s_k) */
+  void* v_sum;    /* [n_rows, capacity, D] bf16  sums of values         (kvm_s_v) */
+  float* vlen;    /* [n_rows, capacity]    fp32  value magnitudes       (kvm_s_vlen) */
+  void* k_attn;   /* [n_rows, capacity, D] bf16  LayerNorm(k_sum): the keys attention reads */
+  void* v_attn;   /* [n_rows, capacity, D] bf16  normalize(v_sum)*vlen: the values attention reads */
+  int32_t capacity;
+} kvm_memory;
+
+/* Per-update schedule entry (host computes it with the reference's own integer/float rules,
+ * model/kvm_mixer.py:131-172; the kernels only see the table).  Update u consumes the token block
+ * [u*C, (u+1)*C) and produces memory version u; version 0 is the initial memory. */
+typedef struct kvm_update_plan {
+  int32_t state_before;  /* rows before the update */
+  int32_t n_append;      /* 0..C rows appended (the least similar tokens), the rest are merged */
+  int32_t version_row;   /* first row of the version written after this update inside the version store */
+  int32_t reserved;
+} kvm_update_plan;
+
+/* Bytes of scratch kvm_prefill_forward needs for the given shape (versions + routing scratch).
+ * Replaces the workspace allocation inside build_prefill_forward
+ * (model/kernels/kvm_triton_training_kernels.py:3416-3448). */
+size_t kvm_prefill_workspace_bytes(const kvm_layer* layer, int32_t batch, int64_t seq_len,
+                                   int64_t total_version_rows);
+
+/* Whole-prompt prefill: front attention, block-recurrent memory updates and joint attention of
+ * every query block over [memory version ; sliding window].
+ * Replaces SequenceMixer.forward_prefill between the post-QKV tensors and the input of c_proj
+ * (model/kvm_mixer.py:403-492, model/kvm_triton_mixer.py:560-611) and the Triton host driver
+ * build_prefill_forward (model/kernels/kvm_triton_training_kernels.py:3386-3602).
+ *   q [B,Hq,T,D], k,v [B,Hkv,T,D], gate [B,Hkv,T,1] (stride_t in elements, last dim 1)
+ *   plan_dev     [n_updates+1] kvm_update_plan on the device; entry 0 describes the initial memory
+ *                (state_before = 0, n_append = min(T,C), version_row = 0)
+ *   plan_host    the same table in host memory (used for launch geometry only)
+ *   memory       receives the final memory (capacity >= final length), n_rows = B*Hkv
+ *   out          [B,T,Hq*D] bf16, contiguous
+ *   route_dev    optional [B*Hkv, n_updates+1, C] int32: for every token of every consumed block the
+ *                memory row it was merged into (>= 0) or -(1+row) if it was appended as that row
+ */
+int kvm_prefill_forward(const kvm_layer* layer, int32_t batch, int64_t seq_len,
+                        kvm_tensor4 q, kvm_tensor4 k, kvm_tensor4 v, kvm_tensor4 gate,
+                        const kvm_update_plan* plan_dev, const kvm_update_plan* plan_host,
+                        int32_t n_updates, int64_t total_version_rows,
+                        kvm_memory memory, void* out, int32_t* route_dev,
+                        void* workspace, size_t workspace_bytes, void* stream);
+
+/* The decode-time cache of one layer for `batch` sequences with ragged lengths (all device memory,
+ * caller-owned).  Replaces TritonKVMDecodeCache (model/kvm_triton_decode.py:34-400); unlike the
+ * reference's cache, lengths are per sequence. */
+typedef struct kvm_decode_cache {
+  kvm_memory memory;      /* n_rows = batch*Hkv */
+  void* ring_k;           /* [batch*Hkv, W*C, D] bf16: token t lives at slot t mod (W*C) */
+  void* ring_v;           /* [batch*Hkv, W*C, D] bf16 */
+  void* ring_gate;        /* [batch*Hkv, W*C]    bf16 */
+  int32_t* total_len;     /* [batch] tokens seen so far (advanced by kvm_decode_step) */
+  int32_t* state_len;     /* [batch] memory rows in use */
+} kvm_decode_cache;
+
+size_t kvm_decode_workspace_bytes(const kvm_layer* layer, int32_t batch, int32_t max_rows_per_seq);
+
+/* One decode token for every sequence of the batch: append to the ring, run the memory update for
+ * the sequences that cross a block boundary at this step, then joint attention over
+ * [memory ; window].  Replaces SequenceMixer.forward_single / _decode_one_token
+ * (model/kvm_mixer.py:572-713, model/kvm_triton_mixer.py:717-757, 902-929) and the kernels
+ * write_recent_ring / gather_overflow / kvm_decode_attention (model/kernels/kvm_triton_decode.py).
+ *   q [B,Hq,1,D], k,v [B,Hkv,1,D], gate [B,Hkv,1,1] as kvm_tensor4 (stride_t unused)
+ *   n_append_dev  [batch] int32: -1 = no memory update for this sequence at this step, otherwise
+ *                 the number of rows the update appends (host schedule); may be NULL when
+ *                 any_update == 0
+ *   any_update    host flag: launch the update kernel at all
+ *   max_rows      upper bound of (memory rows + window rows) over the batch (launch geometry)
+ *   out           [B,1,Hq*D] bf16
+ *   route_dev     optional [batch*Hkv, C] int32, written for updated sequences (see prefill)
+ */
+int kvm_decode_step(const kvm_layer* layer, int32_t batch, kvm_decode_cache cache,
+                    kvm_tensor4 q, kvm_tensor4 k, kvm_tensor4 v, kvm_tensor4 gate,
+                    const int32_t* n_append_dev, int32_t any_update, int32_t max_rows,
+                    void* out, int32_t* route_dev, void* workspace, size_t workspace_bytes,
+                    void* stream);
+
+/* Build k_attn / v_attn from k_sum / v_sum / vlen for rows [0, state_len[b]) of every sequence
+ * (used when a cache is initialised from the reference's eager cache layout).
+ * Replaces the normalised-copy refresh in TritonKVMDecodeCache.reset_
+ * (model/kvm_triton_decode.py:264-317). */
+int kvm_memory_refresh(const kvm_layer* layer, int32_t batch, kvm_memory memory,
+                       const int32_t* state_len_dev, void* stream);
+
+/* Description of the last error of the calling thread ("" if none). */
+const char* kvm_last_error_string(void);
+
+/* Library/ABI version (major*100 + minor). */
+int kvm_abi_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* KVM_B200_H_ */

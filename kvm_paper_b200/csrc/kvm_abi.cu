@@ -1,0 +1,258 @@
+// extern "C" entry points of libkvm_b200: argument validation, workspace carve-up, launches.
+// Nothing here allocates device memory or keeps state between calls.
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+
+#include "kvm_common.cuh"
+
+namespace kvm {
+cudaError_t prefill_dispatch(int D, const LayerDev& L, int batch, long long T, Tensor4 q, Tensor4 k, Tensor4 v,
+                             Tensor4 gate, const kvm_update_plan* plan_dev, int n_plan, long long ver_rows,
+                             MemoryDev mem, bf16* out, int* route, bf16* ver_k, bf16* ver_v, bf16* pk_scr,
+                             bf16* gk_scr, cudaStream_t stream);
+size_t update_smem_bytes(int D, int C, int capacity);
+cudaError_t decode_dispatch(int D, const LayerDev& L, int batch, const DecodeCacheDev& cache, Tensor4 q, Tensor4 k,
+                            Tensor4 v, Tensor4 gate, const int* n_append, int any_update, int max_rows, bf16* out,
+                            int* route, bf16* pk_scr, bf16* gk_scr, float* partial, int* counters, int rows_per_split,
+                            cudaStream_t stream);
+cudaError_t refresh_dispatch(int D, const LayerDev& L, int batch, MemoryDev mem, const int* state_len,
+                             cudaStream_t stream);
+}  // namespace kvm
+
+using namespace kvm;
+
+namespace {
+
+thread_local char g_err[512] = "";
+
+int fail(int code, const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_err, sizeof(g_err), fmt, ap);
+  va_end(ap);
+  return code;
+}
+
+int cuda_fail(cudaError_t e, const char* where) {
+  return fail(KVM_ERR_CUDA, "%s: CUDA error %d (%s)", where, (int)e, cudaGetErrorString(e));
+}
+
+constexpr int kMaxSmem = 227 * 1024;
+constexpr int kDecodeRowsPerSplit = 128;
+
+size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
+
+int check_layer(const kvm_layer* l) {
+  if (!l) return fail(KVM_ERR_BAD_ARGUMENT, "layer is NULL");
+  if (l->head_dim != 32 && l->head_dim != 64 && l->head_dim != 128)
+    return fail(KVM_ERR_UNSUPPORTED, "head_dim %d not supported (32, 64 or 128; d_qk_head must equal d_v_head)", l->head_dim);
+  if (l->n_kv_heads <= 0 || l->n_q_heads <= 0 || l->n_q_heads % l->n_kv_heads)
+    return fail(KVM_ERR_BAD_ARGUMENT, "n_q_heads %d must be a positive multiple of n_kv_heads %d", l->n_q_heads, l->n_kv_heads);
+  if (l->chunk_len < 16 || l->chunk_len % 16 || l->chunk_len > 512)
+    return fail(KVM_ERR_UNSUPPORTED, "chunk_len %d must be a multiple of 16 in [16, 512]", l->chunk_len);
+  if (l->n_bswa_chunks < 1) return fail(KVM_ERR_BAD_ARGUMENT, "n_bswa_chunks %d must be >= 1", l->n_bswa_chunks);
+  if (l->rope_dim < 0 || l->rope_dim > l->head_dim)
+    return fail(KVM_ERR_BAD_ARGUMENT, "rope_dim %d outside [0, head_dim]", l->rope_dim);
+  if (l->sink_len < 0) return fail(KVM_ERR_BAD_ARGUMENT, "sink_len %d negative", l->sink_len);
+  if (!l->ln_weight_dev || !l->ln_bias_dev || !l->front_temp_dev || !l->state_temp_dev)
+    return fail(KVM_ERR_BAD_ARGUMENT, "layer parameter arrays must not be NULL");
+  return KVM_OK;
+}
+
+LayerDev to_dev(const kvm_layer* l) {
+  LayerDev L;
+  L.Hq = l->n_q_heads; L.Hkv = l->n_kv_heads; L.C = l->chunk_len; L.W = l->n_bswa_chunks;
+  L.rope_dim = l->rope_dim; L.sink_len = l->sink_len;
+  L.gate_keys = l->gate_keys; L.gate_values = l->gate_values; L.gate_appends = l->gate_appends;
+  L.gate_initial = l->gate_initial; L.ln_eps = l->ln_eps;
+  L.ln_w = l->ln_weight_dev; L.ln_b = l->ln_bias_dev; L.front_temp = l->front_temp_dev; L.state_temp = l->state_temp_dev;
+  return L;
+}
+
+Tensor4 to_dev(const kvm_tensor4& t) {
+  Tensor4 r;
+  r.ptr = static_cast<const bf16*>(t.ptr); r.sb = t.stride_b; r.sh = t.stride_h; r.st = t.stride_t;
+  return r;
+}
+
+int check_tensor(const kvm_tensor4& t, const char* name, int row_elems) {
+  if (!t.ptr) return fail(KVM_ERR_BAD_ARGUMENT, "%s is NULL", name);
+  if (row_elems >= 8) {
+    if (((uintptr_t)t.ptr) % 16 || t.stride_b % 8 || t.stride_h % 8 || t.stride_t % 8)
+      return fail(KVM_ERR_BAD_ARGUMENT, "%s: base pointer and strides must be multiples of 16 bytes", name);
+  }
+  return KVM_OK;
+}
+
+MemoryDev to_dev(const kvm_memory& m) {
+  MemoryDev r;
+  r.k_sum = static_cast<bf16*>(m.k_sum); r.v_sum = static_cast<bf16*>(m.v_sum); r.vlen = m.vlen;
+  r.k_attn = static_cast<bf16*>(m.k_attn); r.v_attn = static_cast<bf16*>(m.v_attn); r.capacity = m.capacity;
+  return r;
+}
+
+int check_memory(const kvm_memory& m, const kvm_layer* l) {
+  if (!m.k_sum || !m.v_sum || !m.vlen || !m.k_attn || !m.v_attn) return fail(KVM_ERR_BAD_ARGUMENT, "memory arrays must not be NULL");
+  if (m.capacity <= 0) return fail(KVM_ERR_CAPACITY, "memory capacity %d must be positive", m.capacity);
+  const size_t smem = update_smem_bytes(l->head_dim, l->chunk_len, m.capacity);
+  if (smem > (size_t)kMaxSmem)
+    return fail(KVM_ERR_CAPACITY, "memory capacity %d rows needs %zu bytes of shared memory for the update (limit %d)",
+                m.capacity, smem, kMaxSmem);
+  return KVM_OK;
+}
+
+struct PrefillWs {
+  size_t ver_k, ver_v, pk, gk, total;
+};
+PrefillWs prefill_ws(const kvm_layer* l, int batch, long long ver_rows) {
+  const size_t rows = (size_t)batch * l->n_kv_heads;
+  const size_t D = l->head_dim;
+  PrefillWs w;
+  size_t off = 0;
+  w.ver_k = off; off = align_up(off + rows * (size_t)ver_rows * D * 2, 256);
+  w.ver_v = off; off = align_up(off + rows * (size_t)ver_rows * D * 2, 256);
+  w.pk = off; off = align_up(off + rows * (size_t)l->chunk_len * D * 2, 256);
+  w.gk = off; off = align_up(off + rows * (size_t)l->chunk_len * D * 2, 256);
+  w.total = off;
+  return w;
+}
+
+struct DecodeWs {
+  size_t pk, gk, partial, counters, total;
+  int nsplit_max;
+};
+DecodeWs decode_ws(const kvm_layer* l, int batch, int max_rows) {
+  const size_t rows = (size_t)batch * l->n_kv_heads;
+  const size_t D = l->head_dim;
+  DecodeWs w;
+  w.nsplit_max = (max_rows + kDecodeRowsPerSplit - 1) / kDecodeRowsPerSplit;
+  if (w.nsplit_max < 1) w.nsplit_max = 1;
+  size_t off = 0;
+  w.counters = off; off = align_up(off + (rows + batch) * 4, 256);
+  w.pk = off; off = align_up(off + rows * (size_t)l->chunk_len * D * 2, 256);
+  w.gk = off; off = align_up(off + rows * (size_t)l->chunk_len * D * 2, 256);
+  w.partial = off; off = align_up(off + (size_t)batch * l->n_q_heads * w.nsplit_max * (D + 2) * 4, 256);
+  w.total = off;
+  return w;
+}
+
+}  // namespace
+
+extern "C" {
+
+const char* kvm_last_error_string(void) { return g_err; }
+
+int kvm_abi_version(void) { return 100; }
+
+size_t kvm_prefill_workspace_bytes(const kvm_layer* layer, int32_t batch, int64_t seq_len, int64_t total_version_rows) {
+  (void)seq_len;
+  if (!layer || batch <= 0 || total_version_rows < 0) return 0;
+  return prefill_ws(layer, batch, total_version_rows).total;
+}
+
+int kvm_prefill_forward(const kvm_layer* layer, int32_t batch, int64_t seq_len, kvm_tensor4 q, kvm_tensor4 k,
+                        kvm_tensor4 v, kvm_tensor4 gate, const kvm_update_plan* plan_dev,
+                        const kvm_update_plan* plan_host, int32_t n_updates, int64_t total_version_rows,
+                        kvm_memory memory, void* out, int32_t* route_dev, void* workspace, size_t workspace_bytes,
+                        void* stream) {
+  g_err[0] = 0;
+  if (int rc = check_layer(layer)) return rc;
+  if (batch <= 0 || seq_len <= 0) return fail(KVM_ERR_BAD_ARGUMENT, "batch %d and seq_len %lld must be positive", batch, (long long)seq_len);
+  const int D = layer->head_dim, C = layer->chunk_len, W = layer->n_bswa_chunks;
+  if (int rc = check_tensor(q, "q", D)) return rc;
+  if (int rc = check_tensor(k, "k", D)) return rc;
+  if (int rc = check_tensor(v, "v", D)) return rc;
+  if (int rc = check_tensor(gate, "gate", 1)) return rc;
+  if (int rc = check_memory(memory, layer)) return rc;
+  if (!plan_dev || !plan_host || !out) return fail(KVM_ERR_BAD_ARGUMENT, "plan and out must not be NULL");
+  const long long n_qblocks = (seq_len + C - 1) / C;
+  const long long want_plan = n_qblocks > W ? n_qblocks - W : 1;
+  if (n_updates + 1 != want_plan)
+    return fail(KVM_ERR_BAD_ARGUMENT, "plan has %d entries, seq_len %lld with block %d and window %d needs %lld", n_updates + 1,
+                (long long)seq_len, C, W, want_plan);
+  // the plan must be self-consistent and fit the buffers (no kernel is launched otherwise)
+  long long S = 0, max_ver_end = 0;
+  for (int u = 0; u <= n_updates; ++u) {
+    const kvm_update_plan& p = plan_host[u];
+    const long long expect_append_max = (u == 0) ? (seq_len < C ? seq_len : C) : C;
+    if (p.state_before != S || p.n_append < 0 || p.n_append > expect_append_max || (u == 0 && p.n_append != expect_append_max))
+      return fail(KVM_ERR_BAD_ARGUMENT, "plan entry %d inconsistent (state_before %d, n_append %d, expected state %lld)", u,
+                  p.state_before, p.n_append, S);
+    S += p.n_append;
+    if (S > memory.capacity) return fail(KVM_ERR_CAPACITY, "plan entry %d grows the memory to %lld rows, capacity is %d", u, S, memory.capacity);
+    if (u > 0 && S <= (layer->sink_len < S ? layer->sink_len : S) && p.n_append < C)
+      return fail(KVM_ERR_BAD_ARGUMENT, "update %d merges into a memory with no non-sink row", u);
+    if (n_qblocks > W) {
+      if (p.version_row < 0) return fail(KVM_ERR_BAD_ARGUMENT, "plan entry %d: version_row %d must not be negative", u, p.version_row);
+      if (p.version_row + S > max_ver_end) max_ver_end = p.version_row + S;
+    }
+  }
+  if (max_ver_end > total_version_rows) return fail(KVM_ERR_CAPACITY, "versions need %lld rows, store has %lld", max_ver_end, (long long)total_version_rows);
+  const PrefillWs ws = prefill_ws(layer, batch, total_version_rows);
+  if (!workspace || workspace_bytes < ws.total) return fail(KVM_ERR_CAPACITY, "workspace of %zu bytes given, %zu needed", workspace_bytes, ws.total);
+  if (((uintptr_t)workspace) % 256 || ((uintptr_t)out) % 16) return fail(KVM_ERR_BAD_ARGUMENT, "workspace must be 256-byte aligned and out 16-byte aligned");
+
+  unsigned char* wsb = static_cast<unsigned char*>(workspace);
+  cudaError_t e = prefill_dispatch(D, to_dev(layer), batch, seq_len, to_dev(q), to_dev(k), to_dev(v), to_dev(gate), plan_dev,
+                                   n_updates + 1, total_version_rows, to_dev(memory), static_cast<bf16*>(out), route_dev,
+                                   reinterpret_cast<bf16*>(wsb + ws.ver_k), reinterpret_cast<bf16*>(wsb + ws.ver_v),
+                                   reinterpret_cast<bf16*>(wsb + ws.pk), reinterpret_cast<bf16*>(wsb + ws.gk),
+                                   static_cast<cudaStream_t>(stream));
+  if (e != cudaSuccess) return cuda_fail(e, "kvm_prefill_forward");
+  return KVM_OK;
+}
+
+size_t kvm_decode_workspace_bytes(const kvm_layer* layer, int32_t batch, int32_t max_rows_per_seq) {
+  if (!layer || batch <= 0 || max_rows_per_seq <= 0) return 0;
+  return decode_ws(layer, batch, max_rows_per_seq).total;
+}
+
+int kvm_decode_step(const kvm_layer* layer, int32_t batch, kvm_decode_cache cache, kvm_tensor4 q, kvm_tensor4 k,
+                    kvm_tensor4 v, kvm_tensor4 gate, const int32_t* n_append_dev, int32_t any_update, int32_t max_rows,
+                    void* out, int32_t* route_dev, void* workspace, size_t workspace_bytes, void* stream) {
+  g_err[0] = 0;
+  if (int rc = check_layer(layer)) return rc;
+  if (batch <= 0) return fail(KVM_ERR_BAD_ARGUMENT, "batch %d must be positive", batch);
+  const int D = layer->head_dim;
+  if (int rc = check_tensor(q, "q", D)) return rc;
+  if (int rc = check_tensor(k, "k", D)) return rc;
+  if (int rc = check_tensor(v, "v", D)) return rc;
+  if (int rc = check_tensor(gate, "gate", 1)) return rc;
+  if (int rc = check_memory(cache.memory, layer)) return rc;
+  if (!cache.ring_k || !cache.ring_v || !cache.ring_gate || !cache.total_len || !cache.state_len)
+    return fail(KVM_ERR_BAD_ARGUMENT, "decode cache arrays must not be NULL");
+  if (any_update && !n_append_dev) return fail(KVM_ERR_BAD_ARGUMENT, "any_update set but n_append_dev is NULL");
+  if (!out) return fail(KVM_ERR_BAD_ARGUMENT, "out is NULL");
+  const int row_bound = cache.memory.capacity + layer->n_bswa_chunks * layer->chunk_len;
+  if (max_rows <= 0 || max_rows > row_bound) return fail(KVM_ERR_BAD_ARGUMENT, "max_rows %d outside (0, capacity + window = %d]", max_rows, row_bound);
+  const DecodeWs ws = decode_ws(layer, batch, max_rows);
+  if (!workspace || workspace_bytes < ws.total) return fail(KVM_ERR_CAPACITY, "workspace of %zu bytes given, %zu needed", workspace_bytes, ws.total);
+  if (((uintptr_t)workspace) % 256) return fail(KVM_ERR_BAD_ARGUMENT, "workspace must be 256-byte aligned");
+
+  DecodeCacheDev c;
+  c.mem = to_dev(cache.memory);
+  c.ring_k = static_cast<bf16*>(cache.ring_k); c.ring_v = static_cast<bf16*>(cache.ring_v);
+  c.ring_g = static_cast<bf16*>(cache.ring_gate); c.total_len = cache.total_len; c.state_len = cache.state_len;
+  unsigned char* wsb = static_cast<unsigned char*>(workspace);
+  cudaError_t e = decode_dispatch(D, to_dev(layer), batch, c, to_dev(q), to_dev(k), to_dev(v), to_dev(gate), n_append_dev,
+                                  any_update, max_rows, static_cast<bf16*>(out), route_dev,
+                                  reinterpret_cast<bf16*>(wsb + ws.pk), reinterpret_cast<bf16*>(wsb + ws.gk),
+                                  reinterpret_cast<float*>(wsb + ws.partial), reinterpret_cast<int*>(wsb + ws.counters),
+                                  kDecodeRowsPerSplit, static_cast<cudaStream_t>(stream));
+  if (e != cudaSuccess) return cuda_fail(e, "kvm_decode_step");
+  return KVM_OK;
+}
+
+int kvm_memory_refresh(const kvm_layer* layer, int32_t batch, kvm_memory memory, const int32_t* state_len_dev, void* stream) {
+  g_err[0] = 0;
+  if (int rc = check_layer(layer)) return rc;
+  if (batch <= 0 || !state_len_dev) return fail(KVM_ERR_BAD_ARGUMENT, "batch must be positive and state_len_dev not NULL");
+  if (!memory.k_sum || !memory.v_sum || !memory.vlen || !memory.k_attn || !memory.v_attn || memory.capacity <= 0)
+    return fail(KVM_ERR_BAD_ARGUMENT, "memory arrays must not be NULL");
+  cudaError_t e = refresh_dispatch(layer->head_dim, to_dev(layer), batch, to_dev(memory), state_len_dev, static_cast<cudaStream_t>(stream));
+  if (e != cudaSuccess) return cuda_fail(e, "kvm_memory_refresh");
+  return KVM_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,209 @@
+// Shared device helpers of the KVM kernels (sm_100a): bf16 packing, warp reductions, cp.async,
+// warp-level tensor-core MMA wrappers, LayerNorm / value-normalisation of one memory row.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/kvm_b200.h"
+
+namespace kvm {
+
+typedef __nv_bfloat16 bf16;
+
+constexpr int kWarp = 32;
+constexpr float kLog2e = 1.4426950408889634f;
+
+// Device-side copy of kvm_layer (plain values, passed by value to kernels).
+struct LayerDev {
+  int Hq, Hkv, C, W, rope_dim, sink_len;
+  int gate_keys, gate_values, gate_appends, gate_initial;
+  float ln_eps;
+  const float* ln_w;
+  const float* ln_b;
+  const float* front_temp;
+  const float* state_temp;
+};
+
+struct Tensor4 {
+  const bf16* ptr;
+  long long sb, sh, st;
+  __device__ __forceinline__ const bf16* row(int b, int h, long long t) const {
+    return ptr + (long long)b * sb + (long long)h * sh + t * st;
+  }
+};
+
+struct MemoryDev {
+  bf16* k_sum;
+  bf16* v_sum;
+  float* vlen;
+  bf16* k_attn;
+  bf16* v_attn;
+  int capacity;
+};
+
+struct DecodeCacheDev {
+  MemoryDev mem;
+  bf16* ring_k;
+  bf16* ring_v;
+  bf16* ring_g;
+  int* total_len;
+  int* state_len;
+};
+
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ float warp_sum(float x) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) x += __shfl_xor_sync(0xffffffffu, x, o);
+  return x;
+}
+__device__ __forceinline__ float warp_max(float x) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) x = fmaxf(x, __shfl_xor_sync(0xffffffffu, x, o));
+  return x;
+}
+
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+__device__ __forceinline__ float2 unpack_bf16(uint32_t u) {
+  __nv_bfloat162 v = *reinterpret_cast<__nv_bfloat162*>(&u);
+  return __bfloat1622float2(v);
+}
+__device__ __forceinline__ float bf16_round(float x) { return __bfloat162float(__float2bfloat16_rn(x)); }
+
+// 16-byte async global->shared copy; copies `bytes` (0 or 16) and zero-fills the rest.
+__device__ __forceinline__ void cp_async16(void* smem, const void* gmem, int bytes) {
+  uint32_t s = (uint32_t)__cvta_generic_to_shared(smem);
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(s), "l"(gmem), "r"(bytes));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {
+  asm volatile("cp.async.wait_group %0;\n" ::"n"(N));
+}
+
+// D(16x8,f32) += A(16x16,bf16,row) * B(16x8,bf16,col)
+__device__ __forceinline__ void mma_bf16_16816(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+// Four transposed 8x8 bf16 matrices from shared memory (lane l supplies the row address of matrix l/8, row l%8).
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], const void* smem_row) {
+  uint32_t s = (uint32_t)__cvta_generic_to_shared(smem_row);
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"(s));
+}
+
+// ---------------------------------------------------------------------------------------------
+// One row of D elements is spread over a warp: lane l owns the EPL = D/32 contiguous elements
+// [l*EPL, (l+1)*EPL).
+template <int D>
+struct RowVec {
+  static constexpr int EPL = D / 32;
+  float x[EPL];
+};
+
+template <int D>
+__device__ __forceinline__ void load_row(RowVec<D>& r, const bf16* p, int lane) {
+  constexpr int EPL = D / 32;
+  const bf16* q = p + lane * EPL;
+  if constexpr (EPL == 4) {
+    uint2 u = *reinterpret_cast<const uint2*>(q);
+    float2 a = unpack_bf16(u.x), b = unpack_bf16(u.y);
+    r.x[0] = a.x; r.x[1] = a.y; r.x[2] = b.x; r.x[3] = b.y;
+  } else if constexpr (EPL == 2) {
+    float2 a = unpack_bf16(*reinterpret_cast<const uint32_t*>(q));
+    r.x[0] = a.x; r.x[1] = a.y;
+  } else {
+#pragma unroll
+    for (int i = 0; i < EPL; ++i) r.x[i] = __bfloat162float(q[i]);
+  }
+}
+
+template <int D>
+__device__ __forceinline__ void store_row(const RowVec<D>& r, bf16* p, int lane) {
+  constexpr int EPL = D / 32;
+  bf16* q = p + lane * EPL;
+  if constexpr (EPL == 4) {
+    uint2 u;
+    u.x = pack_bf16(r.x[0], r.x[1]);
+    u.y = pack_bf16(r.x[2], r.x[3]);
+    *reinterpret_cast<uint2*>(q) = u;
+  } else if constexpr (EPL == 2) {
+    *reinterpret_cast<uint32_t*>(q) = pack_bf16(r.x[0], r.x[1]);
+  } else {
+#pragma unroll
+    for (int i = 0; i < EPL; ++i) q[i] = __float2bfloat16_rn(r.x[i]);
+  }
+}
+
+template <int D>
+__device__ __forceinline__ void round_row(RowVec<D>& r) {
+#pragma unroll
+  for (int i = 0; i < D / 32; ++i) r.x[i] = bf16_round(r.x[i]);
+}
+
+// LayerNorm over the D elements of a row held by a warp (fp32 statistics, biased variance),
+// result rounded to bf16 precision (kept in fp32 registers).
+template <int D>
+__device__ __forceinline__ void layer_norm_row(RowVec<D>& r, const float* __restrict__ w,
+                                               const float* __restrict__ b, float eps, int lane) {
+  constexpr int EPL = D / 32;
+  float s = 0.f;
+#pragma unroll
+  for (int i = 0; i < EPL; ++i) s += r.x[i];
+  float mean = warp_sum(s) * (1.0f / D);
+  float q = 0.f;
+#pragma unroll
+  for (int i = 0; i < EPL; ++i) {
+    float d = r.x[i] - mean;
+    q += d * d;
+  }
+  float var = warp_sum(q) * (1.0f / D);
+  float rstd = 1.0f / sqrtf(var + eps);
+#pragma unroll
+  for (int i = 0; i < EPL; ++i) {
+    int d = lane * EPL + i;
+    r.x[i] = bf16_round((r.x[i] - mean) * rstd * w[d] + b[d]);
+  }
+}
+
+// L2 norm of a row held by a warp.
+template <int D>
+__device__ __forceinline__ float row_norm(const RowVec<D>& r) {
+  float s = 0.f;
+#pragma unroll
+  for (int i = 0; i < D / 32; ++i) s += r.x[i] * r.x[i];
+  return sqrtf(warp_sum(s));
+}
+
+// Attention view of one memory row: k_attn = LN(k_sum), v_attn = v_sum / max(|v_sum|, 1e-12) * vlen.
+template <int D>
+__device__ __forceinline__ void refresh_memory_row(const LayerDev& L, RowVec<D> ks, RowVec<D> vs, float vlen,
+                                                   bf16* k_attn_row, bf16* v_attn_row, int lane) {
+  layer_norm_row<D>(ks, L.ln_w, L.ln_b, L.ln_eps, lane);
+  store_row<D>(ks, k_attn_row, lane);
+  float n = fmaxf(row_norm<D>(vs), 1e-12f);
+#pragma unroll
+  for (int i = 0; i < D / 32; ++i) vs.x[i] = __fdiv_rn(vs.x[i], n) * vlen;
+  store_row<D>(vs, v_attn_row, lane);
+}
+
+// Prepared key of one token: rotary dims zeroed, LayerNorm, bf16 (model/kvm_mixer.py:120-129).
+template <int D>
+__device__ __forceinline__ void prepare_key_row(const LayerDev& L, RowVec<D>& r, const bf16* k_row, int lane) {
+  load_row<D>(r, k_row, lane);
+#pragma unroll
+  for (int i = 0; i < D / 32; ++i)
+    if (lane * (D / 32) + i < L.rope_dim) r.x[i] = 0.f;
+  layer_norm_row<D>(r, L.ln_w, L.ln_b, L.ln_eps, lane);
+}
+
+}  // namespace kvm

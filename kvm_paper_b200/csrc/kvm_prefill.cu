@@ -1,0 +1,360 @@
+// Prefill kernels: (1) the memory chain -- initial memory, then one block-recurrent update per
+// token block, each followed by a snapshot ("version") of the attention view of the memory;
+// (2) block attention -- every query tile attends jointly to [memory version ; sliding window]
+// with one online softmax (front blocks: plain causal attention over the window only).
+//
+// The memory trajectory depends only on k, v and the merge gate (model/kvm_mixer.py:478-487), never on
+// attention outputs, so the chain runs ahead and attention over all blocks runs in parallel behind it.
+#include "kvm_update.cuh"
+
+namespace kvm {
+
+// ------------------------------------------------------------------------------------------ chain
+template <int D, int NT>
+__global__ void __launch_bounds__(NT, 1)
+kvm_chain_kernel(LayerDev L, long long T, Tensor4 k, Tensor4 v, Tensor4 gate, const kvm_update_plan* __restrict__ plan,
+                 int u_begin, int u_end, MemoryDev mem, bf16* ver_k, bf16* ver_v, long long ver_rows,
+                 bf16* pk_scr, bf16* gk_scr, int* route, int n_plan) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  UpdateSmem<D> s;
+  s.carve(smem_raw, L.C, mem.capacity);
+  const int row = blockIdx.x;
+  const int b = row / L.Hkv, h = row % L.Hkv;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  constexpr int NW = NT / 32;
+  const int C = L.C;
+
+  MemoryRowPtrs m;
+  m.k_sum = mem.k_sum + (size_t)row * mem.capacity * D;
+  m.v_sum = mem.v_sum + (size_t)row * mem.capacity * D;
+  m.vlen = mem.vlen + (size_t)row * mem.capacity;
+  m.k_attn = mem.k_attn + (size_t)row * mem.capacity * D;
+  m.v_attn = mem.v_attn + (size_t)row * mem.capacity * D;
+  bf16* pk = pk_scr + (size_t)row * C * D;
+  bf16* gk = gk_scr + (size_t)row * C * D;
+
+  for (int u = u_begin; u < u_end; ++u) {
+    const kvm_update_plan pl = plan[u];
+    const int S_after = pl.state_before + pl.n_append;
+    if (u == 0) {
+      // initial memory: the first min(T,C) tokens row for row (model/kvm_mixer.py:434-447)
+      for (int tkn = warp; tkn < pl.n_append; tkn += NW) {
+        RowVec<D> kr, vr;
+        prepare_key_row<D>(L, kr, k.row(b, h, tkn), lane);
+        load_row<D>(vr, v.row(b, h, tkn), lane);
+        const float vl = row_norm<D>(vr);  // magnitude of the ungated value
+        if (L.gate_initial) {
+          const float gt = __bfloat162float(*gate.row(b, h, tkn));
+#pragma unroll
+          for (int i = 0; i < D / 32; ++i) {
+            kr.x[i] = bf16_round(kr.x[i] * gt);
+            vr.x[i] = bf16_round(vr.x[i] * gt);
+          }
+        }
+        store_row<D>(kr, m.k_sum + (size_t)tkn * D, lane);
+        store_row<D>(vr, m.v_sum + (size_t)tkn * D, lane);
+        if (lane == 0) m.vlen[tkn] = vl;
+        refresh_memory_row<D>(L, kr, vr, vl, m.k_attn + (size_t)tkn * D, m.v_attn + (size_t)tkn * D, lane);
+      }
+      if (route)
+        for (int i = tid; i < C; i += NT) route[((size_t)row * n_plan) * C + i] = i < pl.n_append ? -(1 + i) : 0;
+      __syncthreads();
+    } else {
+      TokenSrc src;
+      src.k = k.row(b, h, (long long)u * C); src.k_st = k.st;
+      src.v = v.row(b, h, (long long)u * C); src.v_st = v.st;
+      src.g = gate.row(b, h, (long long)u * C); src.g_st = gate.st;
+      memory_update<D, NT>(L, src, m, mem.capacity, pl.state_before, pl.n_append, pk, gk,
+                           route ? route + ((size_t)row * n_plan + u) * C : nullptr, s);
+    }
+    // snapshot of the attention view: version u (only versions some query block reads are stored)
+    if (pl.version_row >= 0) {
+      const uint4* sk = reinterpret_cast<const uint4*>(m.k_attn);
+      const uint4* sv = reinterpret_cast<const uint4*>(m.v_attn);
+      uint4* dk = reinterpret_cast<uint4*>(ver_k + ((size_t)row * ver_rows + pl.version_row) * D);
+      uint4* dv = reinterpret_cast<uint4*>(ver_v + ((size_t)row * ver_rows + pl.version_row) * D);
+      const int n16 = S_after * (D / 8);
+      for (int i = tid; i < n16; i += NT) {
+        dk[i] = sk[i];
+        dv[i] = sv[i];
+      }
+    }
+    __syncthreads();
+  }
+}
+
+// -------------------------------------------------------------------------------------- attention
+constexpr int kAttnBN = 64;  // keys per shared-memory tile
+
+template <int D>
+__host__ __device__ constexpr int attn_tile_stride() { return D + 8; }
+
+template <int D>
+__host__ __device__ constexpr size_t attn_smem_bytes() {
+  return (size_t)2 * 2 * kAttnBN * attn_tile_stride<D>() * sizeof(bf16);
+}
+
+// rows [row0, row0+64) of a [*, D] row-major source with row stride `st` elements; rows >= limit zero-filled
+template <int D, int NT>
+__device__ __forceinline__ void attn_load_tile(bf16* dst, const bf16* src, long long st, long long row0,
+                                               long long limit, int tid) {
+  constexpr int CPR = D / 8;
+  constexpr int STR = attn_tile_stride<D>();
+  for (int c = tid; c < kAttnBN * CPR; c += NT) {
+    const int r = c / CPR, cc = c % CPR;
+    const long long row = row0 + r;
+    const bool ok = row < limit;
+    cp_async16(dst + r * STR + cc * 8, src + (ok ? row : 0) * st + cc * 8, ok ? 16 : 0);
+  }
+}
+
+// One CTA = BM query rows of one (batch, q-head) inside one query block j.
+template <int D, int BM>
+__global__ void __launch_bounds__(BM * 2)
+kvm_attn_prefill_kernel(LayerDev L, long long T, Tensor4 q, Tensor4 k, Tensor4 v,
+                        const kvm_update_plan* __restrict__ plan, const bf16* __restrict__ ver_k,
+                        const bf16* __restrict__ ver_v, long long ver_rows, bf16* __restrict__ out,
+                        int tiles_per_block, int j_begin, float sm_scale) {
+  constexpr int NT = BM * 2;
+  constexpr int KS = D / 16;       // k-steps of QK^T
+  constexpr int NT8 = kAttnBN / 8; // n8 tiles of a score tile
+  constexpr int DT8 = D / 8;       // n8 tiles of the output
+  constexpr int STR = attn_tile_stride<D>();
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  bf16* sK = reinterpret_cast<bf16*>(smem_raw);             // [2][64][STR]
+  bf16* sV = sK + (size_t)2 * kAttnBN * STR;                // [2][64][STR]
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int g = lane >> 2, t = lane & 3;
+  const int C = L.C;
+  // heavier tiles (later rows of a block see more window keys) are scheduled first
+  const int xi = gridDim.x - 1 - blockIdx.x;
+  const int j = j_begin + xi / tiles_per_block;
+  const int ti = xi % tiles_per_block;
+  const int qrow = blockIdx.y;
+  const int b = qrow / L.Hq, hq = qrow % L.Hq;
+  const int hkv = hq / (L.Hq / L.Hkv);
+  const long long q0 = (long long)j * C + (long long)ti * BM;
+  const long long q_blk_end = min(T, (long long)(j + 1) * C);
+  if (q0 >= q_blk_end) return;
+  const long long q_tile_end = min(q_blk_end, q0 + BM);
+
+  // segments
+  int S = 0;
+  const bf16* mk = nullptr;
+  const bf16* mv = nullptr;
+  if (j >= L.W) {
+    const kvm_update_plan pl = plan[j - L.W];
+    S = pl.state_before + pl.n_append;
+    const size_t off = ((size_t)(b * L.Hkv + hkv) * ver_rows + pl.version_row) * D;
+    mk = ver_k + off;
+    mv = ver_v + off;
+  }
+  const long long bb = max(0LL, (long long)(j + 1 - L.W) * C);
+  const int n_mem_tiles = (S + kAttnBN - 1) / kAttnBN;
+  const int n_win_tiles = (int)((q_tile_end - bb + kAttnBN - 1) / kAttnBN);
+  const int n_tiles = n_mem_tiles + n_win_tiles;
+  const bf16* kbase = k.row(b, hkv, 0);
+  const bf16* vbase = v.row(b, hkv, 0);
+  const float scale_mem = sm_scale * L.state_temp[hq] * kLog2e;
+  const float scale_win = sm_scale * L.front_temp[hq] * kLog2e;
+
+  // Q fragments (rows past the tile end are clamped; their results are never stored)
+  uint32_t qa[KS][4];
+  const long long qr0 = min(q0 + warp * 16 + g, q_tile_end - 1);
+  const long long qr1 = min(q0 + warp * 16 + g + 8, q_tile_end - 1);
+  {
+    const bf16* p0 = q.row(b, hq, qr0);
+    const bf16* p1 = q.row(b, hq, qr1);
+#pragma unroll
+    for (int ks = 0; ks < KS; ++ks) {
+      const int c0 = ks * 16 + t * 2;
+      qa[ks][0] = *reinterpret_cast<const uint32_t*>(p0 + c0);
+      qa[ks][1] = *reinterpret_cast<const uint32_t*>(p1 + c0);
+      qa[ks][2] = *reinterpret_cast<const uint32_t*>(p0 + c0 + 8);
+      qa[ks][3] = *reinterpret_cast<const uint32_t*>(p1 + c0 + 8);
+    }
+  }
+  const long long qpos0 = q0 + warp * 16 + g, qpos1 = qpos0 + 8;
+
+  float o[DT8][4];
+#pragma unroll
+  for (int i = 0; i < DT8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+  float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
+
+  auto issue = [&](int it, int stage) {
+    bf16* dK = sK + (size_t)stage * kAttnBN * STR;
+    bf16* dV = sV + (size_t)stage * kAttnBN * STR;
+    if (it < n_mem_tiles) {
+      attn_load_tile<D, NT>(dK, mk, D, (long long)it * kAttnBN, S, tid);
+      attn_load_tile<D, NT>(dV, mv, D, (long long)it * kAttnBN, S, tid);
+    } else {
+      const long long r0 = bb + (long long)(it - n_mem_tiles) * kAttnBN;
+      attn_load_tile<D, NT>(dK, kbase, k.st, r0, q_tile_end, tid);
+      attn_load_tile<D, NT>(dV, vbase, v.st, r0, q_tile_end, tid);
+    }
+    cp_async_commit();
+  };
+
+  issue(0, 0);
+  for (int it = 0; it < n_tiles; ++it) {
+    const int cur = it & 1;
+    if (it + 1 < n_tiles) {
+      issue(it + 1, cur ^ 1);
+      cp_async_wait<1>();
+    } else {
+      cp_async_wait<0>();
+    }
+    __syncthreads();
+    const bf16* tK = sK + (size_t)cur * kAttnBN * STR;
+    const bf16* tV = sV + (size_t)cur * kAttnBN * STR;
+    const bool is_mem = it < n_mem_tiles;
+    const long long base = is_mem ? (long long)it * kAttnBN : bb + (long long)(it - n_mem_tiles) * kAttnBN;
+    const long long limit = is_mem ? (long long)S : q_tile_end;
+    const float sc = is_mem ? scale_mem : scale_win;
+
+    // S = Q K^T
+    float sacc[NT8][4];
+#pragma unroll
+    for (int nt = 0; nt < NT8; ++nt) {
+      sacc[nt][0] = sacc[nt][1] = sacc[nt][2] = sacc[nt][3] = 0.f;
+      const bf16* brow = tK + (size_t)(nt * 8 + g) * STR + t * 2;
+#pragma unroll
+      for (int ks = 0; ks < KS; ++ks) {
+        uint32_t b0 = *reinterpret_cast<const uint32_t*>(brow + ks * 16);
+        uint32_t b1 = *reinterpret_cast<const uint32_t*>(brow + ks * 16 + 8);
+        mma_bf16_16816(sacc[nt], qa[ks], b0, b1);
+      }
+    }
+    // scale, mask, online softmax (base 2)
+    float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+    for (int nt = 0; nt < NT8; ++nt) {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const long long n = base + nt * 8 + t * 2 + (e & 1);
+        const long long qp = (e >> 1) ? qpos1 : qpos0;
+        const bool ok = n < limit && (is_mem || n <= qp);
+        const float x = ok ? sacc[nt][e] * sc : -INFINITY;
+        sacc[nt][e] = x;
+        mx[e >> 1] = fmaxf(mx[e >> 1], x);
+      }
+    }
+    float alpha[2], m_use[2];
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+      mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
+      mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
+      const float m_new = fmaxf(m_run[r], mx[r]);
+      m_use[r] = (m_new == -INFINITY) ? 0.f : m_new;
+      alpha[r] = exp2f(m_run[r] - m_use[r]);  // m_run = -inf -> 0
+      m_run[r] = m_new;
+    }
+    uint32_t pa[NT8 / 2][4];
+    float ls[2] = {0.f, 0.f};
+#pragma unroll
+    for (int nt = 0; nt < NT8; ++nt) {
+      const float p0 = exp2f(sacc[nt][0] - m_use[0]);
+      const float p1 = exp2f(sacc[nt][1] - m_use[0]);
+      const float p2 = exp2f(sacc[nt][2] - m_use[1]);
+      const float p3 = exp2f(sacc[nt][3] - m_use[1]);
+      ls[0] += p0 + p1;
+      ls[1] += p2 + p3;
+      pa[nt >> 1][(nt & 1) * 2 + 0] = pack_bf16(p0, p1);
+      pa[nt >> 1][(nt & 1) * 2 + 1] = pack_bf16(p2, p3);
+    }
+#pragma unroll
+    for (int r = 0; r < 2; ++r) l_run[r] = l_run[r] * alpha[r] + ls[r];
+#pragma unroll
+    for (int i = 0; i < DT8; ++i) {
+      o[i][0] *= alpha[0];
+      o[i][1] *= alpha[0];
+      o[i][2] *= alpha[1];
+      o[i][3] *= alpha[1];
+    }
+    // O += P V   (V fragments through transposed ldmatrix: 16 keys x 16 value columns per call)
+#pragma unroll
+    for (int kk = 0; kk < kAttnBN / 16; ++kk) {
+#pragma unroll
+      for (int dp = 0; dp < DT8 / 2; ++dp) {
+        uint32_t vb[4];
+        const bf16* vrow = tV + (size_t)(kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * STR + dp * 16 + (lane >> 4) * 8;
+        ldmatrix_x4_trans(vb, vrow);
+        mma_bf16_16816(o[dp * 2 + 0], pa[kk], vb[0], vb[1]);
+        mma_bf16_16816(o[dp * 2 + 1], pa[kk], vb[2], vb[3]);
+      }
+    }
+    __syncthreads();
+  }
+
+  // normalise and store [B, T, Hq*D]
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 1);
+    l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 2);
+  }
+  const float inv0 = l_run[0] > 0.f ? 1.0f / l_run[0] : 0.f;
+  const float inv1 = l_run[1] > 0.f ? 1.0f / l_run[1] : 0.f;
+  const long long ostride = (long long)L.Hq * D;
+  if (qpos0 < q_tile_end) {
+    bf16* p = out + ((long long)b * T + qpos0) * ostride + (long long)hq * D + t * 2;
+#pragma unroll
+    for (int i = 0; i < DT8; ++i) *reinterpret_cast<uint32_t*>(p + i * 8) = pack_bf16(o[i][0] * inv0, o[i][1] * inv0);
+  }
+  if (qpos1 < q_tile_end) {
+    bf16* p = out + ((long long)b * T + qpos1) * ostride + (long long)hq * D + t * 2;
+#pragma unroll
+    for (int i = 0; i < DT8; ++i) *reinterpret_cast<uint32_t*>(p + i * 8) = pack_bf16(o[i][2] * inv1, o[i][3] * inv1);
+  }
+}
+
+// ------------------------------------------------------------------------------------- host side
+template <int D>
+static cudaError_t launch_prefill(const LayerDev& L, int batch, long long T, Tensor4 q, Tensor4 k, Tensor4 v, Tensor4 gate,
+                                  const kvm_update_plan* plan_dev, int n_plan, long long ver_rows, MemoryDev mem,
+                                  bf16* out, int* route, bf16* ver_k, bf16* ver_v, bf16* pk_scr, bf16* gk_scr,
+                                  cudaStream_t stream) {
+  constexpr int NT = 512;
+  const int rows = batch * L.Hkv;
+  const size_t smem_u = UpdateSmem<D>::bytes(L.C, mem.capacity);
+  cudaError_t e = cudaFuncSetAttribute(kvm_chain_kernel<D, NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_u);
+  if (e != cudaSuccess) return e;
+  kvm_chain_kernel<D, NT><<<rows, NT, smem_u, stream>>>(L, T, k, v, gate, plan_dev, 0, n_plan, mem, ver_k, ver_v,
+                                                       ver_rows, pk_scr, gk_scr, route, n_plan);
+  e = cudaGetLastError();
+  if (e != cudaSuccess) return e;
+
+  constexpr int BM = 64;
+  const int n_qblocks = (int)((T + L.C - 1) / L.C);
+  const int tiles_per_block = (L.C + BM - 1) / BM;
+  const size_t smem_a = attn_smem_bytes<D>();
+  e = cudaFuncSetAttribute(kvm_attn_prefill_kernel<D, BM>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_a);
+  if (e != cudaSuccess) return e;
+  dim3 grid(n_qblocks * tiles_per_block, batch * L.Hq);
+  kvm_attn_prefill_kernel<D, BM><<<grid, BM * 2, smem_a, stream>>>(L, T, q, k, v, plan_dev, ver_k, ver_v, ver_rows, out,
+                                                                  tiles_per_block, 0, 1.0f / sqrtf((float)D));
+  return cudaGetLastError();
+}
+
+cudaError_t prefill_dispatch(int D, const LayerDev& L, int batch, long long T, Tensor4 q, Tensor4 k, Tensor4 v,
+                             Tensor4 gate, const kvm_update_plan* plan_dev, int n_plan, long long ver_rows,
+                             MemoryDev mem, bf16* out, int* route, bf16* ver_k, bf16* ver_v, bf16* pk_scr,
+                             bf16* gk_scr, cudaStream_t stream) {
+  switch (D) {
+    case 32: return launch_prefill<32>(L, batch, T, q, k, v, gate, plan_dev, n_plan, ver_rows, mem, out, route, ver_k, ver_v, pk_scr, gk_scr, stream);
+    case 64: return launch_prefill<64>(L, batch, T, q, k, v, gate, plan_dev, n_plan, ver_rows, mem, out, route, ver_k, ver_v, pk_scr, gk_scr, stream);
+    case 128: return launch_prefill<128>(L, batch, T, q, k, v, gate, plan_dev, n_plan, ver_rows, mem, out, route, ver_k, ver_v, pk_scr, gk_scr, stream);
+  }
+  return cudaErrorInvalidValue;
+}
+
+size_t update_smem_bytes(int D, int C, int capacity) {
+  switch (D) {
+    case 32: return UpdateSmem<32>::bytes(C, capacity);
+    case 64: return UpdateSmem<64>::bytes(C, capacity);
+    case 128: return UpdateSmem<128>::bytes(C, capacity);
+  }
+  return 0;
+}
+
+}  // namespace kvm

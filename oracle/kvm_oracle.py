@@ -87,6 +87,12 @@ class UpdateRecord:
     best_idx: torch.Tensor | None  # [B,Hkv,n_merge] slot chosen for each merged token
     margin: torch.Tensor | None  # [B,Hkv,n_merge] fp32 top-1 minus top-2 logit
     append_scores: torch.Tensor | None = None  # [B,Hkv,C] fp32 novelty scores
+    # filled when decisions are forced from outside (see ``forced`` below)
+    append_rows_differ: int = 0    # kv rows whose forced append set differs from the oracle's own
+    append_rows_illegal: int = 0   # ... and is not explained by a tie / one-ulp score difference at the cut
+    merge_differ: int = 0          # merged tokens whose forced row differs from the oracle's own argmax
+    merge_differ_fp32: int = 0     # ... with an oracle-side logit gap within fp32 summation noise
+    merge_illegal: int = 0         # ... with a gap larger than the stated tie tolerance
 
 
 # ----------------------------------------------------------------------------- small helpers
@@ -254,7 +260,16 @@ def append_to_state(spec: KvmSpec, s_k, s_v, s_vlen, k_new, v_new):
     )
 
 
-def merge_into_state(spec: KvmSpec, k_merge, v_merge, s_k, s_v, s_vlen, protected_slots: int, rec=None):
+# Tie tolerances of the decision comparison (used only when decisions are forced from outside):
+# a forced merge row is accepted if its oracle-side logit is within MERGE_TIE_TOL of the maximum
+# (one bf16 rounding step of one key element moves a logit by about this much); gaps below
+# MERGE_FP32_TOL * max(1,|logit|) are plain fp32 summation-order noise.
+MERGE_TIE_TOL = 2e-2
+MERGE_FP32_TOL = 1e-5
+
+
+def merge_into_state(spec: KvmSpec, k_merge, v_merge, s_k, s_v, s_vlen, protected_slots: int, rec=None,
+                     forced_best: torch.Tensor | None = None):
     # fp32 routing: model/kvm_fp32_routing_reference.py:24-49; key dtype: model/kvm_mixer.py:321-340
     s_k_norm = _ln(spec, s_k)
     if spec.routing == "fp32":
@@ -263,11 +278,22 @@ def merge_into_state(spec: KvmSpec, k_merge, v_merge, s_k, s_v, s_vlen, protecte
         logits = torch.matmul(k_merge, s_k_norm.transpose(-1, -2))
     logits[..., :protected_slots] = float("-inf")
     best = logits.max(dim=-1, keepdim=True).indices
+    own_best = best
+    if forced_best is not None:
+        fb = forced_best.long().unsqueeze(-1)
+        top = logits.float().max(dim=-1, keepdim=True).values
+        gap = top - logits.float().gather(-1, fb)
+        differ = fb != best
+        if rec is not None:
+            rec.merge_differ = int(differ.sum())
+            rec.merge_differ_fp32 = int((differ & (gap <= MERGE_FP32_TOL * top.abs().clamp_min(1.0))).sum())
+            rec.merge_illegal = int((differ & ~(gap <= MERGE_TIE_TOL)).sum())
+        best = fb
     scores = torch.scatter(
         torch.zeros_like(logits, dtype=k_merge.dtype), -1, best, torch.ones_like(logits, dtype=k_merge.dtype)
     )
     if rec is not None:
-        rec.best_idx = best.squeeze(-1).clone()
+        rec.best_idx = own_best.squeeze(-1).clone()
         if int(logits.size(-1)) >= 2:
             top2 = logits.float().topk(2, dim=-1).values
             rec.margin = top2[..., 0] - top2[..., 1]
@@ -280,8 +306,11 @@ def merge_into_state(spec: KvmSpec, k_merge, v_merge, s_k, s_v, s_vlen, protecte
 
 def update_state_from_overflow_tokens(
     spec: KvmSpec, s_k, s_v, s_vlen, overflow_k, overflow_v, merge_gate, ctx_len: int, available_context: int,
-    trace: list | None = None,
+    trace: list | None = None, forced: dict | None = None,
 ):
+    """``forced`` (test use): {"append_idx": [B,Hkv,n_append] sorted token indices or None,
+    "best_idx": [B,Hkv,n_merge] memory rows or None}.  The oracle then follows these decisions instead
+    of its own, after recording whether each one is identical to its own, a legal tie, or wrong."""
     # model/kvm_mixer.py:250-319
     if int(overflow_k.size(2)) == 0:
         return s_k, s_v, s_vlen
@@ -302,9 +331,20 @@ def update_state_from_overflow_tokens(
         rec = UpdateRecord(int(ctx_len), int(available_context), cur, cur + n_append, n_append, None, None, None, None)
         trace.append(rec)
     if n_append > 0:
-        append_idx, merge_idx, sc = split_append_merge_idx_by_maxsim(k_un, n_append, _ln(spec, s_k), rec is not None)
+        want_sc = rec is not None or forced is not None
+        append_idx, merge_idx, sc = split_append_merge_idx_by_maxsim(k_un, n_append, _ln(spec, s_k), want_sc)
         if rec is not None:
             rec.append_idx, rec.merge_idx, rec.append_scores = append_idx.clone(), merge_idx.clone(), sc
+        if forced is not None and forced.get("append_idx") is not None and sc is not None:
+            f_app = forced["append_idx"].long()
+            differ_rows, illegal_rows = _check_forced_append(sc, n_append, append_idx, f_app)
+            if rec is not None:
+                rec.append_rows_differ, rec.append_rows_illegal = differ_rows, illegal_rows
+            member = torch.zeros(sc.shape, dtype=torch.bool)
+            member.scatter_(-1, f_app, True)
+            all_idx = torch.arange(overflow_len).view(1, 1, -1).expand_as(member)
+            append_idx = f_app
+            merge_idx = all_idx[~member].view(sc.size(0), sc.size(1), overflow_len - n_append)
         k_append = _gather_by_idx(k_ap, append_idx)
         v_append = _gather_by_idx(v_ap, append_idx)
         k_merge = _gather_by_idx(k_g, merge_idx)
@@ -318,14 +358,37 @@ def update_state_from_overflow_tokens(
     protected = min(spec.sink_len, cur)
     if cur <= protected:
         raise AssertionError("KVM state update requires at least one non-sink slot before merging.")
-    return merge_into_state(spec, k_merge, v_merge, s_k, s_v, s_vlen, protected, rec)
+    return merge_into_state(spec, k_merge, v_merge, s_k, s_v, s_vlen, protected, rec,
+                            forced_best=None if forced is None else forced.get("best_idx"))
+
+
+def _check_forced_append(scores, n_append: int, own_idx, forced_idx):
+    """Rows whose forced append set differs from the oracle's, and how many of those are not explained
+    by equal (or one-bf16-step apart) scores at the cut between appended and merged tokens."""
+    differ = illegal = 0
+    B, H, C = scores.shape
+    for b in range(B):
+        for h in range(H):
+            own = set(own_idx[b, h].tolist())
+            got = set(forced_idx[b, h].tolist())
+            if own == got:
+                continue
+            differ += 1
+            sc = scores[b, h]
+            thr = float(sc.sort().values[n_append - 1])
+            tol = abs(thr) * 2.0 ** -7 + 1e-6
+            must = {i for i in range(C) if float(sc[i]) < thr - tol}
+            may = {i for i in range(C) if float(sc[i]) <= thr + tol}
+            if not (must <= got <= may) or len(got) != n_append:
+                illegal += 1
+    return differ, illegal
 
 
 # ----------------------------------------------------------------------------- prefill / decode
 
 
 def prefill(spec: KvmSpec, q, k, v, merge_gate, *, training: bool = False, trace: list | None = None,
-            snapshots: list | None = None):
+            snapshots: list | None = None, forced: list | None = None):
     """model/kvm_mixer.py:403-516 up to (not including) ``c_proj``.
 
     Returns (y [B,T,Hq*Dv], state) where ``state`` holds exactly the entries the reference writes
@@ -349,6 +412,7 @@ def prefill(spec: KvmSpec, q, k, v, merge_gate, *, training: bool = False, trace
     else:
         s_vlen = torch.ones_like(v[..., :init_len, :1])
     coverage = init_len
+    n_upd = 0
 
     for qb in range(front, T, C):
         qe = min(T, qb + C)
@@ -367,7 +431,9 @@ def prefill(spec: KvmSpec, q, k, v, merge_gate, *, training: bool = False, trace
             s_k, s_v, s_vlen = update_state_from_overflow_tokens(
                 spec, s_k, s_v, s_vlen, k[:, :, bb:nb], v[:, :, bb:nb], merge_gate[:, :, bb:nb],
                 ctx_len=qe, available_context=nb, trace=trace,
+                forced=None if forced is None else forced[n_upd],
             )
+            n_upd += 1
             coverage = nb
 
     y = torch.cat(outs, dim=-2).transpose(1, 2).contiguous().view(B, T, -1)
@@ -388,7 +454,8 @@ def prefill(spec: KvmSpec, q, k, v, merge_gate, *, training: bool = False, trace
     return y, state
 
 
-def decode_step(spec: KvmSpec, q, k, v, merge_gate, state: dict[str, Any], trace: list | None = None):
+def decode_step(spec: KvmSpec, q, k, v, merge_gate, state: dict[str, Any], trace: list | None = None,
+                forced: dict | None = None):
     """model/kvm_mixer.py:572-713 up to ``c_proj``; returns (y [B,1,Hq*Dv], new state)."""
     B, _, n, _ = q.size()
     if n != 1:
@@ -423,6 +490,7 @@ def decode_step(spec: KvmSpec, q, k, v, merge_gate, state: dict[str, Any], trace
         s_k, s_v, s_vlen = update_state_from_overflow_tokens(
             spec, s_k, s_v, s_vlen, full_k[:, :, lo:hi], full_v[:, :, lo:hi], full_g[:, :, lo:hi],
             ctx_len=spec.n_bswa_chunks * C + coverage, available_context=coverage + C, trace=trace,
+            forced=forced,
         )
         coverage = new_cov
     lo = max(new_begin - old_begin, 0)

@@ -1,0 +1,136 @@
+"""GPU parity of the decode path (ring write, boundary memory update, split-K attention)."""
+
+import pytest
+import torch
+
+from kvm_paper_b200 import ops
+from oracle import kvm_oracle as ko
+from tests.helpers import SMALL_FIXTURES, load_fixture, spec_from_fixture, assert_close_bf16
+from tests import gpu_helpers as gh
+
+pytestmark = pytest.mark.gpu
+
+
+def _decode_against_oracle(spec, cache, state, dq, dk, dv, dg, seqs=None):
+    """Step the device cache and the oracle in lockstep; the oracle follows the device's routing
+    decisions after checking them (see oracle ``forced``)."""
+    B = dq.size(0)
+    Hkv = spec.num_key_value_heads
+    trace = []
+    ys_dev, ys_ref = [], []
+    for i in range(dq.size(2)):
+        qi, ki, vi, gi = (t[:, :, i:i + 1] for t in (dq, dk, dv, dg))
+        out = cache.step(qi.cuda(), ki.cuda(), vi.cuda(), gi.cuda(), want_route=True).clone()
+        forced = None
+        if cache._last_any_update:
+            forced = gh.decisions_from_route(cache.route, B, Hkv)
+        with torch.no_grad():
+            y, state = ko.decode_step(spec, qi, ki, vi, gi, state, trace=trace, forced=forced)
+        ys_dev.append(out.cpu())
+        ys_ref.append(y)
+    return torch.cat(ys_dev, 1), torch.cat(ys_ref, 1), state, trace
+
+
+@pytest.mark.parametrize("name", SMALL_FIXTURES)
+def test_decode_after_prefill_matches_oracle(name):
+    fix = load_fixture(name)
+    if fix["decode_qkv"] is None:
+        pytest.skip("fixture has no decode steps")
+    spec = gh.bf16_spec(spec_from_fixture(fix))
+    pq = fix["post_qkv"]
+    q, k, v, g = (pq[n].to(torch.bfloat16) for n in ("q", "k", "v", "merge_gate"))
+    B = q.size(0)
+    params, plan, res = gh.device_prefill(spec, q, k, v, g)
+    forced = [gh.decisions_from_route(res.route[:, u], B, spec.num_key_value_heads) for u in range(1, plan.n_updates + 1)]
+    with torch.no_grad():
+        _, state = ko.prefill(spec, q, k, v, g, forced=forced)
+    cache = ops.decode_cache_from_prefill(params, res, k.cuda(), v.cuda(), g.cuda(), gh.desired_fn(spec))
+    dq, dk, dv, dg = (t.to(torch.bfloat16) for t in fix["decode_qkv"])
+    y_dev, y_ref, state, trace = _decode_against_oracle(spec, cache, state, dq, dk, dv, dg)
+    gh.assert_routing_ok(gh.summarize(trace))
+    assert_close_bf16(y_dev, y_ref, f"{name} decode activations")
+    if pq["q"].dtype == torch.bfloat16:
+        assert_close_bf16(y_dev, fix["y_decode"], f"{name} decode activations vs reference fixture")
+    # carried state in the reference's eager layout
+    sd = cache.logical_state_dict()
+    S = state["kvm_s_k"].size(2)
+    assert sd["kvm_s_k"].size(2) == S
+    assert sd["kvm_state_coverage_len"] == state["kvm_state_coverage_len"]
+    assert sd["kvm_bswa_begin"] == state["kvm_bswa_begin"]
+    gh.compare_memory(cache.memory, state, S, name + " decode")
+    assert torch.equal(sd["kvm_bswa_k"].cpu(), state["kvm_bswa_k"])
+    assert torch.equal(sd["kvm_bswa_v"].cpu(), state["kvm_bswa_v"])
+    assert torch.equal(sd["kvm_bswa_merge_gate"].cpu(), state["kvm_bswa_merge_gate"])
+    assert cache.total_len.cpu().tolist() == [state["total_len"]] * B
+    assert cache.state_len.cpu().tolist() == [S] * B
+
+
+def test_decode_ragged_batch_matches_per_sequence_oracle():
+    """Sequences with different context lengths in one batch (the reference cannot batch these): every
+    sequence is checked against its own B=1 oracle run; different sequences cross block boundaries at
+    different steps."""
+    torch.manual_seed(21)
+    spec = ko.KvmSpec(4, 2, 64, 64, 32, 32, 2, 8, 1, "power_law", state_growth_factor=4.0, state_min_len=32)
+    lens = [70, 150, 97, 255, 31, 128]
+    n_steps = 70
+    B = len(lens)
+    params = gh.layer_params(spec)
+    states, inputs = [], []
+    cache = ops.KvmDecodeCache(params, B, 64, gh.desired_fn(spec))
+    for b, T in enumerate(lens):
+        q = torch.randn(1, 4, T + n_steps, 64).bfloat16()
+        k = torch.nn.functional.layer_norm(torch.randn(1, 2, T + n_steps, 64), (64,)).bfloat16()
+        v = torch.randn(1, 2, T + n_steps, 64).bfloat16()
+        g = (1 + torch.nn.functional.elu(torch.randn(1, 2, T + n_steps, 1))).bfloat16()
+        inputs.append((q, k, v, g))
+        _, plan, res = gh.device_prefill(spec, q[:, :, :T], k[:, :, :T], v[:, :, :T], g[:, :, :T])
+        forced = [gh.decisions_from_route(res.route[:, u], 1, 2) for u in range(1, plan.n_updates + 1)]
+        with torch.no_grad():
+            _, st = ko.prefill(spec, q[:, :, :T], k[:, :, :T], v[:, :, :T], g[:, :, :T], forced=forced)
+        states.append(st)
+        S = plan.final_state_len
+        bb = plan.bswa_begin
+        cache.load_sequence(b, k_sum=res.memory.k_sum[:, :S], v_sum=res.memory.v_sum[:, :S], vlen=res.memory.vlen[:, :S],
+                            k_attn=res.memory.k_attn[:, :S], v_attn=res.memory.v_attn[:, :S],
+                            window_k=k[0, :, bb:T].cuda(), window_v=v[0, :, bb:T].cuda(), window_gate=g[0, :, bb:T].cuda(),
+                            total_len=T)
+    cache.commit_lengths()
+    traces = [[] for _ in lens]
+    for i in range(n_steps):
+        step_in = [torch.cat([inp[j][:, :, lens[b] + i: lens[b] + i + 1] for b, inp in enumerate(inputs)], 0) for j in range(4)]
+        out = cache.step(*(t.cuda() for t in step_in), want_route=True).clone().cpu()
+        for b in range(B):
+            forced = None
+            if cache._last_n_append is not None and cache._last_n_append[b] >= 0:
+                forced = gh.decisions_from_route(cache.route[b * 2:(b + 1) * 2], 1, 2)
+            with torch.no_grad():
+                y, states[b] = ko.decode_step(spec, *(t[b:b + 1] for t in step_in), states[b], trace=traces[b], forced=forced)
+            assert_close_bf16(out[b:b + 1], y, f"seq {b} step {i}", mean_rel_tol=5e-3)
+    for b in range(B):
+        gh.assert_routing_ok(gh.summarize(traces[b]))
+        sd = cache.logical_state_dict(b)
+        assert sd["kvm_s_k"].size(2) == states[b]["kvm_s_k"].size(2)
+        assert torch.equal(sd["kvm_bswa_k"].cpu(), states[b]["kvm_bswa_k"])
+    assert cache.total_len.cpu().tolist() == [t + n_steps for t in lens]
+    assert sum(len(t) for t in traces) >= 8  # several boundary updates happened
+
+
+def test_decode_adopts_reference_eager_cache():
+    """A cache written in the reference's eager layout (from the fixture) is adopted: the attention
+    view of the memory is rebuilt on the device and decoding continues from it."""
+    fix = load_fixture("powerlaw_bf16")
+    spec = gh.bf16_spec(spec_from_fixture(fix))
+    params = gh.layer_params(spec)
+    st = fix["state_prefill"]
+    B, Hkv, S, D = st["kvm_s_k"].shape
+    cache = ops.KvmDecodeCache(params, B, S + spec.chunk_len, gh.desired_fn(spec))
+    for b in range(B):
+        cache.load_sequence(b, k_sum=st["kvm_s_k"][b].cuda(), v_sum=st["kvm_s_v"][b].cuda(), vlen=st["kvm_s_vlen"][b].cuda(),
+                            window_k=st["kvm_bswa_k"][b].cuda(), window_v=st["kvm_bswa_v"][b].cuda(),
+                            window_gate=st["kvm_bswa_merge_gate"][b].cuda(), total_len=st["total_len"])
+    cache.commit_lengths(refresh_attention_view=True)
+    dq, dk, dv, dg = fix["decode_qkv"]
+    state = {k: v for k, v in st.items()}
+    y_dev, y_ref, state, trace = _decode_against_oracle(spec, cache, state, dq, dk, dv, dg)
+    gh.assert_routing_ok(gh.summarize(trace))
+    assert_close_bf16(y_dev, fix["y_decode"], "decode from adopted eager cache vs reference fixture")
