@@ -1,0 +1,499 @@
+"""Benchmark of the KVM sequence-mixer hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl b200|reference] [--no-decode]
+
+Workload (N=1): one KVM layer, bf16 prefill, batch 4 x 32768 tokens, 16 heads x 128, block 256,
+memory growing by one mean per block (cap 1024) -- the configuration the headline metric
+"KVM prefill tok/s @32k" is quoted on.  Synthetic seeded inputs: hidden ~ LayerNorm(N(0,1)), random-init
+projection weights (seed 1); the post-QKV tensors are produced once by the mixer's own PyTorch prologue,
+the timed step is the operator between the post-QKV tensors and the input of ``c_proj`` (the boundary the
+reference's own kernel benchmark times).  For N>1 (torchrun) heads are sharded over the ranks and the
+step includes the NCCL all-gather of the mixer outputs.
+
+One JSON line is printed by rank 0:  value = prefill tokens/s (inputs resident in HBM), e2e = the same
+through the public operator call with pinned HOST buffers (H2D of q,k,v,gate and D2H of the output inside
+the timed region), roofline = block-attention kernel against the measured bf16 tensor peak,
+cpu_baseline = the CPU oracle (a port of the reference's eager mixer) on a bounded sample,
+decode = decode tokens/s of 64 ragged sequences (the second half of the metric).
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import math
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+CFG2 = dict(B=4, T=32768, H=16, D=128, C=256, W=2, cap_chunks=4, rope=64, sink=1, hidden=2048)
+CFG3 = dict(n_seq=64, ctx_lo=4096, ctx_hi=65536, steps=512, H=16, D=128, C=256, W=2, cap_chunks=4, rope=64, sink=1)
+METRIC = "kvm_prefill_tokens_per_s_T32768"
+UNIT = "tokens/s"
+
+
+def _peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            p = json.load(f)
+        return dict(bf16_tflops=float(p["bf16_tflops"]), hbm_gbs=float(p["hbm_gbs"]), source="measured")
+    return dict(bf16_tflops=1590.0, hbm_gbs=6650.0, source="fallback")
+
+
+def plus_one_schedule(max_state_len):
+    def desired(ctx_len, available_context, current):
+        cur = max(int(current), 0)
+        return max(min(cur + 1, max(int(available_context), 0), max_state_len), cur)
+    return desired
+
+
+def attention_pairs(T, C, W, plan):
+    """Exact (query, key) pair count of one (batch, head) row: causal front + window + memory."""
+    F = min(T, W * C)
+    pairs = F * (F + 1) // 2
+    for j in range(W, (T + C - 1) // C):
+        qb, qe = j * C, min(T, (j + 1) * C)
+        n = qe - qb
+        bb = max(0, (j + 1 - W) * C)
+        S = plan.state_before[j - W] + plan.n_append[j - W]
+        pairs += n * (qb - bb) + n * (n + 1) // 2 + n * S
+    return pairs
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons with nvidia-smi while the timed region runs."""
+
+    Q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index, self.rows, self._stop = index, [], threading.Event()
+        self._t = threading.Thread(target=self._run, daemon=True)
+
+    def _run(self):
+        while not self._stop.is_set():
+            try:
+                out = subprocess.run(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-i", str(self.index)],
+                                     capture_output=True, text=True, timeout=5).stdout.strip()
+                if out:
+                    self.rows.append([c.strip() for c in out.split(",")])
+            except Exception:
+                pass
+            self._stop.wait(0.2)
+
+    def __enter__(self):
+        self._t.start()
+        return self
+
+    def __exit__(self, *a):
+        self._stop.set()
+        self._t.join(timeout=6)
+
+    def summary(self):
+        sm = sorted(int(r[0]) for r in self.rows if r and r[0].isdigit())
+        mx = [int(r[1]) for r in self.rows if len(r) > 1 and r[1].isdigit()]
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = sorted({n for r in self.rows for n, c in zip(names, r[2:6]) if c.lower().startswith("active")})
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": max(mx) if mx else None, "reasons": reasons,
+                "samples": len(self.rows)}
+
+
+# ------------------------------------------------------------------------------------ workload
+
+def make_mixer(cfg, heads, device):
+    """The drop-in mixer with random-init weights (seed 1) for `heads` of the layer's heads."""
+    import types
+
+    from kvm_paper_b200.mixer import SequenceMixer
+
+    c = types.SimpleNamespace(
+        num_attention_heads=heads, num_key_value_heads=None, d_qk_head=None, d_v_head=None, d_head=cfg["D"],
+        hidden_size=cfg["hidden"], num_hidden_layers=1, mup_base_dim=768, rope_partial_dim=cfg["rope"],
+        use_value_residual=0, kvm_value_residual_mode="rwkv", kvm_token_shift_mode="rwkv", use_tokenshift_att=0,
+        kvm_apply_merge_gate_to_initial_state=0, kvm_apply_merge_gate_to_appends=0, kvm_use_merge_gate_keys=1,
+        kvm_use_merge_gate_values=1, kvm_use_head_temps=1, kvm_use_vlens=1, sink_len=cfg["sink"], chunk_len=cfg["C"],
+        n_max_d_chunks=cfg["cap_chunks"], n_bswa_chunks=cfg["W"], state_budget_mode="fixed", state_growth_factor=1.0,
+        state_growth_exponent=0.5, state_round_down=1, state_min_len=cfg["C"], state_saturation_n=None)
+    torch.manual_seed(1)
+    old = torch.get_default_dtype()
+    torch.set_default_dtype(torch.bfloat16)
+    try:
+        m = SequenceMixer(c, 0)
+    finally:
+        torch.set_default_dtype(old)
+    m._desired_state_len = plus_one_schedule(m.max_state_len)
+    return m.to(device).eval()
+
+
+def rotary_tables(T, D, rope, device):
+    freq = (1 / 10000.0) ** torch.linspace(0.0, 1.0, steps=rope // 2, dtype=torch.float32, device=device)
+    freq = torch.cat([freq.repeat_interleave(2), freq.new_zeros(D - rope)])
+    theta = torch.arange(T, device=device, dtype=torch.float32).view(1, T, 1, 1) * freq.view(1, 1, 1, -1)
+    cos, sin = theta.cos().bfloat16(), theta.sin().bfloat16()
+    sin[..., 1::2] *= -1
+    return cos, sin
+
+
+def post_qkv_inputs(cfg, heads, head0, device, batch=None, T=None):
+    """Seeded synthetic post-QKV tensors for heads [head0, head0+heads) of the layer: the full layer's
+    projection weights are drawn with seed 1 and sliced, so every sharding sees the same numbers."""
+    B = cfg["B"] if batch is None else batch
+    T = cfg["T"] if T is None else T
+    full = make_mixer(cfg, cfg["H"], device)
+    D = cfg["D"]
+    sl = slice(head0 * D, (head0 + heads) * D)
+    g = torch.Generator(device=device).manual_seed(1)
+    cos, sin = rotary_tables(T, D, cfg["rope"], device)
+    qs, ks, vs, gs = [], [], [], []
+    with torch.no_grad():
+        for b in range(B):  # one batch row at a time keeps the transient projections small
+            x = torch.randn(1, T, cfg["hidden"], generator=g, device=device, dtype=torch.float32)
+            x = torch.nn.functional.layer_norm(x, (cfg["hidden"],)).bfloat16()
+            q = torch.nn.functional.linear(x, full.c_q.weight[sl]).view(1, T, heads, D)
+            k = torch.nn.functional.linear(x, full.c_k.weight[sl]).view(1, T, heads, D)
+            v = torch.nn.functional.linear(x, full.c_v.weight[sl]).view(1, T, heads, D)
+            q, k = full.ln_q(q), full.ln_k(k)
+            from kvm_paper_b200.mixer import apply_rotary
+            q, k = apply_rotary(q, (cos, sin)), apply_rotary(k, (cos, sin))
+            gate = 1.0 + torch.nn.functional.elu(torch.nn.functional.linear(x, full.key_weighting.weight[head0:head0 + heads]))
+            qs.append(q); ks.append(k); vs.append(v); gs.append(gate.view(1, T, heads, 1))
+    # [B,T,h,D] storage, handed to the operator as the transposed [B,h,T,D] views the mixer produces
+    q, k, v, gate = (torch.cat(t, 0) for t in (qs, ks, vs, gs))
+    return q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2), gate.transpose(1, 2)
+
+
+# ------------------------------------------------------------------------------------- b200 arm
+
+def run_b200(args):
+    import torch.distributed as dist
+
+    from kvm_paper_b200 import _lib, ops
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus:
+        if world == 1 and args.gpus > 1:
+            raise SystemExit("launch with torchrun --nproc-per-node N for --gpus N")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    _lib.load()
+    cfg = CFG2
+    H, D, B, T, C, W = cfg["H"], cfg["D"], cfg["B"], cfg["T"], cfg["C"], cfg["W"]
+    if H % world:
+        raise SystemExit(f"{H} heads cannot be sharded over {world} ranks")
+    h_loc = H // world
+    head0 = rank * h_loc
+
+    mixer = make_mixer(cfg, h_loc, dev)
+    q, k, v, gate = post_qkv_inputs(cfg, h_loc, head0, dev)
+    plan = mixer.make_prefill_plan(T)
+    params = mixer.layer_params(dev)
+    runner = ops.PrefillRunner(params, B, plan)
+    gathered = torch.empty(world, B, T, h_loc * D, device=dev, dtype=torch.bfloat16) if world > 1 else None
+
+    def step():
+        out = runner.run(q, k, v, gate)
+        if world > 1:
+            dist.all_gather_into_tensor(gathered, out)
+        return out
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    barrier()
+    ev = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps + 1)]
+    with ClockSampler(local) as clocks:
+        barrier()
+        ev[0].record()
+        for i in range(args.steps):
+            step()
+            ev[i + 1].record()
+        barrier()
+    total_ms = ev[0].elapsed_time(ev[-1])
+    t = torch.tensor([total_ms], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    total_ms = float(t.item())
+    ms_per_step = total_ms / args.steps
+    value = B * T / (ms_per_step * 1e-3)
+
+    # ---- per-phase kernel times (CUDA events on the launching stream), attention roofline
+    def time_phase(phases, reps):
+        runner.run(q, k, v, gate, phases=phases)
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(reps):
+            runner.run(q, k, v, gate, phases=phases)
+        b.record()
+        torch.cuda.synchronize()
+        return a.elapsed_time(b) / reps
+
+    chain_ms = time_phase(_lib.PREFILL_CHAIN, max(3, args.steps // 2))
+    attn_ms = time_phase(_lib.PREFILL_ATTENTION, max(3, args.steps // 2))
+    peaks = _peaks()
+    pairs = attention_pairs(T, C, W, plan)
+    attn_flops = 4.0 * D * pairs * B * h_loc          # QK^T and PV of this rank's heads
+    achieved = attn_flops / (attn_ms * 1e-3) / 1e12
+    roofline = {"bound": "tensor", "kernel": "kvm_attn_prefill_kernel", "achieved": round(achieved, 2),
+                "peak": peaks["bf16_tflops"], "unit": "TFLOP/s", "frac": round(achieved / peaks["bf16_tflops"], 4),
+                "peak_source": peaks["source"], "traffic": _traffic("attn_prefill", B * h_loc * T),
+                "ms": round(attn_ms, 4), "chain_ms": round(chain_ms, 4),
+                "algorithmic_flops": attn_flops}
+
+    # ---- end to end through the operator call with host buffers
+    e2e = None
+    if rank == 0 or world > 1:
+        hq, hk, hv, hg = (torch.empty(t_.shape, dtype=t_.dtype).pin_memory() for t_ in
+                          (q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2), gate.transpose(1, 2)))
+        for h_, d_ in ((hq, q), (hk, k), (hv, v), (hg, gate)):
+            h_.copy_(d_.transpose(1, 2))
+        dq, dk, dv, dg = (torch.empty_like(h_, device=dev) for h_ in (hq, hk, hv, hg))
+        h_out = torch.empty(B, T, h_loc * D, dtype=torch.bfloat16).pin_memory()
+
+        def e2e_step():
+            dq.copy_(hq, non_blocking=True); dk.copy_(hk, non_blocking=True)
+            dv.copy_(hv, non_blocking=True); dg.copy_(hg, non_blocking=True)
+            out = runner.run(dq.transpose(1, 2), dk.transpose(1, 2), dv.transpose(1, 2), dg.transpose(1, 2))
+            h_out.copy_(out, non_blocking=True)
+
+        n_e2e = max(2, min(args.steps, 5))
+        e2e_step()
+        barrier()
+        a, b_ = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(n_e2e):
+            e2e_step()
+        b_.record()
+        barrier()
+        t2 = torch.tensor([a.elapsed_time(b_) / n_e2e], device=dev, dtype=torch.float64)
+        if world > 1:
+            dist.all_reduce(t2, op=dist.ReduceOp.MAX)
+        h2d = sum(t_.numel() * t_.element_size() for t_ in (hq, hk, hv, hg))
+        e2e = {"value": round(B * T / (float(t2.item()) * 1e-3), 1), "unit": UNIT, "ms_per_step": round(float(t2.item()), 3),
+               "h2d_bytes_per_step": h2d * world, "d2h_bytes_per_step": h_out.numel() * 2 * world}
+        del hq, hk, hv, hg, dq, dk, dv, dg, h_out
+
+    del runner, q, k, v, gate, gathered
+    torch.cuda.empty_cache()
+    decode = None if args.no_decode else run_decode(args, dev, rank, world, peaks)
+
+    cpu = None
+    if rank == 0 and world == 1 and not args.no_cpu:
+        cpu = cpu_baseline(cfg, seconds_hint=20)
+
+    if rank == 0:
+        line = {
+            "metric": METRIC, "value": round(value, 1), "unit": UNIT, "n_gpus": world, "steps": args.steps,
+            "warmup": max(args.warmup, 3), "ms_per_step": round(ms_per_step, 4), "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": "BASELINE configs[1]: single KVM layer bf16 prefill, B4 x T32768, 16 heads x 128, "
+                                   "block 256, +1 mean per block (cap 1024), post-QKV operator boundary",
+                       "global_batch": B, "seq_len": T, "heads_per_gpu": h_loc,
+                       "parallelism": f"heads/{world}" + (" + all-gather of outputs" if world > 1 else ""),
+                       "l2": "inputs (1.6 GB) larger than L2, no flush needed"},
+            "e2e": e2e, "gpu_launches": 2 * args.steps, "roofline": roofline, "cpu_baseline": cpu,
+            "clocks": clocks.summary(), "decode": decode,
+        }
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def _traffic(kernel, units):
+    """DRAM bytes per launch from the committed ncu summary (bytes per unit x units), or None."""
+    path = os.path.join(ROOT, "profiles", "traffic.json")
+    if not os.path.exists(path):
+        return None
+    with open(path) as f:
+        t = json.load(f)
+    if kernel not in t:
+        return None
+    return t[kernel]["dram_bytes_per_unit"] * units
+
+
+def run_decode(args, dev, rank, world, peaks):
+    """Decode tokens/s of 64 sequences with ragged prefilled contexts, sequences sharded over ranks."""
+    import numpy as np
+    import torch.distributed as dist
+
+    from kvm_paper_b200 import ops
+
+    c = CFG3
+    n_loc = c["n_seq"] // world
+    rng = np.random.RandomState(3)
+    ctx = rng.randint(c["ctx_lo"], c["ctx_hi"] + 1, size=c["n_seq"])
+    mine = ctx[rank * n_loc:(rank + 1) * n_loc]
+    cfgm = dict(CFG2, H=c["H"])
+    mixer = make_mixer(cfgm, c["H"], dev)
+    params = mixer.layer_params(dev)
+    H, D, C, W = c["H"], c["D"], c["C"], c["W"]
+    steps = c["steps"] if args.decode_steps is None else args.decode_steps
+    cache = ops.KvmDecodeCache(params, n_loc, 1024 + C, mixer._desired_state_len)
+    gen = torch.Generator(device=dev).manual_seed(3 + rank)
+    for b, T in enumerate(mine.tolist()):
+        # state built by a seeded chain-only prefill of this sequence's context
+        k = torch.nn.functional.layer_norm(torch.randn(1, T, H, D, generator=gen, device=dev), (D,)).bfloat16().transpose(1, 2)
+        v = torch.randn(1, T, H, D, generator=gen, device=dev).bfloat16().transpose(1, 2)
+        g = (1 + torch.nn.functional.elu(torch.randn(1, T, H, 1, generator=gen, device=dev))).bfloat16().transpose(1, 2)
+        plan = ops.build_prefill_plan(T, C, W, mixer._desired_state_len, keep_versions=False)
+        r = ops.PrefillRunner(params, 1, plan)
+        r.run(k, k, v, g, phases=1)
+        S, bb = plan.final_state_len, plan.bswa_begin
+        m = r.memory
+        cache.load_sequence(b, k_sum=m.k_sum[:, :S], v_sum=m.v_sum[:, :S], vlen=m.vlen[:, :S], k_attn=m.k_attn[:, :S],
+                            v_attn=m.v_attn[:, :S], window_k=k[0, :, bb:], window_v=v[0, :, bb:], window_gate=g[0, :, bb:],
+                            total_len=T)
+        del r, k, v, g
+    cache.commit_lengths()
+    q = torch.randn(steps, n_loc, H, 1, D, generator=gen, device=dev).bfloat16()
+    k = torch.nn.functional.layer_norm(torch.randn(steps, n_loc, H, 1, D, generator=gen, device=dev), (D,)).bfloat16()
+    v = torch.randn(steps, n_loc, H, 1, D, generator=gen, device=dev).bfloat16()
+    g = (1 + torch.nn.functional.elu(torch.randn(steps, n_loc, H, 1, 1, generator=gen, device=dev))).bfloat16()
+    outs = torch.empty(steps, n_loc, H * D, device=dev, dtype=torch.bfloat16)
+    gathered = torch.empty(world, steps, n_loc, H * D, device=dev, dtype=torch.bfloat16) if world > 1 else None
+    # algorithmic bytes of the timed steps: memory + window rows of every sequence, K and V, bf16
+    tl, sl = cache.total_len_h.copy(), cache.state_len_h.copy()
+    snap = (cache.memory.k_sum.clone(), cache.memory.v_sum.clone(), cache.memory.vlen.clone(), cache.memory.k_attn.clone(),
+            cache.memory.v_attn.clone(), cache.ring_k.clone(), cache.ring_v.clone(), cache.ring_gate.clone())
+
+    def restore():
+        for dst, src in zip((cache.memory.k_sum, cache.memory.v_sum, cache.memory.vlen, cache.memory.k_attn,
+                             cache.memory.v_attn, cache.ring_k, cache.ring_v, cache.ring_gate), snap):
+            dst.copy_(src)
+        cache.total_len_h[:] = tl
+        cache.state_len_h[:] = sl
+        cache.commit_lengths()
+
+    def run_all():
+        nbytes = 0
+        for i in range(steps):
+            out = cache.step(q[i], k[i], v[i], g[i])
+            outs[i].copy_(out.view(n_loc, H * D))
+            begin = np.maximum(0, ((cache.total_len_h + C - 1) // C) * C - W * C)
+            rows = np.where(begin > 0, cache.state_len_h, 0) + (cache.total_len_h - begin)
+            nbytes += int(rows.sum()) * H * 2 * D * 2
+        if world > 1:
+            dist.all_gather_into_tensor(gathered, outs)
+        return nbytes
+
+    run_all()  # warm-up pass over the whole trajectory
+    restore()
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    a, b_ = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0 = time.perf_counter()
+    a.record()
+    nbytes = run_all()
+    b_.record()
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    wall = time.perf_counter() - t0
+    t = torch.tensor([a.elapsed_time(b_)], device=dev, dtype=torch.float64)
+    nb = torch.tensor([float(nbytes)], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        dist.all_reduce(nb, op=dist.ReduceOp.SUM)
+    ms = float(t.item())
+    gbs = float(nb.item()) / world / (ms * 1e-3) / 1e9  # per GPU
+    return {"metric": "kvm_decode_tokens_per_s", "value": round(c["n_seq"] * steps / (ms * 1e-3), 1), "unit": UNIT,
+            "sequences": c["n_seq"], "steps": steps, "ms_per_step": round(ms / steps, 4),
+            "host_wall_ms_per_step": round(wall * 1e3 / steps, 4), "memory_updates": int(cache.update_count),
+            "workload": "BASELINE configs[2]: 64 ragged sequences, contexts U[4096,65536] (seed 3), 16 heads x 128, "
+                        "block 256, +1 mean per block; sequences sharded over ranks",
+            "roofline": {"bound": "hbm", "kernel": "kvm_decode_attn_kernel", "achieved": round(gbs, 1),
+                         "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": round(gbs / peaks["hbm_gbs"], 4),
+                         "peak_source": peaks["source"],
+                         "note": "algorithmic K/V bytes of all steps / whole-step device time (ring write, boundary updates and combine included)"}}
+
+
+# ------------------------------------------------------------------------------------ CPU oracle
+
+def cpu_baseline(cfg, seconds_hint=20, heads=4, T=None):
+    """The CPU oracle (port of the reference's eager mixer) on a bounded sample of the prefill workload:
+    batch 1, `heads` of the 16 heads, full length; throughput scaled by heads/16 (work is linear in heads)."""
+    from oracle import kvm_oracle as ko
+
+    T = cfg["T"] if T is None else T
+    D = cfg["D"]
+    threads = os.cpu_count() or 1
+    torch.set_num_threads(threads)
+    spec = ko.KvmSpec(heads, heads, D, D, cfg["rope"], cfg["C"], cfg["W"], cfg["cap_chunks"], cfg["sink"], "plus_one",
+                      state_min_len=cfg["C"])
+    g = torch.Generator().manual_seed(1)
+    q = torch.nn.functional.layer_norm(torch.randn(1, T, heads, D, generator=g), (D,)).bfloat16().transpose(1, 2)
+    k = torch.nn.functional.layer_norm(torch.randn(1, T, heads, D, generator=g), (D,)).bfloat16().transpose(1, 2)
+    v = torch.randn(1, T, heads, D, generator=g).bfloat16().transpose(1, 2)
+    gate = (1 + torch.nn.functional.elu(torch.randn(1, T, heads, 1, generator=g))).bfloat16().transpose(1, 2)
+    times = []
+    with torch.no_grad():
+        t0 = time.perf_counter()
+        ko.prefill(spec, q, k, v, gate)
+        first = time.perf_counter() - t0
+        reps = max(1, min(5, int(seconds_hint / max(first, 1e-3)) - 1))
+        for _ in range(reps):
+            t0 = time.perf_counter()
+            ko.prefill(spec, q, k, v, gate)
+            times.append(time.perf_counter() - t0)
+    best = sorted(times)[len(times) // 2] if times else first
+    value = T * (heads / cfg["H"]) / cfg["B"] * cfg["B"] / best  # layer-equivalent tokens/s for one batch row stream
+    return {"value": round(value, 1), "unit": UNIT, "cores": threads, "kind": "port",
+            "sample": f"oracle/kvm_oracle.py prefill, bf16, batch 1 x {heads} of {cfg['H']} heads x T={T}, median of {len(times) or 1} runs "
+                      f"({best:.2f} s each); value = T * ({heads}/{cfg['H']}) / time (work is linear in heads and batch)",
+            "torch": torch.__version__}
+
+
+def run_reference(args):
+    """Reference arm: the reference's own CPU implementation of the path.  The reference is Python and is
+    not present on the benchmark box, so its line-by-line CPU port (oracle/) is what is timed."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    cfg = CFG2
+    steps = max(1, min(args.steps, 3))
+    cpu = cpu_baseline(cfg, seconds_hint=10 * steps)
+    line = {"impl": "reference", "metric": METRIC, "value": cpu["value"], "unit": UNIT, "n_gpus": args.gpus,
+            "steps": steps, "warmup": 1, "ms_per_step": None, "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": "BASELINE configs[1] (bounded sample, see cpu_baseline.sample)", "global_batch": cfg["B"],
+                       "seq_len": cfg["T"], "parallelism": "host CPU threads"},
+            "cpu_baseline": cpu,
+            "e2e": {"value": cpu["value"], "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    print(json.dumps(line))
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--no-decode", action="store_true")
+    ap.add_argument("--no-cpu", action="store_true")
+    ap.add_argument("--decode-steps", type=int, default=None)
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_b200(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -98,13 +98,17 @@ size_t kvm_prefill_workspace_bytes(const kvm_layer* layer, int32_t batch, int64_
  *   out          [B,T,Hq*D] bf16, contiguous
  *   route_dev    optional [B*Hkv, n_updates+1, C] int32: for every token of every consumed block the
  *                memory row it was merged into (>= 0) or -(1+row) if it was appended as that row
+ *   phases       KVM_PREFILL_CHAIN | KVM_PREFILL_ATTENTION for the whole operator; one bit alone runs
+ *                that phase only (attention alone needs the versions a chain run left in `workspace`)
  */
+#define KVM_PREFILL_CHAIN 1u      /* run the memory chain (fills `memory`, the versions and route_dev) */
+#define KVM_PREFILL_ATTENTION 2u  /* run block attention (reads the versions in `workspace`, fills out) */
 int kvm_prefill_forward(const kvm_layer* layer, int32_t batch, int64_t seq_len,
                         kvm_tensor4 q, kvm_tensor4 k, kvm_tensor4 v, kvm_tensor4 gate,
                         const kvm_update_plan* plan_dev, const kvm_update_plan* plan_host,
                         int32_t n_updates, int64_t total_version_rows,
                         kvm_memory memory, void* out, int32_t* route_dev,
-                        void* workspace, size_t workspace_bytes, void* stream);
+                        void* workspace, size_t workspace_bytes, uint32_t phases, void* stream);
 
 /* The decode-time cache of one layer for `batch` sequences with ragged lengths (all device memory,
  * caller-owned).  Replaces TritonKVMDecodeCache (model/kvm_triton_decode.py:34-400); unlike the

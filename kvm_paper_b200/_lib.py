@@ -13,6 +13,7 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_HERE, "libkvm_b200.so")
 
 KVM_OK = 0
+PREFILL_CHAIN, PREFILL_ATTENTION = 1, 2
 ERROR_NAMES = {1: "bad argument", 2: "capacity", 3: "device timeout", 4: "CUDA error", 5: "unsupported"}
 
 
@@ -71,7 +72,7 @@ def load():
     lib.kvm_prefill_forward.argtypes = [
         LP(KvmLayer), C.c_int32, C.c_int64, KvmTensor4, KvmTensor4, KvmTensor4, KvmTensor4,
         C.c_void_p, LP(KvmUpdatePlan), C.c_int32, C.c_int64, KvmMemory, C.c_void_p, C.c_void_p,
-        C.c_void_p, C.c_size_t, C.c_void_p]
+        C.c_void_p, C.c_size_t, C.c_uint32, C.c_void_p]
     lib.kvm_decode_workspace_bytes.restype = C.c_size_t
     lib.kvm_decode_workspace_bytes.argtypes = [LP(KvmLayer), C.c_int32, C.c_int32]
     lib.kvm_decode_step.restype = C.c_int

@@ -10,7 +10,7 @@ namespace kvm {
 cudaError_t prefill_dispatch(int D, const LayerDev& L, int batch, long long T, Tensor4 q, Tensor4 k, Tensor4 v,
                              Tensor4 gate, const kvm_update_plan* plan_dev, int n_plan, long long ver_rows,
                              MemoryDev mem, bf16* out, int* route, bf16* ver_k, bf16* ver_v, bf16* pk_scr,
-                             bf16* gk_scr, cudaStream_t stream);
+                             bf16* gk_scr, unsigned phases, cudaStream_t stream);
 size_t update_smem_bytes(int D, int C, int capacity);
 cudaError_t decode_dispatch(int D, const LayerDev& L, int batch, const DecodeCacheDev& cache, Tensor4 q, Tensor4 k,
                             Tensor4 v, Tensor4 gate, const int* n_append, int any_update, int max_rows, bf16* out,
@@ -155,10 +155,11 @@ int kvm_prefill_forward(const kvm_layer* layer, int32_t batch, int64_t seq_len, 
                         kvm_tensor4 v, kvm_tensor4 gate, const kvm_update_plan* plan_dev,
                         const kvm_update_plan* plan_host, int32_t n_updates, int64_t total_version_rows,
                         kvm_memory memory, void* out, int32_t* route_dev, void* workspace, size_t workspace_bytes,
-                        void* stream) {
+                        uint32_t phases, void* stream) {
   g_err[0] = 0;
   if (int rc = check_layer(layer)) return rc;
   if (batch <= 0 || seq_len <= 0) return fail(KVM_ERR_BAD_ARGUMENT, "batch %d and seq_len %lld must be positive", batch, (long long)seq_len);
+  if ((phases & 3u) == 0 || (phases & ~3u)) return fail(KVM_ERR_BAD_ARGUMENT, "phases %u must be a combination of KVM_PREFILL_CHAIN and KVM_PREFILL_ATTENTION", phases);
   const int D = layer->head_dim, C = layer->chunk_len, W = layer->n_bswa_chunks;
   if (int rc = check_tensor(q, "q", D)) return rc;
   if (int rc = check_tensor(k, "k", D)) return rc;
@@ -183,7 +184,7 @@ int kvm_prefill_forward(const kvm_layer* layer, int32_t batch, int64_t seq_len, 
     if (S > memory.capacity) return fail(KVM_ERR_CAPACITY, "plan entry %d grows the memory to %lld rows, capacity is %d", u, S, memory.capacity);
     if (u > 0 && S <= (layer->sink_len < S ? layer->sink_len : S) && p.n_append < C)
       return fail(KVM_ERR_BAD_ARGUMENT, "update %d merges into a memory with no non-sink row", u);
-    if (n_qblocks > W) {
+    if (n_qblocks > W && (phases & KVM_PREFILL_ATTENTION)) {
       if (p.version_row < 0) return fail(KVM_ERR_BAD_ARGUMENT, "plan entry %d: version_row %d must not be negative", u, p.version_row);
       if (p.version_row + S > max_ver_end) max_ver_end = p.version_row + S;
     }
@@ -198,7 +199,7 @@ int kvm_prefill_forward(const kvm_layer* layer, int32_t batch, int64_t seq_len, 
                                    n_updates + 1, total_version_rows, to_dev(memory), static_cast<bf16*>(out), route_dev,
                                    reinterpret_cast<bf16*>(wsb + ws.ver_k), reinterpret_cast<bf16*>(wsb + ws.ver_v),
                                    reinterpret_cast<bf16*>(wsb + ws.pk), reinterpret_cast<bf16*>(wsb + ws.gk),
-                                   static_cast<cudaStream_t>(stream));
+                                   phases, static_cast<cudaStream_t>(stream));
   if (e != cudaSuccess) return cuda_fail(e, "kvm_prefill_forward");
   return KVM_OK;
 }

@@ -313,16 +313,20 @@ template <int D>
 static cudaError_t launch_prefill(const LayerDev& L, int batch, long long T, Tensor4 q, Tensor4 k, Tensor4 v, Tensor4 gate,
                                   const kvm_update_plan* plan_dev, int n_plan, long long ver_rows, MemoryDev mem,
                                   bf16* out, int* route, bf16* ver_k, bf16* ver_v, bf16* pk_scr, bf16* gk_scr,
-                                  cudaStream_t stream) {
+                                  unsigned phases, cudaStream_t stream) {
   constexpr int NT = 512;
   const int rows = batch * L.Hkv;
-  const size_t smem_u = UpdateSmem<D>::bytes(L.C, mem.capacity);
-  cudaError_t e = cudaFuncSetAttribute(kvm_chain_kernel<D, NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_u);
-  if (e != cudaSuccess) return e;
-  kvm_chain_kernel<D, NT><<<rows, NT, smem_u, stream>>>(L, T, k, v, gate, plan_dev, 0, n_plan, mem, ver_k, ver_v,
-                                                       ver_rows, pk_scr, gk_scr, route, n_plan);
-  e = cudaGetLastError();
-  if (e != cudaSuccess) return e;
+  cudaError_t e;
+  if (phases & KVM_PREFILL_CHAIN) {
+    const size_t smem_u = UpdateSmem<D>::bytes(L.C, mem.capacity);
+    e = cudaFuncSetAttribute(kvm_chain_kernel<D, NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_u);
+    if (e != cudaSuccess) return e;
+    kvm_chain_kernel<D, NT><<<rows, NT, smem_u, stream>>>(L, T, k, v, gate, plan_dev, 0, n_plan, mem, ver_k, ver_v,
+                                                         ver_rows, pk_scr, gk_scr, route, n_plan);
+    e = cudaGetLastError();
+    if (e != cudaSuccess) return e;
+  }
+  if (!(phases & KVM_PREFILL_ATTENTION)) return cudaSuccess;
 
   constexpr int BM = 64;
   const int n_qblocks = (int)((T + L.C - 1) / L.C);
@@ -339,11 +343,11 @@ static cudaError_t launch_prefill(const LayerDev& L, int batch, long long T, Ten
 cudaError_t prefill_dispatch(int D, const LayerDev& L, int batch, long long T, Tensor4 q, Tensor4 k, Tensor4 v,
                              Tensor4 gate, const kvm_update_plan* plan_dev, int n_plan, long long ver_rows,
                              MemoryDev mem, bf16* out, int* route, bf16* ver_k, bf16* ver_v, bf16* pk_scr,
-                             bf16* gk_scr, cudaStream_t stream) {
+                             bf16* gk_scr, unsigned phases, cudaStream_t stream) {
   switch (D) {
-    case 32: return launch_prefill<32>(L, batch, T, q, k, v, gate, plan_dev, n_plan, ver_rows, mem, out, route, ver_k, ver_v, pk_scr, gk_scr, stream);
-    case 64: return launch_prefill<64>(L, batch, T, q, k, v, gate, plan_dev, n_plan, ver_rows, mem, out, route, ver_k, ver_v, pk_scr, gk_scr, stream);
-    case 128: return launch_prefill<128>(L, batch, T, q, k, v, gate, plan_dev, n_plan, ver_rows, mem, out, route, ver_k, ver_v, pk_scr, gk_scr, stream);
+    case 32: return launch_prefill<32>(L, batch, T, q, k, v, gate, plan_dev, n_plan, ver_rows, mem, out, route, ver_k, ver_v, pk_scr, gk_scr, phases, stream);
+    case 64: return launch_prefill<64>(L, batch, T, q, k, v, gate, plan_dev, n_plan, ver_rows, mem, out, route, ver_k, ver_v, pk_scr, gk_scr, phases, stream);
+    case 128: return launch_prefill<128>(L, batch, T, q, k, v, gate, plan_dev, n_plan, ver_rows, mem, out, route, ver_k, ver_v, pk_scr, gk_scr, phases, stream);
   }
   return cudaErrorInvalidValue;
 }

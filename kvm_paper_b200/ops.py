@@ -128,7 +128,7 @@ class PrefillPlan:
 
 
 def build_prefill_plan(seq_len: int, chunk_len: int, n_bswa_chunks: int,
-                       desired_state_len: Callable[[int, int, int], int]) -> PrefillPlan:
+                       desired_state_len: Callable[[int, int, int], int], keep_versions: bool = True) -> PrefillPlan:
     """Walk the block loop of the reference prefill (model/kvm_mixer.py:450-488) on integers only.
 
     ``desired_state_len(ctx_len, available_context, current)`` is the mixer's own schedule method, so an
@@ -153,8 +153,10 @@ def build_prefill_plan(seq_len: int, chunk_len: int, n_bswa_chunks: int,
         S += na
         version_row.append(rows)
         rows += _round8(S)
-    if not keeps_versions:
-        version_row = [-1]
+    if not keeps_versions or not keep_versions:
+        # no query block reads a memory version (short prompt), or only the final memory is wanted
+        version_row = [-1] * len(n_append)
+        rows = 0
     bb = bswa_begin_for_total_len(T, Cn, W)
     return PrefillPlan(T, state_before, n_append, version_row, rows, S, max(init, bb), bb)
 
@@ -197,40 +199,61 @@ class PrefillResult:
     route: torch.Tensor | None        # [B*Hkv, n_updates+1, C] int32 if requested
 
 
+class PrefillRunner:
+    """Preallocated buffers for repeated prefills of one shape (memory, version store, output).
+
+    ``run`` only enqueues kernels on the current stream; nothing is allocated per call."""
+
+    def __init__(self, params: LayerParams, batch: int, plan: PrefillPlan, *, memory_capacity: int | None = None,
+                 want_route: bool = False):
+        lib = _lib.load()
+        cfg = params.cfg
+        self.params, self.plan, self.batch = params, plan, int(batch)
+        dev = params.device
+        cap = max(plan.final_state_len, 1) if memory_capacity is None else int(memory_capacity)
+        self.memory = MemoryBuffers(batch * cfg.n_kv_heads, cap, cfg.head_dim, dev)
+        self.ws_bytes = lib.kvm_prefill_workspace_bytes(C.byref(params.c), batch, plan.seq_len, plan.total_version_rows)
+        self.ws = torch.empty(self.ws_bytes, device=dev, dtype=torch.uint8)
+        self.out = torch.empty(batch, plan.seq_len, cfg.n_q_heads * cfg.head_dim, device=dev, dtype=torch.bfloat16)
+        self.route = None
+        if want_route:
+            self.route = torch.zeros(batch * cfg.n_kv_heads, plan.n_updates + 1, cfg.chunk_len, device=dev, dtype=torch.int32)
+        self.plan_dev = plan.to_tensor(dev)
+        self.plan_host = plan.to_ctypes()
+
+    def run(self, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, gate: torch.Tensor,
+            phases: int = _lib.PREFILL_CHAIN | _lib.PREFILL_ATTENTION) -> torch.Tensor:
+        cfg, plan = self.params.cfg, self.plan
+        B, Hq, T, D = q.shape
+        if (B, Hq, D) != (self.batch, cfg.n_q_heads, cfg.head_dim) or k.shape != (B, cfg.n_kv_heads, T, D) or v.shape != k.shape:
+            raise ValueError(f"shape mismatch: q {tuple(q.shape)}, k {tuple(k.shape)}, v {tuple(v.shape)} for {cfg}")
+        if gate.shape != (B, cfg.n_kv_heads, T, 1):
+            raise ValueError(f"merge gate must be [B,Hkv,T,1], got {tuple(gate.shape)}")
+        if T != plan.seq_len:
+            raise ValueError("plan was built for another sequence length")
+        q, k, v, gate = (_as_bf16_view(t) for t in (q, k, v, gate))
+        rc = _lib.load().kvm_prefill_forward(
+            C.byref(self.params.c), B, T, _tensor4(q, "q"), _tensor4(k, "k"), _tensor4(v, "v"), _tensor4(gate, "gate"),
+            self.plan_dev.data_ptr(), self.plan_host, plan.n_updates, plan.total_version_rows, self.memory.c(),
+            self.out.data_ptr(), _ptr(self.route), self.ws.data_ptr(), self.ws_bytes, phases,
+            _stream_ptr(self.params.device))
+        _lib.check(rc)
+        return self.out
+
+
 def prefill_forward(params: LayerParams, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, gate: torch.Tensor,
                     plan: PrefillPlan, *, memory_capacity: int | None = None, want_route: bool = False) -> PrefillResult:
     """Whole-prompt prefill through ``kvm_prefill_forward``.
 
     q [B,Hq,T,D], k/v [B,Hkv,T,D], gate [B,Hkv,T,1]; strided views are passed as they are."""
-    lib = _lib.load()
-    cfg = params.cfg
-    B, Hq, T, D = q.shape
-    if (Hq, D) != (cfg.n_q_heads, cfg.head_dim) or k.shape != (B, cfg.n_kv_heads, T, D) or v.shape != k.shape:
-        raise ValueError(f"shape mismatch: q {tuple(q.shape)}, k {tuple(k.shape)}, v {tuple(v.shape)} for {cfg}")
-    if gate.shape != (B, cfg.n_kv_heads, T, 1):
-        raise ValueError(f"merge gate must be [B,Hkv,T,1], got {tuple(gate.shape)}")
-    if T != plan.seq_len:
-        raise ValueError("plan was built for another sequence length")
-    dev = q.device
-    q, k, v, gate = (_as_bf16_view(t) for t in (q, k, v, gate))
-    cap = max(plan.final_state_len, 1) if memory_capacity is None else int(memory_capacity)
-    mem = MemoryBuffers(B * cfg.n_kv_heads, cap, D, dev)
-    ws_bytes = lib.kvm_prefill_workspace_bytes(C.byref(params.c), B, T, plan.total_version_rows)
-    ws = torch.empty(ws_bytes, device=dev, dtype=torch.uint8)
-    out = torch.empty(B, T, Hq * D, device=dev, dtype=torch.bfloat16)
-    route = None
-    if want_route:
-        route = torch.zeros(B * cfg.n_kv_heads, plan.n_updates + 1, cfg.chunk_len, device=dev, dtype=torch.int32)
-    plan_dev = plan.to_tensor(dev)
-    plan_host = plan.to_ctypes()
-    rc = lib.kvm_prefill_forward(
-        C.byref(params.c), B, T, _tensor4(q, "q"), _tensor4(k, "k"), _tensor4(v, "v"), _tensor4(gate, "gate"),
-        plan_dev.data_ptr(), plan_host, plan.n_updates, plan.total_version_rows, mem.c(), out.data_ptr(),
-        _ptr(route), ws.data_ptr(), ws_bytes, _stream_ptr(dev))
-    _lib.check(rc)
-    # the workspace is released when the caller's stream has consumed it
-    ws.record_stream(torch.cuda.current_stream(dev))
-    return PrefillResult(out, mem, plan, route)
+    if q.dim() != 4:
+        raise ValueError(f"q must be [B,Hq,T,D], got {tuple(q.shape)}")
+    if not q.is_cuda:
+        raise RuntimeError("kvm_b200 runs on CUDA tensors only (there is no CPU path)")
+    runner = PrefillRunner(params, q.size(0), plan, memory_capacity=memory_capacity, want_route=want_route)
+    out = runner.run(q, k, v, gate)
+    # buffers are released by the caching allocator in stream order
+    return PrefillResult(out, runner.memory, plan, runner.route)
 
 
 # ------------------------------------------------------------------------------------ decode cache

@@ -95,3 +95,10 @@ def compare_memory(mem: ops.MemoryBuffers, state, S: int, what=""):
     assert_close_bf16(k_sum, state["kvm_s_k"], what + " kvm_s_k", max_abs_tol=2e-2 * scale_k)
     assert_close_bf16(v_sum, state["kvm_s_v"], what + " kvm_s_v", max_abs_tol=2e-2 * scale_v)
     assert torch.allclose(vlen, state["kvm_s_vlen"].float(), rtol=1e-5, atol=1e-6), what + " kvm_s_vlen"
+
+
+def fp32_spec(spec: ko.KvmSpec) -> ko.KvmSpec:
+    import dataclasses
+    conv = lambda t: None if t is None else t.detach().cpu().float()  # noqa: E731
+    return dataclasses.replace(spec, ln_weight=conv(spec.ln_weight), ln_bias=conv(spec.ln_bias),
+                               front_head_temp=conv(spec.front_head_temp), state_head_temp=conv(spec.state_head_temp))

