@@ -42,14 +42,16 @@ def test_decode_after_prefill_matches_oracle(name):
     B = q.size(0)
     params, plan, res = gh.device_prefill(spec, q, k, v, g)
     forced = [gh.decisions_from_route(res.route[:, u], B, spec.num_key_value_heads) for u in range(1, plan.n_updates + 1)]
+    ptrace = []
     with torch.no_grad():
-        _, state = ko.prefill(spec, q, k, v, g, forced=forced)
+        _, state = ko.prefill(spec, q, k, v, g, forced=forced, trace=ptrace)
     cache = ops.decode_cache_from_prefill(params, res, k.cuda(), v.cuda(), g.cuda(), gh.desired_fn(spec))
     dq, dk, dv, dg = (t.to(torch.bfloat16) for t in fix["decode_qkv"])
     y_dev, y_ref, state, trace = _decode_against_oracle(spec, cache, state, dq, dk, dv, dg)
     gh.assert_routing_ok(gh.summarize(trace))
     assert_close_bf16(y_dev, y_ref, f"{name} decode activations")
-    if pq["q"].dtype == torch.bfloat16:
+    total = gh.summarize(ptrace + trace)
+    if pq["q"].dtype == torch.bfloat16 and total["merge_differ"] == 0 and total["append_rows_differ"] == 0:
         assert_close_bf16(y_dev, fix["y_decode"], f"{name} decode activations vs reference fixture")
     # carried state in the reference's eager layout
     sd = cache.logical_state_dict()
@@ -132,5 +134,8 @@ def test_decode_adopts_reference_eager_cache():
     dq, dk, dv, dg = fix["decode_qkv"]
     state = {k: v for k, v in st.items()}
     y_dev, y_ref, state, trace = _decode_against_oracle(spec, cache, state, dq, dk, dv, dg)
-    gh.assert_routing_ok(gh.summarize(trace))
-    assert_close_bf16(y_dev, fix["y_decode"], "decode from adopted eager cache vs reference fixture")
+    summary = gh.summarize(trace)
+    gh.assert_routing_ok(summary)
+    assert_close_bf16(y_dev, y_ref, "decode from adopted eager cache vs oracle")
+    if summary["merge_differ"] == 0 and summary["append_rows_differ"] == 0:
+        assert_close_bf16(y_dev, fix["y_decode"], "decode from adopted eager cache vs reference fixture")

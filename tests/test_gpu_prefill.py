@@ -45,10 +45,11 @@ def test_prefill_matches_oracle_and_reference_fixture(name):
         y32, _ = ko.prefill(gh.fp32_spec(spec), q.float(), k.float(), v.float(), g.float(), forced=forced)
     assert_not_worse_than_reference(res.out.cpu(), y, y32, name)
 
-    if pq["q"].dtype == torch.bfloat16:
-        # direct comparison with what the reference itself produced
+    if pq["q"].dtype == torch.bfloat16 and summary["merge_differ"] == 0 and summary["append_rows_differ"] == 0:
+        # every decision equals the reference's own: compare directly with what the reference produced
+        # (after a legal tie-break difference the two memory trajectories are no longer comparable)
         assert_close_bf16(res.out.cpu(), fix["y_prefill"], f"{name} activations vs reference fixture")
-        if summary["merge_differ"] == 0 and summary["append_rows_differ"] == 0:
+        if True:
             for u, r in enumerate(recs, start=1):
                 d = gh.decisions_from_route(res.route[:, u], B, spec.num_key_value_heads)
                 if "append_idx" in r and 0 < r["append_idx"].size(-1) < spec.chunk_len:
