@@ -209,10 +209,10 @@ size_t kvm_decode_workspace_bytes(const kvm_layer* layer, int32_t batch, int32_t
   return decode_ws(layer, batch, max_rows_per_seq).total;
 }
 
-int kvm_decode_step(const kvm_layer* layer, int32_t batch, kvm_decode_cache cache, kvm_tensor4 q, kvm_tensor4 k,
-                    kvm_tensor4 v, kvm_tensor4 gate, const int32_t* n_append_dev, int32_t any_update, int32_t max_rows,
-                    void* out, int32_t* route_dev, void* workspace, size_t workspace_bytes, void* stream) {
-  g_err[0] = 0;
+static int decode_step_impl(const kvm_layer* layer, int32_t batch, const kvm_decode_cache& cache, kvm_tensor4 q, kvm_tensor4 k,
+                            kvm_tensor4 v, kvm_tensor4 gate, const int32_t* n_append_dev, int32_t any_update, int32_t max_rows,
+                            void* out, int32_t* route_dev, void* workspace, size_t workspace_bytes, void* stream,
+                            const char* who) {
   if (int rc = check_layer(layer)) return rc;
   if (batch <= 0) return fail(KVM_ERR_BAD_ARGUMENT, "batch %d must be positive", batch);
   const int D = layer->head_dim;
@@ -228,7 +228,7 @@ int kvm_decode_step(const kvm_layer* layer, int32_t batch, kvm_decode_cache cach
   const int row_bound = cache.memory.capacity + layer->n_bswa_chunks * layer->chunk_len;
   if (max_rows <= 0 || max_rows > row_bound) return fail(KVM_ERR_BAD_ARGUMENT, "max_rows %d outside (0, capacity + window = %d]", max_rows, row_bound);
   const DecodeWs ws = decode_ws(layer, batch, max_rows);
-  if (!workspace || workspace_bytes < ws.total) return fail(KVM_ERR_CAPACITY, "workspace of %zu bytes given, %zu needed", workspace_bytes, ws.total);
+  if (!workspace || workspace_bytes < ws.total) return fail(KVM_ERR_CAPACITY, "%s: scratch of %zu bytes available, %zu needed", who, workspace_bytes, ws.total);
   if (((uintptr_t)workspace) % 256) return fail(KVM_ERR_BAD_ARGUMENT, "workspace must be 256-byte aligned");
 
   DecodeCacheDev c;
@@ -241,8 +241,16 @@ int kvm_decode_step(const kvm_layer* layer, int32_t batch, kvm_decode_cache cach
                                   reinterpret_cast<bf16*>(wsb + ws.pk), reinterpret_cast<bf16*>(wsb + ws.gk),
                                   reinterpret_cast<float*>(wsb + ws.partial), reinterpret_cast<int*>(wsb + ws.counters),
                                   kDecodeRowsPerSplit, static_cast<cudaStream_t>(stream));
-  if (e != cudaSuccess) return cuda_fail(e, "kvm_decode_step");
+  if (e != cudaSuccess) return cuda_fail(e, who);
   return KVM_OK;
+}
+
+int kvm_decode_step(const kvm_layer* layer, int32_t batch, kvm_decode_cache cache, kvm_tensor4 q, kvm_tensor4 k,
+                    kvm_tensor4 v, kvm_tensor4 gate, const int32_t* n_append_dev, int32_t any_update, int32_t max_rows,
+                    void* out, int32_t* route_dev, void* workspace, size_t workspace_bytes, void* stream) {
+  g_err[0] = 0;
+  return decode_step_impl(layer, batch, cache, q, k, v, gate, n_append_dev, any_update, max_rows, out, route_dev, workspace,
+                          workspace_bytes, stream, "kvm_decode_step");
 }
 
 int kvm_memory_refresh(const kvm_layer* layer, int32_t batch, kvm_memory memory, const int32_t* state_len_dev, void* stream) {
