@@ -144,6 +144,28 @@ int kvm_decode_step(const kvm_layer* layer, int32_t batch, kvm_decode_cache cach
                     void* out, int32_t* route_dev, void* workspace, size_t workspace_bytes,
                     void* stream);
 
+/* Same decode step for callers that cannot allocate device memory.  It has no counterpart in the
+ * reference.  Some hosts of this library only receive tensors and a stream from their runtime and are
+ * not allowed to call cudaMalloc themselves -- a plug-in inside an inference server whose memory pool is
+ * closed to plug-ins, a callback running while its framework forbids allocation, a process whose device
+ * memory was handed out in full at start-up.  For them the scratch that kvm_decode_step takes as
+ * `workspace` lives in a fixed array inside the library image instead: KVM_STATIC_SCRATCH_BYTES per GPU
+ * that loads the library, held until the process exits.  The caller still passes the cache, inputs and
+ * output.  No cudaMalloc / cudaFree or other allocating routine is called.
+ *   - Shapes whose scratch (kvm_decode_workspace_bytes) exceeds KVM_STATIC_SCRATCH_BYTES are rejected
+ *     with KVM_ERR_CAPACITY and a message naming both sizes; use kvm_decode_step then.
+ *   - The first call on each device looks up the array's device address (with that device current);
+ *     make that first call outside any stream capture.
+ *   - All calls on a device share the one array, which keeps the previous call's contents (the
+ *     part that must start at zero is cleared on the stream by every call): two calls whose kernels can
+ *     overlap on the GPU -- different streams, or different threads -- race.  Serialise them on one stream.
+ */
+#define KVM_STATIC_SCRATCH_BYTES (32u << 20)
+int kvm_decode_step_static(const kvm_layer* layer, int32_t batch, kvm_decode_cache cache,
+                           kvm_tensor4 q, kvm_tensor4 k, kvm_tensor4 v, kvm_tensor4 gate,
+                           const int32_t* n_append_dev, int32_t any_update, int32_t max_rows,
+                           void* out, int32_t* route_dev, void* stream);
+
 /* Build k_attn / v_attn from k_sum / v_sum / vlen for rows [0, state_len[b]) of every sequence
  * (used when a cache is initialised from the reference's eager cache layout).
  * Replaces the normalised-copy refresh in TritonKVMDecodeCache.reset_

@@ -3,6 +3,7 @@
 #include <cstdarg>
 #include <cstdio>
 #include <cstring>
+#include <mutex>
 
 #include "kvm_common.cuh"
 
@@ -137,6 +138,32 @@ DecodeWs decode_ws(const kvm_layer* l, int batch, int max_rows) {
   return w;
 }
 
+// ---- scratch for kvm_decode_step_static: lives in the library image, one copy per GPU that loads it.
+// In host code the name below is only a host-side handle of the symbol, never a device address: the
+// address a kernel can use is looked up with cudaGetSymbolAddress, once per device.
+static __device__ __align__(256) unsigned char g_static_scratch[KVM_STATIC_SCRATCH_BYTES];
+
+constexpr int kMaxDevices = 64;
+std::mutex g_static_mu;
+void* g_static_ptr[kMaxDevices] = {nullptr};
+
+int static_scratch_for_current_device(void** out) {
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return cuda_fail(e, "kvm_decode_step_static: cudaGetDevice");
+  if (dev < 0 || dev >= kMaxDevices) return fail(KVM_ERR_UNSUPPORTED, "kvm_decode_step_static: device ordinal %d not supported", dev);
+  std::lock_guard<std::mutex> lock(g_static_mu);
+  if (!g_static_ptr[dev]) {
+    void* p = nullptr;
+    e = cudaGetSymbolAddress(&p, g_static_scratch);
+    if (e != cudaSuccess) return cuda_fail(e, "kvm_decode_step_static: cudaGetSymbolAddress");
+    if (!p) return fail(KVM_ERR_CUDA, "kvm_decode_step_static: symbol address is NULL");
+    g_static_ptr[dev] = p;
+  }
+  *out = g_static_ptr[dev];
+  return KVM_OK;
+}
+
 }  // namespace
 
 extern "C" {
@@ -251,6 +278,28 @@ int kvm_decode_step(const kvm_layer* layer, int32_t batch, kvm_decode_cache cach
   g_err[0] = 0;
   return decode_step_impl(layer, batch, cache, q, k, v, gate, n_append_dev, any_update, max_rows, out, route_dev, workspace,
                           workspace_bytes, stream, "kvm_decode_step");
+}
+
+int kvm_decode_step_static(const kvm_layer* layer, int32_t batch, kvm_decode_cache cache, kvm_tensor4 q, kvm_tensor4 k,
+                           kvm_tensor4 v, kvm_tensor4 gate, const int32_t* n_append_dev, int32_t any_update,
+                           int32_t max_rows, void* out, int32_t* route_dev, void* stream) {
+  g_err[0] = 0;
+  if (int rc = check_layer(layer)) return rc;
+  if (batch <= 0 || max_rows <= 0) return fail(KVM_ERR_BAD_ARGUMENT, "batch %d and max_rows %d must be positive", batch, max_rows);
+  const DecodeWs ws = decode_ws(layer, batch, max_rows);
+  if (ws.total > (size_t)KVM_STATIC_SCRATCH_BYTES)
+    return fail(KVM_ERR_CAPACITY,
+                "kvm_decode_step_static: this shape needs %zu bytes of scratch, the built-in scratch holds %u "
+                "(batch %d x %d kv heads, block %d, head_dim %d, %d rows); use kvm_decode_step with a caller workspace",
+                ws.total, (unsigned)KVM_STATIC_SCRATCH_BYTES, batch, layer->n_kv_heads, layer->chunk_len, layer->head_dim, max_rows);
+  void* scratch = nullptr;
+  if (int rc = static_scratch_for_current_device(&scratch)) return rc;
+  // the array keeps whatever the previous call left: the split counters must start at zero
+  cudaError_t e = cudaMemsetAsync(static_cast<unsigned char*>(scratch) + ws.counters, 0,
+                                  ((size_t)batch * layer->n_kv_heads + batch) * sizeof(int), static_cast<cudaStream_t>(stream));
+  if (e != cudaSuccess) return cuda_fail(e, "kvm_decode_step_static: cudaMemsetAsync");
+  return decode_step_impl(layer, batch, cache, q, k, v, gate, n_append_dev, any_update, max_rows, out, route_dev, scratch,
+                          (size_t)KVM_STATIC_SCRATCH_BYTES, stream, "kvm_decode_step_static");
 }
 
 int kvm_memory_refresh(const kvm_layer* layer, int32_t batch, kvm_memory memory, const int32_t* state_len_dev, void* stream) {
