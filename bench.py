@@ -195,6 +195,11 @@ def run_b200(args):
     h_loc = H // world
     head0 = rank * h_loc
 
+    if args.decode_only:
+        d = run_decode(args, dev, rank, world, _peaks())
+        if rank == 0:
+            print(json.dumps({"metric": d["metric"], "value": d["value"], "unit": UNIT, "n_gpus": world, "decode": d}))
+        return
     mixer = make_mixer(cfg, h_loc, dev)
     q, k, v, gate = post_qkv_inputs(cfg, h_loc, head0, dev)
     plan = mixer.make_prefill_plan(T)
@@ -213,7 +218,8 @@ def run_b200(args):
             dist.barrier()
         torch.cuda.synchronize()
 
-    for _ in range(max(args.warmup, 3)):
+    n_warm = args.warmup if args.prefill_only else max(args.warmup, 3)
+    for _ in range(n_warm):
         step()
     barrier()
     ev = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps + 1)]
@@ -244,8 +250,9 @@ def run_b200(args):
         torch.cuda.synchronize()
         return a.elapsed_time(b) / reps
 
-    chain_ms = time_phase(_lib.PREFILL_CHAIN, max(3, args.steps // 2))
-    attn_ms = time_phase(_lib.PREFILL_ATTENTION, max(3, args.steps // 2))
+    n_rep = 1 if args.prefill_only else max(3, args.steps // 2)
+    chain_ms = time_phase(_lib.PREFILL_CHAIN, n_rep)
+    attn_ms = time_phase(_lib.PREFILL_ATTENTION, n_rep)
     peaks = _peaks()
     pairs = attention_pairs(T, C, W, plan)
     attn_flops = 4.0 * D * pairs * B * h_loc          # QK^T and PV of this rank's heads
@@ -258,7 +265,7 @@ def run_b200(args):
 
     # ---- end to end through the operator call with host buffers
     e2e = None
-    if rank == 0 or world > 1:
+    if not args.prefill_only:
         hq, hk, hv, hg = (torch.empty(t_.shape, dtype=t_.dtype).pin_memory() for t_ in
                           (q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2), gate.transpose(1, 2)))
         for h_, d_ in ((hq, q), (hk, k), (hv, v), (hg, gate)):
@@ -300,10 +307,11 @@ def run_b200(args):
     if rank == 0:
         line = {
             "metric": METRIC, "value": round(value, 1), "unit": UNIT, "n_gpus": world, "steps": args.steps,
-            "warmup": max(args.warmup, 3), "ms_per_step": round(ms_per_step, 4), "higher_is_better": True,
+            "warmup": n_warm, "ms_per_step": round(ms_per_step, 4), "higher_is_better": True,
             "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-            "config": {"workload": "BASELINE configs[1]: single KVM layer bf16 prefill, B4 x T32768, 16 heads x 128, "
-                                   "block 256, +1 mean per block (cap 1024), post-QKV operator boundary",
+            "config": {"workload": ("BASELINE configs[1]: single KVM layer bf16 prefill, B4 x T32768, 16 heads x 128, "
+                                    "block 256, +1 mean per block (cap 1024), post-QKV operator boundary")
+                       if (B, T) == (4, 32768) else f"REDUCED profiling case of configs[1]: B{B} x T{T}",
                        "global_batch": B, "seq_len": T, "heads_per_gpu": h_loc,
                        "parallelism": f"heads/{world}" + (" + all-gather of outputs" if world > 1 else ""),
                        "l2": "inputs (1.6 GB) larger than L2, no flush needed"},
@@ -488,7 +496,21 @@ def main():
     ap.add_argument("--no-decode", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--decode-steps", type=int, default=None)
+    # smaller cases of the same kernels for profiler captures (the JSON line then names the reduced shape)
+    ap.add_argument("--batch", type=int, default=None)
+    ap.add_argument("--seq-len", type=int, default=None)
+    ap.add_argument("--prefill-only", action="store_true", help="skip e2e, decode and the CPU baseline")
+    ap.add_argument("--decode-only", action="store_true", help="run only the decode workload")
+    ap.add_argument("--decode-seqs", type=int, default=None)
     args = ap.parse_args()
+    if args.batch is not None:
+        CFG2["B"] = args.batch
+    if args.seq_len is not None:
+        CFG2["T"] = args.seq_len
+    if args.decode_seqs is not None:
+        CFG3["n_seq"] = args.decode_seqs
+    if args.prefill_only:
+        args.no_decode = args.no_cpu = True
     if args.impl == "reference":
         run_reference(args)
     else:
