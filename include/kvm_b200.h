@@ -103,12 +103,20 @@ size_t kvm_prefill_workspace_bytes(const kvm_layer* layer, int32_t batch, int64_
  */
 #define KVM_PREFILL_CHAIN 1u      /* run the memory chain (fills `memory`, the versions and route_dev) */
 #define KVM_PREFILL_ATTENTION 2u  /* run block attention (reads the versions in `workspace`, fills out) */
+#define KVM_PREFILL_LEGACY_ATTENTION 4u /* with ATTENTION: use the warp-level mma.sync kernel even where the
+                                           tcgen05 kernel applies (head_dim 128, block multiple of 128) */
 int kvm_prefill_forward(const kvm_layer* layer, int32_t batch, int64_t seq_len,
                         kvm_tensor4 q, kvm_tensor4 k, kvm_tensor4 v, kvm_tensor4 gate,
                         const kvm_update_plan* plan_dev, const kvm_update_plan* plan_host,
                         int32_t n_updates, int64_t total_version_rows,
                         kvm_memory memory, void* out, int32_t* route_dev,
                         void* workspace, size_t workspace_bytes, uint32_t phases, void* stream);
+
+/* Waits for `stream` and returns what the kernels of the last kvm_prefill_forward on this workspace
+ * reported: KVM_OK, or KVM_ERR_DEVICE_TIMEOUT if a bounded device-side wait (mbarrier / tensor-memory
+ * pipeline) expired -- the kernels then leave through their normal exit, nothing hangs, the output is
+ * undefined.  No counterpart in the reference (its Triton kernels have no device-side waits). */
+int kvm_prefill_status(const void* workspace, void* stream);
 
 /* The decode-time cache of one layer for `batch` sequences with ragged lengths (all device memory,
  * caller-owned).  Replaces TritonKVMDecodeCache (model/kvm_triton_decode.py:34-400); unlike the

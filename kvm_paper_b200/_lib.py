@@ -10,10 +10,11 @@ import ctypes as C
 import os
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "libkvm_b200.so")
+# KVM_B200_LIB selects another build of the same library (e.g. an instrumented development build)
+LIB_PATH = os.environ.get("KVM_B200_LIB") or os.path.join(_HERE, "libkvm_b200.so")
 
 KVM_OK = 0
-PREFILL_CHAIN, PREFILL_ATTENTION = 1, 2
+PREFILL_CHAIN, PREFILL_ATTENTION, PREFILL_LEGACY_ATTENTION = 1, 2, 4
 ERROR_NAMES = {1: "bad argument", 2: "capacity", 3: "device timeout", 4: "CUDA error", 5: "unsupported"}
 
 
@@ -49,7 +50,7 @@ class KvmDecodeCache(C.Structure):
 
 EXPORTS = [
     "kvm_prefill_workspace_bytes", "kvm_prefill_forward", "kvm_decode_workspace_bytes", "kvm_decode_step",
-    "kvm_memory_refresh", "kvm_last_error_string", "kvm_abi_version", "kvm_decode_step_static",
+    "kvm_memory_refresh", "kvm_last_error_string", "kvm_abi_version", "kvm_decode_step_static", "kvm_prefill_status",
 ]
 STATIC_SCRATCH_BYTES = 32 << 20
 
@@ -74,6 +75,8 @@ def load():
         LP(KvmLayer), C.c_int32, C.c_int64, KvmTensor4, KvmTensor4, KvmTensor4, KvmTensor4,
         C.c_void_p, LP(KvmUpdatePlan), C.c_int32, C.c_int64, KvmMemory, C.c_void_p, C.c_void_p,
         C.c_void_p, C.c_size_t, C.c_uint32, C.c_void_p]
+    lib.kvm_prefill_status.restype = C.c_int
+    lib.kvm_prefill_status.argtypes = [C.c_void_p, C.c_void_p]
     lib.kvm_decode_workspace_bytes.restype = C.c_size_t
     lib.kvm_decode_workspace_bytes.argtypes = [LP(KvmLayer), C.c_int32, C.c_int32]
     lib.kvm_decode_step.restype = C.c_int

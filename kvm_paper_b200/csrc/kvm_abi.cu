@@ -10,8 +10,8 @@
 namespace kvm {
 cudaError_t prefill_dispatch(int D, const LayerDev& L, int batch, long long T, Tensor4 q, Tensor4 k, Tensor4 v,
                              Tensor4 gate, const kvm_update_plan* plan_dev, int n_plan, long long ver_rows,
-                             MemoryDev mem, bf16* out, int* route, bf16* ver_k, bf16* ver_v, bf16* pk_scr,
-                             bf16* gk_scr, unsigned phases, cudaStream_t stream);
+                             MemoryDev mem, bf16* out, int* route, bf16* pool_k, bf16* pool_v, long long pool_rows,
+                             int* ver_idx, bf16* pk_scr, int* status, unsigned phases, cudaStream_t stream);
 size_t update_smem_bytes(int D, int C, int capacity);
 cudaError_t decode_dispatch(int D, const LayerDev& L, int batch, const DecodeCacheDev& cache, Tensor4 q, Tensor4 k,
                             Tensor4 v, Tensor4 gate, const int* n_append, int any_update, int max_rows, bf16* out,
@@ -103,18 +103,27 @@ int check_memory(const kvm_memory& m, const kvm_layer* l) {
   return KVM_OK;
 }
 
+// Prefill scratch: the row pool of the memory's attention view (every update writes at most C fresh
+// rows per kv row), the per-version index tables, and the prepared-key scratch of the update variant
+// that cannot stage a block in shared memory.
 struct PrefillWs {
-  size_t ver_k, ver_v, pk, gk, total;
+  size_t status, pool_k, pool_v, ver_idx, pk, total;
+  long long pool_rows;
 };
-PrefillWs prefill_ws(const kvm_layer* l, int batch, long long ver_rows) {
+PrefillWs prefill_ws(const kvm_layer* l, int batch, long long seq_len, long long ver_rows) {
   const size_t rows = (size_t)batch * l->n_kv_heads;
   const size_t D = l->head_dim;
+  const long long C = l->chunk_len;
+  const long long n_qblocks = (seq_len + C - 1) / C;
+  const long long n_plan = n_qblocks > l->n_bswa_chunks ? n_qblocks - l->n_bswa_chunks : 1;
   PrefillWs w;
+  w.pool_rows = ver_rows > 0 ? C * n_plan : 0;
   size_t off = 0;
-  w.ver_k = off; off = align_up(off + rows * (size_t)ver_rows * D * 2, 256);
-  w.ver_v = off; off = align_up(off + rows * (size_t)ver_rows * D * 2, 256);
-  w.pk = off; off = align_up(off + rows * (size_t)l->chunk_len * D * 2, 256);
-  w.gk = off; off = align_up(off + rows * (size_t)l->chunk_len * D * 2, 256);
+  w.status = off; off = 256;  // device status word written by kernels whose bounded waits expire
+  w.pool_k = off; off = align_up(off + rows * (size_t)w.pool_rows * D * 2, 256);
+  w.pool_v = off; off = align_up(off + rows * (size_t)w.pool_rows * D * 2, 256);
+  w.ver_idx = off; off = align_up(off + rows * (size_t)ver_rows * 4, 256);
+  w.pk = off; off = align_up(off + rows * (size_t)C * D * 2, 256);
   w.total = off;
   return w;
 }
@@ -173,9 +182,8 @@ const char* kvm_last_error_string(void) { return g_err; }
 int kvm_abi_version(void) { return 100; }
 
 size_t kvm_prefill_workspace_bytes(const kvm_layer* layer, int32_t batch, int64_t seq_len, int64_t total_version_rows) {
-  (void)seq_len;
   if (!layer || batch <= 0 || total_version_rows < 0) return 0;
-  return prefill_ws(layer, batch, total_version_rows).total;
+  return prefill_ws(layer, batch, seq_len, total_version_rows).total;
 }
 
 int kvm_prefill_forward(const kvm_layer* layer, int32_t batch, int64_t seq_len, kvm_tensor4 q, kvm_tensor4 k,
@@ -186,7 +194,7 @@ int kvm_prefill_forward(const kvm_layer* layer, int32_t batch, int64_t seq_len, 
   g_err[0] = 0;
   if (int rc = check_layer(layer)) return rc;
   if (batch <= 0 || seq_len <= 0) return fail(KVM_ERR_BAD_ARGUMENT, "batch %d and seq_len %lld must be positive", batch, (long long)seq_len);
-  if ((phases & 3u) == 0 || (phases & ~3u)) return fail(KVM_ERR_BAD_ARGUMENT, "phases %u must be a combination of KVM_PREFILL_CHAIN and KVM_PREFILL_ATTENTION", phases);
+  if ((phases & 3u) == 0 || (phases & ~7u)) return fail(KVM_ERR_BAD_ARGUMENT, "phases %u must be a combination of KVM_PREFILL_CHAIN and KVM_PREFILL_ATTENTION", phases);
   const int D = layer->head_dim, C = layer->chunk_len, W = layer->n_bswa_chunks;
   if (int rc = check_tensor(q, "q", D)) return rc;
   if (int rc = check_tensor(k, "k", D)) return rc;
@@ -217,17 +225,32 @@ int kvm_prefill_forward(const kvm_layer* layer, int32_t batch, int64_t seq_len, 
     }
   }
   if (max_ver_end > total_version_rows) return fail(KVM_ERR_CAPACITY, "versions need %lld rows, store has %lld", max_ver_end, (long long)total_version_rows);
-  const PrefillWs ws = prefill_ws(layer, batch, total_version_rows);
+  const PrefillWs ws = prefill_ws(layer, batch, seq_len, total_version_rows);
   if (!workspace || workspace_bytes < ws.total) return fail(KVM_ERR_CAPACITY, "workspace of %zu bytes given, %zu needed", workspace_bytes, ws.total);
   if (((uintptr_t)workspace) % 256 || ((uintptr_t)out) % 16) return fail(KVM_ERR_BAD_ARGUMENT, "workspace must be 256-byte aligned and out 16-byte aligned");
 
   unsigned char* wsb = static_cast<unsigned char*>(workspace);
-  cudaError_t e = prefill_dispatch(D, to_dev(layer), batch, seq_len, to_dev(q), to_dev(k), to_dev(v), to_dev(gate), plan_dev,
+  cudaError_t e = cudaMemsetAsync(wsb + ws.status, 0, sizeof(int), static_cast<cudaStream_t>(stream));
+  if (e != cudaSuccess) return cuda_fail(e, "kvm_prefill_forward: cudaMemsetAsync");
+  e = prefill_dispatch(D, to_dev(layer), batch, seq_len, to_dev(q), to_dev(k), to_dev(v), to_dev(gate), plan_dev,
                                    n_updates + 1, total_version_rows, to_dev(memory), static_cast<bf16*>(out), route_dev,
-                                   reinterpret_cast<bf16*>(wsb + ws.ver_k), reinterpret_cast<bf16*>(wsb + ws.ver_v),
-                                   reinterpret_cast<bf16*>(wsb + ws.pk), reinterpret_cast<bf16*>(wsb + ws.gk),
-                                   phases, static_cast<cudaStream_t>(stream));
+                                   reinterpret_cast<bf16*>(wsb + ws.pool_k), reinterpret_cast<bf16*>(wsb + ws.pool_v),
+                                   ws.pool_rows, reinterpret_cast<int*>(wsb + ws.ver_idx),
+                                   reinterpret_cast<bf16*>(wsb + ws.pk), reinterpret_cast<int*>(wsb + ws.status), phases,
+                                   static_cast<cudaStream_t>(stream));
   if (e != cudaSuccess) return cuda_fail(e, "kvm_prefill_forward");
+  return KVM_OK;
+}
+
+int kvm_prefill_status(const void* workspace, void* stream) {
+  g_err[0] = 0;
+  if (!workspace) return fail(KVM_ERR_BAD_ARGUMENT, "workspace is NULL");
+  int st = 0;
+  cudaError_t e = cudaMemcpyAsync(&st, workspace, sizeof(int), cudaMemcpyDeviceToHost, static_cast<cudaStream_t>(stream));
+  if (e == cudaSuccess) e = cudaStreamSynchronize(static_cast<cudaStream_t>(stream));
+  if (e != cudaSuccess) return cuda_fail(e, "kvm_prefill_status");
+  if (st == KVM_ERR_DEVICE_TIMEOUT) return fail(st, "a bounded wait inside a prefill kernel expired (device-side timeout)");
+  if (st != 0) return fail(st, "a prefill kernel reported status %d", st);
   return KVM_OK;
 }
 

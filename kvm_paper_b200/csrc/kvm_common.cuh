@@ -102,19 +102,34 @@ __device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], const void* 
 }
 
 // ---------------------------------------------------------------------------------------------
-// One row of D elements is spread over a warp: lane l owns the EPL = D/32 contiguous elements
-// [l*EPL, (l+1)*EPL).
-template <int D>
+// One row of D elements is spread over a group of GL lanes (GL = 32: a warp per row; GL = 8: four rows
+// per warp): lane l of the group owns the EPL = D/GL contiguous elements [l*EPL, (l+1)*EPL).
+template <int GL>
+__device__ __forceinline__ float group_sum(float x) {
+#pragma unroll
+  for (int o = GL / 2; o > 0; o >>= 1) x += __shfl_xor_sync(0xffffffffu, x, o);
+  return x;
+}
+
+template <int D, int GL = 32>
 struct RowVec {
-  static constexpr int EPL = D / 32;
+  static constexpr int EPL = D / GL;
   float x[EPL];
 };
 
-template <int D>
-__device__ __forceinline__ void load_row(RowVec<D>& r, const bf16* p, int lane) {
-  constexpr int EPL = D / 32;
-  const bf16* q = p + lane * EPL;
-  if constexpr (EPL == 4) {
+template <int D, int GL = 32>
+__device__ __forceinline__ void load_row(RowVec<D, GL>& r, const bf16* p, int gl) {
+  constexpr int EPL = D / GL;
+  const bf16* q = p + gl * EPL;
+  if constexpr (EPL % 8 == 0) {
+#pragma unroll
+    for (int c = 0; c < EPL / 8; ++c) {
+      uint4 u = *reinterpret_cast<const uint4*>(q + c * 8);
+      float2 a = unpack_bf16(u.x), b = unpack_bf16(u.y), d = unpack_bf16(u.z), e = unpack_bf16(u.w);
+      r.x[c * 8 + 0] = a.x; r.x[c * 8 + 1] = a.y; r.x[c * 8 + 2] = b.x; r.x[c * 8 + 3] = b.y;
+      r.x[c * 8 + 4] = d.x; r.x[c * 8 + 5] = d.y; r.x[c * 8 + 6] = e.x; r.x[c * 8 + 7] = e.y;
+    }
+  } else if constexpr (EPL == 4) {
     uint2 u = *reinterpret_cast<const uint2*>(q);
     float2 a = unpack_bf16(u.x), b = unpack_bf16(u.y);
     r.x[0] = a.x; r.x[1] = a.y; r.x[2] = b.x; r.x[3] = b.y;
@@ -127,11 +142,21 @@ __device__ __forceinline__ void load_row(RowVec<D>& r, const bf16* p, int lane) 
   }
 }
 
-template <int D>
-__device__ __forceinline__ void store_row(const RowVec<D>& r, bf16* p, int lane) {
-  constexpr int EPL = D / 32;
-  bf16* q = p + lane * EPL;
-  if constexpr (EPL == 4) {
+template <int D, int GL = 32>
+__device__ __forceinline__ void store_row(const RowVec<D, GL>& r, bf16* p, int gl) {
+  constexpr int EPL = D / GL;
+  bf16* q = p + gl * EPL;
+  if constexpr (EPL % 8 == 0) {
+#pragma unroll
+    for (int c = 0; c < EPL / 8; ++c) {
+      uint4 u;
+      u.x = pack_bf16(r.x[c * 8 + 0], r.x[c * 8 + 1]);
+      u.y = pack_bf16(r.x[c * 8 + 2], r.x[c * 8 + 3]);
+      u.z = pack_bf16(r.x[c * 8 + 4], r.x[c * 8 + 5]);
+      u.w = pack_bf16(r.x[c * 8 + 6], r.x[c * 8 + 7]);
+      *reinterpret_cast<uint4*>(q + c * 8) = u;
+    }
+  } else if constexpr (EPL == 4) {
     uint2 u;
     u.x = pack_bf16(r.x[0], r.x[1]);
     u.y = pack_bf16(r.x[2], r.x[3]);
@@ -144,66 +169,62 @@ __device__ __forceinline__ void store_row(const RowVec<D>& r, bf16* p, int lane)
   }
 }
 
-template <int D>
-__device__ __forceinline__ void round_row(RowVec<D>& r) {
-#pragma unroll
-  for (int i = 0; i < D / 32; ++i) r.x[i] = bf16_round(r.x[i]);
-}
-
-// LayerNorm over the D elements of a row held by a warp (fp32 statistics, biased variance),
+// LayerNorm over the D elements of a row held by a lane group (fp32 statistics, biased variance),
 // result rounded to bf16 precision (kept in fp32 registers).
-template <int D>
-__device__ __forceinline__ void layer_norm_row(RowVec<D>& r, const float* __restrict__ w,
-                                               const float* __restrict__ b, float eps, int lane) {
-  constexpr int EPL = D / 32;
+template <int D, int GL = 32>
+__device__ __forceinline__ void layer_norm_row(RowVec<D, GL>& r, const float* __restrict__ w,
+                                               const float* __restrict__ b, float eps, int gl) {
+  constexpr int EPL = D / GL;
   float s = 0.f;
 #pragma unroll
   for (int i = 0; i < EPL; ++i) s += r.x[i];
-  float mean = warp_sum(s) * (1.0f / D);
+  float mean = group_sum<GL>(s) * (1.0f / D);
   float q = 0.f;
 #pragma unroll
   for (int i = 0; i < EPL; ++i) {
     float d = r.x[i] - mean;
     q += d * d;
   }
-  float var = warp_sum(q) * (1.0f / D);
+  float var = group_sum<GL>(q) * (1.0f / D);
   float rstd = 1.0f / sqrtf(var + eps);
 #pragma unroll
   for (int i = 0; i < EPL; ++i) {
-    int d = lane * EPL + i;
+    int d = gl * EPL + i;
     r.x[i] = bf16_round((r.x[i] - mean) * rstd * w[d] + b[d]);
   }
 }
 
-// L2 norm of a row held by a warp.
-template <int D>
-__device__ __forceinline__ float row_norm(const RowVec<D>& r) {
+// L2 norm of a row held by a lane group.
+template <int D, int GL = 32>
+__device__ __forceinline__ float row_norm(const RowVec<D, GL>& r) {
   float s = 0.f;
 #pragma unroll
-  for (int i = 0; i < D / 32; ++i) s += r.x[i] * r.x[i];
-  return sqrtf(warp_sum(s));
+  for (int i = 0; i < D / GL; ++i) s += r.x[i] * r.x[i];
+  return sqrtf(group_sum<GL>(s));
 }
 
 // Attention view of one memory row: k_attn = LN(k_sum), v_attn = v_sum / max(|v_sum|, 1e-12) * vlen.
-template <int D>
-__device__ __forceinline__ void refresh_memory_row(const LayerDev& L, RowVec<D> ks, RowVec<D> vs, float vlen,
-                                                   bf16* k_attn_row, bf16* v_attn_row, int lane) {
-  layer_norm_row<D>(ks, L.ln_w, L.ln_b, L.ln_eps, lane);
-  store_row<D>(ks, k_attn_row, lane);
-  float n = fmaxf(row_norm<D>(vs), 1e-12f);
+template <int D, int GL = 32>
+__device__ __forceinline__ void refresh_memory_row(const LayerDev& L, RowVec<D, GL> ks, RowVec<D, GL> vs, float vlen,
+                                                   bf16* k_attn_row, bf16* v_attn_row, int gl, bool do_store = true) {
+  layer_norm_row<D, GL>(ks, L.ln_w, L.ln_b, L.ln_eps, gl);
+  float n = fmaxf(row_norm<D, GL>(vs), 1e-12f);
 #pragma unroll
-  for (int i = 0; i < D / 32; ++i) vs.x[i] = __fdiv_rn(vs.x[i], n) * vlen;
-  store_row<D>(vs, v_attn_row, lane);
+  for (int i = 0; i < D / GL; ++i) vs.x[i] = __fdiv_rn(vs.x[i], n) * vlen;
+  if (do_store) {
+    store_row<D, GL>(ks, k_attn_row, gl);
+    store_row<D, GL>(vs, v_attn_row, gl);
+  }
 }
 
 // Prepared key of one token: rotary dims zeroed, LayerNorm, bf16 (model/kvm_mixer.py:120-129).
-template <int D>
-__device__ __forceinline__ void prepare_key_row(const LayerDev& L, RowVec<D>& r, const bf16* k_row, int lane) {
-  load_row<D>(r, k_row, lane);
+template <int D, int GL = 32>
+__device__ __forceinline__ void prepare_key_row(const LayerDev& L, RowVec<D, GL>& r, const bf16* k_row, int gl) {
+  load_row<D, GL>(r, k_row, gl);
 #pragma unroll
-  for (int i = 0; i < D / 32; ++i)
-    if (lane * (D / 32) + i < L.rope_dim) r.x[i] = 0.f;
-  layer_norm_row<D>(r, L.ln_w, L.ln_b, L.ln_eps, lane);
+  for (int i = 0; i < D / GL; ++i)
+    if (gl * (D / GL) + i < L.rope_dim) r.x[i] = 0.f;
+  layer_norm_row<D, GL>(r, L.ln_w, L.ln_b, L.ln_eps, gl);
 }
 
 }  // namespace kvm

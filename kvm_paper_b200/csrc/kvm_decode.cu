@@ -16,10 +16,10 @@ __device__ __forceinline__ int bswa_begin_dev(int total, int C, int W) {
 }
 
 // ------------------------------------------------------------------------------------------- pre
-template <int D, int NT, bool UPDATE>
+template <int D, int NT, bool UPDATE, bool SB>
 __global__ void __launch_bounds__(NT, 1)
 kvm_decode_pre_kernel(LayerDev L, DecodeCacheDev cache, Tensor4 k, Tensor4 v, Tensor4 gate,
-                      const int* __restrict__ n_append_arr, bf16* pk_scr, bf16* gk_scr, int* route) {
+                      const int* __restrict__ n_append_arr, bf16* pk_scr, int* route) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   const int row = blockIdx.x;
   const int b = row / L.Hkv, h = row % L.Hkv;
@@ -44,15 +44,18 @@ kvm_decode_pre_kernel(LayerDev L, DecodeCacheDev cache, Tensor4 k, Tensor4 v, Te
     if (n_app >= 0) {
       // the block [old_begin, old_begin + C) leaves the window (model/kvm_mixer.py:646-669)
       UpdateSmem<D> s;
-      s.carve(smem_raw, C, cap);
+      s.carve(smem_raw, C, cap, SB);
       const int old_begin = bswa_begin_dev(past, C, L.W);
       const int slot0 = old_begin % WC;
       TokenSrc src;
       src.k = rk + (size_t)slot0 * D; src.k_st = D;
       src.v = rv + (size_t)slot0 * D; src.v_st = D;
       src.g = rg + slot0; src.g_st = 1;
-      memory_update<D, NT>(L, src, m, cap, S, n_app, pk_scr + (size_t)row * C * D, gk_scr + (size_t)row * C * D,
-                           route ? route + (size_t)row * C : nullptr, s);
+      src.next_k = nullptr; src.next_v = nullptr;
+      ViewStore view;  // decode keeps one live copy of the attention view: rows are refreshed in place
+      view.k = m.k_attn; view.v = m.v_attn; view.cur = nullptr; view.ver_idx = nullptr; view.pool_next = 0;
+      memory_update<D, NT, SB>(L, src, m, view, cap, S, n_app, pk_scr + (size_t)row * C * D,
+                               route ? route + (size_t)row * C : nullptr, s);
     }
   }
   // the new token
@@ -280,12 +283,14 @@ static cudaError_t launch_decode(const LayerDev& L, int batch, const DecodeCache
   const int rows = batch * L.Hkv;
   cudaError_t e;
   if (any_update) {
-    const size_t smem_u = UpdateSmem<D>::bytes(L.C, cache.mem.capacity);
-    e = cudaFuncSetAttribute(kvm_decode_pre_kernel<D, NT, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_u);
+    const bool sb = update_block_fits_smem<D>(L.C, cache.mem.capacity);
+    const size_t smem_u = UpdateSmem<D>::bytes(L.C, cache.mem.capacity, sb);
+    auto kern = sb ? kvm_decode_pre_kernel<D, NT, true, true> : kvm_decode_pre_kernel<D, NT, true, false>;
+    e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_u);
     if (e != cudaSuccess) return e;
-    kvm_decode_pre_kernel<D, NT, true><<<rows, NT, smem_u, stream>>>(L, cache, k, v, gate, n_append, pk_scr, gk_scr, route);
+    kern<<<rows, NT, smem_u, stream>>>(L, cache, k, v, gate, n_append, pk_scr, route);
   } else {
-    kvm_decode_pre_kernel<D, 32, false><<<rows, 32, 0, stream>>>(L, cache, k, v, gate, nullptr, pk_scr, gk_scr, route);
+    kvm_decode_pre_kernel<D, 32, false, false><<<rows, 32, 0, stream>>>(L, cache, k, v, gate, nullptr, pk_scr, route);
   }
   e = cudaGetLastError();
   if (e != cudaSuccess) return e;

@@ -10,19 +10,24 @@
 namespace kvm {
 
 // ------------------------------------------------------------------------------------------ chain
-template <int D, int NT>
+// One CTA per kv row walks the whole prompt: initial memory, then one update per token block.  The
+// attention view of the memory is kept in a row pool with per-version index tables (see ViewStore);
+// after the last update the final view is gathered into `mem.k_attn` / `mem.v_attn`.
+template <int D, int NT, bool SB>
 __global__ void __launch_bounds__(NT, 1)
 kvm_chain_kernel(LayerDev L, long long T, Tensor4 k, Tensor4 v, Tensor4 gate, const kvm_update_plan* __restrict__ plan,
-                 int u_begin, int u_end, MemoryDev mem, bf16* ver_k, bf16* ver_v, long long ver_rows,
-                 bf16* pk_scr, bf16* gk_scr, int* route, int n_plan) {
+                 int n_plan, MemoryDev mem, bf16* pool_k, bf16* pool_v, long long pool_rows, int* ver_idx,
+                 long long ver_rows, bf16* pk_scr, int* route) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   UpdateSmem<D> s;
-  s.carve(smem_raw, L.C, mem.capacity);
+  s.carve(smem_raw, L.C, mem.capacity, SB);
   const int row = blockIdx.x;
   const int b = row / L.Hkv, h = row % L.Hkv;
-  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  constexpr int NW = NT / 32;
+  const int tid = threadIdx.x;
   const int C = L.C;
+  constexpr int GL = 8;
+  constexpr int GROUPS = NT / GL;
+  const int gl = tid % GL, grp = tid / GL;
 
   MemoryRowPtrs m;
   m.k_sum = mem.k_sum + (size_t)row * mem.capacity * D;
@@ -31,55 +36,75 @@ kvm_chain_kernel(LayerDev L, long long T, Tensor4 k, Tensor4 v, Tensor4 gate, co
   m.k_attn = mem.k_attn + (size_t)row * mem.capacity * D;
   m.v_attn = mem.v_attn + (size_t)row * mem.capacity * D;
   bf16* pk = pk_scr + (size_t)row * C * D;
-  bf16* gk = gk_scr + (size_t)row * C * D;
+  const bool pool = ver_idx != nullptr;  // some query block reads memory versions
+  ViewStore view;
+  view.k = pool ? pool_k + (size_t)row * pool_rows * D : m.k_attn;
+  view.v = pool ? pool_v + (size_t)row * pool_rows * D : m.v_attn;
+  view.cur = pool ? s.cur : nullptr;
+  view.pool_next = 0;
+  int* my_ver = pool ? ver_idx + (size_t)row * ver_rows : nullptr;
 
-  for (int u = u_begin; u < u_end; ++u) {
+  for (int u = 0; u < n_plan; ++u) {
     const kvm_update_plan pl = plan[u];
-    const int S_after = pl.state_before + pl.n_append;
+    view.ver_idx = (pool && pl.version_row >= 0) ? my_ver + pl.version_row : nullptr;
     if (u == 0) {
-      // initial memory: the first min(T,C) tokens row for row (model/kvm_mixer.py:434-447)
-      for (int tkn = warp; tkn < pl.n_append; tkn += NW) {
-        RowVec<D> kr, vr;
-        prepare_key_row<D>(L, kr, k.row(b, h, tkn), lane);
-        load_row<D>(vr, v.row(b, h, tkn), lane);
-        const float vl = row_norm<D>(vr);  // magnitude of the ungated value
+      // initial memory: the first min(T,C) tokens row for row (model/kvm_mixer.py:434-447); 8 lanes per row
+      const int n0 = pl.n_append;
+      for (int base = 0; base < n0; base += GROUPS) {
+        const int tkn = base + grp;
+        const bool act = tkn < n0;
+        const int t_ = act ? tkn : 0;
+        RowVec<D, GL> kr, vr;
+        prepare_key_row<D, GL>(L, kr, k.row(b, h, t_), gl);
+        load_row<D, GL>(vr, v.row(b, h, t_), gl);
+        const float vl = row_norm<D, GL>(vr);  // magnitude of the ungated value
         if (L.gate_initial) {
-          const float gt = __bfloat162float(*gate.row(b, h, tkn));
+          const float gt = __bfloat162float(*gate.row(b, h, t_));
 #pragma unroll
-          for (int i = 0; i < D / 32; ++i) {
+          for (int i = 0; i < D / GL; ++i) {
             kr.x[i] = bf16_round(kr.x[i] * gt);
             vr.x[i] = bf16_round(vr.x[i] * gt);
           }
         }
-        store_row<D>(kr, m.k_sum + (size_t)tkn * D, lane);
-        store_row<D>(vr, m.v_sum + (size_t)tkn * D, lane);
-        if (lane == 0) m.vlen[tkn] = vl;
-        refresh_memory_row<D>(L, kr, vr, vl, m.k_attn + (size_t)tkn * D, m.v_attn + (size_t)tkn * D, lane);
+        if (act) {
+          store_row<D, GL>(kr, m.k_sum + (size_t)t_ * D, gl);
+          store_row<D, GL>(vr, m.v_sum + (size_t)t_ * D, gl);
+          if (gl == 0) {
+            m.vlen[t_] = vl;
+            if (pool) s.cur[t_] = t_;
+          }
+        }
+        refresh_memory_row<D, GL>(L, kr, vr, vl, view.k + (size_t)t_ * D, view.v + (size_t)t_ * D, gl, act);
       }
+      view.pool_next = n0;
       if (route)
-        for (int i = tid; i < C; i += NT) route[((size_t)row * n_plan) * C + i] = i < pl.n_append ? -(1 + i) : 0;
+        for (int i = tid; i < C; i += NT) route[((size_t)row * n_plan) * C + i] = i < n0 ? -(1 + i) : 0;
+      if (view.ver_idx)
+        for (int i = tid; i < n0; i += NT) view.ver_idx[i] = i;
       __syncthreads();
     } else {
       TokenSrc src;
       src.k = k.row(b, h, (long long)u * C); src.k_st = k.st;
       src.v = v.row(b, h, (long long)u * C); src.v_st = v.st;
       src.g = gate.row(b, h, (long long)u * C); src.g_st = gate.st;
-      memory_update<D, NT>(L, src, m, mem.capacity, pl.state_before, pl.n_append, pk, gk,
-                           route ? route + ((size_t)row * n_plan + u) * C : nullptr, s);
+      const bool has_next = u + 1 < n_plan;
+      src.next_k = has_next ? k.row(b, h, (long long)(u + 1) * C) : nullptr;
+      src.next_v = has_next ? v.row(b, h, (long long)(u + 1) * C) : nullptr;
+      memory_update<D, NT, SB>(L, src, m, view, mem.capacity, pl.state_before, pl.n_append, pk,
+                               route ? route + ((size_t)row * n_plan + u) * C : nullptr, s);
     }
-    // snapshot of the attention view: version u (only versions some query block reads are stored)
-    if (pl.version_row >= 0) {
-      const uint4* sk = reinterpret_cast<const uint4*>(m.k_attn);
-      const uint4* sv = reinterpret_cast<const uint4*>(m.v_attn);
-      uint4* dk = reinterpret_cast<uint4*>(ver_k + ((size_t)row * ver_rows + pl.version_row) * D);
-      uint4* dv = reinterpret_cast<uint4*>(ver_v + ((size_t)row * ver_rows + pl.version_row) * D);
-      const int n16 = S_after * (D / 8);
-      for (int i = tid; i < n16; i += NT) {
-        dk[i] = sk[i];
-        dv[i] = sv[i];
-      }
+  }
+  if (pool) {
+    // final attention view, row order, for whoever continues from this memory (the decode cache)
+    const kvm_update_plan pl = plan[n_plan - 1];
+    const int S = pl.state_before + pl.n_append;
+    constexpr int CPR = D / 8;
+    for (int c = tid; c < S * CPR; c += NT) {
+      const int r = c / CPR, cc = c % CPR;
+      const size_t src_off = (size_t)s.cur[r] * D + cc * 8;
+      *reinterpret_cast<uint4*>(m.k_attn + (size_t)r * D + cc * 8) = *reinterpret_cast<const uint4*>(view.k + src_off);
+      *reinterpret_cast<uint4*>(m.v_attn + (size_t)r * D + cc * 8) = *reinterpret_cast<const uint4*>(view.v + src_off);
     }
-    __syncthreads();
   }
 }
 
@@ -108,13 +133,28 @@ __device__ __forceinline__ void attn_load_tile(bf16* dst, const bf16* src, long 
   }
 }
 
+// rows [row0, row0+64) of a memory version: row r lives at pool row idx[r]; rows >= limit zero-filled
+template <int D, int NT>
+__device__ __forceinline__ void attn_load_tile_idx(bf16* dst, const bf16* pool, const int* __restrict__ idx, int row0,
+                                                   int limit, int tid) {
+  constexpr int CPR = D / 8;
+  constexpr int STR = attn_tile_stride<D>();
+  for (int c = tid; c < kAttnBN * CPR; c += NT) {
+    const int r = c / CPR, cc = c % CPR;
+    const int row = row0 + r;
+    const bool ok = row < limit;
+    const int slot = ok ? __ldg(idx + row) : 0;
+    cp_async16(dst + r * STR + cc * 8, pool + (size_t)slot * D + cc * 8, ok ? 16 : 0);
+  }
+}
+
 // One CTA = BM query rows of one (batch, q-head) inside one query block j.
 template <int D, int BM>
 __global__ void __launch_bounds__(BM * 2)
 kvm_attn_prefill_kernel(LayerDev L, long long T, Tensor4 q, Tensor4 k, Tensor4 v,
-                        const kvm_update_plan* __restrict__ plan, const bf16* __restrict__ ver_k,
-                        const bf16* __restrict__ ver_v, long long ver_rows, bf16* __restrict__ out,
-                        int tiles_per_block, int j_begin, float sm_scale) {
+                        const kvm_update_plan* __restrict__ plan, const bf16* __restrict__ pool_k,
+                        const bf16* __restrict__ pool_v, long long pool_rows, const int* __restrict__ ver_idx,
+                        long long ver_rows, bf16* __restrict__ out, int tiles_per_block, int j_begin, float sm_scale) {
   constexpr int NT = BM * 2;
   constexpr int KS = D / 16;       // k-steps of QK^T
   constexpr int NT8 = kAttnBN / 8; // n8 tiles of a score tile
@@ -143,12 +183,14 @@ kvm_attn_prefill_kernel(LayerDev L, long long T, Tensor4 q, Tensor4 k, Tensor4 v
   int S = 0;
   const bf16* mk = nullptr;
   const bf16* mv = nullptr;
+  const int* midx = nullptr;
   if (j >= L.W) {
     const kvm_update_plan pl = plan[j - L.W];
     S = pl.state_before + pl.n_append;
-    const size_t off = ((size_t)(b * L.Hkv + hkv) * ver_rows + pl.version_row) * D;
-    mk = ver_k + off;
-    mv = ver_v + off;
+    const size_t kvrow = (size_t)(b * L.Hkv + hkv);
+    mk = pool_k + kvrow * pool_rows * D;
+    mv = pool_v + kvrow * pool_rows * D;
+    midx = ver_idx + kvrow * ver_rows + pl.version_row;
   }
   const long long bb = max(0LL, (long long)(j + 1 - L.W) * C);
   const int n_mem_tiles = (S + kAttnBN - 1) / kAttnBN;
@@ -186,8 +228,8 @@ kvm_attn_prefill_kernel(LayerDev L, long long T, Tensor4 q, Tensor4 k, Tensor4 v
     bf16* dK = sK + (size_t)stage * kAttnBN * STR;
     bf16* dV = sV + (size_t)stage * kAttnBN * STR;
     if (it < n_mem_tiles) {
-      attn_load_tile<D, NT>(dK, mk, D, (long long)it * kAttnBN, S, tid);
-      attn_load_tile<D, NT>(dV, mv, D, (long long)it * kAttnBN, S, tid);
+      attn_load_tile_idx<D, NT>(dK, mk, midx, it * kAttnBN, S, tid);
+      attn_load_tile_idx<D, NT>(dV, mv, midx, it * kAttnBN, S, tid);
     } else {
       const long long r0 = bb + (long long)(it - n_mem_tiles) * kAttnBN;
       attn_load_tile<D, NT>(dK, kbase, k.st, r0, q_tile_end, tid);
@@ -309,54 +351,77 @@ kvm_attn_prefill_kernel(LayerDev L, long long T, Tensor4 q, Tensor4 k, Tensor4 v
 }
 
 // ------------------------------------------------------------------------------------- host side
+cudaError_t launch_attn_tc(const LayerDev& L, int batch, long long T, Tensor4 q, Tensor4 k, Tensor4 v,
+                           const kvm_update_plan* plan_dev, const bf16* pool_k, const bf16* pool_v, long long pool_rows,
+                           const int* ver_idx, long long ver_rows, bf16* out, int* status, cudaStream_t stream);
+
 template <int D>
 static cudaError_t launch_prefill(const LayerDev& L, int batch, long long T, Tensor4 q, Tensor4 k, Tensor4 v, Tensor4 gate,
                                   const kvm_update_plan* plan_dev, int n_plan, long long ver_rows, MemoryDev mem,
-                                  bf16* out, int* route, bf16* ver_k, bf16* ver_v, bf16* pk_scr, bf16* gk_scr,
-                                  unsigned phases, cudaStream_t stream) {
+                                  bf16* out, int* route, bf16* pool_k, bf16* pool_v, long long pool_rows, int* ver_idx,
+                                  bf16* pk_scr, int* status, unsigned phases, cudaStream_t stream) {
   constexpr int NT = 512;
   const int rows = batch * L.Hkv;
+  const int n_qblocks = (int)((T + L.C - 1) / L.C);
+  const bool versions = n_qblocks > L.W && ver_rows > 0;
   cudaError_t e;
   if (phases & KVM_PREFILL_CHAIN) {
-    const size_t smem_u = UpdateSmem<D>::bytes(L.C, mem.capacity);
-    e = cudaFuncSetAttribute(kvm_chain_kernel<D, NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_u);
+    const bool sb = update_block_fits_smem<D>(L.C, mem.capacity);
+    const size_t smem_u = UpdateSmem<D>::bytes(L.C, mem.capacity, sb);
+    auto kern = sb ? kvm_chain_kernel<D, NT, true> : kvm_chain_kernel<D, NT, false>;
+    e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_u);
     if (e != cudaSuccess) return e;
-    kvm_chain_kernel<D, NT><<<rows, NT, smem_u, stream>>>(L, T, k, v, gate, plan_dev, 0, n_plan, mem, ver_k, ver_v,
-                                                         ver_rows, pk_scr, gk_scr, route, n_plan);
+    kern<<<rows, NT, smem_u, stream>>>(L, T, k, v, gate, plan_dev, n_plan, mem, pool_k, pool_v, pool_rows,
+                                      versions ? ver_idx : nullptr, ver_rows, pk_scr, route);
     e = cudaGetLastError();
     if (e != cudaSuccess) return e;
   }
   if (!(phases & KVM_PREFILL_ATTENTION)) return cudaSuccess;
+  if constexpr (D == 128) {
+    // tcgen05 / tensor-memory kernel: head_dim 128 and blocks that are whole 128-row query tiles
+    if (L.C % 128 == 0 && !(phases & KVM_PREFILL_LEGACY_ATTENTION))
+      return launch_attn_tc(L, batch, T, q, k, v, plan_dev, pool_k, pool_v, pool_rows, ver_idx, ver_rows, out, status, stream);
+  }
 
   constexpr int BM = 64;
-  const int n_qblocks = (int)((T + L.C - 1) / L.C);
   const int tiles_per_block = (L.C + BM - 1) / BM;
   const size_t smem_a = attn_smem_bytes<D>();
   e = cudaFuncSetAttribute(kvm_attn_prefill_kernel<D, BM>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_a);
   if (e != cudaSuccess) return e;
   dim3 grid(n_qblocks * tiles_per_block, batch * L.Hq);
-  kvm_attn_prefill_kernel<D, BM><<<grid, BM * 2, smem_a, stream>>>(L, T, q, k, v, plan_dev, ver_k, ver_v, ver_rows, out,
-                                                                  tiles_per_block, 0, 1.0f / sqrtf((float)D));
+  kvm_attn_prefill_kernel<D, BM><<<grid, BM * 2, smem_a, stream>>>(L, T, q, k, v, plan_dev, pool_k, pool_v, pool_rows, ver_idx,
+                                                                  ver_rows, out, tiles_per_block, 0, 1.0f / sqrtf((float)D));
   return cudaGetLastError();
 }
 
 cudaError_t prefill_dispatch(int D, const LayerDev& L, int batch, long long T, Tensor4 q, Tensor4 k, Tensor4 v,
                              Tensor4 gate, const kvm_update_plan* plan_dev, int n_plan, long long ver_rows,
-                             MemoryDev mem, bf16* out, int* route, bf16* ver_k, bf16* ver_v, bf16* pk_scr,
-                             bf16* gk_scr, unsigned phases, cudaStream_t stream) {
+                             MemoryDev mem, bf16* out, int* route, bf16* pool_k, bf16* pool_v, long long pool_rows,
+                             int* ver_idx, bf16* pk_scr, int* status, unsigned phases, cudaStream_t stream) {
   switch (D) {
-    case 32: return launch_prefill<32>(L, batch, T, q, k, v, gate, plan_dev, n_plan, ver_rows, mem, out, route, ver_k, ver_v, pk_scr, gk_scr, phases, stream);
-    case 64: return launch_prefill<64>(L, batch, T, q, k, v, gate, plan_dev, n_plan, ver_rows, mem, out, route, ver_k, ver_v, pk_scr, gk_scr, phases, stream);
-    case 128: return launch_prefill<128>(L, batch, T, q, k, v, gate, plan_dev, n_plan, ver_rows, mem, out, route, ver_k, ver_v, pk_scr, gk_scr, phases, stream);
+    case 32: return launch_prefill<32>(L, batch, T, q, k, v, gate, plan_dev, n_plan, ver_rows, mem, out, route, pool_k, pool_v, pool_rows, ver_idx, pk_scr, status, phases, stream);
+    case 64: return launch_prefill<64>(L, batch, T, q, k, v, gate, plan_dev, n_plan, ver_rows, mem, out, route, pool_k, pool_v, pool_rows, ver_idx, pk_scr, status, phases, stream);
+    case 128: return launch_prefill<128>(L, batch, T, q, k, v, gate, plan_dev, n_plan, ver_rows, mem, out, route, pool_k, pool_v, pool_rows, ver_idx, pk_scr, status, phases, stream);
   }
   return cudaErrorInvalidValue;
 }
 
-size_t update_smem_bytes(int D, int C, int capacity) {
+#ifdef KVM_PROFILE_PHASES
+extern "C" int kvm_debug_phase_cycles(long long* out16, int reset) {
+  cudaError_t e = cudaMemcpyFromSymbol(out16, g_phase_cycles, sizeof(long long) * 16);
+  if (e == cudaSuccess && reset) {
+    long long z[16] = {0};
+    e = cudaMemcpyToSymbol(g_phase_cycles, z, sizeof(z));
+  }
+  return (int)e;
+}
+#endif
+
+size_t update_smem_bytes(int D, int C, int capacity) {  // of the variant without the staged block
   switch (D) {
-    case 32: return UpdateSmem<32>::bytes(C, capacity);
-    case 64: return UpdateSmem<64>::bytes(C, capacity);
-    case 128: return UpdateSmem<128>::bytes(C, capacity);
+    case 32: return UpdateSmem<32>::bytes(C, capacity, false);
+    case 64: return UpdateSmem<64>::bytes(C, capacity, false);
+    case 128: return UpdateSmem<128>::bytes(C, capacity, false);
   }
   return 0;
 }

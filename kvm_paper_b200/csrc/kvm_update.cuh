@@ -10,11 +10,34 @@
 //   4. per touched row: delta = sum of the routed gk (gv) rows in token order (fp32),
 //      row = bf16(row + bf16(delta)), then the attention view of the row is recomputed.
 // The order of every floating-point sum is fixed, so two runs give identical bits.
+//
+// The update sits on a strictly sequential chain (one update per block and kv row), so it is organised
+// for latency: when it fits (SB = true) the whole token block -- keys, values, gates -- is pulled into
+// shared memory with one wave of cp.async and every later phase works from there; only the prepared
+// key is kept (the gated key is re-derived on the fly, the product of two bf16 numbers rounds the same
+// way everywhere).
 #pragma once
 
 #include "kvm_common.cuh"
 
 namespace kvm {
+
+// Optional per-phase cycle counters of the update (development builds with -DKVM_PROFILE_PHASES only).
+#ifdef KVM_PROFILE_PHASES
+__device__ long long g_phase_cycles[16];
+#define KVM_PHASE_BEGIN() long long _t_prev = clock64()
+#define KVM_PHASE_MARK(i)                                                  \
+  do {                                                                     \
+    if (blockIdx.x == 0 && threadIdx.x == 0) {                             \
+      long long _t = clock64();                                            \
+      g_phase_cycles[i] += _t - _t_prev;                                   \
+      _t_prev = _t;                                                        \
+    }                                                                      \
+  } while (0)
+#else
+#define KVM_PHASE_BEGIN() do {} while (0)
+#define KVM_PHASE_MARK(i) do {} while (0)
+#endif
 
 constexpr int kScanTile = 64;  // memory rows per shared-memory tile of the routing GEMM
 
@@ -25,6 +48,8 @@ struct TokenSrc {  // the C tokens consumed by one update; token t at base + t*s
   long long v_st;
   const bf16* g;
   long long g_st;
+  const bf16* next_k;  // first row of the block the NEXT update consumes (L2 prefetch), or null
+  const bf16* next_v;
 };
 
 struct MemoryRowPtrs {  // the memory of one kv row
@@ -35,56 +60,91 @@ struct MemoryRowPtrs {  // the memory of one kv row
   bf16* v_attn;
 };
 
+struct BlockView {  // where the phases after the load find the block's data
+  const bf16* pk;   // prepared keys, row stride pk_st elements
+  int pk_st;
+  const bf16* v;    // values, row stride v_st elements
+  long long v_st;
+  const float* g;   // gates [C] (shared memory)
+};
+
 template <int D>
 __host__ __device__ constexpr int scan_tile_stride() { return D + 8; }
 
-// Shared-memory carve-up of the update (sizes depend on C and on the memory capacity).
+// Shared-memory carve-up of the update (sizes depend on C, the memory capacity and SB).
 template <int D>
 struct UpdateSmem {
   bf16* btile;   // [2][kScanTile][D+8]
+  bf16* pk_s;    // [C][D+8]   (SB only)
+  bf16* v_s;     // [C][D]     (SB only)
+  float* g_s;    // [C] gates
   float* app;    // [C] novelty score
   float* best;   // [C] best merge logit
-  int* idx;      // [C] best merge row, later: route (row >= 0 merged, -(1+row) appended)
-  int* pos;      // [C] position inside the append list / inside the routed row's token list
+  int* idx;      // [C] merge target row (-1 for appended tokens once grouping starts)
+  int* pos;      // [C] position inside the append list
   int* flag;     // [C] 1 = appended
+  int* ord;      // [C] position of a merged token inside its target row's token list
+  int* lead;     // [C] first token routed to the same row
+  int* tcnt;     // [C] (by leading token) tokens routed to the row
+  int* tstart;   // [C] (by leading token) start of the row's token list inside `list`
   int* list;     // [C] merged tokens grouped by row, token order inside a group
-  int* touched;  // [C] rows that received at least one token
-  int* cnt;      // [capacity]
-  int* start;    // [capacity]
-  int* counters; // [4]
-  __host__ __device__ static size_t bytes(int C, int capacity) {
+  int* touched;  // [C] leading tokens, one per row that received tokens
+  int* cur;      // [capacity] pool slot holding the attention view of each memory row (pool mode)
+  int* counters; // [4 + 32]
+  static constexpr int kTokenArrays = 13;
+  __host__ __device__ static size_t bytes(int C, int capacity, bool sb) {
     size_t b = (size_t)2 * kScanTile * scan_tile_stride<D>() * sizeof(bf16);
-    b += (size_t)C * 4 * 7;
-    b += (size_t)capacity * 4 * 2;
-    b += 16;
+    if (sb) b += (size_t)C * (D + 8) * sizeof(bf16) + (size_t)C * D * sizeof(bf16);
+    b += (size_t)C * 4 * kTokenArrays;
+    b += (size_t)((capacity + 3) / 4 * 4) * 4;
+    b += 36 * 4;
     return b;
   }
-  __device__ void carve(unsigned char* base, int C, int capacity) {
+  __device__ void carve(unsigned char* base, int C, int capacity, bool sb) {
     btile = reinterpret_cast<bf16*>(base);
     base += (size_t)2 * kScanTile * scan_tile_stride<D>() * sizeof(bf16);
-    app = reinterpret_cast<float*>(base); base += (size_t)C * 4;
-    best = reinterpret_cast<float*>(base); base += (size_t)C * 4;
-    idx = reinterpret_cast<int*>(base); base += (size_t)C * 4;
-    pos = reinterpret_cast<int*>(base); base += (size_t)C * 4;
-    flag = reinterpret_cast<int*>(base); base += (size_t)C * 4;
-    list = reinterpret_cast<int*>(base); base += (size_t)C * 4;
-    touched = reinterpret_cast<int*>(base); base += (size_t)C * 4;
-    cnt = reinterpret_cast<int*>(base); base += (size_t)capacity * 4;
-    start = reinterpret_cast<int*>(base); base += (size_t)capacity * 4;
+    pk_s = v_s = nullptr;
+    if (sb) {
+      pk_s = reinterpret_cast<bf16*>(base); base += (size_t)C * (D + 8) * sizeof(bf16);
+      v_s = reinterpret_cast<bf16*>(base); base += (size_t)C * D * sizeof(bf16);
+    }
+    int** arr[kTokenArrays] = {reinterpret_cast<int**>(&g_s), reinterpret_cast<int**>(&app), reinterpret_cast<int**>(&best),
+                               &idx, &pos, &flag, &ord, &lead, &tcnt, &tstart, &list, &touched, nullptr};
+    for (int i = 0; i < kTokenArrays - 1; ++i) {
+      *arr[i] = reinterpret_cast<int*>(base);
+      base += (size_t)C * 4;
+    }
+    base += (size_t)C * 4;  // spare
+    cur = reinterpret_cast<int*>(base); base += (size_t)((capacity + 3) / 4 * 4) * 4;
     counters = reinterpret_cast<int*>(base);
   }
 };
 
+constexpr size_t kSmemLimit = 227 * 1024;
+
+template <int D>
+__host__ __device__ inline bool update_block_fits_smem(int C, int capacity) {
+  return UpdateSmem<D>::bytes(C, capacity, true) <= kSmemLimit;
+}
+
+__device__ __forceinline__ uint32_t mul_bf16x2(uint32_t a, __nv_bfloat162 g2) {
+  __nv_bfloat162 x = *reinterpret_cast<__nv_bfloat162*>(&a);
+  x = __hmul2(x, g2);
+  return *reinterpret_cast<uint32_t*>(&x);
+}
+
 // Issue the cp.async copies of one tile of memory rows [row0, row0+kScanTile) (rows >= n_end zero-filled).
+// `slots` (shared memory, may be null = identity) maps a memory row to the row of `k_attn` that holds it.
 template <int D, int NT>
-__device__ __forceinline__ void scan_load_tile(bf16* dst, const bf16* k_attn, int row0, int n_end, int tid) {
+__device__ __forceinline__ void scan_load_tile(bf16* dst, const bf16* k_attn, const int* slots, int row0, int n_end, int tid) {
   constexpr int CPR = D / 8;  // 16-byte chunks per row
   constexpr int STR = scan_tile_stride<D>();
   for (int c = tid; c < kScanTile * CPR; c += NT) {
     int r = c / CPR, cc = c % CPR;
     int row = row0 + r;
     bool ok = row < n_end;
-    const bf16* src = k_attn + (size_t)(ok ? row : 0) * D + cc * 8;
+    int slot = ok ? (slots ? slots[row] : row) : 0;
+    const bf16* src = k_attn + (size_t)slot * D + cc * 8;
     cp_async16(dst + r * STR + cc * 8, src, ok ? 16 : 0);
   }
 }
@@ -93,9 +153,8 @@ __device__ __forceinline__ void scan_load_tile(bf16* dst, const bf16* k_attn, in
 // pk scores (novelty, only if want_app) and the running fp32 argmax of the gk logits (rows below
 // `protected_rows` excluded).  Results are merged into s.app / s.best / s.idx.
 template <int D, int NT>
-__device__ void scan_memory(const bf16* __restrict__ pk, const bf16* __restrict__ gk, int C,
-                            const bf16* __restrict__ k_attn, int n_begin, int n_end, bool want_app,
-                            int protected_rows, UpdateSmem<D>& s) {
+__device__ __noinline__ void scan_memory(const BlockView& blk, bool gate_keys, int C, const bf16* __restrict__ k_attn, const int* slots,
+                            int n_begin, int n_end, bool want_app, int protected_rows, UpdateSmem<D>& s) {
   constexpr int NW = NT / 32;
   constexpr int KS = D / 16;
   constexpr int STR = scan_tile_stride<D>();
@@ -111,20 +170,23 @@ __device__ void scan_memory(const bf16* __restrict__ pk, const bf16* __restrict_
     uint32_t ap[KS][4], ag[KS][4];
     if (active) {
       const int r0 = mt * 16 + g, r1 = r0 + 8;
+      const bf16* p0 = blk.pk + (size_t)r0 * blk.pk_st + t * 2;
+      const bf16* p1 = blk.pk + (size_t)r1 * blk.pk_st + t * 2;
+      const __nv_bfloat162 g0 = __float2bfloat162_rn(blk.g[r0]);
+      const __nv_bfloat162 g1 = __float2bfloat162_rn(blk.g[r1]);
 #pragma unroll
       for (int ks = 0; ks < KS; ++ks) {
-        const int c0 = ks * 16 + t * 2;
-        ag[ks][0] = *reinterpret_cast<const uint32_t*>(gk + (size_t)r0 * D + c0);
-        ag[ks][1] = *reinterpret_cast<const uint32_t*>(gk + (size_t)r1 * D + c0);
-        ag[ks][2] = *reinterpret_cast<const uint32_t*>(gk + (size_t)r0 * D + c0 + 8);
-        ag[ks][3] = *reinterpret_cast<const uint32_t*>(gk + (size_t)r1 * D + c0 + 8);
-        if (want_app) {
-          ap[ks][0] = *reinterpret_cast<const uint32_t*>(pk + (size_t)r0 * D + c0);
-          ap[ks][1] = *reinterpret_cast<const uint32_t*>(pk + (size_t)r1 * D + c0);
-          ap[ks][2] = *reinterpret_cast<const uint32_t*>(pk + (size_t)r0 * D + c0 + 8);
-          ap[ks][3] = *reinterpret_cast<const uint32_t*>(pk + (size_t)r1 * D + c0 + 8);
+        ap[ks][0] = *reinterpret_cast<const uint32_t*>(p0 + ks * 16);
+        ap[ks][1] = *reinterpret_cast<const uint32_t*>(p1 + ks * 16);
+        ap[ks][2] = *reinterpret_cast<const uint32_t*>(p0 + ks * 16 + 8);
+        ap[ks][3] = *reinterpret_cast<const uint32_t*>(p1 + ks * 16 + 8);
+        if (gate_keys) {
+          ag[ks][0] = mul_bf16x2(ap[ks][0], g0);
+          ag[ks][1] = mul_bf16x2(ap[ks][1], g1);
+          ag[ks][2] = mul_bf16x2(ap[ks][2], g0);
+          ag[ks][3] = mul_bf16x2(ap[ks][3], g1);
         } else {
-          ap[ks][0] = ap[ks][1] = ap[ks][2] = ap[ks][3] = 0u;
+          ag[ks][0] = ap[ks][0]; ag[ks][1] = ap[ks][1]; ag[ks][2] = ap[ks][2]; ag[ks][3] = ap[ks][3];
         }
       }
     }
@@ -133,12 +195,12 @@ __device__ void scan_memory(const bf16* __restrict__ pk, const bf16* __restrict_
     int bidx[2] = {-1, -1};
 
     __syncthreads();  // previous users of the tile buffers are done
-    scan_load_tile<D, NT>(s.btile, k_attn, n_begin, n_end, tid);
+    scan_load_tile<D, NT>(s.btile, k_attn, slots, n_begin, n_end, tid);
     cp_async_commit();
     for (int it = 0; it < n_tiles; ++it) {
       const int cur = it & 1;
       if (it + 1 < n_tiles) {
-        scan_load_tile<D, NT>(s.btile + (size_t)(cur ^ 1) * kScanTile * STR, k_attn,
+        scan_load_tile<D, NT>(s.btile + (size_t)(cur ^ 1) * kScanTile * STR, k_attn, slots,
                               n_begin + (it + 1) * kScanTile, n_end, tid);
         cp_async_commit();
         cp_async_wait<1>();
@@ -205,164 +267,280 @@ __device__ void scan_memory(const bf16* __restrict__ pk, const bf16* __restrict_
   __syncthreads();
 }
 
-// One full update of one kv row.  `pk_scr` / `gk_scr` are [C][D] bf16 global scratch rows private to
-// this block.  `route_out` ([C] int32, may be null) receives the decision for every token.
-template <int D, int NT>
-__device__ void memory_update(const LayerDev& L, const TokenSrc& src, const MemoryRowPtrs& mem, int capacity,
-                              int S_before, int n_append, bf16* pk_scr, bf16* gk_scr, int* route_out,
-                              UpdateSmem<D>& s) {
-  constexpr int NW = NT / 32;
+// Where the attention view (k_attn / v_attn rows) of the memory lives.
+//   in place (decode, short prompts): row r of the memory is row r of `k` / `v`;  `cur` == nullptr
+//   pool (prefill): every refreshed or appended row is written to a fresh pool row, `cur[r]` (shared
+//   memory) names the pool row currently holding memory row r, and after the update `ver_idx`
+//   receives a copy of `cur` -- a "version" of the memory costs S integers instead of S rows, and
+//   block attention reads old versions through these tables while the chain runs ahead.
+struct ViewStore {
+  bf16* k;
+  bf16* v;
+  int* cur;       // shared memory [capacity] or null
+  int* ver_idx;   // global [S_after] table to write after this update, or null
+  int pool_next;  // first free pool row (pool mode)
+};
+
+// One full update of one kv row.  With SB the block is staged in shared memory; otherwise `pk_scr`
+// ([C][D] bf16 global scratch private to this block) holds the prepared keys and values are read from
+// their source.  `route_out` ([C] int32, may be null) receives the decision for every token.
+// Requires C <= NT.
+template <int D, int NT, bool SB>
+__device__ void memory_update(const LayerDev& L, const TokenSrc& src, const MemoryRowPtrs& mem, ViewStore& view, int capacity,
+                              int S_before, int n_append, bf16* pk_scr, int* route_out, UpdateSmem<D>& s) {
+  constexpr int CPR = D / 8;
+  constexpr int PST = D + 8;
+  constexpr int GL = 8;                 // lanes per row in the row-parallel phases
+  constexpr int GROUPS = NT / GL;
   const int C = L.C;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int gl = tid % GL, grp = tid / GL;
   const int S_after = S_before + n_append;
   const int n_merge = C - n_append;
+  const bool pool = view.cur != nullptr;
 
-  // ---- 1. prepared / gated keys of the block -> scratch
-  for (int tkn = warp; tkn < C; tkn += NW) {
-    RowVec<D> r;
-    prepare_key_row<D>(L, r, src.k + (long long)tkn * src.k_st, lane);
-    store_row<D>(r, pk_scr + (size_t)tkn * D, lane);
-    if (L.gate_keys) {
-      const float gt = __bfloat162float(src.g[(long long)tkn * src.g_st]);
-#pragma unroll
-      for (int i = 0; i < D / 32; ++i) r.x[i] = bf16_round(r.x[i] * gt);
+  KVM_PHASE_BEGIN();
+  // ---- 0. bring the block in: keys first (needed at once), values behind them
+  BlockView blk;
+  blk.g = s.g_s;
+  if constexpr (SB) {
+    for (int c = tid; c < C * CPR; c += NT) {
+      const int r = c / CPR, cc = c % CPR;
+      cp_async16(s.pk_s + (size_t)r * PST + cc * 8, src.k + (long long)r * src.k_st + cc * 8, 16);
     }
-    store_row<D>(r, gk_scr + (size_t)tkn * D, lane);
+    cp_async_commit();
+    for (int c = tid; c < C * CPR; c += NT) {
+      const int r = c / CPR, cc = c % CPR;
+      cp_async16(s.v_s + (size_t)r * D + cc * 8, src.v + (long long)r * src.v_st + cc * 8, 16);
+    }
+    cp_async_commit();
+    blk.pk = s.pk_s; blk.pk_st = PST; blk.v = s.v_s; blk.v_st = D;
+  } else {
+    blk.pk = pk_scr; blk.pk_st = D; blk.v = src.v; blk.v_st = src.v_st;
   }
   for (int i = tid; i < C; i += NT) {
+    s.g_s[i] = __bfloat162float(src.g[(long long)i * src.g_st]);
     s.app[i] = -INFINITY;
     s.best[i] = -INFINITY;
     s.idx[i] = -1;
     s.pos[i] = 0;
     s.flag[i] = (n_merge == 0) ? 1 : 0;
   }
-  if (tid < 4) s.counters[tid] = 0;
+  if (tid < 36) s.counters[tid] = 0;
+  if (src.next_k != nullptr) {  // warm L2 with the block the next update of this row consumes
+    constexpr int LPRW = D * 2 / 128 > 0 ? D * 2 / 128 : 1;  // 128-byte lines per row
+    for (int c = tid; c < C * LPRW; c += NT) {
+      const int r = c / LPRW, l = c % LPRW;
+      asm volatile("prefetch.global.L2 [%0];" ::"l"(src.next_k + (long long)r * src.k_st + l * 64));
+      asm volatile("prefetch.global.L2 [%0];" ::"l"(src.next_v + (long long)r * src.v_st + l * 64));
+    }
+  }
+  if constexpr (SB) cp_async_wait<1>();
   __syncthreads();
+  KVM_PHASE_MARK(0);
+
+  // ---- 1. prepared keys (in place in shared memory, or into the global scratch); 8 lanes per token
+#pragma unroll 2
+  for (int base = 0; base < C; base += GROUPS) {
+    const int tkn = base + grp;
+    const bool act = tkn < C;
+    const int t_ = act ? tkn : 0;
+    RowVec<D, GL> r;
+    if constexpr (SB) {
+      prepare_key_row<D, GL>(L, r, s.pk_s + (size_t)t_ * PST, gl);
+      if (act) store_row<D, GL>(r, s.pk_s + (size_t)t_ * PST, gl);
+    } else {
+      prepare_key_row<D, GL>(L, r, src.k + (long long)t_ * src.k_st, gl);
+      if (act) store_row<D, GL>(r, pk_scr + (size_t)t_ * D, gl);
+    }
+  }
+  __syncthreads();
+  KVM_PHASE_MARK(1);
 
   const int protected_rows = min(L.sink_len, S_after);
 
   // ---- 2. scores against the old memory, append selection
-  if (n_merge > 0) scan_memory<D, NT>(pk_scr, gk_scr, C, mem.k_attn, 0, S_before, n_append > 0, protected_rows, s);
+  if (n_merge > 0)
+    scan_memory<D, NT>(blk, L.gate_keys != 0, C, view.k, view.cur, 0, S_before, n_append > 0, protected_rows, s);
+  KVM_PHASE_MARK(2);
   if (n_append > 0 && n_merge > 0) {
-    for (int i = tid; i < C; i += NT) {
-      const float si = s.app[i];
+    if (tid < C) {
+      const float si = s.app[tid];
       int rank = 0;
-      for (int u = 0; u < C; ++u) {
-        const float su = s.app[u];
-        rank += (su < si || (su == si && u < i)) ? 1 : 0;
+#pragma unroll 4
+      for (int u0 = 0; u0 < C; u0 += 4) {
+        const float4 a = *reinterpret_cast<const float4*>(s.app + u0);
+        rank += (a.x < si || (a.x == si && u0 + 0 < tid)) ? 1 : 0;
+        rank += (a.y < si || (a.y == si && u0 + 1 < tid)) ? 1 : 0;
+        rank += (a.z < si || (a.z == si && u0 + 2 < tid)) ? 1 : 0;
+        rank += (a.w < si || (a.w == si && u0 + 3 < tid)) ? 1 : 0;
       }
-      s.flag[i] = rank < n_append ? 1 : 0;
+      s.flag[tid] = rank < n_append ? 1 : 0;
     }
     __syncthreads();
   }
+  KVM_PHASE_MARK(3);
   if (n_append > 0) {
-    for (int i = tid; i < C; i += NT) {
-      int p = 0;
-      for (int u = 0; u < i; ++u) p += s.flag[u];
-      s.pos[i] = p;
+    // position of every appended token among the appended ones (token order): ballot prefix
+    const int f = tid < C ? s.flag[tid] : 0;
+    const unsigned bal = __ballot_sync(0xffffffffu, f != 0);
+    if (lane == 0) s.counters[4 + warp] = __popc(bal);
+    if constexpr (SB) cp_async_wait<0>();  // the values of the block have landed
+    __syncthreads();
+    if (tid < C) {
+      int p = __popc(bal & ((1u << lane) - 1u));
+      for (int w = 0; w < warp; ++w) p += s.counters[4 + w];
+      s.pos[tid] = p;
     }
     __syncthreads();
-    // appended rows, in token order
-    for (int tkn = warp; tkn < C; tkn += NW) {
-      if (!s.flag[tkn]) continue;
-      const int row = S_before + s.pos[tkn];
-      if (row >= capacity) continue;  // guarded by the host-side capacity check
-      RowVec<D> kr, vr;
-      load_row<D>(kr, (L.gate_appends ? gk_scr : pk_scr) + (size_t)tkn * D, lane);
-      load_row<D>(vr, src.v + (long long)tkn * src.v_st, lane);
-      if (L.gate_appends && L.gate_values) {
-        const float gt = __bfloat162float(src.g[(long long)tkn * src.g_st]);
+    // appended rows, in token order; 8 lanes per row
+    for (int base = 0; base < C; base += GROUPS) {
+      const int tkn = base + grp;
+      const bool act = tkn < C && s.flag[tkn] && (S_before + s.pos[tkn]) < capacity;
+      const int t_ = tkn < C ? tkn : 0;
+      const int row = act ? S_before + s.pos[t_] : 0;
+      RowVec<D, GL> kr, vr;
+      load_row<D, GL>(kr, blk.pk + (size_t)t_ * blk.pk_st, gl);
+      load_row<D, GL>(vr, blk.v + (long long)t_ * blk.v_st, gl);
+      if (L.gate_appends) {
+        const float gt = s.g_s[t_];
 #pragma unroll
-        for (int i = 0; i < D / 32; ++i) vr.x[i] = bf16_round(vr.x[i] * gt);
+        for (int i = 0; i < D / GL; ++i) {
+          if (L.gate_keys) kr.x[i] = bf16_round(kr.x[i] * gt);
+          if (L.gate_values) vr.x[i] = bf16_round(vr.x[i] * gt);
+        }
       }
-      const float vl = row_norm<D>(vr);
-      store_row<D>(kr, mem.k_sum + (size_t)row * D, lane);
-      store_row<D>(vr, mem.v_sum + (size_t)row * D, lane);
-      if (lane == 0) mem.vlen[row] = vl;
-      refresh_memory_row<D>(L, kr, vr, vl, mem.k_attn + (size_t)row * D, mem.v_attn + (size_t)row * D, lane);
+      const float vl = row_norm<D, GL>(vr);
+      const int slot = pool ? view.pool_next + s.pos[t_] : row;
+      if (act) {
+        store_row<D, GL>(kr, mem.k_sum + (size_t)row * D, gl);
+        store_row<D, GL>(vr, mem.v_sum + (size_t)row * D, gl);
+        if (gl == 0) {
+          mem.vlen[row] = vl;
+          if (pool) view.cur[row] = slot;
+        }
+      }
+      refresh_memory_row<D, GL>(L, kr, vr, vl, view.k + (size_t)slot * D, view.v + (size_t)slot * D, gl, act);
     }
+    if (pool) view.pool_next += n_append;
     __syncthreads();
+  } else {
+    if constexpr (SB) cp_async_wait<0>();
   }
   if (n_merge == 0) {
     if (route_out)
       for (int i = tid; i < C; i += NT) route_out[i] = -(1 + S_before + s.pos[i]);
+    if (view.ver_idx)
+      for (int i = tid; i < S_after; i += NT) view.ver_idx[i] = view.cur[i];
     __syncthreads();
     return;
   }
+  KVM_PHASE_MARK(4);
 
   // ---- 3. merge targets among the rows that were just appended (append-before-merge)
-  if (n_append > 0) scan_memory<D, NT>(pk_scr, gk_scr, C, mem.k_attn, S_before, S_after, false, protected_rows, s);
+  if (n_append > 0)
+    scan_memory<D, NT>(blk, L.gate_keys != 0, C, view.k, view.cur, S_before, S_after, false, protected_rows, s);
+  KVM_PHASE_MARK(5);
 
   // ---- 4. group the merged tokens by target row, token order inside a group
-  for (int i = tid; i < S_after; i += NT) s.cnt[i] = 0;
+  if (tid < C && s.flag[tid]) s.idx[tid] = -1;
   __syncthreads();
-  if (warp == 0) {
-    for (int base = 0; base < C; base += 32) {
-      const int tkn = base + lane;
-      const bool merged = tkn < C && !s.flag[tkn] && s.idx[tkn] >= 0;
-      const int row = merged ? s.idx[tkn] : -(1 + lane);
-      const unsigned grp = __match_any_sync(0xffffffffu, row);
-      if (merged) {
-        s.pos[tkn] = s.cnt[row] + __popc(grp & ((1u << lane) - 1u));
+  if (tid < C) {
+    const int mine = s.idx[tid];
+    if (mine >= 0) {
+      int before = 0, total = 0, first = tid;
+#pragma unroll 4
+      for (int u0 = 0; u0 < C; u0 += 4) {
+        const int4 a = *reinterpret_cast<const int4*>(s.idx + u0);
+        const int e0 = a.x == mine, e1 = a.y == mine, e2 = a.z == mine, e3 = a.w == mine;
+        total += e0 + e1 + e2 + e3;
+        before += (e0 & (u0 + 0 < tid)) + (e1 & (u0 + 1 < tid)) + (e2 & (u0 + 2 < tid)) + (e3 & (u0 + 3 < tid));
+        if (e3 && u0 + 3 < first) first = u0 + 3;
+        if (e2 && u0 + 2 < first) first = u0 + 2;
+        if (e1 && u0 + 1 < first) first = u0 + 1;
+        if (e0 && u0 + 0 < first) first = u0 + 0;
       }
-      __syncwarp();
-      if (merged && (int)(__ffs(grp) - 1) == lane) s.cnt[row] += __popc(grp);
-      __syncwarp();
+      s.ord[tid] = before;
+      s.lead[tid] = first;
+      if (before == 0) {
+        s.tcnt[tid] = total;
+        s.tstart[tid] = atomicAdd(&s.counters[0], total);
+        s.touched[atomicAdd(&s.counters[1], 1)] = tid;
+      }
     }
   }
   __syncthreads();
-  for (int i = tid; i < C; i += NT) {
-    if (!s.flag[i] && s.idx[i] >= 0 && s.pos[i] == 0) {
-      const int row = s.idx[i];
-      s.start[row] = atomicAdd(&s.counters[0], s.cnt[row]);
-      s.touched[atomicAdd(&s.counters[1], 1)] = row;
-    }
+  if (tid < C) {
+    if (s.idx[tid] >= 0) s.list[s.tstart[s.lead[tid]] + s.ord[tid]] = tid;
+    if (route_out) route_out[tid] = s.flag[tid] ? -(1 + S_before + s.pos[tid]) : s.idx[tid];
   }
   __syncthreads();
-  for (int i = tid; i < C; i += NT) {
-    if (!s.flag[i] && s.idx[i] >= 0) s.list[s.start[s.idx[i]] + s.pos[i]] = i;
-    if (route_out) route_out[i] = s.flag[i] ? -(1 + S_before + s.pos[i]) : s.idx[i];
-  }
-  __syncthreads();
+  KVM_PHASE_MARK(6);
 
-  // ---- 5. fixed-order accumulation into the touched rows and refresh of their attention view
+  // ---- 5. fixed-order accumulation into the touched rows and refresh of their attention view;
+  //         eight lanes per row; the first half of the block does the key rows, the second half the values
   const int n_touched = s.counters[1];
-  for (int i = warp; i < n_touched; i += NW) {
-    const int row = s.touched[i];
-    const int n = s.cnt[row];
-    const int b0 = s.start[row];
-    RowVec<D> ak, av;
+  {
+    constexpr int HG = GROUPS / 2;
+    const bool is_v = grp >= HG;
+    const int hgrp = grp % HG;
+    for (int base = 0; base < n_touched; base += HG) {  // trip count uniform: the refresh uses shuffles
+      const int i = base + hgrp;
+      const bool act = i < n_touched;
+      const int lt = s.touched[act ? i : 0];
+      const int row = s.idx[lt];
+      const int n = act ? s.tcnt[lt] : 0;
+      const int b0 = s.tstart[lt];
+      const int slot = pool ? view.pool_next + i : row;
+      bf16* sum_row = (is_v ? mem.v_sum : mem.k_sum) + (size_t)row * D;
+      RowVec<D, GL> sum, acc;
+      load_row<D, GL>(sum, sum_row, gl);  // issued first: its latency hides behind the accumulation
 #pragma unroll
-    for (int e = 0; e < D / 32; ++e) ak.x[e] = av.x[e] = 0.f;
-    for (int j = 0; j < n; ++j) {
-      const int tkn = s.list[b0 + j];
-      RowVec<D> kr, vr;
-      load_row<D>(kr, gk_scr + (size_t)tkn * D, lane);
-      load_row<D>(vr, src.v + (long long)tkn * src.v_st, lane);
-      if (L.gate_values) {
-        const float gt = __bfloat162float(src.g[(long long)tkn * src.g_st]);
+      for (int e = 0; e < D / GL; ++e) acc.x[e] = 0.f;
+      if (!is_v) {
+        for (int j = 0; j < n; ++j) {
+          const int tkn = s.list[b0 + j];
+          const float gt = s.g_s[tkn];
+          RowVec<D, GL> kr;
+          load_row<D, GL>(kr, blk.pk + (size_t)tkn * blk.pk_st, gl);
 #pragma unroll
-        for (int e = 0; e < D / 32; ++e) vr.x[e] = bf16_round(vr.x[e] * gt);
+          for (int e = 0; e < D / GL; ++e) acc.x[e] += L.gate_keys ? bf16_round(kr.x[e] * gt) : kr.x[e];
+        }
+      } else {
+        for (int j = 0; j < n; ++j) {
+          const int tkn = s.list[b0 + j];
+          const float gt = s.g_s[tkn];
+          RowVec<D, GL> vr;
+          load_row<D, GL>(vr, blk.v + (long long)tkn * blk.v_st, gl);
+#pragma unroll
+          for (int e = 0; e < D / GL; ++e) acc.x[e] += L.gate_values ? bf16_round(vr.x[e] * gt) : vr.x[e];
+        }
       }
 #pragma unroll
-      for (int e = 0; e < D / 32; ++e) {
-        ak.x[e] += kr.x[e];
-        av.x[e] += vr.x[e];
+      for (int e = 0; e < D / GL; ++e) sum.x[e] = bf16_round(sum.x[e] + bf16_round(acc.x[e]));
+      if (act) store_row<D, GL>(sum, sum_row, gl);
+      if (!is_v) {
+        layer_norm_row<D, GL>(sum, L.ln_w, L.ln_b, L.ln_eps, gl);
+        if (act) store_row<D, GL>(sum, view.k + (size_t)slot * D, gl);
+      } else {
+        const float nrm = fmaxf(row_norm<D, GL>(sum), 1e-12f);
+        const float vl = mem.vlen[row];
+#pragma unroll
+        for (int e = 0; e < D / GL; ++e) sum.x[e] = __fdiv_rn(sum.x[e], nrm) * vl;
+        if (act) store_row<D, GL>(sum, view.v + (size_t)slot * D, gl);
       }
     }
-    RowVec<D> ks, vs;
-    load_row<D>(ks, mem.k_sum + (size_t)row * D, lane);
-    load_row<D>(vs, mem.v_sum + (size_t)row * D, lane);
-#pragma unroll
-    for (int e = 0; e < D / 32; ++e) {
-      ks.x[e] = bf16_round(ks.x[e] + bf16_round(ak.x[e]));
-      vs.x[e] = bf16_round(vs.x[e] + bf16_round(av.x[e]));
-    }
-    store_row<D>(ks, mem.k_sum + (size_t)row * D, lane);
-    store_row<D>(vs, mem.v_sum + (size_t)row * D, lane);
-    refresh_memory_row<D>(L, ks, vs, mem.vlen[row], mem.k_attn + (size_t)row * D, mem.v_attn + (size_t)row * D, lane);
   }
   __syncthreads();
+  if (pool) {
+    for (int i = tid; i < n_touched; i += NT) view.cur[s.idx[s.touched[i]]] = view.pool_next + i;
+    view.pool_next += n_touched;
+    __syncthreads();
+    if (view.ver_idx)
+      for (int i = tid; i < S_after; i += NT) view.ver_idx[i] = view.cur[i];
+  }
+  __syncthreads();
+  KVM_PHASE_MARK(7);
 }
 
 }  // namespace kvm

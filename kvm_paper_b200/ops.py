@@ -240,9 +240,15 @@ class PrefillRunner:
         _lib.check(rc)
         return self.out
 
+    def check_status(self) -> None:
+        """Synchronise and raise if a kernel of the last run reported a device-side timeout."""
+        rc = _lib.load().kvm_prefill_status(self.ws.data_ptr(), _stream_ptr(self.params.device))
+        _lib.check(rc)
+
 
 def prefill_forward(params: LayerParams, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, gate: torch.Tensor,
-                    plan: PrefillPlan, *, memory_capacity: int | None = None, want_route: bool = False) -> PrefillResult:
+                    plan: PrefillPlan, *, memory_capacity: int | None = None, want_route: bool = False,
+                    phases: int = _lib.PREFILL_CHAIN | _lib.PREFILL_ATTENTION, check: bool = False) -> PrefillResult:
     """Whole-prompt prefill through ``kvm_prefill_forward``.
 
     q [B,Hq,T,D], k/v [B,Hkv,T,D], gate [B,Hkv,T,1]; strided views are passed as they are."""
@@ -251,7 +257,9 @@ def prefill_forward(params: LayerParams, q: torch.Tensor, k: torch.Tensor, v: to
     if not q.is_cuda:
         raise RuntimeError("kvm_b200 runs on CUDA tensors only (there is no CPU path)")
     runner = PrefillRunner(params, q.size(0), plan, memory_capacity=memory_capacity, want_route=want_route)
-    out = runner.run(q, k, v, gate)
+    out = runner.run(q, k, v, gate, phases=phases)
+    if check:
+        runner.check_status()
     # buffers are released by the caching allocator in stream order
     return PrefillResult(out, runner.memory, plan, runner.route)
 

@@ -37,12 +37,13 @@ def bf16_spec(spec: ko.KvmSpec) -> ko.KvmSpec:
                                front_head_temp=conv(spec.front_head_temp), state_head_temp=conv(spec.state_head_temp))
 
 
-def device_prefill(spec: ko.KvmSpec, q, k, v, gate, want_route=True, memory_capacity=None):
+def device_prefill(spec: ko.KvmSpec, q, k, v, gate, want_route=True, memory_capacity=None, phases=3):
     params = layer_params(spec)
     T = q.size(2)
     plan = ops.build_prefill_plan(T, spec.chunk_len, spec.n_bswa_chunks, desired_fn(spec))
     dev = [t.to("cuda", torch.bfloat16) for t in (q, k, v, gate)]
-    res = ops.prefill_forward(params, *dev, plan, want_route=want_route, memory_capacity=memory_capacity)
+    res = ops.prefill_forward(params, *dev, plan, want_route=want_route, memory_capacity=memory_capacity,
+                              phases=phases, check=True)
     torch.cuda.synchronize()
     return params, plan, res
 

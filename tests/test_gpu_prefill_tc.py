@@ -1,0 +1,62 @@
+"""GPU parity of the tcgen05 / tensor-memory block-attention kernel (head_dim 128, blocks that are whole
+128-row query tiles) against the oracle and against the warp-level mma.sync kernel on the same inputs."""
+
+import pytest
+import torch
+
+from kvm_paper_b200 import _lib
+from oracle import kvm_oracle as ko
+from tests.helpers import assert_close_bf16, assert_not_worse_than_reference, max_abs
+from tests import gpu_helpers as gh
+
+pytestmark = pytest.mark.gpu
+
+
+def _inputs(B, Hq, Hkv, T, seed):
+    g = torch.Generator().manual_seed(seed)
+    D = 128
+    q = torch.nn.functional.layer_norm(torch.randn(B, T, Hq, D, generator=g), (D,)).bfloat16().transpose(1, 2)
+    k = torch.nn.functional.layer_norm(torch.randn(B, T, Hkv, D, generator=g), (D,)).bfloat16().transpose(1, 2)
+    v = torch.randn(B, T, Hkv, D, generator=g).bfloat16().transpose(1, 2)
+    gate = (1 + torch.nn.functional.elu(0.5 * torch.randn(B, T, Hkv, 1, generator=g))).bfloat16().transpose(1, 2)
+    return q, k, v, gate
+
+
+@pytest.mark.parametrize("C,T,Hq,Hkv,mode", [
+    (128, 128 * 5 + 40, 2, 2, "plus_one"),      # ragged end, growing memory
+    (128, 128 * 3, 4, 2, "fixed"),               # grouped queries share a kv row
+    (256, 256 * 4 + 130, 2, 2, "power_law"),     # two query tiles per block, memory with a partial last tile
+    (128, 100, 2, 2, "fixed"),                   # shorter than one block: front attention only
+])
+def test_tc_attention_matches_oracle(C, T, Hq, Hkv, mode):
+    temps = dict(front_head_temp=torch.linspace(0.9, 1.2, Hq), state_head_temp=torch.linspace(1.1, 0.8, Hq))
+    spec = ko.KvmSpec(Hq, Hkv, 128, 128, 64, C, 2, 4, 1, mode, state_growth_factor=8.0, state_min_len=C, **temps)
+    spec = gh.bf16_spec(spec)
+    q, k, v, g = _inputs(1, Hq, Hkv, T, seed=T + C)
+    params, plan, res = gh.device_prefill(spec, q, k, v, g)
+    forced = [gh.decisions_from_route(res.route[:, u], 1, Hkv) for u in range(1, plan.n_updates + 1)]
+    trace = []
+    with torch.no_grad():
+        y, st = ko.prefill(spec, q, k, v, g, trace=trace, forced=forced)
+        y32, _ = ko.prefill(gh.fp32_spec(spec), q.float(), k.float(), v.float(), g.float(), forced=forced)
+    gh.assert_routing_ok(gh.summarize(trace))
+    assert_close_bf16(res.out.cpu(), y, f"tcgen05 attention C={C} T={T}")
+    assert_not_worse_than_reference(res.out.cpu(), y, y32, f"tcgen05 attention C={C} T={T}")
+    # same inputs through the warp-level kernel
+    _, _, legacy = gh.device_prefill(spec, q, k, v, g, phases=_lib.PREFILL_CHAIN | _lib.PREFILL_ATTENTION | _lib.PREFILL_LEGACY_ATTENTION)
+    assert_close_bf16(res.out.cpu(), legacy.out.cpu(), "tcgen05 vs mma.sync kernel", mean_rel_tol=2.5e-3)
+
+
+def test_tc_attention_large_logits_need_rescaling():
+    """Keys whose similarity grows along the sequence force the running maximum to be raised repeatedly
+    (the tensor-memory rescale path)."""
+    C, T = 128, 128 * 6
+    spec = gh.bf16_spec(ko.KvmSpec(2, 2, 128, 128, 64, C, 2, 2, 1, "fixed", state_min_len=C))
+    q, k, v, g = _inputs(1, 2, 2, T, seed=5)
+    ramp = torch.linspace(0.2, 3.0, T).view(1, 1, T, 1)
+    k = (q * ramp).bfloat16()  # q.k grows with the key position: later tiles exceed the stale maximum by > 2^8
+    params, plan, res = gh.device_prefill(spec, q, k, v, g)
+    forced = [gh.decisions_from_route(res.route[:, u], 1, 2) for u in range(1, plan.n_updates + 1)]
+    with torch.no_grad():
+        y, _ = ko.prefill(spec, q, k, v, g, forced=forced)
+    assert_close_bf16(res.out.cpu(), y, "rescale path")
