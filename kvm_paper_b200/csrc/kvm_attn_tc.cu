@@ -30,15 +30,20 @@ constexpr int kThreads = 224;
 constexpr int kTmemCols = 256;
 constexpr float kRescaleThreshold = 8.0f;  // log2 units
 
+#ifndef KVM_TC_STAGES
+#define KVM_TC_STAGES 4
+#endif
+constexpr int kStages = KVM_TC_STAGES;              // K/V tiles in flight per CTA
+constexpr int kCtasPerSm = kStages <= 2 ? 2 : 1;
 constexpr uint32_t kOffQ = 0;                       // 2 x [128][64] bf16
-constexpr uint32_t kOffK = 32768;                   // 2 stages x 2 x [64][64]
-constexpr uint32_t kOffV = kOffK + 2 * 16384;       // 2 stages x 2 x [64 keys][64]
-constexpr uint32_t kOffP = kOffV + 2 * 16384;       // [128][64]
+constexpr uint32_t kOffK = 32768;                   // kStages x 2 x [64][64]
+constexpr uint32_t kOffV = kOffK + kStages * 16384; // kStages x 2 x [64 keys][64]
+constexpr uint32_t kOffP = kOffV + kStages * 16384; // [128][64]
 constexpr uint32_t kOffBar = kOffP + 16384;         // barriers and scalars
 constexpr uint32_t kSmemBytes = kOffBar + 128;
 
 struct Bars {
-  uint64_t q_full, kv_full[2], kv_empty[2], s_full[2], p_full, pv_done;
+  uint64_t q_full, kv_full[kStages], kv_empty[kStages], s_full[2], p_full, pv_done;
   uint32_t tmem_base;
   uint32_t abort_flag;
 };
@@ -57,7 +62,7 @@ __device__ __forceinline__ float ex2(float x) {
 
 }  // namespace
 
-__global__ void __launch_bounds__(kThreads, 2)
+__global__ void __launch_bounds__(kThreads, kCtasPerSm)
 kvm_attn_prefill_tc_kernel(LayerDev L, long long T, Tensor4 q, Tensor4 k, Tensor4 v,
                            const kvm_update_plan* __restrict__ plan, const bf16* __restrict__ pool_k,
                            const bf16* __restrict__ pool_v, long long pool_rows, const int* __restrict__ ver_idx,
@@ -102,11 +107,11 @@ kvm_attn_prefill_tc_kernel(LayerDev L, long long T, Tensor4 q, Tensor4 k, Tensor
 
   if (tid == 0) {
     tc::mbar_init(&bars->q_full, 1);
-    for (int i = 0; i < 2; ++i) {
+    for (int i = 0; i < kStages; ++i) {
       tc::mbar_init(&bars->kv_full[i], 1);
       tc::mbar_init(&bars->kv_empty[i], 1);
-      tc::mbar_init(&bars->s_full[i], 1);
     }
+    for (int i = 0; i < 2; ++i) tc::mbar_init(&bars->s_full[i], 1);
     tc::mbar_init(&bars->p_full, 4);
     tc::mbar_init(&bars->pv_done, 1);
     bars->abort_flag = 0;
@@ -123,10 +128,10 @@ kvm_attn_prefill_tc_kernel(LayerDev L, long long T, Tensor4 q, Tensor4 k, Tensor
 
   if (warp == 4 || warp == 5) {
     // ------------------------------------------------------------------ loaders (warp 4: even tiles + Q, warp 5: odd tiles)
-    const int stage = warp - 4;
+    const int lw = warp - 4;  // this loader takes the tiles t with t % 2 == lw
     const bf16* kbase = k.row(b, hkv, 0);
     const bf16* vbase = v.row(b, hkv, 0);
-    if (stage == 0) {
+    if (lw == 0) {
       for (int c = lane; c < BM * 16; c += 32) {
         const int r = c >> 4, cc = c & 15;
         const long long row = q0 + r;
@@ -135,37 +140,40 @@ kvm_attn_prefill_tc_kernel(LayerDev L, long long T, Tensor4 q, Tensor4 k, Tensor
         cp_async16(smem + kOffQ + (cc >> 3) * 16384 + tc::sw128_offset(r, (cc & 7) * 8), src, ok ? 16 : 0);
       }
     }
-    unsigned char* dK = smem + kOffK + stage * 16384;
-    unsigned char* dV = smem + kOffV + stage * 16384;
-    for (int t = stage; t < n_tiles; t += 2) {
-      if (t >= 2 && !warp_wait(&bars->kv_empty[stage], ((t >> 1) - 1) & 1)) { failed = true; break; }
+    for (int t = lw; t < n_tiles; t += 2) {
+      const int stage = t % kStages;
+      unsigned char* dK = smem + kOffK + stage * 16384;
+      unsigned char* dV = smem + kOffV + stage * 16384;
+      if (t >= kStages && !warp_wait(&bars->kv_empty[stage], ((t / kStages) - 1) & 1)) { failed = true; break; }
+      // lane -> fixed 16-byte column chunk cc and row parity; iteration `it` covers rows 2*it and 2*it+1
+      const int cc = lane & 15, rh = lane >> 4;
+      const uint32_t col_off = (uint32_t)(cc >> 3) * 8192u;
       if (t < n_mem_tiles) {
         const int row0 = t * BN;
         const int i0 = row0 + lane < S ? __ldg(midx + row0 + lane) : 0;
         const int i1 = row0 + 32 + lane < S ? __ldg(midx + row0 + 32 + lane) : 0;
-#pragma unroll 4
-        for (int it = 0; it < BN * 16 / 32; ++it) {
-          const int c = it * 32 + lane;
-          const int r = c >> 4, cc = c & 15;
-          const int a0 = __shfl_sync(0xffffffffu, i0, r & 31);
-          const int a1 = __shfl_sync(0xffffffffu, i1, r & 31);
-          const int slot = r < 32 ? a0 : a1;
+#pragma unroll
+        for (int it = 0; it < BN / 2; ++it) {
+          const int r = it * 2 + rh;
+          const int a0 = __shfl_sync(0xffffffffu, it < 16 ? i0 : i1, r & 31);
           const bool ok = row0 + r < S;
-          const uint32_t off = (cc >> 3) * 8192 + tc::sw128_offset(r, (cc & 7) * 8);
-          cp_async16(dK + off, mk + (size_t)slot * HD + cc * 8, ok ? 16 : 0);
-          cp_async16(dV + off, mv + (size_t)slot * HD + cc * 8, ok ? 16 : 0);
+          const uint32_t off = col_off + (uint32_t)(r * 128) + (uint32_t)((((cc & 7) ^ (r & 7)) & 7) << 4);
+          const size_t src = (size_t)a0 * HD + cc * 8;
+          cp_async16(dK + off, mk + src, ok ? 16 : 0);
+          cp_async16(dV + off, mv + src, ok ? 16 : 0);
         }
       } else {
         const long long r0 = bb + (long long)(t - n_mem_tiles) * BN;
-#pragma unroll 4
-        for (int it = 0; it < BN * 16 / 32; ++it) {
-          const int c = it * 32 + lane;
-          const int r = c >> 4, cc = c & 15;
-          const long long row = r0 + r;
-          const bool ok = row < q_tile_end;
-          const uint32_t off = (cc >> 3) * 8192 + tc::sw128_offset(r, (cc & 7) * 8);
-          cp_async16(dK + off, kbase + (ok ? row : 0) * k.st + cc * 8, ok ? 16 : 0);
-          cp_async16(dV + off, vbase + (ok ? row : 0) * v.st + cc * 8, ok ? 16 : 0);
+        const bf16* pk = kbase + (r0 + rh) * k.st + cc * 8;
+        const bf16* pv = vbase + (r0 + rh) * v.st + cc * 8;
+        const int n_ok = (int)min((long long)BN, q_tile_end - r0);  // rows of this tile that exist
+#pragma unroll
+        for (int it = 0; it < BN / 2; ++it) {
+          const int r = it * 2 + rh;
+          const bool ok = r < n_ok;
+          const uint32_t off = col_off + (uint32_t)(r * 128) + (uint32_t)((((cc & 7) ^ (r & 7)) & 7) << 4);
+          cp_async16(dK + off, ok ? pk + (long long)it * 2 * k.st : kbase, ok ? 16 : 0);
+          cp_async16(dV + off, ok ? pv + (long long)it * 2 * v.st : vbase, ok ? 16 : 0);
         }
       }
       cp_async_commit();
@@ -184,26 +192,26 @@ kvm_attn_prefill_tc_kernel(LayerDev L, long long T, Tensor4 q, Tensor4 k, Tensor
       constexpr uint32_t idesc_qk = tc::make_idesc(BM, BN, 0, 0);
       constexpr uint32_t idesc_pv = tc::make_idesc(BM, HD, 0, 1);
       auto issue_qk = [&](int t) {
-        const int stage = t & 1;
-        const uint32_t d = tmem + (uint32_t)(stage * BN);
+        const int stage = t % kStages, sbuf = t & 1;
+        const uint32_t d = tmem + (uint32_t)(sbuf * BN);
 #pragma unroll
         for (int ks = 0; ks < HD / 16; ++ks) {
           const uint64_t da = tc::make_desc(sQ + (ks >> 2) * 16384 + (ks & 3) * 32, 16, 1024);
           const uint64_t db = tc::make_desc(sK + stage * 16384 + (ks >> 2) * 8192 + (ks & 3) * 32, 16, 1024);
           tc::mma_ss(d, da, db, idesc_qk, ks > 0);
         }
-        tc::mma_commit(&bars->s_full[stage]);
+        tc::mma_commit(&bars->s_full[sbuf]);
       };
       if (!tc::mbar_wait(&bars->q_full, 0)) failed = true;
       for (int t = 0; t < 2 && t < n_tiles && !failed; ++t) {
-        if (!tc::mbar_wait(&bars->kv_full[t & 1], 0)) { failed = true; break; }
+        if (!tc::mbar_wait(&bars->kv_full[t % kStages], 0)) { failed = true; break; }
         tc::tc_fence_after_sync();
         issue_qk(t);
       }
       for (int t = 0; t < n_tiles && !failed; ++t) {
         if (!tc::mbar_wait(&bars->p_full, t & 1)) { failed = true; break; }
         tc::tc_fence_after_sync();
-        const int stage = t & 1;
+        const int stage = t % kStages;
 #pragma unroll
         for (int ks = 0; ks < BN / 16; ++ks) {
           const uint64_t da = tc::make_desc(sP + ks * 32, 16, 1024);
@@ -213,7 +221,7 @@ kvm_attn_prefill_tc_kernel(LayerDev L, long long T, Tensor4 q, Tensor4 k, Tensor
         tc::mma_commit(&bars->kv_empty[stage]);
         tc::mma_commit(&bars->pv_done);
         if (t + 2 < n_tiles) {
-          if (!tc::mbar_wait(&bars->kv_full[stage], ((t + 2) >> 1) & 1)) { failed = true; break; }
+          if (!tc::mbar_wait(&bars->kv_full[(t + 2) % kStages], ((t + 2) / kStages) & 1)) { failed = true; break; }
           tc::tc_fence_after_sync();
           issue_qk(t + 2);
         }
@@ -240,15 +248,21 @@ kvm_attn_prefill_tc_kernel(LayerDev L, long long T, Tensor4 q, Tensor4 k, Tensor
       const bool is_mem = t < n_mem_tiles;
       const long long base = is_mem ? (long long)t * BN : bb + (long long)(t - n_mem_tiles) * BN;
       const float sc = is_mem ? scale_mem : scale_win;
-      const long long last_ok = is_mem ? (long long)S - 1 : qpos;  // highest visible key index / position
-      float x[64];
-      float tmax = -INFINITY;
+      // keys [0, n_ok) of this tile are visible to this row (memory: rows below S; window: causal)
+      const int n_ok = (int)max(0LL, min((long long)BN, (is_mem ? (long long)S : qpos + 1) - base));
+      const bool tile_masked = is_mem ? (base + BN > S) : (base + BN > q0 + 1);  // uniform over the CTA
+      if (tile_masked) {
 #pragma unroll
-      for (int i = 0; i < 64; ++i) {
-        const float sv = __uint_as_float(sr[i >> 5][i & 31]) * sc;
-        x[i] = (base + i <= last_ok) ? sv : -INFINITY;
-        tmax = fmaxf(tmax, x[i]);
+        for (int i = 0; i < 64; ++i)
+          if (i >= n_ok) sr[i >> 5][i & 31] = 0xff800000u;  // -inf
       }
+      float tm0 = -INFINITY, tm1 = -INFINITY;
+#pragma unroll
+      for (int i = 0; i < 32; ++i) {
+        tm0 = fmaxf(tm0, __uint_as_float(sr[0][i]));
+        tm1 = fmaxf(tm1, __uint_as_float(sr[1][i]));
+      }
+      const float tmax = fmaxf(tm0, tm1) * sc;  // sc > 0
       const bool need = tmax > m_run + kRescaleThreshold || (m_run == -INFINITY && tmax > -INFINITY);
       const bool warp_need = __any_sync(0xffffffffu, need);
       if (t > 0 && !warp_wait(&bars->pv_done, (t - 1) & 1)) { failed = true; break; }
@@ -271,20 +285,23 @@ kvm_attn_prefill_tc_kernel(LayerDev L, long long T, Tensor4 q, Tensor4 k, Tensor
         }
         m_run = m_new;
       }
-      const float m_use = (m_run == -INFINITY) ? 0.f : m_run;
-      float ls = 0.f;
+      const float neg_m = (m_run == -INFINITY) ? 0.f : -m_run;
+      float ls0 = 0.f, ls1 = 0.f;
 #pragma unroll
       for (int cchunk = 0; cchunk < 8; ++cchunk) {
         uint32_t pk[4];
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
-          const float p0 = ex2(x[cchunk * 8 + e * 2] - m_use);
-          const float p1 = ex2(x[cchunk * 8 + e * 2 + 1] - m_use);
-          ls += p0 + p1;
+          const int i = cchunk * 8 + e * 2;
+          const float p0 = ex2(fmaf(__uint_as_float(sr[i >> 5][i & 31]), sc, neg_m));
+          const float p1 = ex2(fmaf(__uint_as_float(sr[(i + 1) >> 5][(i + 1) & 31]), sc, neg_m));
+          ls0 += p0;
+          ls1 += p1;
           pk[e] = pack_bf16(p0, p1);
         }
         *reinterpret_cast<uint4*>(prow + (((cchunk ^ (row & 7)) & 7) << 4)) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
       }
+      const float ls = ls0 + ls1;
       l_run += ls;
       tc::fence_proxy_async();
       tc::tc_fence_before_sync();
