@@ -39,9 +39,13 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   return ok != 0;
 }
 // Waits for the phase with the given parity; gives up after kSpinLimit attempts (returns false).
+// After a few immediate retries the waiter backs off with nanosleep so that it does not take issue
+// slots from the warps that do the work.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
-  for (uint32_t i = 0; i < kSpinLimit; ++i)
+  for (uint32_t i = 0; i < kSpinLimit; ++i) {
     if (mbar_try_wait(bar, parity)) return true;
+    if (i >= 4) __nanosleep(i < 64 ? 40 : 200);
+  }
   return false;
 }
 
