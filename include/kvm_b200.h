@@ -152,6 +152,19 @@ int kvm_decode_step(const kvm_layer* layer, int32_t batch, kvm_decode_cache cach
                     void* out, int32_t* route_dev, void* workspace, size_t workspace_bytes,
                     void* stream);
 
+/* `n_steps` consecutive decode steps whose inputs are already on the device (teacher-forced or synthetic
+ * decoding, as in the reference's kernel benchmark, which pre-generates the per-token q/k/v/gate:
+ * scripts/kvm_benchmark/common.py:341-512, 684-709).  Step i reads q/k/v/gate at
+ * base + i*step_stride elements, n_append_dev + i*batch, and writes out + i*batch*Hq*D; any_update_host
+ * and max_rows_host ([n_steps], host memory) carry the per-step launch flags of kvm_decode_step.
+ * Equivalent to calling kvm_decode_step n_steps times; exists so that the host loop costs two kernel
+ * launches per token and nothing else. */
+int kvm_decode_run(const kvm_layer* layer, int32_t batch, kvm_decode_cache cache, int32_t n_steps,
+                   kvm_tensor4 q, kvm_tensor4 k, kvm_tensor4 v, kvm_tensor4 gate,
+                   int64_t q_step_stride, int64_t kv_step_stride, int64_t gate_step_stride,
+                   const int32_t* n_append_dev, const int32_t* any_update_host, const int32_t* max_rows_host,
+                   void* out, void* workspace, size_t workspace_bytes, void* stream);
+
 /* Same decode step for callers that cannot allocate device memory.  It has no counterpart in the
  * reference.  Some hosts of this library only receive tensors and a stream from their runtime and are
  * not allowed to call cudaMalloc themselves -- a plug-in inside an inference server whose memory pool is

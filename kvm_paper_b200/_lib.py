@@ -50,7 +50,7 @@ class KvmDecodeCache(C.Structure):
 
 EXPORTS = [
     "kvm_prefill_workspace_bytes", "kvm_prefill_forward", "kvm_decode_workspace_bytes", "kvm_decode_step",
-    "kvm_memory_refresh", "kvm_last_error_string", "kvm_abi_version", "kvm_decode_step_static", "kvm_prefill_status",
+    "kvm_memory_refresh", "kvm_last_error_string", "kvm_abi_version", "kvm_decode_step_static", "kvm_prefill_status", "kvm_decode_run",
 ]
 STATIC_SCRATCH_BYTES = 32 << 20
 
@@ -83,6 +83,11 @@ def load():
     lib.kvm_decode_step.argtypes = [
         LP(KvmLayer), C.c_int32, KvmDecodeCache, KvmTensor4, KvmTensor4, KvmTensor4, KvmTensor4,
         C.c_void_p, C.c_int32, C.c_int32, C.c_void_p, C.c_void_p, C.c_void_p, C.c_size_t, C.c_void_p]
+    lib.kvm_decode_run.restype = C.c_int
+    lib.kvm_decode_run.argtypes = [
+        LP(KvmLayer), C.c_int32, KvmDecodeCache, C.c_int32, KvmTensor4, KvmTensor4, KvmTensor4, KvmTensor4,
+        C.c_int64, C.c_int64, C.c_int64, C.c_void_p, LP(C.c_int32), LP(C.c_int32), C.c_void_p, C.c_void_p,
+        C.c_size_t, C.c_void_p]
     # decode step with the scratch inside the library (for callers that cannot allocate device memory)
     lib.kvm_decode_step_static.restype = C.c_int
     lib.kvm_decode_step_static.argtypes = [

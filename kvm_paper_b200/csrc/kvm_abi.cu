@@ -11,7 +11,7 @@ namespace kvm {
 cudaError_t prefill_dispatch(int D, const LayerDev& L, int batch, long long T, Tensor4 q, Tensor4 k, Tensor4 v,
                              Tensor4 gate, const kvm_update_plan* plan_dev, int n_plan, long long ver_rows,
                              MemoryDev mem, bf16* out, int* route, bf16* pool_k, bf16* pool_v, long long pool_rows,
-                             int* ver_idx, bf16* pk_scr, int* status, unsigned phases, cudaStream_t stream);
+                             int* ver_idx, bf16* pk_scr, bf16* pk_all, int* status, unsigned phases, cudaStream_t stream);
 size_t update_smem_bytes(int D, int C, int capacity);
 cudaError_t decode_dispatch(int D, const LayerDev& L, int batch, const DecodeCacheDev& cache, Tensor4 q, Tensor4 k,
                             Tensor4 v, Tensor4 gate, const int* n_append, int any_update, int max_rows, bf16* out,
@@ -107,7 +107,7 @@ int check_memory(const kvm_memory& m, const kvm_layer* l) {
 // rows per kv row), the per-version index tables, and the prepared-key scratch of the update variant
 // that cannot stage a block in shared memory.
 struct PrefillWs {
-  size_t status, pool_k, pool_v, ver_idx, pk, total;
+  size_t status, pool_k, pool_v, ver_idx, pk, pk_all, total;
   long long pool_rows;
 };
 PrefillWs prefill_ws(const kvm_layer* l, int batch, long long seq_len, long long ver_rows) {
@@ -124,6 +124,7 @@ PrefillWs prefill_ws(const kvm_layer* l, int batch, long long seq_len, long long
   w.pool_v = off; off = align_up(off + rows * (size_t)w.pool_rows * D * 2, 256);
   w.ver_idx = off; off = align_up(off + rows * (size_t)ver_rows * 4, 256);
   w.pk = off; off = align_up(off + rows * (size_t)C * D * 2, 256);
+  w.pk_all = off; off = align_up(off + (n_plan > 1 ? rows * (size_t)(n_plan * C) * D * 2 : 0), 256);  // prepared keys of all consumed tokens
   w.total = off;
   return w;
 }
@@ -236,7 +237,8 @@ int kvm_prefill_forward(const kvm_layer* layer, int32_t batch, int64_t seq_len, 
                                    n_updates + 1, total_version_rows, to_dev(memory), static_cast<bf16*>(out), route_dev,
                                    reinterpret_cast<bf16*>(wsb + ws.pool_k), reinterpret_cast<bf16*>(wsb + ws.pool_v),
                                    ws.pool_rows, reinterpret_cast<int*>(wsb + ws.ver_idx),
-                                   reinterpret_cast<bf16*>(wsb + ws.pk), reinterpret_cast<int*>(wsb + ws.status), phases,
+                                   reinterpret_cast<bf16*>(wsb + ws.pk), reinterpret_cast<bf16*>(wsb + ws.pk_all),
+                                   reinterpret_cast<int*>(wsb + ws.status), phases,
                                    static_cast<cudaStream_t>(stream));
   if (e != cudaSuccess) return cuda_fail(e, "kvm_prefill_forward");
   return KVM_OK;
@@ -301,6 +303,32 @@ int kvm_decode_step(const kvm_layer* layer, int32_t batch, kvm_decode_cache cach
   g_err[0] = 0;
   return decode_step_impl(layer, batch, cache, q, k, v, gate, n_append_dev, any_update, max_rows, out, route_dev, workspace,
                           workspace_bytes, stream, "kvm_decode_step");
+}
+
+int kvm_decode_run(const kvm_layer* layer, int32_t batch, kvm_decode_cache cache, int32_t n_steps, kvm_tensor4 q,
+                   kvm_tensor4 k, kvm_tensor4 v, kvm_tensor4 gate, int64_t q_step_stride, int64_t kv_step_stride,
+                   int64_t gate_step_stride, const int32_t* n_append_dev, const int32_t* any_update_host,
+                   const int32_t* max_rows_host, void* out, void* workspace, size_t workspace_bytes, void* stream) {
+  g_err[0] = 0;
+  if (n_steps <= 0 || !any_update_host || !max_rows_host)
+    return fail(KVM_ERR_BAD_ARGUMENT, "n_steps must be positive and the per-step host arrays not NULL");
+  if (!layer) return fail(KVM_ERR_BAD_ARGUMENT, "layer is NULL");
+  if (q_step_stride % 8 || kv_step_stride % 8) return fail(KVM_ERR_BAD_ARGUMENT, "step strides must be multiples of 16 bytes");
+  const size_t out_stride = (size_t)batch * layer->n_q_heads * layer->head_dim;
+  for (int i = 0; i < n_steps; ++i) {
+    kvm_tensor4 qi = q, ki = k, vi = v, gi = gate;
+    qi.ptr = static_cast<const uint16_t*>(q.ptr) + (size_t)i * q_step_stride;
+    ki.ptr = static_cast<const uint16_t*>(k.ptr) + (size_t)i * kv_step_stride;
+    vi.ptr = static_cast<const uint16_t*>(v.ptr) + (size_t)i * kv_step_stride;
+    gi.ptr = static_cast<const uint16_t*>(gate.ptr) + (size_t)i * gate_step_stride;
+    const int upd = any_update_host[i];
+    if (upd && !n_append_dev) return fail(KVM_ERR_BAD_ARGUMENT, "step %d updates the memory but n_append_dev is NULL", i);
+    int rc = decode_step_impl(layer, batch, cache, qi, ki, vi, gi, upd ? n_append_dev + (size_t)i * batch : nullptr, upd,
+                              max_rows_host[i], static_cast<uint16_t*>(out) + (size_t)i * out_stride, nullptr, workspace,
+                              workspace_bytes, stream, "kvm_decode_run");
+    if (rc) return rc;
+  }
+  return KVM_OK;
 }
 
 int kvm_decode_step_static(const kvm_layer* layer, int32_t batch, kvm_decode_cache cache, kvm_tensor4 q, kvm_tensor4 k,

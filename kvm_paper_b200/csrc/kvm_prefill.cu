@@ -9,6 +9,23 @@
 
 namespace kvm {
 
+// ------------------------------------------------------------------------------------ prepared keys
+// Parallel pre-pass: prepared key (rotary dims zeroed, LayerNorm, bf16) of every token an update will
+// consume, written as [kv row][token][D].  Takes the LayerNorm off the sequential chain.
+template <int D>
+__global__ void __launch_bounds__(256)
+kvm_prepare_keys_kernel(LayerDev L, Tensor4 k, bf16* __restrict__ pk_all, long long n_tok) {
+  constexpr int GL = 8;
+  const int gl = threadIdx.x % GL;
+  const long long tkn = (long long)blockIdx.x * (256 / GL) + threadIdx.x / GL;
+  const int row = blockIdx.y;
+  const int b = row / L.Hkv, h = row % L.Hkv;
+  const bool act = tkn < n_tok;
+  RowVec<D, GL> r;
+  prepare_key_row<D, GL>(L, r, k.row(b, h, act ? tkn : 0), gl);
+  if (act) store_row<D, GL>(r, pk_all + ((size_t)row * n_tok + tkn) * D, gl);
+}
+
 // ------------------------------------------------------------------------------------------ chain
 // One CTA per kv row walks the whole prompt: initial memory, then one update per token block.  The
 // attention view of the memory is kept in a row pool with per-version index tables (see ViewStore);
@@ -17,7 +34,7 @@ template <int D, int NT, bool SB>
 __global__ void __launch_bounds__(NT, 1)
 kvm_chain_kernel(LayerDev L, long long T, Tensor4 k, Tensor4 v, Tensor4 gate, const kvm_update_plan* __restrict__ plan,
                  int n_plan, MemoryDev mem, bf16* pool_k, bf16* pool_v, long long pool_rows, int* ver_idx,
-                 long long ver_rows, bf16* pk_scr, int* route) {
+                 long long ver_rows, bf16* pk_scr, const bf16* __restrict__ pk_all, int* route) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   UpdateSmem<D> s;
   s.carve(smem_raw, L.C, mem.capacity, SB);
@@ -84,13 +101,14 @@ kvm_chain_kernel(LayerDev L, long long T, Tensor4 k, Tensor4 v, Tensor4 gate, co
       __syncthreads();
     } else {
       TokenSrc src;
-      src.k = k.row(b, h, (long long)u * C); src.k_st = k.st;
+      const long long n_tok = (long long)n_plan * C;  // tokens covered by the prepared-key pre-pass
+      src.k = pk_all + ((size_t)row * n_tok + (size_t)u * C) * D; src.k_st = D;
       src.v = v.row(b, h, (long long)u * C); src.v_st = v.st;
       src.g = gate.row(b, h, (long long)u * C); src.g_st = gate.st;
       const bool has_next = u + 1 < n_plan;
-      src.next_k = has_next ? k.row(b, h, (long long)(u + 1) * C) : nullptr;
+      src.next_k = has_next ? src.k + (size_t)C * D : nullptr;
       src.next_v = has_next ? v.row(b, h, (long long)(u + 1) * C) : nullptr;
-      memory_update<D, NT, SB>(L, src, m, view, mem.capacity, pl.state_before, pl.n_append, pk,
+      memory_update<D, NT, SB, true>(L, src, m, view, mem.capacity, pl.state_before, pl.n_append, pk,
                                route ? route + ((size_t)row * n_plan + u) * C : nullptr, s);
     }
   }
@@ -359,7 +377,7 @@ template <int D>
 static cudaError_t launch_prefill(const LayerDev& L, int batch, long long T, Tensor4 q, Tensor4 k, Tensor4 v, Tensor4 gate,
                                   const kvm_update_plan* plan_dev, int n_plan, long long ver_rows, MemoryDev mem,
                                   bf16* out, int* route, bf16* pool_k, bf16* pool_v, long long pool_rows, int* ver_idx,
-                                  bf16* pk_scr, int* status, unsigned phases, cudaStream_t stream) {
+                                  bf16* pk_scr, bf16* pk_all, int* status, unsigned phases, cudaStream_t stream) {
   constexpr int NT = 512;
   const int rows = batch * L.Hkv;
   const int n_qblocks = (int)((T + L.C - 1) / L.C);
@@ -368,11 +386,18 @@ static cudaError_t launch_prefill(const LayerDev& L, int batch, long long T, Ten
   if (phases & KVM_PREFILL_CHAIN) {
     const bool sb = update_block_fits_smem<D>(L.C, mem.capacity);
     const size_t smem_u = UpdateSmem<D>::bytes(L.C, mem.capacity, sb);
+    if (n_plan > 1) {
+      const long long n_tok = (long long)n_plan * L.C;
+      dim3 pgrid((unsigned)((n_tok + 31) / 32), rows);
+      kvm_prepare_keys_kernel<D><<<pgrid, 256, 0, stream>>>(L, k, pk_all, n_tok);
+      e = cudaGetLastError();
+      if (e != cudaSuccess) return e;
+    }
     auto kern = sb ? kvm_chain_kernel<D, NT, true> : kvm_chain_kernel<D, NT, false>;
     e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_u);
     if (e != cudaSuccess) return e;
     kern<<<rows, NT, smem_u, stream>>>(L, T, k, v, gate, plan_dev, n_plan, mem, pool_k, pool_v, pool_rows,
-                                      versions ? ver_idx : nullptr, ver_rows, pk_scr, route);
+                                      versions ? ver_idx : nullptr, ver_rows, pk_scr, pk_all, route);
     e = cudaGetLastError();
     if (e != cudaSuccess) return e;
   }
@@ -397,11 +422,11 @@ static cudaError_t launch_prefill(const LayerDev& L, int batch, long long T, Ten
 cudaError_t prefill_dispatch(int D, const LayerDev& L, int batch, long long T, Tensor4 q, Tensor4 k, Tensor4 v,
                              Tensor4 gate, const kvm_update_plan* plan_dev, int n_plan, long long ver_rows,
                              MemoryDev mem, bf16* out, int* route, bf16* pool_k, bf16* pool_v, long long pool_rows,
-                             int* ver_idx, bf16* pk_scr, int* status, unsigned phases, cudaStream_t stream) {
+                             int* ver_idx, bf16* pk_scr, bf16* pk_all, int* status, unsigned phases, cudaStream_t stream) {
   switch (D) {
-    case 32: return launch_prefill<32>(L, batch, T, q, k, v, gate, plan_dev, n_plan, ver_rows, mem, out, route, pool_k, pool_v, pool_rows, ver_idx, pk_scr, status, phases, stream);
-    case 64: return launch_prefill<64>(L, batch, T, q, k, v, gate, plan_dev, n_plan, ver_rows, mem, out, route, pool_k, pool_v, pool_rows, ver_idx, pk_scr, status, phases, stream);
-    case 128: return launch_prefill<128>(L, batch, T, q, k, v, gate, plan_dev, n_plan, ver_rows, mem, out, route, pool_k, pool_v, pool_rows, ver_idx, pk_scr, status, phases, stream);
+    case 32: return launch_prefill<32>(L, batch, T, q, k, v, gate, plan_dev, n_plan, ver_rows, mem, out, route, pool_k, pool_v, pool_rows, ver_idx, pk_scr, pk_all, status, phases, stream);
+    case 64: return launch_prefill<64>(L, batch, T, q, k, v, gate, plan_dev, n_plan, ver_rows, mem, out, route, pool_k, pool_v, pool_rows, ver_idx, pk_scr, pk_all, status, phases, stream);
+    case 128: return launch_prefill<128>(L, batch, T, q, k, v, gate, plan_dev, n_plan, ver_rows, mem, out, route, pool_k, pool_v, pool_rows, ver_idx, pk_scr, pk_all, status, phases, stream);
   }
   return cudaErrorInvalidValue;
 }

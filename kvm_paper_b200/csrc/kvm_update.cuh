@@ -285,7 +285,8 @@ struct ViewStore {
 // ([C][D] bf16 global scratch private to this block) holds the prepared keys and values are read from
 // their source.  `route_out` ([C] int32, may be null) receives the decision for every token.
 // Requires C <= NT.
-template <int D, int NT, bool SB>
+// PKR: `src.k` already holds prepared keys (a parallel pre-pass ran the LayerNorm), phase 1 is skipped.
+template <int D, int NT, bool SB, bool PKR = false>
 __device__ void memory_update(const LayerDev& L, const TokenSrc& src, const MemoryRowPtrs& mem, ViewStore& view, int capacity,
                               int S_before, int n_append, bf16* pk_scr, int* route_out, UpdateSmem<D>& s) {
   constexpr int CPR = D / 8;
@@ -340,8 +341,12 @@ __device__ void memory_update(const LayerDev& L, const TokenSrc& src, const Memo
   KVM_PHASE_MARK(0);
 
   // ---- 1. prepared keys (in place in shared memory, or into the global scratch); 8 lanes per token
+  if constexpr (PKR && !SB) {
+    blk.pk = src.k;
+    blk.pk_st = (int)src.k_st;
+  }
 #pragma unroll 2
-  for (int base = 0; base < C; base += GROUPS) {
+  for (int base = 0; base < (PKR ? 0 : C); base += GROUPS) {
     const int tkn = base + grp;
     const bool act = tkn < C;
     const int t_ = act ? tkn : 0;
@@ -391,14 +396,15 @@ __device__ void memory_update(const LayerDev& L, const TokenSrc& src, const Memo
       int p = __popc(bal & ((1u << lane) - 1u));
       for (int w = 0; w < warp; ++w) p += s.counters[4 + w];
       s.pos[tid] = p;
+      if (f) s.list[p] = tid;  // appended tokens in token order (the list is rebuilt for the merged ones later)
     }
     __syncthreads();
     // appended rows, in token order; 8 lanes per row
-    for (int base = 0; base < C; base += GROUPS) {
-      const int tkn = base + grp;
-      const bool act = tkn < C && s.flag[tkn] && (S_before + s.pos[tkn]) < capacity;
-      const int t_ = tkn < C ? tkn : 0;
-      const int row = act ? S_before + s.pos[t_] : 0;
+    for (int base = 0; base < n_append; base += GROUPS) {
+      const int p_ = base + grp;
+      const bool act = p_ < n_append && (S_before + p_) < capacity;
+      const int t_ = s.list[p_ < n_append ? p_ : 0];
+      const int row = act ? S_before + p_ : 0;
       RowVec<D, GL> kr, vr;
       load_row<D, GL>(kr, blk.pk + (size_t)t_ * blk.pk_st, gl);
       load_row<D, GL>(vr, blk.v + (long long)t_ * blk.v_st, gl);

@@ -413,6 +413,42 @@ class KvmDecodeCache:
         _lib.check(rc)
         return self.out
 
+    def run(self, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, gate: torch.Tensor) -> torch.Tensor:
+        """``n`` consecutive decode tokens with inputs already on the device (teacher-forced / synthetic
+        decoding): q [n,B,Hq,1,D], k/v [n,B,Hkv,1,D], gate [n,B,Hkv,1,1], contiguous.  Returns [n,B,Hq*D].
+        The host walks the per-sequence schedule for all n tokens first, then issues one C call."""
+        lib = _lib.load()
+        cfg, B = self.cfg, self.batch
+        n = q.size(0)
+        if q.shape != (n, B, cfg.n_q_heads, 1, cfg.head_dim) or k.shape != (n, B, cfg.n_kv_heads, 1, cfg.head_dim):
+            raise ValueError(f"run expects [n,B,H,1,D] inputs, got q {tuple(q.shape)} k {tuple(k.shape)}")
+        q, k, v, gate = (t.to(torch.bfloat16).contiguous() for t in (q, k, v, gate))
+        n_app_all = np.full((n, B), -1, dtype=np.int32)
+        any_upd = (C.c_int32 * n)()
+        max_rows = (C.c_int32 * n)()
+        for i in range(n):
+            na, mr = self._plan_step()
+            if na is not None:
+                n_app_all[i] = na
+                any_upd[i] = 1
+            max_rows[i] = min(mr, self.memory.capacity + self.ring_capacity)
+        if int(self.state_len_h.max()) > self.memory.capacity:
+            self._reserve(int(self.state_len_h.max()))
+            max_rows_bound = self.memory.capacity + self.ring_capacity
+            for i in range(n):
+                max_rows[i] = min(max_rows[i], max_rows_bound)
+        n_app_dev = torch.from_numpy(n_app_all).to(self.device)
+        out = torch.empty(n, B, cfg.n_q_heads * cfg.head_dim, device=self.device, dtype=torch.bfloat16)
+        ccache = _CCache(self.memory.c(), self.ring_k.data_ptr(), self.ring_v.data_ptr(), self.ring_gate.data_ptr(),
+                         self.total_len.data_ptr(), self.state_len.data_ptr())
+        rc = lib.kvm_decode_run(
+            C.byref(self.params.c), B, ccache, n, _tensor4(q[0], "q"), _tensor4(k[0], "k"), _tensor4(v[0], "v"),
+            _tensor4(gate[0], "gate"), q.stride(0), k.stride(0), gate.stride(0), n_app_dev.data_ptr(), any_upd, max_rows,
+            out.data_ptr(), self._ws.data_ptr(), self._ws_bytes, _stream_ptr(self.device))
+        _lib.check(rc)
+        self._keepalive = (q, k, v, gate, n_app_dev)
+        return out
+
     # -- inspection -----------------------------------------------------------------------------
     def logical_state_dict(self, b: int | None = None) -> dict[str, Any]:
         """The reference's eager cache entries (model/kvm_mixer.py:501-525).  For a batch with uniform

@@ -139,3 +139,27 @@ def test_decode_adopts_reference_eager_cache():
     assert_close_bf16(y_dev, y_ref, "decode from adopted eager cache vs oracle")
     if summary["merge_differ"] == 0 and summary["append_rows_differ"] == 0:
         assert_close_bf16(y_dev, fix["y_decode"], "decode from adopted eager cache vs reference fixture")
+
+
+def test_decode_run_equals_step_by_step():
+    """kvm_decode_run (n tokens in one C call) gives the same bits as n calls of kvm_decode_step."""
+    torch.manual_seed(9)
+    spec = ko.KvmSpec(4, 2, 64, 64, 32, 32, 2, 8, 1, "power_law", state_growth_factor=4.0, state_min_len=32)
+    B, T, n = 3, 32 * 4 + 20, 50
+    q = torch.randn(B, 4, T, 64).bfloat16()
+    k = torch.nn.functional.layer_norm(torch.randn(B, 2, T, 64), (64,)).bfloat16()
+    v = torch.randn(B, 2, T, 64).bfloat16()
+    g = (1 + torch.nn.functional.elu(torch.randn(B, 2, T, 1))).bfloat16()
+    params, plan, res = gh.device_prefill(spec, q, k, v, g)
+    mk = lambda: ops.decode_cache_from_prefill(params, res, k.cuda(), v.cuda(), g.cuda(), gh.desired_fn(spec))  # noqa: E731
+    c1, c2 = mk(), mk()
+    dq = torch.randn(n, B, 4, 1, 64).bfloat16().cuda()
+    dk = torch.nn.functional.layer_norm(torch.randn(n, B, 2, 1, 64), (64,)).bfloat16().cuda()
+    dv = torch.randn(n, B, 2, 1, 64).bfloat16().cuda()
+    dg = (1 + torch.nn.functional.elu(torch.randn(n, B, 2, 1, 1))).bfloat16().cuda()
+    want = torch.stack([c1.step(dq[i], dk[i], dv[i], dg[i]).clone().view(B, -1) for i in range(n)])
+    got = c2.run(dq, dk, dv, dg)
+    torch.cuda.synchronize()
+    assert torch.equal(got, want)
+    assert torch.equal(c1.memory.k_sum, c2.memory.k_sum) and torch.equal(c1.total_len, c2.total_len)
+    assert c1.update_count == c2.update_count and c1.update_count >= 3
