@@ -137,10 +137,9 @@ DecodeWs decode_ws(const kvm_layer* l, int batch, int max_rows) {
   const size_t rows = (size_t)batch * l->n_kv_heads;
   const size_t D = l->head_dim;
   DecodeWs w;
-  w.nsplit_max = (max_rows + kDecodeRowsPerSplit - 1) / kDecodeRowsPerSplit;
-  if (w.nsplit_max < 1) w.nsplit_max = 1;
+  w.nsplit_max = (max_rows + kDecodeRowsPerSplit - 1) / kDecodeRowsPerSplit + 2;  // memory / window / wrapped window runs
   size_t off = 0;
-  w.counters = off; off = align_up(off + (rows + batch) * 4, 256);
+  w.counters = off; off = align_up(off + (rows + batch + 1) * 4, 256);  // split counters, sequence counters, status word
   w.pk = off; off = align_up(off + rows * (size_t)l->chunk_len * D * 2, 256);
   w.gk = off; off = align_up(off + rows * (size_t)l->chunk_len * D * 2, 256);
   w.partial = off; off = align_up(off + (size_t)batch * l->n_q_heads * w.nsplit_max * (D + 2) * 4, 256);
@@ -272,6 +271,8 @@ static int decode_step_impl(const kvm_layer* layer, int32_t batch, const kvm_dec
   if (int rc = check_tensor(k, "k", D)) return rc;
   if (int rc = check_tensor(v, "v", D)) return rc;
   if (int rc = check_tensor(gate, "gate", 1)) return rc;
+  if (layer->n_q_heads / layer->n_kv_heads > 16)
+    return fail(KVM_ERR_UNSUPPORTED, "decode supports at most 16 query heads per kv head, got %d", layer->n_q_heads / layer->n_kv_heads);
   if (int rc = check_memory(cache.memory, layer)) return rc;
   if (!cache.ring_k || !cache.ring_v || !cache.ring_gate || !cache.total_len || !cache.state_len)
     return fail(KVM_ERR_BAD_ARGUMENT, "decode cache arrays must not be NULL");
@@ -347,7 +348,7 @@ int kvm_decode_step_static(const kvm_layer* layer, int32_t batch, kvm_decode_cac
   if (int rc = static_scratch_for_current_device(&scratch)) return rc;
   // the array keeps whatever the previous call left: the split counters must start at zero
   cudaError_t e = cudaMemsetAsync(static_cast<unsigned char*>(scratch) + ws.counters, 0,
-                                  ((size_t)batch * layer->n_kv_heads + batch) * sizeof(int), static_cast<cudaStream_t>(stream));
+                                  ((size_t)batch * layer->n_kv_heads + batch + 1) * sizeof(int), static_cast<cudaStream_t>(stream));
   if (e != cudaSuccess) return cuda_fail(e, "kvm_decode_step_static: cudaMemsetAsync");
   return decode_step_impl(layer, batch, cache, q, k, v, gate, n_append_dev, any_update, max_rows, out, route_dev, scratch,
                           (size_t)KVM_STATIC_SCRATCH_BYTES, stream, "kvm_decode_step_static");

@@ -7,6 +7,7 @@
 //                           sequence advances the sequence's lengths
 // Follows model/kvm_mixer.py:572-713 (eager single-token step).
 #include "kvm_update.cuh"
+#include "kvm_tc.cuh"
 
 namespace kvm {
 
@@ -86,27 +87,47 @@ kvm_decode_pre_kernel(LayerDev L, DecodeCacheDev cache, Tensor4 k, Tensor4 v, Te
 
 // ------------------------------------------------------------------------------------- attention
 constexpr int kDecThreads = 128;
+constexpr int kDecChunk = 128;  // rows per CTA
 
-// Partial result of one split: [m, l, acc[D]] in fp32.
+template <int D>
+__host__ __device__ constexpr int dec_row_stride() { return D + 8; }  // padded rows: conflict-free fragment loads
+
+__host__ __device__ inline size_t decode_attn_smem_bytes(int D, int G) {
+  return (size_t)2 * kDecChunk * (D + 8) * 2 + (size_t)4 * G * D * 4 + (size_t)2 * 4 * 16 * 4 + 16;
+}
+
+// Split-K joint attention of one new token over [memory ; window] on the tensor cores.
+// The rows of one kv row form up to three contiguous runs (memory rows, window part up to the end of the
+// ring, wrapped window part); CTA z takes one chunk of <= 128 rows of one run.  Every thread pulls one key
+// row and one value row into (padded) shared memory with bulk (TMA) copies issued before anything else:
+// 64 KB in flight per CTA at no register cost.  All query heads of the kv head (G <= 16) form the M=16
+// tile of warp-level MMAs: S = Q K^T (each warp 32 keys), softmax over the chunk, O = P V; one chunk
+// costs ~250 warp instructions per warp, so the kernel stays bandwidth-bound.
+// Partial result of one chunk and query head: [m, l, acc[D]] in fp32; the last chunk of a kv row combines.
 template <int D>
 __global__ void __launch_bounds__(kDecThreads)
 kvm_decode_attn_kernel(LayerDev L, DecodeCacheDev cache, Tensor4 q, const int* __restrict__ n_append_arr,
-                       int rows_per_split, float* __restrict__ partial, int* __restrict__ counters,
-                       bf16* __restrict__ out, float sm_scale) {
-  constexpr int LPR = D / 8;              // lanes per row (16 bytes each)
-  constexpr int RG = kDecThreads / LPR;   // rows in flight per pass
-  extern __shared__ __align__(16) unsigned char smem_raw[];
-  float* sc = reinterpret_cast<float*>(smem_raw);   // [rows_per_split]
-  float* red = sc + rows_per_split;                 // [RG][D]
-  __shared__ float s_red[kDecThreads / 32];
+                       float* __restrict__ partial, int* __restrict__ counters, bf16* __restrict__ out, float sm_scale,
+                       int* __restrict__ status) {
+  constexpr int STR = dec_row_stride<D>();
+  constexpr int KS = D / 16;   // k-steps of Q K^T
+  constexpr int DT8 = D / 8;   // n8 tiles of the output
+  extern __shared__ __align__(128) unsigned char smem_raw[];
+  const int G = L.Hq / L.Hkv;
+  bf16* sK = reinterpret_cast<bf16*>(smem_raw);                    // [kDecChunk][STR]
+  bf16* sV = sK + (size_t)kDecChunk * STR;                          // [kDecChunk][STR]
+  float* ored = reinterpret_cast<float*>(sV + (size_t)kDecChunk * STR);  // [4 warps][G][D]
+  float* wmax = ored + (size_t)4 * G * D;                           // [4][16]
+  float* wsum = wmax + 64;                                          // [4][16]
+  uint64_t* bar = reinterpret_cast<uint64_t*>(wsum + 64);
   __shared__ int s_last;
 
   const int z = blockIdx.x, nsplit = gridDim.x;
   const int row = blockIdx.y;
   const int b = row / L.Hkv, hkv = row % L.Hkv;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int rgi = tid / LPR, li = tid % LPR;
-  const int C = L.C, WC = L.W * L.C, G = L.Hq / L.Hkv;
+  const int g = lane >> 2, t = lane & 3;
+  const int C = L.C, WC = L.W * L.C;
   const int cap = cache.mem.capacity;
 
   const int past = cache.total_len[b];
@@ -116,109 +137,172 @@ kvm_decode_attn_kernel(LayerDev L, DecodeCacheDev cache, Tensor4 q, const int* _
   const int total = past + 1;
   const int new_begin = bswa_begin_dev(total, C, L.W);
   const int S_act = new_begin > 0 ? S : 0;
-  const int n_rows = S_act + (total - new_begin);
-  const int r_begin = z * rows_per_split;
-  const int r_end = min(n_rows, r_begin + rows_per_split);
+  // runs: memory [0,S_act), window part A (ring slots slot0..), window part B (ring slots 0..)
+  const int n_win = total - new_begin;
+  const int slot0 = new_begin % WC;
+  const int len_a = min(n_win, WC - slot0), len_b = n_win - len_a;
+  const int c_mem = (S_act + kDecChunk - 1) / kDecChunk, c_a = (len_a + kDecChunk - 1) / kDecChunk;
+  const int c_b = (len_b + kDecChunk - 1) / kDecChunk;
+  int n = 0;
+  bool is_mem = false;
+  const bf16* src_k = nullptr;
+  const bf16* src_v = nullptr;
+  if (z < c_mem) {
+    const int r0 = z * kDecChunk;
+    n = min(kDecChunk, S_act - r0);
+    is_mem = true;
+    src_k = cache.mem.k_attn + ((size_t)row * cap + r0) * D;
+    src_v = cache.mem.v_attn + ((size_t)row * cap + r0) * D;
+  } else if (z < c_mem + c_a) {
+    const int r0 = (z - c_mem) * kDecChunk;
+    n = min(kDecChunk, len_a - r0);
+    src_k = cache.ring_k + ((size_t)row * WC + slot0 + r0) * D;
+    src_v = cache.ring_v + ((size_t)row * WC + slot0 + r0) * D;
+  } else if (z < c_mem + c_a + c_b) {
+    const int r0 = (z - c_mem - c_a) * kDecChunk;
+    n = min(kDecChunk, len_b - r0);
+    src_k = cache.ring_k + ((size_t)row * WC + r0) * D;
+    src_v = cache.ring_v + ((size_t)row * WC + r0) * D;
+  }
+  if (tid == 0) {
+    tc::mbar_init(bar, 1);
+    tc::fence_barrier_init();
+  }
+  __syncthreads();
+  if (n > 0) {
+    if (tid == 0) tc::mbar_arrive_expect_tx(bar, (uint32_t)(2 * n * D * 2));
+    if (tid < n) {  // one key row and one value row per thread
+      tc::bulk_g2s(sK + (size_t)tid * STR, src_k + (size_t)tid * D, D * 2, bar);
+      tc::bulk_g2s(sV + (size_t)tid * STR, src_v + (size_t)tid * D, D * 2, bar);
+    } else {        // rows past the run: zeros (their scores are masked, their values must be finite)
+      for (int c = 0; c < D / 8; ++c) {
+        *reinterpret_cast<uint4*>(sK + (size_t)tid * STR + c * 8) = make_uint4(0, 0, 0, 0);
+        *reinterpret_cast<uint4*>(sV + (size_t)tid * STR + c * 8) = make_uint4(0, 0, 0, 0);
+      }
+    }
+  }
+  // query fragments of the kv head's G query heads (rows g and g+8 of the M=16 tile), per-row scales
+  uint32_t qa[KS][4];
+  float scl[2];
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    const int qh = g + r * 8;
+    const bool okq = qh < G;
+    const int hq = hkv * G + (okq ? qh : 0);
+    scl[r] = sm_scale * (is_mem ? L.state_temp[hq] : L.front_temp[hq]) * kLog2e;
+    const bf16* qp = q.row(b, hq, 0) + t * 2;
+#pragma unroll
+    for (int ks = 0; ks < KS; ++ks) {
+      qa[ks][r] = okq ? *reinterpret_cast<const uint32_t*>(qp + ks * 16) : 0u;
+      qa[ks][2 + r] = okq ? *reinterpret_cast<const uint32_t*>(qp + ks * 16 + 8) : 0u;
+    }
+  }
+  bool ok = true;
+  if (n > 0) {
+    ok = tc::mbar_wait(bar, 0);
+    if (!ok && tid == 0) atomicExch(status, KVM_ERR_DEVICE_TIMEOUT);
+  }
+  __syncthreads();  // zero-filled rows visible
 
-  const bf16* mk = cache.mem.k_attn + (size_t)row * cap * D;
-  const bf16* mv = cache.mem.v_attn + (size_t)row * cap * D;
-  const bf16* rk = cache.ring_k + (size_t)row * WC * D;
-  const bf16* rv = cache.ring_v + (size_t)row * WC * D;
-
-  auto krow = [&](int r) -> const bf16* {
-    return r < S_act ? mk + (size_t)r * D : rk + (size_t)((new_begin + (r - S_act)) % WC) * D;
-  };
-  auto vrow = [&](int r) -> const bf16* {
-    return r < S_act ? mv + (size_t)r * D : rv + (size_t)((new_begin + (r - S_act)) % WC) * D;
-  };
-
+  float m_row[2] = {-INFINITY, -INFINITY}, l_row[2] = {0.f, 0.f};
+  float o[DT8][4];
+#pragma unroll
+  for (int i = 0; i < DT8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+  float sacc[4][4];
+  if (n > 0 && ok) {
+    // S = Q K^T for this warp's 32 keys
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      sacc[j][0] = sacc[j][1] = sacc[j][2] = sacc[j][3] = 0.f;
+      const bf16* brow = sK + (size_t)(warp * 32 + j * 8 + g) * STR + t * 2;
+#pragma unroll
+      for (int ks = 0; ks < KS; ++ks) {
+        const uint32_t b0 = *reinterpret_cast<const uint32_t*>(brow + ks * 16);
+        const uint32_t b1 = *reinterpret_cast<const uint32_t*>(brow + ks * 16 + 8);
+        mma_bf16_16816(sacc[j], qa[ks], b0, b1);
+      }
+    }
+    float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int key = warp * 32 + j * 8 + t * 2 + (e & 1);
+        const float x = key < n ? sacc[j][e] * scl[e >> 1] : -INFINITY;
+        sacc[j][e] = x;
+        mx[e >> 1] = fmaxf(mx[e >> 1], x);
+      }
+    }
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+      mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
+      mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
+      if (t == 0) wmax[warp * 16 + g + r * 8] = mx[r];
+    }
+  } else if (t == 0) {
+    wmax[warp * 16 + g] = -INFINITY;
+    wmax[warp * 16 + g + 8] = -INFINITY;
+  }
+  __syncthreads();
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    const int rr = g + r * 8;
+    m_row[r] = fmaxf(fmaxf(wmax[rr], wmax[16 + rr]), fmaxf(wmax[32 + rr], wmax[48 + rr]));
+  }
+  if (n > 0 && ok) {
+    // P = exp2(S - m) and O = P V for this warp's keys
+    const float mu0 = m_row[0] == -INFINITY ? 0.f : m_row[0];
+    const float mu1 = m_row[1] == -INFINITY ? 0.f : m_row[1];
+    uint32_t pa[2][4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float p0 = exp2f(sacc[j][0] - mu0), p1 = exp2f(sacc[j][1] - mu0);
+      const float p2 = exp2f(sacc[j][2] - mu1), p3 = exp2f(sacc[j][3] - mu1);
+      l_row[0] += p0 + p1;
+      l_row[1] += p2 + p3;
+      pa[j >> 1][(j & 1) * 2 + 0] = pack_bf16(p0, p1);
+      pa[j >> 1][(j & 1) * 2 + 1] = pack_bf16(p2, p3);
+    }
+#pragma unroll
+    for (int kk = 0; kk < 2; ++kk) {
+#pragma unroll
+      for (int dp = 0; dp < DT8 / 2; ++dp) {
+        uint32_t vb[4];
+        const bf16* vrow = sV + (size_t)(warp * 32 + kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * STR + dp * 16 + (lane >> 4) * 8;
+        ldmatrix_x4_trans(vb, vrow);
+        mma_bf16_16816(o[dp * 2 + 0], pa[kk], vb[0], vb[1]);
+        mma_bf16_16816(o[dp * 2 + 1], pa[kk], vb[2], vb[3]);
+      }
+    }
+  }
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    l_row[r] += __shfl_xor_sync(0xffffffffu, l_row[r], 1);
+    l_row[r] += __shfl_xor_sync(0xffffffffu, l_row[r], 2);
+    if (t == 0) wsum[warp * 16 + g + r * 8] = l_row[r];
+  }
+  // this warp's partial output rows of the real query heads -> shared memory
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    const int qh = g + r * 8;
+    if (qh < G) {
+      float* dst = ored + ((size_t)warp * G + qh) * D + t * 2;
+#pragma unroll
+      for (int i = 0; i < DT8; ++i) *reinterpret_cast<float2*>(dst + i * 8) = make_float2(o[i][r * 2], o[i][r * 2 + 1]);
+    }
+  }
+  __syncthreads();
   for (int gq = 0; gq < G; ++gq) {
     const int hq = hkv * G + gq;
-    const float sc_mem = sm_scale * L.state_temp[hq] * kLog2e;
-    const float sc_win = sm_scale * L.front_temp[hq] * kLog2e;
-    float qf[8];
-    {
-      const uint4 u = *reinterpret_cast<const uint4*>(q.row(b, hq, 0) + li * 8);
-      float2 a = unpack_bf16(u.x), c = unpack_bf16(u.y), d = unpack_bf16(u.z), e = unpack_bf16(u.w);
-      qf[0] = a.x; qf[1] = a.y; qf[2] = c.x; qf[3] = c.y; qf[4] = d.x; qf[5] = d.y; qf[6] = e.x; qf[7] = e.y;
-    }
-    // pass 1: scores
-    float mloc = -INFINITY;
-    for (int base = r_begin; base < r_end; base += 4 * RG) {  // trip count uniform over the block
-      const int r0 = base + rgi;
-      uint4 kv[4];
-#pragma unroll
-      for (int u = 0; u < 4; ++u) {
-        const int r = r0 + u * RG;
-        kv[u] = r < r_end ? *reinterpret_cast<const uint4*>(krow(r) + li * 8) : make_uint4(0, 0, 0, 0);
-      }
-#pragma unroll
-      for (int u = 0; u < 4; ++u) {
-        const int r = r0 + u * RG;
-        float2 a = unpack_bf16(kv[u].x), c = unpack_bf16(kv[u].y), d = unpack_bf16(kv[u].z), e = unpack_bf16(kv[u].w);
-        float dot = qf[0] * a.x + qf[1] * a.y + qf[2] * c.x + qf[3] * c.y + qf[4] * d.x + qf[5] * d.y + qf[6] * e.x + qf[7] * e.y;
-#pragma unroll
-        for (int off = LPR / 2; off > 0; off >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, off);
-        if (r < r_end) {
-          const float x = dot * (r < S_act ? sc_mem : sc_win);
-          if (li == 0) sc[r - r_begin] = x;
-          mloc = fmaxf(mloc, x);
-        }
-      }
-    }
-    mloc = warp_max(mloc);
-    if (lane == 0) s_red[warp] = mloc;
-    __syncthreads();
-    float mblk = s_red[0];
-#pragma unroll
-    for (int w = 1; w < kDecThreads / 32; ++w) mblk = fmaxf(mblk, s_red[w]);
-    const float m_use = mblk == -INFINITY ? 0.f : mblk;
-    // pass 2: probabilities and P.V
-    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-    float lsum = 0.f;
-    for (int base = r_begin; base < r_end; base += 4 * RG) {
-      const int r0 = base + rgi;
-      uint4 vv[4];
-#pragma unroll
-      for (int u = 0; u < 4; ++u) {
-        const int r = r0 + u * RG;
-        vv[u] = r < r_end ? *reinterpret_cast<const uint4*>(vrow(r) + li * 8) : make_uint4(0, 0, 0, 0);
-      }
-#pragma unroll
-      for (int u = 0; u < 4; ++u) {
-        const int r = r0 + u * RG;
-        if (r < r_end) {
-          const float p = exp2f(sc[r - r_begin] - m_use);
-          lsum += p;
-          float2 a = unpack_bf16(vv[u].x), c = unpack_bf16(vv[u].y), d = unpack_bf16(vv[u].z), e = unpack_bf16(vv[u].w);
-          acc[0] += p * a.x; acc[1] += p * a.y; acc[2] += p * c.x; acc[3] += p * c.y;
-          acc[4] += p * d.x; acc[5] += p * d.y; acc[6] += p * e.x; acc[7] += p * e.y;
-        }
-      }
-    }
-#pragma unroll
-    for (int i = 0; i < 8; ++i) red[rgi * D + li * 8 + i] = acc[i];
-    // every lane of a row group added the same p: keep one copy per row group
-    if (li != 0) lsum = 0.f;
-    lsum = warp_sum(lsum);
-    __syncthreads();  // red[] complete; s_red (max) consumed by everyone
-    if (lane == 0) s_red[warp] = lsum;
-    __syncthreads();
     float* pout = partial + ((size_t)(b * L.Hq + hq) * nsplit + z) * (D + 2);
     if (tid < D) {
-      float a = 0.f;
-#pragma unroll 4
-      for (int rg = 0; rg < RG; ++rg) a += red[rg * D + tid];
-      pout[2 + tid] = a;
+      const float* src = ored + (size_t)gq * D + tid;
+      pout[2 + tid] = src[0] + src[(size_t)G * D] + src[(size_t)2 * G * D] + src[(size_t)3 * G * D];
     }
     if (tid == 0) {
-      float l = 0.f;
-#pragma unroll
-      for (int w = 0; w < kDecThreads / 32; ++w) l += s_red[w];
-      pout[0] = mblk;
-      pout[1] = l;
+      pout[0] = fmaxf(fmaxf(wmax[gq], wmax[16 + gq]), fmaxf(wmax[32 + gq], wmax[48 + gq]));
+      pout[1] = wsum[gq] + wsum[16 + gq] + wsum[32 + gq] + wsum[48 + gq];
     }
-    __syncthreads();
   }
 
   // ---- the last split of this kv row combines; the last kv row of the sequence advances lengths
@@ -294,13 +378,17 @@ static cudaError_t launch_decode(const LayerDev& L, int batch, const DecodeCache
   }
   e = cudaGetLastError();
   if (e != cudaSuccess) return e;
-  const int nsplit = (max_rows + rows_per_split - 1) / rows_per_split;
-  constexpr int RG = kDecThreads / (D / 8);
-  const size_t smem_a = (size_t)rows_per_split * 4 + (size_t)RG * D * 4;
-  dim3 grid(nsplit > 0 ? nsplit : 1, rows);
-  kvm_decode_attn_kernel<D><<<grid, kDecThreads, smem_a, stream>>>(L, cache, q, any_update ? n_append : nullptr,
-                                                                  rows_per_split, partial, counters, out,
-                                                                  1.0f / sqrtf((float)D));
+  // up to three runs of rows per kv row (memory, window, wrapped window): two chunks more than the row count needs
+  const int nsplit = (max_rows + kDecChunk - 1) / kDecChunk + 2;
+  (void)rows_per_split;
+  if (L.Hq / L.Hkv > 16) return cudaErrorInvalidValue;  // the query heads of a kv head form one M=16 MMA tile
+  const size_t smem_a = decode_attn_smem_bytes(D, L.Hq / L.Hkv);
+  e = cudaFuncSetAttribute(kvm_decode_attn_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_a);
+  if (e != cudaSuccess) return e;
+  dim3 grid(nsplit, rows);
+  kvm_decode_attn_kernel<D><<<grid, kDecThreads, smem_a, stream>>>(L, cache, q, any_update ? n_append : nullptr, partial,
+                                                                  counters, out, 1.0f / sqrtf((float)D),
+                                                                  counters + rows + batch);
   return cudaGetLastError();
 }
 
