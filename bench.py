@@ -205,13 +205,11 @@ def run_b200(args):
     plan = mixer.make_prefill_plan(T)
     params = mixer.layer_params(dev)
     runner = ops.PrefillRunner(params, B, plan)
-    gathered = torch.empty(world, B, T, h_loc * D, device=dev, dtype=torch.bfloat16) if world > 1 else None
+    from kvm_paper_b200 import sharding
 
     def step():
         out = runner.run(q, k, v, gate)
-        if world > 1:
-            dist.all_gather_into_tensor(gathered, out)
-        return out
+        return sharding.gather_heads(out, world)  # [B,T,H*D] on every rank (NCCL all-gather + head-order permute)
 
     def barrier():
         if world > 1:
@@ -296,7 +294,7 @@ def run_b200(args):
                "h2d_bytes_per_step": h2d * world, "d2h_bytes_per_step": h_out.numel() * 2 * world}
         del hq, hk, hv, hg, dq, dk, dv, dg, h_out
 
-    del runner, q, k, v, gate, gathered
+    del runner, q, k, v, gate
     torch.cuda.empty_cache()
     decode = None if args.no_decode else run_decode(args, dev, rank, world, peaks)
 
@@ -373,7 +371,7 @@ def run_decode(args, dev, rank, world, peaks):
     k = torch.nn.functional.layer_norm(torch.randn(steps, n_loc, H, 1, D, generator=gen, device=dev), (D,)).bfloat16()
     v = torch.randn(steps, n_loc, H, 1, D, generator=gen, device=dev).bfloat16()
     g = (1 + torch.nn.functional.elu(torch.randn(steps, n_loc, H, 1, 1, generator=gen, device=dev))).bfloat16()
-    gathered = torch.empty(world, steps, n_loc, H * D, device=dev, dtype=torch.bfloat16) if world > 1 else None
+    from kvm_paper_b200 import sharding
     # algorithmic bytes of the timed steps: memory + window rows of every sequence, K and V, bf16
     tl, sl = cache.total_len_h.copy(), cache.state_len_h.copy()
     snap = (cache.memory.k_sum.clone(), cache.memory.v_sum.clone(), cache.memory.vlen.clone(), cache.memory.k_attn.clone(),
@@ -406,9 +404,7 @@ def run_decode(args, dev, rank, world, peaks):
 
     def run_all():
         out = cache.run(q, k, v, g)       # one C call: two kernel launches per token
-        if world > 1:
-            dist.all_gather_into_tensor(gathered, out)
-        return out
+        return sharding.gather_sequences(out, world, seq_dim=1)  # [steps, all sequences, H*D]
 
     run_all()  # warm-up pass over the whole trajectory
     restore()

@@ -1,0 +1,62 @@
+"""Sharding of the KVM mixer over the GPUs of one node: heads for prefill, sequences for decode.
+
+Every (batch, kv-head) pair owns an independent memory and window, so no term of the mixer crosses heads
+or sequences: each rank runs the kernels on its slice and the only collective is one all-gather of the
+mixer outputs (NCCL over NVLink on GPUs, gloo on CPU ranks in the tests).  The reference has no
+counterpart (it is data-parallel only).
+"""
+
+from __future__ import annotations
+
+import torch
+import torch.distributed as dist
+
+
+def head_shard(n_q_heads: int, n_kv_heads: int, rank: int, world: int) -> tuple[slice, slice]:
+    """Contiguous slice of query heads and of kv heads owned by ``rank`` (GQA groups stay whole)."""
+    if n_q_heads % n_kv_heads:
+        raise ValueError("n_q_heads must be a multiple of n_kv_heads")
+    if n_kv_heads % world:
+        raise ValueError(f"{n_kv_heads} kv heads cannot be split over {world} ranks")
+    if not 0 <= rank < world:
+        raise ValueError(f"rank {rank} outside [0, {world})")
+    kv = n_kv_heads // world
+    g = n_q_heads // n_kv_heads
+    return slice(rank * kv * g, (rank + 1) * kv * g), slice(rank * kv, (rank + 1) * kv)
+
+
+def shard_heads(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, gate: torch.Tensor, rank: int, world: int):
+    """Views of the post-QKV tensors ([B,H,T,D] layout) for this rank's heads."""
+    qs, kvs = head_shard(q.size(1), k.size(1), rank, world)
+    return q[:, qs], k[:, kvs], v[:, kvs], gate[:, kvs]
+
+
+def gather_heads(out_local: torch.Tensor, world: int, group=None) -> torch.Tensor:
+    """[B,T,h_loc*D] per rank -> [B,T,H*D] on every rank, heads in rank order (the single-rank layout)."""
+    if world == 1:
+        return out_local
+    out_local = out_local.contiguous()
+    B, T, hd = out_local.shape
+    buf = torch.empty((world * B, T, hd), device=out_local.device, dtype=out_local.dtype)  # rank-major concatenation
+    dist.all_gather_into_tensor(buf, out_local, group=group)
+    return buf.view(world, B, T, hd).permute(1, 2, 0, 3).reshape(B, T, world * hd)
+
+
+def sequence_shard(n_seq: int, rank: int, world: int) -> slice:
+    """Contiguous slice of sequences owned by ``rank`` (decode)."""
+    if n_seq % world:
+        raise ValueError(f"{n_seq} sequences cannot be split evenly over {world} ranks")
+    if not 0 <= rank < world:
+        raise ValueError(f"rank {rank} outside [0, {world})")
+    per = n_seq // world
+    return slice(rank * per, (rank + 1) * per)
+
+
+def gather_sequences(out_local: torch.Tensor, world: int, seq_dim: int = 0, group=None) -> torch.Tensor:
+    """Per-rank decode outputs with the local sequences on ``seq_dim`` -> all sequences in rank order."""
+    if world == 1:
+        return out_local
+    x = out_local.movedim(seq_dim, 0).contiguous()
+    full = torch.empty((world * x.size(0),) + tuple(x.shape[1:]), device=x.device, dtype=x.dtype)
+    dist.all_gather_into_tensor(full, x, group=group)
+    return full.movedim(0, seq_dim)
