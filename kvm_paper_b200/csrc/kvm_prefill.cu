@@ -34,11 +34,12 @@ template <int D, int NT, bool SB>
 __global__ void __launch_bounds__(NT, 1)
 kvm_chain_kernel(LayerDev L, long long T, Tensor4 k, Tensor4 v, Tensor4 gate, const kvm_update_plan* __restrict__ plan,
                  int n_plan, MemoryDev mem, bf16* pool_k, bf16* pool_v, long long pool_rows, int* ver_idx,
-                 long long ver_rows, bf16* pk_scr, const bf16* __restrict__ pk_all, int* route) {
+                 long long ver_rows, bf16* pk_scr, const bf16* __restrict__ pk_all, int* route, int nc) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   UpdateSmem<D> s;
   s.carve(smem_raw, L.C, mem.capacity, SB);
-  const int row = blockIdx.x;
+  const int row = blockIdx.x / nc;     // the nc CTAs of a cluster share one kv row
+  const int crank = blockIdx.x % nc;
   const int b = row / L.Hkv, h = row % L.Hkv;
   const int tid = threadIdx.x;
   const int C = L.C;
@@ -83,22 +84,23 @@ kvm_chain_kernel(LayerDev L, long long T, Tensor4 k, Tensor4 v, Tensor4 gate, co
             vr.x[i] = bf16_round(vr.x[i] * gt);
           }
         }
-        if (act) {
+        const bool mine = act && (t_ % nc == crank);
+        if (mine) {
           store_row<D, GL>(kr, m.k_sum + (size_t)t_ * D, gl);
           store_row<D, GL>(vr, m.v_sum + (size_t)t_ * D, gl);
-          if (gl == 0) {
-            m.vlen[t_] = vl;
-            if (pool) s.cur[t_] = t_;
-          }
+          if (gl == 0) m.vlen[t_] = vl;
         }
-        refresh_memory_row<D, GL>(L, kr, vr, vl, view.k + (size_t)t_ * D, view.v + (size_t)t_ * D, gl, act);
+        refresh_memory_row<D, GL>(L, kr, vr, vl, view.k + (size_t)t_ * D, view.v + (size_t)t_ * D, gl, mine);
       }
+      if (pool)
+        for (int i = tid; i < n0; i += NT) s.cur[i] = i;
       view.pool_next = n0;
-      if (route)
+      if (route && crank == 0)
         for (int i = tid; i < C; i += NT) route[((size_t)row * n_plan) * C + i] = i < n0 ? -(1 + i) : 0;
-      if (view.ver_idx)
+      if (view.ver_idx && crank == 0)
         for (int i = tid; i < n0; i += NT) view.ver_idx[i] = i;
       __syncthreads();
+      if (nc > 1) cluster_sync_all();
     } else {
       TokenSrc src;
       const long long n_tok = (long long)n_plan * C;  // tokens covered by the prepared-key pre-pass
@@ -109,7 +111,7 @@ kvm_chain_kernel(LayerDev L, long long T, Tensor4 k, Tensor4 v, Tensor4 gate, co
       src.next_k = has_next ? src.k + (size_t)C * D : nullptr;
       src.next_v = has_next ? v.row(b, h, (long long)(u + 1) * C) : nullptr;
       memory_update<D, NT, SB, true>(L, src, m, view, mem.capacity, pl.state_before, pl.n_append, pk,
-                               route ? route + ((size_t)row * n_plan + u) * C : nullptr, s);
+                               route ? route + ((size_t)row * n_plan + u) * C : nullptr, s, nc, crank);
     }
   }
   if (pool) {
@@ -117,7 +119,7 @@ kvm_chain_kernel(LayerDev L, long long T, Tensor4 k, Tensor4 v, Tensor4 gate, co
     const kvm_update_plan pl = plan[n_plan - 1];
     const int S = pl.state_before + pl.n_append;
     constexpr int CPR = D / 8;
-    for (int c = tid; c < S * CPR; c += NT) {
+    for (int c = tid + crank * NT; c < S * CPR; c += NT * nc) {
       const int r = c / CPR, cc = c % CPR;
       const size_t src_off = (size_t)s.cur[r] * D + cc * 8;
       *reinterpret_cast<uint4*>(m.k_attn + (size_t)r * D + cc * 8) = *reinterpret_cast<const uint4*>(view.k + src_off);
@@ -396,9 +398,27 @@ static cudaError_t launch_prefill(const LayerDev& L, int batch, long long T, Ten
     auto kern = sb ? kvm_chain_kernel<D, NT, true> : kvm_chain_kernel<D, NT, false>;
     e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_u);
     if (e != cudaSuccess) return e;
-    kern<<<rows, NT, smem_u, stream>>>(L, T, k, v, gate, plan_dev, n_plan, mem, pool_k, pool_v, pool_rows,
-                                      versions ? ver_idx : nullptr, ver_rows, pk_scr, pk_all, route);
-    e = cudaGetLastError();
+    // a cluster of CTAs per kv row when the GPU has more SMs than rows (the chain is latency-bound per row)
+    int dev = 0, n_sm = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, dev);
+    int nc = 1;
+    while (nc * 2 <= kMaxCluster && rows * nc * 2 <= n_sm && n_plan > 1) nc *= 2;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(rows * nc);
+    cfg.blockDim = dim3(NT);
+    cfg.dynamicSmemBytes = smem_u;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = nc;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    int* ver_arg = versions ? ver_idx : nullptr;
+    e = cudaLaunchKernelEx(&cfg, kern, L, T, k, v, gate, plan_dev, n_plan, mem, pool_k, pool_v, pool_rows, ver_arg, ver_rows,
+                           pk_scr, (const bf16*)pk_all, route, nc);
     if (e != cudaSuccess) return e;
   }
   if (!(phases & KVM_PREFILL_ATTENTION)) return cudaSuccess;

@@ -91,7 +91,10 @@ struct UpdateSmem {
   int* touched;  // [C] leading tokens, one per row that received tokens
   int* cur;      // [capacity] pool slot holding the attention view of each memory row (pool mode)
   int* counters; // [4 + 32]
-  static constexpr int kTokenArrays = 13;
+  float* xapp;   // [kMaxCluster][C] partial novelty maxima of the CTAs of a cluster
+  float* xbest;  // [kMaxCluster][C] partial best logits
+  int* xidx;     // [kMaxCluster][C] partial best rows
+  static constexpr int kTokenArrays = 13 + 3 * 4;
   __host__ __device__ static size_t bytes(int C, int capacity, bool sb) {
     size_t b = (size_t)2 * kScanTile * scan_tile_stride<D>() * sizeof(bf16);
     if (sb) b += (size_t)C * (D + 8) * sizeof(bf16) + (size_t)C * D * sizeof(bf16);
@@ -108,13 +111,16 @@ struct UpdateSmem {
       pk_s = reinterpret_cast<bf16*>(base); base += (size_t)C * (D + 8) * sizeof(bf16);
       v_s = reinterpret_cast<bf16*>(base); base += (size_t)C * D * sizeof(bf16);
     }
-    int** arr[kTokenArrays] = {reinterpret_cast<int**>(&g_s), reinterpret_cast<int**>(&app), reinterpret_cast<int**>(&best),
+    int** arr[13] = {reinterpret_cast<int**>(&g_s), reinterpret_cast<int**>(&app), reinterpret_cast<int**>(&best),
                                &idx, &pos, &flag, &ord, &lead, &tcnt, &tstart, &list, &touched, nullptr};
-    for (int i = 0; i < kTokenArrays - 1; ++i) {
+    for (int i = 0; i < 12; ++i) {
       *arr[i] = reinterpret_cast<int*>(base);
       base += (size_t)C * 4;
     }
     base += (size_t)C * 4;  // spare
+    xapp = reinterpret_cast<float*>(base); base += (size_t)4 * C * 4;
+    xbest = reinterpret_cast<float*>(base); base += (size_t)4 * C * 4;
+    xidx = reinterpret_cast<int*>(base); base += (size_t)4 * C * 4;
     cur = reinterpret_cast<int*>(base); base += (size_t)((capacity + 3) / 4 * 4) * 4;
     counters = reinterpret_cast<int*>(base);
   }
@@ -125,6 +131,25 @@ constexpr size_t kSmemLimit = 227 * 1024;
 template <int D>
 __host__ __device__ inline bool update_block_fits_smem(int C, int capacity) {
   return UpdateSmem<D>::bytes(C, capacity, true) <= kSmemLimit;
+}
+
+// A cluster of up to kMaxCluster CTAs may share one kv row: the memory rows of the routing scan and the
+// touched rows of the scatter are split between them, partial routing results are exchanged through
+// distributed shared memory, everything else is computed redundantly (it is deterministic).
+constexpr int kMaxCluster = 4;
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ uint32_t peer_smem_addr(const void* local, int peer) {
+  uint32_t a = (uint32_t)__cvta_generic_to_shared(local), r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(peer));
+  return r;
+}
+__device__ __forceinline__ void st_peer_f32(uint32_t addr, float v) {
+  asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(addr), "f"(v) : "memory");
+}
+__device__ __forceinline__ void st_peer_s32(uint32_t addr, int v) {
+  asm volatile("st.shared::cluster.s32 [%0], %1;" ::"r"(addr), "r"(v) : "memory");
 }
 
 __device__ __forceinline__ uint32_t mul_bf16x2(uint32_t a, __nv_bfloat162 g2) {
@@ -288,7 +313,8 @@ struct ViewStore {
 // PKR: `src.k` already holds prepared keys (a parallel pre-pass ran the LayerNorm), phase 1 is skipped.
 template <int D, int NT, bool SB, bool PKR = false>
 __device__ void memory_update(const LayerDev& L, const TokenSrc& src, const MemoryRowPtrs& mem, ViewStore& view, int capacity,
-                              int S_before, int n_append, bf16* pk_scr, int* route_out, UpdateSmem<D>& s) {
+                              int S_before, int n_append, bf16* pk_scr, int* route_out, UpdateSmem<D>& s, int nc = 1,
+                              int crank = 0) {
   constexpr int CPR = D / 8;
   constexpr int PST = D + 8;
   constexpr int GL = 8;                 // lanes per row in the row-parallel phases
@@ -365,8 +391,35 @@ __device__ void memory_update(const LayerDev& L, const TokenSrc& src, const Memo
   const int protected_rows = min(L.sink_len, S_after);
 
   // ---- 2. scores against the old memory, append selection
-  if (n_merge > 0)
-    scan_memory<D, NT>(blk, L.gate_keys != 0, C, view.k, view.cur, 0, S_before, n_append > 0, protected_rows, s);
+  if (n_merge > 0) {
+    // this CTA scans the tiles [crank, crank+1) * n_tiles / nc of the old memory
+    const int n_tiles_all = (S_before + kScanTile - 1) / kScanTile;
+    const int nb = min(S_before, (crank * n_tiles_all / nc) * kScanTile);
+    const int ne = min(S_before, ((crank + 1) * n_tiles_all / nc) * kScanTile);
+    scan_memory<D, NT>(blk, L.gate_keys != 0, C, view.k, view.cur, nb, ne, n_append > 0, protected_rows, s);
+    if (nc > 1) {
+      // all-gather of the partial results through distributed shared memory, then a local combine
+      for (int i = tid; i < C * nc; i += NT) {
+        const int peer = i / C, tkn = i % C;
+        st_peer_f32(peer_smem_addr(s.xapp + crank * C + tkn, peer), s.app[tkn]);
+        st_peer_f32(peer_smem_addr(s.xbest + crank * C + tkn, peer), s.best[tkn]);
+        st_peer_s32(peer_smem_addr(s.xidx + crank * C + tkn, peer), s.idx[tkn]);
+      }
+      cluster_sync_all();
+      for (int i = tid; i < C; i += NT) {
+        float a = -INFINITY, bb = -INFINITY;
+        int bi = -1;
+        for (int c = 0; c < nc; ++c) {  // ranks hold increasing row ranges: strict > keeps the lowest row on ties
+          a = fmaxf(a, s.xapp[c * C + i]);
+          const int ci = s.xidx[c * C + i];
+          const float cb = s.xbest[c * C + i];
+          if (ci >= 0 && (bi < 0 || cb > bb)) { bb = cb; bi = ci; }
+        }
+        s.app[i] = a; s.best[i] = bb; s.idx[i] = bi;
+      }
+      __syncthreads();
+    }
+  }
   KVM_PHASE_MARK(2);
   if (n_append > 0 && n_merge > 0) {
     if (tid < C) {
@@ -402,7 +455,7 @@ __device__ void memory_update(const LayerDev& L, const TokenSrc& src, const Memo
     // appended rows, in token order; 8 lanes per row
     for (int base = 0; base < n_append; base += GROUPS) {
       const int p_ = base + grp;
-      const bool act = p_ < n_append && (S_before + p_) < capacity;
+      const bool act = p_ < n_append && (S_before + p_) < capacity && (p_ % nc == crank);
       const int t_ = s.list[p_ < n_append ? p_ : 0];
       const int row = act ? S_before + p_ : 0;
       RowVec<D, GL> kr, vr;
@@ -421,22 +474,24 @@ __device__ void memory_update(const LayerDev& L, const TokenSrc& src, const Memo
       if (act) {
         store_row<D, GL>(kr, mem.k_sum + (size_t)row * D, gl);
         store_row<D, GL>(vr, mem.v_sum + (size_t)row * D, gl);
-        if (gl == 0) {
-          mem.vlen[row] = vl;
-          if (pool) view.cur[row] = slot;
-        }
+        if (gl == 0) mem.vlen[row] = vl;
       }
       refresh_memory_row<D, GL>(L, kr, vr, vl, view.k + (size_t)slot * D, view.v + (size_t)slot * D, gl, act);
     }
-    if (pool) view.pool_next += n_append;
+    if (pool) {
+      for (int i = tid; i < n_append; i += NT)
+        if (S_before + i < capacity) view.cur[S_before + i] = view.pool_next + i;
+      view.pool_next += n_append;
+    }
     __syncthreads();
+    if (nc > 1) cluster_sync_all();  // the appended rows written by the other CTAs are visible
   } else {
     if constexpr (SB) cp_async_wait<0>();
   }
   if (n_merge == 0) {
-    if (route_out)
+    if (route_out && crank == 0)
       for (int i = tid; i < C; i += NT) route_out[i] = -(1 + S_before + s.pos[i]);
-    if (view.ver_idx)
+    if (view.ver_idx && crank == 0)
       for (int i = tid; i < S_after; i += NT) view.ver_idx[i] = view.cur[i];
     __syncthreads();
     return;
@@ -451,6 +506,7 @@ __device__ void memory_update(const LayerDev& L, const TokenSrc& src, const Memo
   // ---- 4. group the merged tokens by target row, token order inside a group
   if (tid < C && s.flag[tid]) s.idx[tid] = -1;
   __syncthreads();
+  bool is_leader = false;
   if (tid < C) {
     const int mine = s.idx[tid];
     if (mine >= 0) {
@@ -471,14 +527,27 @@ __device__ void memory_update(const LayerDev& L, const TokenSrc& src, const Memo
       if (before == 0) {
         s.tcnt[tid] = total;
         s.tstart[tid] = atomicAdd(&s.counters[0], total);
-        s.touched[atomicAdd(&s.counters[1], 1)] = tid;
+        is_leader = true;
       }
     }
+  }
+  {  // touched rows in token order of their first token: the same order in every CTA of a cluster
+    const unsigned bal = __ballot_sync(0xffffffffu, is_leader);
+    if (lane == 0) s.counters[4 + warp] = __popc(bal);
+    __syncthreads();
+    int p = __popc(bal & ((1u << lane) - 1u)), tot = 0;
+    for (int w = 0; w < NT / 32; ++w) {
+      const int c = s.counters[4 + w];
+      if (w < warp) p += c;
+      tot += c;
+    }
+    if (is_leader) s.touched[p] = tid;
+    if (tid == 0) s.counters[1] = tot;
   }
   __syncthreads();
   if (tid < C) {
     if (s.idx[tid] >= 0) s.list[s.tstart[s.lead[tid]] + s.ord[tid]] = tid;
-    if (route_out) route_out[tid] = s.flag[tid] ? -(1 + S_before + s.pos[tid]) : s.idx[tid];
+    if (route_out && crank == 0) route_out[tid] = s.flag[tid] ? -(1 + S_before + s.pos[tid]) : s.idx[tid];
   }
   __syncthreads();
   KVM_PHASE_MARK(6);
@@ -490,8 +559,8 @@ __device__ void memory_update(const LayerDev& L, const TokenSrc& src, const Memo
     constexpr int HG = GROUPS / 2;
     const bool is_v = grp >= HG;
     const int hgrp = grp % HG;
-    for (int base = 0; base < n_touched; base += HG) {  // trip count uniform: the refresh uses shuffles
-      const int i = base + hgrp;
+    for (int base = 0; crank + nc * base < n_touched; base += HG) {  // trip count uniform: the refresh uses shuffles
+      const int i = crank + nc * (base + hgrp);  // this CTA takes every nc-th touched row
       const bool act = i < n_touched;
       const int lt = s.touched[act ? i : 0];
       const int row = s.idx[lt];
@@ -542,10 +611,11 @@ __device__ void memory_update(const LayerDev& L, const TokenSrc& src, const Memo
     for (int i = tid; i < n_touched; i += NT) view.cur[s.idx[s.touched[i]]] = view.pool_next + i;
     view.pool_next += n_touched;
     __syncthreads();
-    if (view.ver_idx)
+    if (view.ver_idx && crank == 0)
       for (int i = tid; i < S_after; i += NT) view.ver_idx[i] = view.cur[i];
   }
   __syncthreads();
+  if (nc > 1) cluster_sync_all();  // rows refreshed by the other CTAs are visible before the next update scans them
   KVM_PHASE_MARK(7);
 }
 
