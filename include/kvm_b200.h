@@ -141,7 +141,12 @@ size_t kvm_decode_workspace_bytes(const kvm_layer* layer, int32_t batch, int32_t
  *   n_append_dev  [batch] int32: -1 = no memory update for this sequence at this step, otherwise
  *                 the number of rows the update appends (host schedule); may be NULL when
  *                 any_update == 0
- *   any_update    host flag: launch the update kernel at all
+ *   any_update    host count of sequences with n_append_dev[b] >= 0 (0: launch no update kernel; a
+ *                 negative value or one above batch means "some, count unknown").  With a known
+ *                 count the update runs on a stream owned by the library, next to the attention of
+ *                 the other sequences, and is joined back into `stream` before the call's last
+ *                 kernel; all work of the call is ordered after prior work in `stream` and before
+ *                 later work in it
  *   max_rows      upper bound of (memory rows + window rows) over the batch (launch geometry)
  *   out           [B,1,Hq*D] bf16
  *   route_dev     optional [batch*Hkv, C] int32, written for updated sequences (see prefill)
@@ -158,7 +163,7 @@ int kvm_decode_step(const kvm_layer* layer, int32_t batch, kvm_decode_cache cach
  * base + i*step_stride elements, n_append_dev + i*batch, and writes out + i*batch*Hq*D; any_update_host
  * and max_rows_host ([n_steps], host memory) carry the per-step launch flags of kvm_decode_step.
  * Equivalent to calling kvm_decode_step n_steps times; exists so that the host loop costs two kernel
- * launches per token and nothing else. */
+ * launches per token and nothing else (any_update_host[i] is the count described above). */
 int kvm_decode_run(const kvm_layer* layer, int32_t batch, kvm_decode_cache cache, int32_t n_steps,
                    kvm_tensor4 q, kvm_tensor4 k, kvm_tensor4 v, kvm_tensor4 gate,
                    int64_t q_step_stride, int64_t kv_step_stride, int64_t gate_step_stride,

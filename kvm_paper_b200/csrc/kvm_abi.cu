@@ -15,7 +15,7 @@ cudaError_t prefill_dispatch(int D, const LayerDev& L, int batch, long long T, T
 size_t update_smem_bytes(int D, int C, int capacity);
 cudaError_t decode_dispatch(int D, const LayerDev& L, int batch, const DecodeCacheDev& cache, Tensor4 q, Tensor4 k,
                             Tensor4 v, Tensor4 gate, const int* n_append, int any_update, int max_rows, bf16* out,
-                            int* route, bf16* pk_scr, bf16* gk_scr, float* partial, int* counters, int rows_per_split,
+                            int* route, bf16* pk_scr, bf16* gk_scr, float* partial, int* counters, int overlap,
                             cudaStream_t stream);
 cudaError_t refresh_dispatch(int D, const LayerDev& L, int batch, MemoryDev mem, const int* state_len,
                              cudaStream_t stream);
@@ -263,7 +263,7 @@ size_t kvm_decode_workspace_bytes(const kvm_layer* layer, int32_t batch, int32_t
 static int decode_step_impl(const kvm_layer* layer, int32_t batch, const kvm_decode_cache& cache, kvm_tensor4 q, kvm_tensor4 k,
                             kvm_tensor4 v, kvm_tensor4 gate, const int32_t* n_append_dev, int32_t any_update, int32_t max_rows,
                             void* out, int32_t* route_dev, void* workspace, size_t workspace_bytes, void* stream,
-                            const char* who) {
+                            int overlap, const char* who) {
   if (int rc = check_layer(layer)) return rc;
   if (batch <= 0) return fail(KVM_ERR_BAD_ARGUMENT, "batch %d must be positive", batch);
   const int D = layer->head_dim;
@@ -289,11 +289,12 @@ static int decode_step_impl(const kvm_layer* layer, int32_t batch, const kvm_dec
   c.ring_k = static_cast<bf16*>(cache.ring_k); c.ring_v = static_cast<bf16*>(cache.ring_v);
   c.ring_g = static_cast<bf16*>(cache.ring_gate); c.total_len = cache.total_len; c.state_len = cache.state_len;
   unsigned char* wsb = static_cast<unsigned char*>(workspace);
+  if (any_update < 0 || any_update > batch) any_update = batch;  // count unknown: no overlap
   cudaError_t e = decode_dispatch(D, to_dev(layer), batch, c, to_dev(q), to_dev(k), to_dev(v), to_dev(gate), n_append_dev,
                                   any_update, max_rows, static_cast<bf16*>(out), route_dev,
                                   reinterpret_cast<bf16*>(wsb + ws.pk), reinterpret_cast<bf16*>(wsb + ws.gk),
                                   reinterpret_cast<float*>(wsb + ws.partial), reinterpret_cast<int*>(wsb + ws.counters),
-                                  kDecodeRowsPerSplit, static_cast<cudaStream_t>(stream));
+                                  overlap, static_cast<cudaStream_t>(stream));
   if (e != cudaSuccess) return cuda_fail(e, who);
   return KVM_OK;
 }
@@ -303,7 +304,7 @@ int kvm_decode_step(const kvm_layer* layer, int32_t batch, kvm_decode_cache cach
                     void* out, int32_t* route_dev, void* workspace, size_t workspace_bytes, void* stream) {
   g_err[0] = 0;
   return decode_step_impl(layer, batch, cache, q, k, v, gate, n_append_dev, any_update, max_rows, out, route_dev, workspace,
-                          workspace_bytes, stream, "kvm_decode_step");
+                          workspace_bytes, stream, 1, "kvm_decode_step");
 }
 
 int kvm_decode_run(const kvm_layer* layer, int32_t batch, kvm_decode_cache cache, int32_t n_steps, kvm_tensor4 q,
@@ -326,7 +327,7 @@ int kvm_decode_run(const kvm_layer* layer, int32_t batch, kvm_decode_cache cache
     if (upd && !n_append_dev) return fail(KVM_ERR_BAD_ARGUMENT, "step %d updates the memory but n_append_dev is NULL", i);
     int rc = decode_step_impl(layer, batch, cache, qi, ki, vi, gi, upd ? n_append_dev + (size_t)i * batch : nullptr, upd,
                               max_rows_host[i], static_cast<uint16_t*>(out) + (size_t)i * out_stride, nullptr, workspace,
-                              workspace_bytes, stream, "kvm_decode_run");
+                              workspace_bytes, stream, 1, "kvm_decode_run");
     if (rc) return rc;
   }
   return KVM_OK;
@@ -351,7 +352,7 @@ int kvm_decode_step_static(const kvm_layer* layer, int32_t batch, kvm_decode_cac
                                   ((size_t)batch * layer->n_kv_heads + batch + 1) * sizeof(int), static_cast<cudaStream_t>(stream));
   if (e != cudaSuccess) return cuda_fail(e, "kvm_decode_step_static: cudaMemsetAsync");
   return decode_step_impl(layer, batch, cache, q, k, v, gate, n_append_dev, any_update, max_rows, out, route_dev, scratch,
-                          (size_t)KVM_STATIC_SCRATCH_BYTES, stream, "kvm_decode_step_static");
+                          (size_t)KVM_STATIC_SCRATCH_BYTES, stream, 0, "kvm_decode_step_static");
 }
 
 int kvm_memory_refresh(const kvm_layer* layer, int32_t batch, kvm_memory memory, const int32_t* state_len_dev, void* stream) {

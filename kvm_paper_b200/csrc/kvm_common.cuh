@@ -101,6 +101,20 @@ __device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], const void* 
                : "r"(s));
 }
 
+// Four 8x8 bf16 matrices from shared memory, not transposed (thread (g, t) gets elements [g][2t, 2t+1] of each).
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], const void* smem_row) {
+  uint32_t s = (uint32_t)__cvta_generic_to_shared(smem_row);
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"(s));
+}
+// Transpose an 8x8 bf16 matrix held one row per lane group (thread (g, t): [g][2t, 2t+1]) across the warp.
+__device__ __forceinline__ uint32_t movmatrix_trans(uint32_t x) {
+  uint32_t y;
+  asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;\n" : "=r"(y) : "r"(x));
+  return y;
+}
+
 // ---------------------------------------------------------------------------------------------
 // One row of D elements is spread over a group of GL lanes (GL = 32: a warp per row; GL = 8: four rows
 // per warp): lane l of the group owns the EPL = D/GL contiguous elements [l*EPL, (l+1)*EPL).

@@ -7,7 +7,10 @@
 //                           copies; rows cut by a share boundary are combined by their last CTA, the
 //                           last CTA of the launch advances the sequences' lengths
 // Follows model/kvm_mixer.py:572-713 (eager single-token step).
+#include <cuda.h>
+
 #include <algorithm>
+#include <mutex>
 
 #include "kvm_update.cuh"
 #include "kvm_tc.cuh"
@@ -23,10 +26,14 @@ __device__ __forceinline__ int bswa_begin_dev(int total, int C, int W) {
 template <int D, int NT, bool UPDATE, bool SB>
 __global__ void __launch_bounds__(NT, 1)
 kvm_decode_pre_kernel(LayerDev L, DecodeCacheDev cache, Tensor4 k, Tensor4 v, Tensor4 gate,
-                      const int* __restrict__ n_append_arr, bf16* pk_scr, int* route) {
+                      const int* __restrict__ n_append_arr, bf16* pk_scr, int* route, int scope) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   const int row = blockIdx.x;
   const int b = row / L.Hkv, h = row % L.Hkv;
+  if (scope) {  // 1: only sequences without a memory update at this token, 2: only those with one
+    const int na = n_append_arr ? n_append_arr[b] : -1;
+    if ((scope == 1 && na >= 0) || (scope == 2 && na < 0)) return;
+  }
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int C = L.C, WC = L.W * L.C;
   const int past = cache.total_len[b];
@@ -89,26 +96,29 @@ kvm_decode_pre_kernel(LayerDev L, DecodeCacheDev cache, Tensor4 k, Tensor4 v, Te
 }
 
 // ------------------------------------------------------------------------------------- attention
-constexpr int kDecThreads = 128;
-constexpr int kDecChunk = 64;        // rows per pipeline stage
-constexpr int kDecStages = 3;        // stages per CTA (two in flight while one is consumed)
-constexpr int kDecMaxBatch = 1024;   // sequences per launch (their chunk table lives in shared memory)
+constexpr int kDecConsumers = 8;                           // math warps (16 keys of every chunk each)
+constexpr int kDecThreads = (kDecConsumers + 1) * 32;      // + one producer warp
+constexpr int kDecChunk = kDecConsumers * 16;              // rows per pipeline stage
+constexpr int kDecBoxRows = 16;                            // rows per TMA box: the fetch granularity of a run's tail
+constexpr int kDecMaxBatch = 1024;                         // sequences per launch (their chunk table lives in shared memory)
 constexpr int kDecodeRowsPerSplit = 128;  // the workspace holds ceil(max_rows / 128) + 2 partials per query head
-
-template <int D>
-__host__ __device__ constexpr int dec_row_stride() { return D + 8; }  // padded rows: conflict-free fragment loads
+constexpr int kDecMaxSmem = 227 * 1024;   // dynamic shared memory one CTA may use (one CTA per SM)
 
 // Shared-memory layout of the attention kernel (byte offsets), for G query heads per kv head.
+// A stage holds the K rows and the V rows of one chunk as TMA boxes: for D >= 64, D/64 blocks of
+// [chunk rows][64 elements] in the 128-byte swizzle (16-byte piece c of row r at position c ^ (r % 8));
+// for D = 32 plain rows of 64 bytes.
 struct DecSmem {
-  size_t stages, qst, ored, wred, meta, temps, seq, total;
-  __host__ __device__ DecSmem(int D, int G, int Hq, int nb) {
-    const size_t str = (size_t)(D + 8) * 2;
+  size_t stages, stage_bytes, qst, ored, wred, meta, bars, temps, seq, total;
+  __host__ __device__ DecSmem(int D, int G, int Hq, int nb, int ST) {
     size_t off = 0;
-    stages = off; off += (size_t)kDecStages * 2 * kDecChunk * str;   // [stage][K | V][row][padded D] bf16
-    qst = off;    off += (size_t)kDecStages * G * str;               // [stage][query head][padded D] bf16
-    ored = off;   off += (size_t)4 * G * D * 4;                      // [warp][query head][D] fp32
-    wred = off;   off += (size_t)2 * 4 * 16 * 4;                     // per-warp running max / sum
-    meta = off;   off += (size_t)kDecStages * 32;                    // per-stage chunk description (8 ints)
+    stage_bytes = (size_t)2 * kDecChunk * D * 2;
+    stages = off; off += (size_t)ST * stage_bytes;                   // 1024-byte aligned (swizzle atoms)
+    qst = off;    off += (size_t)ST * G * (D + 8) * 2;               // [stage][query head][padded D] bf16
+    ored = off;   off += (size_t)kDecConsumers * G * D * 4;          // [warp][query head][D] fp32
+    wred = off;   off += (size_t)2 * kDecConsumers * 16 * 4;         // per-warp running max / sum
+    meta = off;   off += (size_t)ST * 32;                            // per-stage chunk description (8 ints)
+    bars = off;   off += (size_t)(2 * ST + 1) * 8;                   // full[ST], empty[ST], rendezvous
     temps = off;  off += (size_t)2 * Hq * 4;                         // folded softmax scales per query head
     seq = off;    off += (size_t)(3 * nb + 4) * 4;                   // per sequence: S, total, chunk prefix
     total = (off + 15) & ~(size_t)15;
@@ -136,51 +146,93 @@ __device__ __forceinline__ DecGeo dec_geometry(int S, int total, int C, int W) {
   return g;
 }
 
+// The four row arrays of the decode cache as 2-D tensors [all rows][D] with boxes of kDecBoxRows rows.
+struct DecMaps {
+  CUtensorMap mem_k, mem_v, ring_k, ring_v;
+};
+
+// byte offset of the 16-byte piece j of row r inside the K (or V) part of a stage
+template <int D>
+__device__ __forceinline__ uint32_t dec_piece(int r, int j) {
+  if constexpr (D >= 64) return (uint32_t)((j >> 3) * (kDecChunk * 128) + r * 128 + (((j & 7) ^ (r & 7)) << 4));
+  else return (uint32_t)(r * (D * 2) + j * 16);
+}
+
+// Bounded wait that also gives up when another warp of the CTA has given up.
+__device__ __forceinline__ bool dec_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+  for (uint32_t i = 0; i < tc::kSpinLimit; ++i) {
+    if (tc::mbar_try_wait(bar, parity)) return true;
+    if (i >= 8) {
+      if (*abort_flag) return false;
+      __nanosleep(i < 64 ? 32 : 200);
+    }
+  }
+  return false;
+}
+
 // Joint attention of one new token per sequence over [memory ; window], persistent and bandwidth-bound.
 // All (sequence, kv head, chunk) triples of the launch form one flat list (sequence-major); every CTA
-// takes an equal contiguous range of it and streams the range through a ring of kDecStages shared-memory
-// stages with coalesced 16-byte asynchronous copies (a warp moves 512 contiguous bytes per instruction)
-// into padded rows.  The copies run two chunks ahead of the math and do not stop at row boundaries, so
-// 64 KB per CTA (two CTAs per SM) are in flight from the first to the last chunk of the CTA.
-// All query heads of a kv head (G <= 16) form the M=16 tile of warp-level MMAs; each warp owns 16 keys of
-// every chunk and keeps a running (max, sum, output) that is merged across the warps when the CTA leaves
-// the kv row.  A row that lies inside one CTA's range is finished there; a row cut by a range boundary
-// leaves partial results [m, l, acc[D]] (fp32) and the last of its CTAs combines them.  The last CTA of
-// the launch advances the lengths of the sequences it covered (nobody reads them any more by then).
+// (one per SM) takes an equal contiguous range of it.  A producer warp streams the range through a ring
+// of ST shared-memory stages with tiled TMA copies (boxes of 16 rows, so that the ragged end of a run
+// costs at most 15 rows of extra traffic) and runs ahead of the math across row boundaries; eight math
+// warps follow through full/empty mbarriers without block-wide barriers.
+// Warp-level MMAs with the keys on the M dimension (each math warp owns 16 keys of every chunk) and the
+// query heads of the kv head (G <= 16) on the N dimension, so that a kv head with few query heads costs
+// one 8-wide tile; each warp keeps a running (max, sum, output) that is merged across the warps when the
+// CTA leaves the kv row.  A row that lies inside one CTA's range is finished there; a row cut by a range
+// boundary leaves partial results [m, l, acc[D]] (fp32) and the last of its CTAs combines them.  The last
+// CTA of the launch advances the lengths of the sequences it covered (nobody reads them any more by then).
+// Every wait is bounded; a wait that runs out sets the status word and the CTA drains.
 // `mode`: 0 = all sequences, 1 = only sequences without a memory update at this token, 2 = only those with.
-template <int D>
-__global__ void __launch_bounds__(kDecThreads, 2)
+template <int D, int ST, int NH>
+__global__ void __launch_bounds__(kDecThreads, 1)
 kvm_decode_attn_kernel(LayerDev L, DecodeCacheDev cache, Tensor4 q, const int* __restrict__ n_append_arr,
                        float* __restrict__ partial, int* __restrict__ row_counters, int* __restrict__ done_counter,
-                       bf16* __restrict__ out, float sm_scale, int b0, int nb, int nslots, int per_min, int mode) {
-  constexpr int STR = dec_row_stride<D>();
-  constexpr int KS = D / 16;   // k-steps of Q K^T
-  constexpr int DT8 = D / 8;   // n8 tiles of the output
-  constexpr int CH = kDecChunk, ST = kDecStages;
-  constexpr int CPR = D / 8;                      // 16-byte pieces per row
-  constexpr int RPI = kDecThreads / CPR;          // rows per pass of the CTA
-  extern __shared__ __align__(128) unsigned char smem_raw[];
+                       int* __restrict__ status, bf16* __restrict__ out, float sm_scale, int b0, int nb, int nslots,
+                       int per_min, int mode, const __grid_constant__ DecMaps maps) {
+  constexpr int STRQ = D + 8;  // padded query rows: conflict-free fragment loads
+  constexpr int KS = D / 16;   // k-steps of K Q^T
+  constexpr int CH = kDecChunk, NW = kDecConsumers;
+  constexpr int CPR = D / 8;                          // 16-byte pieces per row
+  constexpr int BOXW = D >= 64 ? 64 : D;              // box width in elements
+  constexpr int NBLK = D / BOXW;                      // boxes side by side per row group
+  constexpr uint32_t kBoxBytes = (uint32_t)kDecBoxRows * BOXW * 2;
+  extern __shared__ __align__(1024) unsigned char smem_raw[];
   const int G = L.Hq / L.Hkv, Hkv = L.Hkv;
-  const DecSmem lay(D, G, L.Hq, nb);
-  bf16* stage0 = reinterpret_cast<bf16*>(smem_raw + lay.stages);
+  const DecSmem lay(D, G, L.Hq, nb, ST);
+  unsigned char* stage0 = smem_raw + lay.stages;
   bf16* qst = reinterpret_cast<bf16*>(smem_raw + lay.qst);
   float* ored = reinterpret_cast<float*>(smem_raw + lay.ored);
   float* wmax = reinterpret_cast<float*>(smem_raw + lay.wred);
-  float* wsum = wmax + 64;
-  int* meta = reinterpret_cast<int*>(smem_raw + lay.meta);          // [ST][8]
-  float* temp_mem = reinterpret_cast<float*>(smem_raw + lay.temps);  // [Hq]
-  float* temp_win = temp_mem + L.Hq;                                 // [Hq]
-  int* sq_S = reinterpret_cast<int*>(smem_raw + lay.seq);            // [nb]
-  int* sq_tot = sq_S + nb;                                           // [nb]
-  int* cpre = sq_tot + nb;                                           // [nb + 1] chunks per kv row, prefix
-  __shared__ int s_flag;
+  float* wsum = wmax + NW * 16;
+  int* meta = reinterpret_cast<int*>(smem_raw + lay.meta);            // [ST][8]
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem_raw + lay.bars);  // [ST] chunk landed (transaction bytes)
+  uint64_t* empty = full + ST;                                        // [ST] chunk consumed (one arrival per math warp)
+  uint64_t* fbar = empty + ST;                                        // rendezvous of the math warps
+  float* temp_mem = reinterpret_cast<float*>(smem_raw + lay.temps);   // [Hq]
+  float* temp_win = temp_mem + L.Hq;                                  // [Hq]
+  int* sq_S = reinterpret_cast<int*>(smem_raw + lay.seq);             // [nb]
+  int* sq_tot = sq_S + nb;                                            // [nb]
+  int* cpre = sq_tot + nb;                                            // [nb + 1] chunks per kv row, prefix
+  __shared__ int s_flag, s_abort;
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int g = lane >> 2, t = lane & 3;
   const int C = L.C, W = L.W, WC = L.W * L.C;
   const int cap = cache.mem.capacity;
 
-  // ---- setup: lengths of the sequences in scope, their chunk counts, the prefix over sequences
+  // ---- setup: barriers, lengths of the sequences in scope, their chunk counts, the prefix over sequences
+  if (tid == 0) {
+#pragma unroll
+    for (int s = 0; s < ST; ++s) {
+      tc::mbar_init(&full[s], 1);
+      tc::mbar_init(&empty[s], NW);
+    }
+    tc::mbar_init(fbar, NW);
+    tc::fence_barrier_init();
+    s_abort = 0;
+    cpre[0] = 0;
+  }
   for (int b = tid; b < nb; b += kDecThreads) {
     const int B = b0 + b;
     const int n_app = n_append_arr ? n_append_arr[B] : -1;
@@ -201,7 +253,6 @@ kvm_decode_attn_kernel(LayerDev L, DecodeCacheDev cache, Tensor4 q, const int* _
     temp_mem[h] = sm_scale * L.state_temp[h] * kLog2e;
     temp_win[h] = sm_scale * L.front_temp[h] * kLog2e;
   }
-  if (tid == 0) cpre[0] = 0;
   __syncthreads();
   if (warp == 0) {  // inclusive scan of cpre[1..nb], 32 entries at a time
     int carry = 0;
@@ -225,294 +276,341 @@ kvm_decode_attn_kernel(LayerDev L, DecodeCacheDev cache, Tensor4 q, const int* _
   if (cta >= active) return;
   const int f_begin = cta * per, f_end = min(total_f, f_begin + per);
   const int nloc = f_end - f_begin;
+  volatile int* abort_flag = &s_abort;
 
-  // ---- producer cursor: (sequence, kv head, chunk) of the next chunk to fetch
-  int pb, ph, pc, pcb;
-  DecGeo pg;
-  {
-    int lo = 0, hi = nb - 1;  // last b with cpre[b] * Hkv <= f_begin and a non-empty range
-    while (lo < hi) {
-      const int mid = (lo + hi + 1) >> 1;
-      if (cpre[mid] * Hkv <= f_begin) lo = mid; else hi = mid - 1;
-    }
-    pb = lo;
-    pcb = cpre[pb + 1] - cpre[pb];
-    const int rem = f_begin - cpre[pb] * Hkv;
-    ph = rem / pcb;
-    pc = rem - ph * pcb;
-    pg = dec_geometry(sq_S[pb], sq_tot[pb], C, W);
-  }
-  const int my_c = tid % CPR, my_r = tid / CPR;
-  // Fetch the producer cursor's chunk into stage s (local chunk index i) and advance the cursor.
-  auto issue = [&](int i, int s) {
-    const int row = (b0 + pb) * Hkv + ph;
-    int n;
-    size_t r0;
-    const bf16 *bk, *bv;
-    const bool is_mem = pc < pg.c_mem;
-    if (is_mem) {
-      n = min(CH, pg.S_act - pc * CH);
-      r0 = (size_t)row * cap + (size_t)pc * CH;
-      bk = cache.mem.k_attn;
-      bv = cache.mem.v_attn;
-    } else if (pc < pg.c_mem + pg.c_a) {
-      const int c = pc - pg.c_mem;
-      n = min(CH, pg.len_a - c * CH);
-      r0 = (size_t)row * WC + pg.slot0 + (size_t)c * CH;
-      bk = cache.ring_k;
-      bv = cache.ring_v;
-    } else {
-      const int c = pc - pg.c_mem - pg.c_a;
-      n = min(CH, pg.len_b - c * CH);
-      r0 = (size_t)row * WC + (size_t)c * CH;
-      bk = cache.ring_k;
-      bv = cache.ring_v;
-    }
-    const bool first = i == 0 || pc == 0;
-    const bool last = i == nloc - 1 || pc == pcb - 1;
-    bf16* dk = stage0 + (size_t)(s * 2) * CH * STR + my_c * 8;
-    bf16* dv = dk + (size_t)CH * STR;
-    const bf16* gk = bk + r0 * D + my_c * 8;
-    const bf16* gv = bv + r0 * D + my_c * 8;
-#pragma unroll
-    for (int k2 = 0; k2 < CH / RPI; ++k2) {
-      const int r = my_r + k2 * RPI;
-      const bool in = r < n;  // rows past the run: zero-filled (scores masked, values must be finite)
-      const size_t go = (size_t)(in ? r : 0) * D;
-      cp_async16(dk + (size_t)r * STR, gk + go, in ? 16 : 0);
-      cp_async16(dv + (size_t)r * STR, gv + go, in ? 16 : 0);
-    }
-    if (first) {  // the query rows of this kv head travel with the first chunk of the row segment
-      for (int p = tid; p < G * CPR; p += kDecThreads) {
-        const int qh = p / CPR, c8 = p - qh * CPR;
-        cp_async16(qst + ((size_t)s * G + qh) * STR + c8 * 8, q.row(b0 + pb, ph * G + qh, 0) + c8 * 8, 16);
-      }
-    }
-    if (tid == 0) {
-      int seg = 0, nsegs = 1;
-      if (last) {
-        const int row_f = cpre[pb] * Hkv + ph * pcb;  // flat index of the row's first chunk
-        const int first_cta = row_f / per;
-        seg = cta - first_cta;
-        nsegs = (row_f + pcb - 1) / per - first_cta + 1;
-      }
-      int* m = meta + s * 8;
-      m[0] = n | (is_mem ? 1 << 16 : 0) | (first ? 1 << 17 : 0) | (last ? 1 << 18 : 0);
-      m[1] = row;
-      m[2] = seg;
-      m[3] = nsegs;
-    }
-    // advance
-    if (++pc == pcb) {
-      pc = 0;
-      if (++ph == Hkv) {
-        ph = 0;
-        ++pb;
-        while (pb < nb && cpre[pb + 1] == cpre[pb]) ++pb;
-        if (pb < nb) {
-          pcb = cpre[pb + 1] - cpre[pb];
-          pg = dec_geometry(sq_S[pb], sq_tot[pb], C, W);
-        }
-      }
-    }
-  };
-
-  // prologue: the first ST-1 chunks in flight (one commit group per chunk, empty groups keep the count uniform)
-#pragma unroll
-  for (int s = 0; s < ST - 1; ++s) {
-    if (s < nloc) issue(s, s);
-    cp_async_commit();
-  }
-
-  uint32_t qa[KS][4];
-  float scl_mem[2] = {0.f, 0.f}, scl_win[2] = {0.f, 0.f};
-  float m_row[2] = {-INFINITY, -INFINITY}, l_row[2] = {0.f, 0.f};
-  float o[DT8][4];
-
-  for (int i = 0; i < nloc; ++i) {
-    const int s = i % ST;
-    cp_async_wait<ST - 2>();  // this thread's pieces of chunk i have landed
-    __syncthreads();          // ... everybody's have, and everybody is done with the stage refilled next
-    if (i + ST - 1 < nloc) issue(i + ST - 1, (i + ST - 1) % ST);
-    cp_async_commit();
-
-    const int4 md = *reinterpret_cast<const int4*>(meta + s * 8);
-    const int n = md.x & 0xffff;
-    const bool is_mem = (md.x >> 16) & 1, first = (md.x >> 17) & 1, last = (md.x >> 18) & 1;
-    const int row = md.y;
-    const int hkv = row % Hkv;
-    if (first) {  // new kv row (or the CTA's first chunk): reset the running state, fetch the query fragments
-#pragma unroll
-      for (int r = 0; r < 2; ++r) {
-        m_row[r] = -INFINITY;
-        l_row[r] = 0.f;
-        const int qh = g + r * 8;
-        const bool okq = qh < G;
-        const int hq = hkv * G + (okq ? qh : 0);
-        scl_mem[r] = temp_mem[hq];
-        scl_win[r] = temp_win[hq];
-        const bf16* qp = qst + ((size_t)s * G + (okq ? qh : 0)) * STR + t * 2;
-#pragma unroll
-        for (int ks = 0; ks < KS; ++ks) {
-          qa[ks][r] = okq ? *reinterpret_cast<const uint32_t*>(qp + ks * 16) : 0u;
-          qa[ks][2 + r] = okq ? *reinterpret_cast<const uint32_t*>(qp + ks * 16 + 8) : 0u;
-        }
-      }
-#pragma unroll
-      for (int d8 = 0; d8 < DT8; ++d8) o[d8][0] = o[d8][1] = o[d8][2] = o[d8][3] = 0.f;
-    }
+  if (warp == NW) {
+    // =============================================================== producer warp (lanes in lockstep)
+    int pb, ph, pc, pcb;
+    DecGeo pg;
     {
-      const bf16* sK = stage0 + (size_t)(s * 2) * CH * STR;
-      const bf16* sV = sK + (size_t)CH * STR;
-      // S = Q K^T for this warp's 16 keys of the chunk
-      float sacc[2][4];
-#pragma unroll
-      for (int j = 0; j < 2; ++j) {
-        sacc[j][0] = sacc[j][1] = sacc[j][2] = sacc[j][3] = 0.f;
-        const bf16* brow = sK + (size_t)(warp * 16 + j * 8 + g) * STR + t * 2;
-#pragma unroll
-        for (int ks = 0; ks < KS; ++ks) {
-          const uint32_t b0r = *reinterpret_cast<const uint32_t*>(brow + ks * 16);
-          const uint32_t b1r = *reinterpret_cast<const uint32_t*>(brow + ks * 16 + 8);
-          mma_bf16_16816(sacc[j], qa[ks], b0r, b1r);
-        }
+      int lo = 0, hi = nb - 1;  // last b with cpre[b] * Hkv <= f_begin: its chunk range holds f_begin
+      while (lo < hi) {
+        const int mid = (lo + hi + 1) >> 1;
+        if (cpre[mid] * Hkv <= f_begin) lo = mid; else hi = mid - 1;
       }
-      const float sc0 = is_mem ? scl_mem[0] : scl_win[0], sc1 = is_mem ? scl_mem[1] : scl_win[1];
-      float mx[2] = {-INFINITY, -INFINITY};
-#pragma unroll
-      for (int j = 0; j < 2; ++j) {
-#pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          const int key = warp * 16 + j * 8 + t * 2 + (e & 1);
-          const float x = key < n ? sacc[j][e] * ((e >> 1) ? sc1 : sc0) : -INFINITY;
-          sacc[j][e] = x;
-          mx[e >> 1] = fmaxf(mx[e >> 1], x);
-        }
-      }
-      bool grew = false;
-#pragma unroll
-      for (int r = 0; r < 2; ++r) {
-        mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
-        mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
-        grew = grew || mx[r] > m_row[r];
-      }
-      if (__any_sync(0xffffffffu, grew)) {  // running maximum moved: rescale what has been accumulated
-        float f[2];
-#pragma unroll
-        for (int r = 0; r < 2; ++r) {
-          const float mn = fmaxf(m_row[r], mx[r]);
-          f[r] = m_row[r] == -INFINITY ? 0.f : exp2f(m_row[r] - mn);
-          m_row[r] = mn;
-          l_row[r] *= f[r];
-        }
-#pragma unroll
-        for (int d8 = 0; d8 < DT8; ++d8) {
-          o[d8][0] *= f[0];
-          o[d8][1] *= f[0];
-          o[d8][2] *= f[1];
-          o[d8][3] *= f[1];
-        }
-      }
-      const float mu0 = m_row[0] == -INFINITY ? 0.f : m_row[0];
-      const float mu1 = m_row[1] == -INFINITY ? 0.f : m_row[1];
-      // P = exp2(S - m) and O += P V for this warp's keys
-      uint32_t pa[4];
-#pragma unroll
-      for (int j = 0; j < 2; ++j) {
-        const float p0 = exp2f(sacc[j][0] - mu0), p1 = exp2f(sacc[j][1] - mu0);
-        const float p2 = exp2f(sacc[j][2] - mu1), p3 = exp2f(sacc[j][3] - mu1);
-        l_row[0] += p0 + p1;
-        l_row[1] += p2 + p3;
-        pa[j * 2 + 0] = pack_bf16(p0, p1);
-        pa[j * 2 + 1] = pack_bf16(p2, p3);
-      }
-#pragma unroll
-      for (int dp = 0; dp < DT8 / 2; ++dp) {
-        uint32_t vb[4];
-        const bf16* vrow = sV + (size_t)(warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * STR + dp * 16 + (lane >> 4) * 8;
-        ldmatrix_x4_trans(vb, vrow);
-        mma_bf16_16816(o[dp * 2 + 0], pa, vb[0], vb[1]);
-        mma_bf16_16816(o[dp * 2 + 1], pa, vb[2], vb[3]);
-      }
+      pb = lo;
+      pcb = cpre[pb + 1] - cpre[pb];
+      const int rem = f_begin - cpre[pb] * Hkv;
+      ph = rem / pcb;
+      pc = rem - ph * pcb;
+      pg = dec_geometry(sq_S[pb], sq_tot[pb], C, W);
     }
-    if (!last) continue;
-
-    // ---- the CTA leaves this kv row: merge the four warps' running states
-    const int seg = md.z, nsegs = md.w;
-    const int b = row / Hkv;  // absolute sequence index
-#pragma unroll
-    for (int r = 0; r < 2; ++r) {
-      float l = l_row[r];
-      l += __shfl_xor_sync(0xffffffffu, l, 1);
-      l += __shfl_xor_sync(0xffffffffu, l, 2);
-      if (t == 0) {
-        wmax[warp * 16 + g + r * 8] = m_row[r];
-        wsum[warp * 16 + g + r * 8] = l;
+    for (int i = 0; i < nloc; ++i) {
+      const int s = i % ST;
+      if (i >= ST) {  // the math warps are done with the chunk that used this stage
+        const bool ok = dec_wait(&empty[s], (uint32_t)((i / ST - 1) & 1), abort_flag);
+        if (!__all_sync(0xffffffffu, ok)) {
+          if (lane == 0) {
+            s_abort = 1;
+            atomicExch(status, KVM_ERR_DEVICE_TIMEOUT);
+          }
+          break;
+        }
       }
-      const int qh = g + r * 8;
-      if (qh < G) {
-        float* dst = ored + ((size_t)warp * G + qh) * D + t * 2;
-#pragma unroll
-        for (int d8 = 0; d8 < DT8; ++d8) *reinterpret_cast<float2*>(dst + d8 * 8) = make_float2(o[d8][r * 2], o[d8][r * 2 + 1]);
-      }
-    }
-    __syncthreads();
-    for (int gq = 0; gq < G; ++gq) {
-      const int hq = hkv * G + gq;
-      const float M = fmaxf(fmaxf(wmax[gq], wmax[16 + gq]), fmaxf(wmax[32 + gq], wmax[48 + gq]));
-      float f[4], lsum = 0.f;
-#pragma unroll
-      for (int w = 0; w < 4; ++w) {
-        f[w] = wmax[w * 16 + gq] == -INFINITY ? 0.f : exp2f(wmax[w * 16 + gq] - M);
-        lsum += f[w] * wsum[w * 16 + gq];
-      }
-      float acc = 0.f;
-      if (tid < D) {
-        const float* src = ored + (size_t)gq * D + tid;
-        acc = f[0] * src[0] + f[1] * src[(size_t)G * D] + f[2] * src[(size_t)2 * G * D] + f[3] * src[(size_t)3 * G * D];
-      }
-      if (nsegs == 1) {  // the whole row was here
-        if (tid < D) out[(size_t)b * L.Hq * D + (size_t)hq * D + tid] = __float2bfloat16_rn(lsum > 0.f ? acc / lsum : 0.f);
+      const int row = (b0 + pb) * Hkv + ph;
+      int n, y0;
+      const bool is_mem = pc < pg.c_mem;
+      if (is_mem) {
+        n = min(CH, pg.S_act - pc * CH);
+        y0 = row * cap + pc * CH;
+      } else if (pc < pg.c_mem + pg.c_a) {
+        const int c = pc - pg.c_mem;
+        n = min(CH, pg.len_a - c * CH);
+        y0 = row * WC + pg.slot0 + c * CH;
       } else {
-        float* pout = partial + ((size_t)(b * L.Hq + hq) * nslots + seg) * (D + 2);
-        if (tid < D) pout[2 + tid] = acc;
-        if (tid == 0) {
-          pout[0] = M;
-          pout[1] = lsum;
+        const int c = pc - pg.c_mem - pg.c_a;
+        n = min(CH, pg.len_b - c * CH);
+        y0 = row * WC + c * CH;
+      }
+      const bool first = i == 0 || pc == 0;
+      const bool last = i == nloc - 1 || pc == pcb - 1;
+      const int groups = (n + kDecBoxRows - 1) / kDecBoxRows;
+      if (lane == 0) {
+        int seg = 0, nsegs = 1;
+        if (last) {
+          const int row_f = cpre[pb] * Hkv + ph * pcb;  // flat index of the row's first chunk
+          const int first_cta = row_f / per;
+          seg = cta - first_cta;
+          nsegs = (row_f + pcb - 1) / per - first_cta + 1;
+        }
+        int* m = meta + s * 8;
+        m[0] = n | (is_mem ? 1 << 16 : 0) | (first ? 1 << 17 : 0) | (last ? 1 << 18 : 0) | (ph << 20);
+        m[1] = row;
+        m[2] = seg;
+        m[3] = nsegs;
+        tc::mbar_arrive_expect_tx(&full[s], (uint32_t)groups * 2u * NBLK * kBoxBytes + (first ? (uint32_t)(G * D * 2) : 0u));
+      }
+      __syncwarp();
+      if (lane < groups) {  // one row group (16 rows of K and of V) per lane
+        const CUtensorMap* mk = is_mem ? &maps.mem_k : &maps.ring_k;
+        const CUtensorMap* mv = is_mem ? &maps.mem_v : &maps.ring_v;
+        unsigned char* dk = stage0 + (size_t)s * lay.stage_bytes + (size_t)lane * kDecBoxRows * (BOXW * 2);
+        unsigned char* dv = dk + (size_t)CH * D * 2;
+        const int y = y0 + lane * kDecBoxRows;
+#pragma unroll
+        for (int blk = 0; blk < NBLK; ++blk) {
+          tc::tma_load_2d(dk + (size_t)blk * CH * 128, mk, blk * 64, y, &full[s]);
+          tc::tma_load_2d(dv + (size_t)blk * CH * 128, mv, blk * 64, y, &full[s]);
         }
       }
-    }
-    if (nsegs > 1) {  // the last CTA of this kv row combines the partial results
-      __threadfence();
-      __syncthreads();
-      if (tid == 0) {
-        const int prev = atomicAdd(&row_counters[row], 1);
-        s_flag = (prev == nsegs - 1);
-      }
-      __syncthreads();
-      if (s_flag) {
-        __threadfence();
-        for (int gq = 0; gq < G; ++gq) {
-          const int hq = hkv * G + gq;
-          const float* pin = partial + ((size_t)(b * L.Hq + hq) * nslots) * (D + 2);
-          float M = -INFINITY;
-          for (int s2 = 0; s2 < nsegs; ++s2) M = fmaxf(M, __ldcg(pin + (size_t)s2 * (D + 2)));
-          if (tid < D) {
-            float Lsum = 0.f, a = 0.f;
-            for (int s2 = 0; s2 < nsegs; ++s2) {
-              const float ms = __ldcg(pin + (size_t)s2 * (D + 2));
-              const float w = ms == -INFINITY ? 0.f : exp2f(ms - M);
-              Lsum += w * __ldcg(pin + (size_t)s2 * (D + 2) + 1);
-              a += w * __ldcg(pin + (size_t)s2 * (D + 2) + 2 + tid);
-            }
-            out[(size_t)b * L.Hq * D + (size_t)hq * D + tid] = __float2bfloat16_rn(Lsum > 0.f ? a / Lsum : 0.f);
+      if (first && lane < G)  // the query rows of this kv head travel with the first chunk of the row segment
+        tc::bulk_g2s(qst + ((size_t)s * G + lane) * STRQ, q.row(b0 + pb, ph * G + lane, 0), D * 2, &full[s]);
+      // advance the cursor
+      if (++pc == pcb) {
+        pc = 0;
+        if (++ph == Hkv) {
+          ph = 0;
+          ++pb;
+          while (pb < nb && cpre[pb + 1] == cpre[pb]) ++pb;
+          if (pb < nb) {
+            pcb = cpre[pb + 1] - cpre[pb];
+            pg = dec_geometry(sq_S[pb], sq_tot[pb], C, W);
           }
         }
-        if (tid == 0) row_counters[row] = 0;
       }
     }
+  } else {
+    // ==================================================================================== math warps
+    // Math layout: the keys are the M dimension of the MMAs (16 keys of this warp per chunk), the query heads
+    // of the kv head the N dimension (NH tiles of 8 heads).  S^T = K Q^T: thread (g, t) holds keys g and g+8
+    // for heads 2t, 2t+1 of each head tile; O^T = V^T P^T accumulates [d][head] with d on the M dimension.
+    constexpr int DT16 = D / 16;
+    uint32_t qb[NH][KS][2];            // B fragments of Q^T: head g (+8 per tile), d = 16 ks + 2t (+8)
+    float scl_mem[NH][2], scl_win[NH][2];
+    float m_run[NH][2], l_run[NH][2];  // running max / partial sum of heads 2t, 2t+1 (this thread's keys)
+    float o[NH][DT16][4];              // [d = 16 dt + g (+8)][head 2t, 2t+1]
+    const int krow = warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8;  // ldmatrix row of the K tile
+    const int vrow = warp * 16 + (lane & 7) + (lane >> 4) * 8;         // ldmatrix row of the V tile
+    uint32_t fphase = 0;               // phase of the rendezvous barrier
+    bool alive = true;
+    // all math warps meet (bounded): false if somebody gave up
+    auto rendezvous = [&]() -> bool {
+      __syncwarp();
+      if (lane == 0) tc::mbar_arrive(fbar);
+      const bool ok = dec_wait(fbar, fphase & 1, abort_flag);
+      ++fphase;
+      return __all_sync(0xffffffffu, ok);
+    };
+
+    for (int i = 0; i < nloc && alive; ++i) {
+      const int s = i % ST;
+      if (!__all_sync(0xffffffffu, dec_wait(&full[s], (uint32_t)((i / ST) & 1), abort_flag))) {
+        alive = false;
+        break;
+      }
+      const int4 md = *reinterpret_cast<const int4*>(meta + s * 8);
+      const int n = md.x & 0xffff;
+      const bool is_mem = (md.x >> 16) & 1, first = (md.x >> 17) & 1, last = (md.x >> 18) & 1;
+      const int row = md.y;
+      const int hkv = md.x >> 20;
+      if (first) {  // new kv row (or the CTA's first chunk): reset the running state, fetch the query fragments
+#pragma unroll
+        for (int h = 0; h < NH; ++h) {
+          const int qh = h * 8 + g;  // head supplied by this thread to the B operand
+          const bool okq = qh < G;
+          const bf16* qp = qst + ((size_t)s * G + (okq ? qh : 0)) * STRQ + t * 2;
+#pragma unroll
+          for (int ks = 0; ks < KS; ++ks) {
+            qb[h][ks][0] = okq ? *reinterpret_cast<const uint32_t*>(qp + ks * 16) : 0u;
+            qb[h][ks][1] = okq ? *reinterpret_cast<const uint32_t*>(qp + ks * 16 + 8) : 0u;
+          }
+#pragma unroll
+          for (int j = 0; j < 2; ++j) {
+            const int hh = h * 8 + t * 2 + j;  // head of this thread's accumulator columns
+            const int hq = hkv * G + (hh < G ? hh : 0);
+            scl_mem[h][j] = temp_mem[hq];
+            scl_win[h][j] = temp_win[hq];
+            m_run[h][j] = -INFINITY;
+            l_run[h][j] = 0.f;
+          }
+#pragma unroll
+          for (int dt = 0; dt < DT16; ++dt) o[h][dt][0] = o[h][dt][1] = o[h][dt][2] = o[h][dt][3] = 0.f;
+        }
+      }
+      if (warp * 16 < n) {
+        unsigned char* sK = stage0 + (size_t)s * lay.stage_bytes;
+        unsigned char* sV = sK + (size_t)CH * D * 2;
+        if (n < warp * 16 + 16) {
+          // ragged end of the run inside this warp's rows: what the box brought in beyond the run is not
+          // part of it; scores are masked below, values are zeroed here (0 * garbage must stay finite)
+          const int r_lo = n, cnt = (warp * 16 + 16 - n) * CPR;
+          for (int p = lane; p < cnt; p += 32) {
+            const int r = r_lo + p / CPR, j = p % CPR;
+            *reinterpret_cast<uint4*>(sV + dec_piece<D>(r, j)) = make_uint4(0, 0, 0, 0);
+          }
+          tc::fence_proxy_async();  // ... before a later TMA copy overwrites these bytes
+          __syncwarp();
+        }
+        // S^T = K Q^T for this warp's 16 keys of the chunk
+        float sacc[NH][4];
+#pragma unroll
+        for (int h = 0; h < NH; ++h) sacc[h][0] = sacc[h][1] = sacc[h][2] = sacc[h][3] = 0.f;
+#pragma unroll
+        for (int ks = 0; ks < KS; ++ks) {
+          uint32_t ka[4];
+          ldmatrix_x4(ka, sK + dec_piece<D>(krow, ks * 2 + (lane >> 4)));
+#pragma unroll
+          for (int h = 0; h < NH; ++h) mma_bf16_16816(sacc[h], ka, qb[h][ks][0], qb[h][ks][1]);
+        }
+        const bool ok_lo = warp * 16 + g < n, ok_hi = warp * 16 + g + 8 < n;
+        uint32_t pb[NH][2];
+#pragma unroll
+        for (int h = 0; h < NH; ++h) {
+          float mx[2], f[2];
+          bool grew = false;
+#pragma unroll
+          for (int j = 0; j < 2; ++j) {
+            const float sc = is_mem ? scl_mem[h][j] : scl_win[h][j];
+            sacc[h][j] = ok_lo ? sacc[h][j] * sc : -INFINITY;
+            sacc[h][2 + j] = ok_hi ? sacc[h][2 + j] * sc : -INFINITY;
+            float x = fmaxf(sacc[h][j], sacc[h][2 + j]);
+            x = fmaxf(x, __shfl_xor_sync(0xffffffffu, x, 4));
+            x = fmaxf(x, __shfl_xor_sync(0xffffffffu, x, 8));
+            x = fmaxf(x, __shfl_xor_sync(0xffffffffu, x, 16));
+            mx[j] = x;
+            grew = grew || x > m_run[h][j];
+          }
+          if (__any_sync(0xffffffffu, grew)) {  // a running maximum moved: rescale what has been accumulated
+#pragma unroll
+            for (int j = 0; j < 2; ++j) {
+              const float mn = fmaxf(m_run[h][j], mx[j]);
+              f[j] = m_run[h][j] == -INFINITY ? 0.f : exp2f(m_run[h][j] - mn);
+              m_run[h][j] = mn;
+              l_run[h][j] *= f[j];
+            }
+#pragma unroll
+            for (int dt = 0; dt < DT16; ++dt) {
+              o[h][dt][0] *= f[0];
+              o[h][dt][1] *= f[1];
+              o[h][dt][2] *= f[0];
+              o[h][dt][3] *= f[1];
+            }
+          }
+          const float mu0 = m_run[h][0] == -INFINITY ? 0.f : m_run[h][0];
+          const float mu1 = m_run[h][1] == -INFINITY ? 0.f : m_run[h][1];
+          const float p0 = exp2f(sacc[h][0] - mu0), p1 = exp2f(sacc[h][1] - mu1);
+          const float p2 = exp2f(sacc[h][2] - mu0), p3 = exp2f(sacc[h][3] - mu1);
+          l_run[h][0] += p0 + p2;
+          l_run[h][1] += p1 + p3;
+          // [key g][heads 2t, 2t+1] -> [head g][keys 2t, 2t+1]: the B operand of O^T += V^T P^T
+          pb[h][0] = movmatrix_trans(pack_bf16(p0, p1));
+          pb[h][1] = movmatrix_trans(pack_bf16(p2, p3));
+        }
+#pragma unroll
+        for (int dt = 0; dt < DT16; ++dt) {
+          uint32_t va[4];
+          ldmatrix_x4_trans(va, sV + dec_piece<D>(vrow, dt * 2 + ((lane >> 3) & 1)));
+#pragma unroll
+          for (int h = 0; h < NH; ++h) mma_bf16_16816(o[h][dt], va, pb[h][0], pb[h][1]);
+        }
+      }
+      __syncwarp();
+      if (lane == 0) tc::mbar_arrive(&empty[s]);  // this warp is done with the stage
+      if (!last) continue;
+
+      // ---- the CTA leaves this kv row: merge the warps' running states
+      const int seg = md.z, nsegs = md.w;
+      const int b = row / Hkv;  // absolute sequence index
+#pragma unroll
+      for (int h = 0; h < NH; ++h) {
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+          float l = l_run[h][j];
+          l += __shfl_xor_sync(0xffffffffu, l, 4);
+          l += __shfl_xor_sync(0xffffffffu, l, 8);
+          l += __shfl_xor_sync(0xffffffffu, l, 16);
+          const int hh = h * 8 + t * 2 + j;
+          if (hh < G) {
+            if (g == 0) {
+              wmax[warp * 16 + hh] = m_run[h][j];
+              wsum[warp * 16 + hh] = l;
+            }
+            float* dst = ored + ((size_t)warp * G + hh) * D + g;
+#pragma unroll
+            for (int dt = 0; dt < DT16; ++dt) {
+              dst[dt * 16] = o[h][dt][j];
+              dst[dt * 16 + 8] = o[h][dt][2 + j];
+            }
+          }
+        }
+      }
+      if (!rendezvous()) {
+        alive = false;
+        break;
+      }
+      for (int gq = 0; gq < G; ++gq) {
+        const int hq = hkv * G + gq;
+        float M = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < NW; ++w) M = fmaxf(M, wmax[w * 16 + gq]);
+        float f[NW], lsum = 0.f;
+#pragma unroll
+        for (int w = 0; w < NW; ++w) {
+          f[w] = wmax[w * 16 + gq] == -INFINITY ? 0.f : exp2f(wmax[w * 16 + gq] - M);
+          lsum += f[w] * wsum[w * 16 + gq];
+        }
+        float acc = 0.f;
+        if (tid < D) {
+          const float* src = ored + (size_t)gq * D + tid;
+#pragma unroll
+          for (int w = 0; w < NW; ++w) acc += f[w] * src[(size_t)w * G * D];
+        }
+        if (nsegs == 1) {  // the whole row was here
+          if (tid < D) out[(size_t)b * L.Hq * D + (size_t)hq * D + tid] = __float2bfloat16_rn(lsum > 0.f ? acc / lsum : 0.f);
+        } else {
+          float* pout = partial + ((size_t)(b * L.Hq + hq) * nslots + seg) * (D + 2);
+          if (tid < D) pout[2 + tid] = acc;
+          if (tid == 0) {
+            pout[0] = M;
+            pout[1] = lsum;
+          }
+        }
+      }
+      if (nsegs > 1) __threadfence();
+      if (!rendezvous()) {  // everybody has read the merge buffers (and fenced its partial results)
+        alive = false;
+        break;
+      }
+      if (nsegs > 1) {  // the last CTA of this kv row combines the partial results
+        if (tid == 0) {
+          const int prev = atomicAdd(&row_counters[row], 1);
+          s_flag = (prev == nsegs - 1);
+        }
+        if (!rendezvous()) {
+          alive = false;
+          break;
+        }
+        if (s_flag) {
+          __threadfence();
+          for (int gq = 0; gq < G; ++gq) {
+            const int hq = hkv * G + gq;
+            const float* pin = partial + ((size_t)(b * L.Hq + hq) * nslots) * (D + 2);
+            float M = -INFINITY;
+            for (int s2 = 0; s2 < nsegs; ++s2) M = fmaxf(M, __ldcg(pin + (size_t)s2 * (D + 2)));
+            if (tid < D) {
+              float Lsum = 0.f, a = 0.f;
+              for (int s2 = 0; s2 < nsegs; ++s2) {
+                const float ms = __ldcg(pin + (size_t)s2 * (D + 2));
+                const float w = ms == -INFINITY ? 0.f : exp2f(ms - M);
+                Lsum += w * __ldcg(pin + (size_t)s2 * (D + 2) + 1);
+                a += w * __ldcg(pin + (size_t)s2 * (D + 2) + 2 + tid);
+              }
+              out[(size_t)b * L.Hq * D + (size_t)hq * D + tid] = __float2bfloat16_rn(Lsum > 0.f ? a / Lsum : 0.f);
+            }
+          }
+          if (tid == 0) row_counters[row] = 0;
+        }
+      }
+    }
+    if (!alive && lane == 0) {
+      s_abort = 1;
+      atomicExch(status, KVM_ERR_DEVICE_TIMEOUT);
+    }
   }
-  cp_async_wait<0>();
+  if (*abort_flag) {
+    // somebody gave up: copies of this CTA may still be in flight, give them a bounded time to land
+    for (int k2 = 0; k2 < 1000; ++k2) __nanosleep(1000);
+  }
 
   // ---- the last CTA of the launch advances the lengths of the sequences in scope
   __syncthreads();
@@ -557,76 +655,190 @@ static int device_sm_count() {
   return n_sm;
 }
 
-template <int D>
-static cudaError_t launch_decode(const LayerDev& L, int batch, const DecodeCacheDev& cache, Tensor4 q, Tensor4 k,
-                                 Tensor4 v, Tensor4 gate, const int* n_append, int any_update, int max_rows, bf16* out,
-                                 int* route, bf16* pk_scr, bf16* gk_scr, float* partial, int* counters,
-                                 int rows_per_split, cudaStream_t stream) {
-  constexpr int NT = 512;
-  const int rows = batch * L.Hkv;
-  cudaError_t e;
-  if (any_update) {
-    const bool sb = update_block_fits_smem<D>(L.C, cache.mem.capacity);
-    const size_t smem_u = UpdateSmem<D>::bytes(L.C, cache.mem.capacity, sb);
-    auto kern = sb ? kvm_decode_pre_kernel<D, NT, true, true> : kvm_decode_pre_kernel<D, NT, true, false>;
-    e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_u);
-    if (e != cudaSuccess) return e;
-    kern<<<rows, NT, smem_u, stream>>>(L, cache, k, v, gate, n_append, pk_scr, route);
-  } else {
-    kvm_decode_pre_kernel<D, 32, false, false><<<rows, 32, 0, stream>>>(L, cache, k, v, gate, nullptr, pk_scr, route);
+typedef CUresult (*TensorMapEncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                      const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                      CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+// [rows][D] bf16 row array -> tensor map with boxes of kDecBoxRows rows x min(D, 64) elements
+static bool encode_rows_map(CUtensorMap* m, const void* base, uint64_t rows, int D) {
+  static TensorMapEncodeFn enc = nullptr;
+  if (!enc) {
+    void* fn = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres) != cudaSuccess || !fn) return false;
+    enc = reinterpret_cast<TensorMapEncodeFn>(fn);
   }
-  e = cudaGetLastError();
-  if (e != cudaSuccess) return e;
+  const cuuint64_t gdim[2] = {(cuuint64_t)D, rows};
+  const cuuint64_t gstr[1] = {(cuuint64_t)D * 2};
+  const cuuint32_t box[2] = {(cuuint32_t)(D >= 64 ? 64 : D), (cuuint32_t)kDecBoxRows};
+  const cuuint32_t es[2] = {1, 1};
+  return enc(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), gdim, gstr, box, es,
+             CU_TENSOR_MAP_INTERLEAVE_NONE, D >= 64 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
+             CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+// The tensor maps of a decode cache (small cache keyed by the array addresses and sizes: a serving loop
+// calls with the same cache every token).
+static bool decode_maps(const DecodeCacheDev& c, uint64_t kv_rows, int cap, int WC, int D, DecMaps* out) {
+  struct Entry {
+    const void *mk, *mv, *rk, *rv;
+    uint64_t kv_rows;
+    int cap, WC, D;
+    DecMaps maps;
+  };
+  static Entry cache[8];
+  static int n_used = 0, next = 0;
+  static std::mutex mu;
+  std::lock_guard<std::mutex> lock(mu);
+  for (int i = 0; i < n_used; ++i) {
+    const Entry& e = cache[i];
+    if (e.mk == c.mem.k_attn && e.mv == c.mem.v_attn && e.rk == c.ring_k && e.rv == c.ring_v && e.kv_rows == kv_rows &&
+        e.cap == cap && e.WC == WC && e.D == D) {
+      *out = e.maps;
+      return true;
+    }
+  }
+  Entry e;
+  e.mk = c.mem.k_attn; e.mv = c.mem.v_attn; e.rk = c.ring_k; e.rv = c.ring_v;
+  e.kv_rows = kv_rows; e.cap = cap; e.WC = WC; e.D = D;
+  if (!encode_rows_map(&e.maps.mem_k, c.mem.k_attn, kv_rows * (uint64_t)cap, D) ||
+      !encode_rows_map(&e.maps.mem_v, c.mem.v_attn, kv_rows * (uint64_t)cap, D) ||
+      !encode_rows_map(&e.maps.ring_k, c.ring_k, kv_rows * (uint64_t)WC, D) ||
+      !encode_rows_map(&e.maps.ring_v, c.ring_v, kv_rows * (uint64_t)WC, D))
+    return false;
+  cache[next] = e;
+  next = (next + 1) % 8;
+  if (n_used < 8) ++n_used;
+  *out = e.maps;
+  return true;
+}
+
+// Side stream and events for overlapping a boundary update with the attention of the other sequences
+// (created once per device, on first use).
+struct DecodeSide {
+  cudaStream_t stream = nullptr;
+  cudaEvent_t fork = nullptr, join = nullptr;
+  bool ok = false;
+};
+static DecodeSide* decode_side() {
+  static DecodeSide side[64];
+  static std::mutex mu;
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+  std::lock_guard<std::mutex> lock(mu);
+  DecodeSide& d = side[dev];
+  if (!d.ok) {
+    if (cudaStreamCreateWithFlags(&d.stream, cudaStreamNonBlocking) != cudaSuccess) return nullptr;
+    if (cudaEventCreateWithFlags(&d.fork, cudaEventDisableTiming) != cudaSuccess) return nullptr;
+    if (cudaEventCreateWithFlags(&d.join, cudaEventDisableTiming) != cudaSuccess) return nullptr;
+    d.ok = true;
+  }
+  return &d;
+}
+
+template <int D, int ST, int NH>
+static cudaError_t launch_decode_attn(const LayerDev& L, int batch, const DecodeCacheDev& cache, Tensor4 q,
+                                      const int* n_append, int max_rows, bf16* out, float* partial, int* counters,
+                                      int mode, int grid, const DecMaps& maps, cudaStream_t stream) {
   // The workspace holds `nslots` partial results per query head; a kv row of at most max_chunks chunks cut
   // into ranges of at least per_min chunks never needs more.
-  (void)rows_per_split;
-  (void)gk_scr;
-  const int G = L.Hq / L.Hkv;
-  if (G > 16) return cudaErrorInvalidValue;  // the query heads of a kv head form one M=16 MMA tile
+  const int G = L.Hq / L.Hkv, rows = batch * L.Hkv;
   const int nslots = (max_rows + kDecodeRowsPerSplit - 1) / kDecodeRowsPerSplit + 2;
   const int max_chunks = (max_rows + kDecChunk - 1) / kDecChunk + 3;
   const int per_min = (max_chunks + nslots - 2) / (nslots - 1);
-  auto kern = kvm_decode_attn_kernel<D>;
-  static size_t smem_set = 0, occ_smem = 0;  // largest dynamic shared memory enabled so far; occupancy cache
-  static int occ_cached = 0, dev_set = -1;
+  auto kern = kvm_decode_attn_kernel<D, ST, NH>;
+  static size_t smem_set = 0;  // largest dynamic shared memory enabled so far on dev_set
+  static int dev_set = -1;
   int dev_now = 0;
   cudaGetDevice(&dev_now);
   if (dev_now != dev_set) {  // function attributes are per device
-    smem_set = occ_smem = 0;
+    smem_set = 0;
     dev_set = dev_now;
   }
   for (int b0 = 0; b0 < batch; b0 += kDecMaxBatch) {
     const int nb = std::min(kDecMaxBatch, batch - b0);
-    const DecSmem lay(D, G, L.Hq, nb);
+    const DecSmem lay(D, G, L.Hq, nb, ST);
     if (lay.total > smem_set) {
-      e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)lay.total);
+      cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)lay.total);
       if (e != cudaSuccess) return e;
       smem_set = lay.total;
     }
-    if (occ_smem != lay.total) {
-      int occ = 0;
-      e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, kern, kDecThreads, lay.total);
-      if (e != cudaSuccess) return e;
-      occ_cached = std::max(1, occ);
-      occ_smem = lay.total;
-    }
-    const int grid = occ_cached * device_sm_count();
-    kern<<<grid, kDecThreads, lay.total, stream>>>(L, cache, q, any_update ? n_append : nullptr, partial, counters,
-                                                   counters + rows, out, 1.0f / sqrtf((float)D), b0, nb, nslots, per_min, 0);
-    e = cudaGetLastError();
+    kern<<<grid, kDecThreads, lay.total, stream>>>(L, cache, q, n_append, partial, counters, counters + rows,
+                                                   counters + rows + batch, out, 1.0f / sqrtf((float)D), b0, nb, nslots,
+                                                   per_min, mode, maps);
+    cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return e;
   }
   return cudaSuccess;
 }
 
+// `any_update`: number of sequences with a memory update at this token (0: none; any positive value is
+// treated as "some" when the count is not known).  `overlap`: a boundary update may run on the library's
+// side stream next to the attention of the sequences without one.
+template <int D>
+static cudaError_t launch_decode(const LayerDev& L, int batch, const DecodeCacheDev& cache, Tensor4 q, Tensor4 k,
+                                 Tensor4 v, Tensor4 gate, const int* n_append, int any_update, int max_rows, bf16* out,
+                                 int* route, bf16* pk_scr, bf16* gk_scr, float* partial, int* counters,
+                                 int overlap, cudaStream_t stream) {
+  constexpr int NT = 512;
+  (void)gk_scr;
+  const int rows = batch * L.Hkv, G = L.Hq / L.Hkv;
+  if (G > 16) return cudaErrorInvalidValue;  // the query heads of a kv head form one M=16 MMA tile
+  const int n_sm = device_sm_count();
+  // three stages when they fit beside the reduction buffers, else two
+  const bool st3 = DecSmem(D, G, L.Hq, std::min(batch, kDecMaxBatch), 3).total <= (size_t)kDecMaxSmem;
+  DecMaps maps;
+  if (!decode_maps(cache, (uint64_t)rows, cache.mem.capacity, L.W * L.C, D, &maps)) return cudaErrorInvalidValue;
+  auto attn = [&](int mode, int grid, const int* na) {
+    if (G <= 8)
+      return st3 ? launch_decode_attn<D, 3, 1>(L, batch, cache, q, na, max_rows, out, partial, counters, mode, grid, maps, stream)
+                 : launch_decode_attn<D, 2, 1>(L, batch, cache, q, na, max_rows, out, partial, counters, mode, grid, maps, stream);
+    return st3 ? launch_decode_attn<D, 3, 2>(L, batch, cache, q, na, max_rows, out, partial, counters, mode, grid, maps, stream)
+               : launch_decode_attn<D, 2, 2>(L, batch, cache, q, na, max_rows, out, partial, counters, mode, grid, maps, stream);
+  };
+  cudaError_t e;
+  if (!any_update) {
+    kvm_decode_pre_kernel<D, 32, false, false><<<rows, 32, 0, stream>>>(L, cache, k, v, gate, nullptr, pk_scr, route, 0);
+    e = cudaGetLastError();
+    if (e != cudaSuccess) return e;
+    return attn(0, n_sm, nullptr);
+  }
+  const bool sb = update_block_fits_smem<D>(L.C, cache.mem.capacity);
+  const size_t smem_u = UpdateSmem<D>::bytes(L.C, cache.mem.capacity, sb);
+  auto upd = sb ? kvm_decode_pre_kernel<D, NT, true, true> : kvm_decode_pre_kernel<D, NT, true, false>;
+  e = cudaFuncSetAttribute(upd, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_u);
+  if (e != cudaSuccess) return e;
+  const int upd_sms = any_update * L.Hkv;  // SMs the updating rows occupy (one CTA each)
+  DecodeSide* side = (overlap && any_update < batch && upd_sms * 2 <= n_sm) ? decode_side() : nullptr;
+  if (!side) {  // one stream: update + ring write for every row, then attention over everything
+    upd<<<rows, NT, smem_u, stream>>>(L, cache, k, v, gate, n_append, pk_scr, route, 0);
+    e = cudaGetLastError();
+    if (e != cudaSuccess) return e;
+    return attn(0, n_sm, n_append);
+  }
+  // fork: the updating sequences' rows on the side stream ...
+  if ((e = cudaEventRecord(side->fork, stream)) != cudaSuccess) return e;
+  if ((e = cudaStreamWaitEvent(side->stream, side->fork, 0)) != cudaSuccess) return e;
+  upd<<<rows, NT, smem_u, side->stream>>>(L, cache, k, v, gate, n_append, pk_scr, route, 2);
+  if ((e = cudaGetLastError()) != cudaSuccess) return e;
+  if ((e = cudaEventRecord(side->join, side->stream)) != cudaSuccess) return e;
+  // ... next to the ring write and the attention of all others, which leave those SMs free
+  kvm_decode_pre_kernel<D, 32, false, false><<<rows, 32, 0, stream>>>(L, cache, k, v, gate, n_append, pk_scr, route, 1);
+  if ((e = cudaGetLastError()) != cudaSuccess) return e;
+  if ((e = attn(1, n_sm - upd_sms, n_append)) != cudaSuccess) return e;
+  // join: attention of the updated sequences
+  if ((e = cudaStreamWaitEvent(stream, side->join, 0)) != cudaSuccess) return e;
+  return attn(2, n_sm, n_append);
+}
+
 cudaError_t decode_dispatch(int D, const LayerDev& L, int batch, const DecodeCacheDev& cache, Tensor4 q, Tensor4 k,
                             Tensor4 v, Tensor4 gate, const int* n_append, int any_update, int max_rows, bf16* out,
-                            int* route, bf16* pk_scr, bf16* gk_scr, float* partial, int* counters, int rows_per_split,
+                            int* route, bf16* pk_scr, bf16* gk_scr, float* partial, int* counters, int overlap,
                             cudaStream_t stream) {
   switch (D) {
-    case 32: return launch_decode<32>(L, batch, cache, q, k, v, gate, n_append, any_update, max_rows, out, route, pk_scr, gk_scr, partial, counters, rows_per_split, stream);
-    case 64: return launch_decode<64>(L, batch, cache, q, k, v, gate, n_append, any_update, max_rows, out, route, pk_scr, gk_scr, partial, counters, rows_per_split, stream);
-    case 128: return launch_decode<128>(L, batch, cache, q, k, v, gate, n_append, any_update, max_rows, out, route, pk_scr, gk_scr, partial, counters, rows_per_split, stream);
+    case 32: return launch_decode<32>(L, batch, cache, q, k, v, gate, n_append, any_update, max_rows, out, route, pk_scr, gk_scr, partial, counters, overlap, stream);
+    case 64: return launch_decode<64>(L, batch, cache, q, k, v, gate, n_append, any_update, max_rows, out, route, pk_scr, gk_scr, partial, counters, overlap, stream);
+    case 128: return launch_decode<128>(L, batch, cache, q, k, v, gate, n_append, any_update, max_rows, out, route, pk_scr, gk_scr, partial, counters, overlap, stream);
   }
   return cudaErrorInvalidValue;
 }

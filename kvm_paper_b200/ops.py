@@ -406,7 +406,8 @@ class KvmDecodeCache:
                          self.total_len.data_ptr(), self.state_len.data_ptr())
         rc = lib.kvm_decode_step(
             C.byref(self.params.c), B, ccache, _tensor4(q, "q"), _tensor4(k, "k"), _tensor4(v, "v"),
-            _tensor4(gate, "gate"), self._n_append.data_ptr() if any_update else None, int(any_update),
+            _tensor4(gate, "gate"), self._n_append.data_ptr() if any_update else None,
+            int((n_app >= 0).sum()) if any_update else 0,
             min(max_rows, self._max_rows_bound), self.out.data_ptr(),
             _ptr(self.route) if (any_update and want_route) else None,
             self._ws.data_ptr(), self._ws_bytes, _stream_ptr(self.device))
@@ -430,7 +431,7 @@ class KvmDecodeCache:
             na, mr = self._plan_step()
             if na is not None:
                 n_app_all[i] = na
-                any_upd[i] = 1
+                any_upd[i] = int((na >= 0).sum())
             max_rows[i] = min(mr, self.memory.capacity + self.ring_capacity)
         if int(self.state_len_h.max()) > self.memory.capacity:
             self._reserve(int(self.state_len_h.max()))
