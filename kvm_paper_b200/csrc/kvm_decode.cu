@@ -22,6 +22,13 @@ __device__ __forceinline__ int bswa_begin_dev(int total, int C, int W) {
   return max(0, end - W * C);
 }
 
+// Programmatic dependent launch: a kernel launched with the programmatic-serialization attribute may start
+// while its predecessor in the stream still runs; pdl_wait() returns once the predecessor has completed
+// and its writes are visible (at once if the launch did not carry the attribute); pdl_trigger() lets the
+// successor start early.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 // ------------------------------------------------------------------------------------------- pre
 template <int D, int NT, bool UPDATE, bool SB>
 __global__ void __launch_bounds__(NT, 1)
@@ -30,6 +37,8 @@ kvm_decode_pre_kernel(LayerDev L, DecodeCacheDev cache, Tensor4 k, Tensor4 v, Te
   extern __shared__ __align__(16) unsigned char smem_raw[];
   const int row = blockIdx.x;
   const int b = row / L.Hkv, h = row % L.Hkv;
+  pdl_wait();     // the previous token's attention kernel has advanced the lengths
+  pdl_trigger();  // this token's attention kernel may set itself up meanwhile
   if (scope) {  // 1: only sequences without a memory update at this token, 2: only those with one
     const int na = n_append_arr ? n_append_arr[b] : -1;
     if ((scope == 1 && na >= 0) || (scope == 2 && na < 0)) return;
@@ -197,7 +206,8 @@ kvm_decode_attn_kernel(LayerDev L, DecodeCacheDev cache, Tensor4 q, const int* _
   constexpr int BOXW = D >= 64 ? 64 : D;              // box width in elements
   constexpr int NBLK = D / BOXW;                      // boxes side by side per row group
   constexpr uint32_t kBoxBytes = (uint32_t)kDecBoxRows * BOXW * 2;
-  extern __shared__ __align__(1024) unsigned char smem_raw[];
+  extern __shared__ __align__(1024) unsigned char dsm_raw[];
+  unsigned char* smem_raw = dsm_raw;
   const int G = L.Hq / L.Hkv, Hkv = L.Hkv;
   const DecSmem lay(D, G, L.Hq, nb, ST);
   unsigned char* stage0 = smem_raw + lay.stages;
@@ -277,6 +287,7 @@ kvm_decode_attn_kernel(LayerDev L, DecodeCacheDev cache, Tensor4 q, const int* _
   const int f_begin = cta * per, f_end = min(total_f, f_begin + per);
   const int nloc = f_end - f_begin;
   volatile int* abort_flag = &s_abort;
+  pdl_trigger();  // the next token's ring-write kernel may be staged (it waits for this grid to complete)
 
   if (warp == NW) {
     // =============================================================== producer warp (lanes in lockstep)
@@ -295,6 +306,7 @@ kvm_decode_attn_kernel(LayerDev L, DecodeCacheDev cache, Tensor4 q, const int* _
       pc = rem - ph * pcb;
       pg = dec_geometry(sq_S[pb], sq_tot[pb], C, W);
     }
+    pdl_wait();  // the ring rows of this token are written (everything above only needs the lengths)
     for (int i = 0; i < nloc; ++i) {
       const int s = i % ST;
       if (i >= ST) {  // the math warps are done with the chunk that used this stage
@@ -736,10 +748,27 @@ static DecodeSide* decode_side() {
   return &d;
 }
 
+// Launch with the programmatic-serialization attribute when `pdl` is set (see pdl_wait above).
+template <typename... KArgs, typename... Args>
+static cudaError_t launch_pdl(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, bool pdl,
+                              Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kern, KArgs(args)...);
+}
+
 template <int D, int ST, int NH>
 static cudaError_t launch_decode_attn(const LayerDev& L, int batch, const DecodeCacheDev& cache, Tensor4 q,
                                       const int* n_append, int max_rows, bf16* out, float* partial, int* counters,
-                                      int mode, int grid, const DecMaps& maps, cudaStream_t stream) {
+                                      int mode, int grid, const DecMaps& maps, bool pdl, cudaStream_t stream) {
   // The workspace holds `nslots` partial results per query head; a kv row of at most max_chunks chunks cut
   // into ranges of at least per_min chunks never needs more.
   const int G = L.Hq / L.Hkv, rows = batch * L.Hkv;
@@ -763,10 +792,9 @@ static cudaError_t launch_decode_attn(const LayerDev& L, int batch, const Decode
       if (e != cudaSuccess) return e;
       smem_set = lay.total;
     }
-    kern<<<grid, kDecThreads, lay.total, stream>>>(L, cache, q, n_append, partial, counters, counters + rows,
-                                                   counters + rows + batch, out, 1.0f / sqrtf((float)D), b0, nb, nslots,
-                                                   per_min, mode, maps);
-    cudaError_t e = cudaGetLastError();
+    cudaError_t e = launch_pdl(kern, dim3(grid), dim3(kDecThreads), lay.total, stream, pdl && batch <= kDecMaxBatch, L, cache, q,
+                               n_append, partial, counters, counters + rows, counters + rows + batch, out,
+                               1.0f / sqrtf((float)D), b0, nb, nslots, per_min, mode, maps);
     if (e != cudaSuccess) return e;
   }
   return cudaSuccess;
@@ -789,19 +817,33 @@ static cudaError_t launch_decode(const LayerDev& L, int batch, const DecodeCache
   const bool st3 = DecSmem(D, G, L.Hq, std::min(batch, kDecMaxBatch), 3).total <= (size_t)kDecMaxSmem;
   DecMaps maps;
   if (!decode_maps(cache, (uint64_t)rows, cache.mem.capacity, L.W * L.C, D, &maps)) return cudaErrorInvalidValue;
-  auto attn = [&](int mode, int grid, const int* na) {
+  auto attn = [&](int mode, int grid, const int* na, bool pdl = false) {
     if (G <= 8)
-      return st3 ? launch_decode_attn<D, 3, 1>(L, batch, cache, q, na, max_rows, out, partial, counters, mode, grid, maps, stream)
-                 : launch_decode_attn<D, 2, 1>(L, batch, cache, q, na, max_rows, out, partial, counters, mode, grid, maps, stream);
-    return st3 ? launch_decode_attn<D, 3, 2>(L, batch, cache, q, na, max_rows, out, partial, counters, mode, grid, maps, stream)
-               : launch_decode_attn<D, 2, 2>(L, batch, cache, q, na, max_rows, out, partial, counters, mode, grid, maps, stream);
+      return st3 ? launch_decode_attn<D, 3, 1>(L, batch, cache, q, na, max_rows, out, partial, counters, mode, grid, maps, pdl, stream)
+                 : launch_decode_attn<D, 2, 1>(L, batch, cache, q, na, max_rows, out, partial, counters, mode, grid, maps, pdl, stream);
+    return st3 ? launch_decode_attn<D, 3, 2>(L, batch, cache, q, na, max_rows, out, partial, counters, mode, grid, maps, pdl, stream)
+               : launch_decode_attn<D, 2, 2>(L, batch, cache, q, na, max_rows, out, partial, counters, mode, grid, maps, pdl, stream);
   };
   cudaError_t e;
+  {
+    // The ring-write kernel runs between attention kernels that use nearly all shared memory of an SM:
+    // give it the same shared-memory carve-out so that the SMs are not reconfigured twice per token.
+    static int carve_dev = -1;
+    int dev_now = 0;
+    cudaGetDevice(&dev_now);
+    if (dev_now != carve_dev) {
+      cudaFuncSetAttribute(kvm_decode_pre_kernel<D, 32, false, false>, cudaFuncAttributePreferredSharedMemoryCarveout,
+                           (int)cudaSharedmemCarveoutMaxShared);
+      carve_dev = dev_now;
+    }
+  }
   if (!any_update) {
-    kvm_decode_pre_kernel<D, 32, false, false><<<rows, 32, 0, stream>>>(L, cache, k, v, gate, nullptr, pk_scr, route, 0);
-    e = cudaGetLastError();
+    // plain token: the two kernels are chained with programmatic dependent launches (`overlap` callers only)
+    const bool pdl = overlap != 0;
+    e = launch_pdl(kvm_decode_pre_kernel<D, 32, false, false>, dim3(rows), dim3(32), 0, stream, pdl, L, cache, k, v, gate,
+                   (const int*)nullptr, pk_scr, route, 0);
     if (e != cudaSuccess) return e;
-    return attn(0, n_sm, nullptr);
+    return attn(0, n_sm, nullptr, pdl);
   }
   const bool sb = update_block_fits_smem<D>(L.C, cache.mem.capacity);
   const size_t smem_u = UpdateSmem<D>::bytes(L.C, cache.mem.capacity, sb);
