@@ -67,26 +67,36 @@ def test_decode_after_prefill_matches_oracle(name):
     assert cache.state_len.cpu().tolist() == [S] * B
 
 
-def test_decode_ragged_batch_matches_per_sequence_oracle():
+RAGGED_CASES = {
+    # query heads, kv heads, head dim, rope dim, block, contexts, decode steps
+    "gqa2_d64": (4, 2, 64, 32, 32, [70, 150, 97, 255, 31, 128], 70),
+    # 16 query heads on one kv head (two 8-wide head tiles per MMA), rows longer than one 128-row chunk
+    "gqa16_d128": (16, 1, 128, 64, 128, [380, 640, 127, 500], 40),
+    # one query head per kv head, head dim 32 (unswizzled TMA boxes)
+    "mha_d32": (2, 2, 32, 16, 64, [200, 66, 450], 70),
+}
+
+
+@pytest.mark.parametrize("case", sorted(RAGGED_CASES))
+def test_decode_ragged_batch_matches_per_sequence_oracle(case):
     """Sequences with different context lengths in one batch (the reference cannot batch these): every
     sequence is checked against its own B=1 oracle run; different sequences cross block boundaries at
     different steps."""
     torch.manual_seed(21)
-    spec = ko.KvmSpec(4, 2, 64, 64, 32, 32, 2, 8, 1, "power_law", state_growth_factor=4.0, state_min_len=32)
-    lens = [70, 150, 97, 255, 31, 128]
-    n_steps = 70
+    Hq, Hkv, D, rope, C, lens, n_steps = RAGGED_CASES[case]
+    spec = ko.KvmSpec(Hq, Hkv, D, D, rope, C, 2, 8, 1, "power_law", state_growth_factor=4.0, state_min_len=C)
     B = len(lens)
     params = gh.layer_params(spec)
     states, inputs = [], []
-    cache = ops.KvmDecodeCache(params, B, 64, gh.desired_fn(spec))
+    cache = ops.KvmDecodeCache(params, B, 2 * C, gh.desired_fn(spec))
     for b, T in enumerate(lens):
-        q = torch.randn(1, 4, T + n_steps, 64).bfloat16()
-        k = torch.nn.functional.layer_norm(torch.randn(1, 2, T + n_steps, 64), (64,)).bfloat16()
-        v = torch.randn(1, 2, T + n_steps, 64).bfloat16()
-        g = (1 + torch.nn.functional.elu(torch.randn(1, 2, T + n_steps, 1))).bfloat16()
+        q = torch.randn(1, Hq, T + n_steps, D).bfloat16()
+        k = torch.nn.functional.layer_norm(torch.randn(1, Hkv, T + n_steps, D), (D,)).bfloat16()
+        v = torch.randn(1, Hkv, T + n_steps, D).bfloat16()
+        g = (1 + torch.nn.functional.elu(torch.randn(1, Hkv, T + n_steps, 1))).bfloat16()
         inputs.append((q, k, v, g))
         _, plan, res = gh.device_prefill(spec, q[:, :, :T], k[:, :, :T], v[:, :, :T], g[:, :, :T])
-        forced = [gh.decisions_from_route(res.route[:, u], 1, 2) for u in range(1, plan.n_updates + 1)]
+        forced = [gh.decisions_from_route(res.route[:, u], 1, Hkv) for u in range(1, plan.n_updates + 1)]
         with torch.no_grad():
             _, st = ko.prefill(spec, q[:, :, :T], k[:, :, :T], v[:, :, :T], g[:, :, :T], forced=forced)
         states.append(st)
@@ -104,7 +114,7 @@ def test_decode_ragged_batch_matches_per_sequence_oracle():
         for b in range(B):
             forced = None
             if cache._last_n_append is not None and cache._last_n_append[b] >= 0:
-                forced = gh.decisions_from_route(cache.route[b * 2:(b + 1) * 2], 1, 2)
+                forced = gh.decisions_from_route(cache.route[b * Hkv:(b + 1) * Hkv], 1, Hkv)
             with torch.no_grad():
                 y, states[b] = ko.decode_step(spec, *(t[b:b + 1] for t in step_in), states[b], trace=traces[b], forced=forced)
             assert_close_bf16(out[b:b + 1], y, f"seq {b} step {i}", mean_rel_tol=5e-3)
@@ -114,7 +124,7 @@ def test_decode_ragged_batch_matches_per_sequence_oracle():
         assert sd["kvm_s_k"].size(2) == states[b]["kvm_s_k"].size(2)
         assert torch.equal(sd["kvm_bswa_k"].cpu(), states[b]["kvm_bswa_k"])
     assert cache.total_len.cpu().tolist() == [t + n_steps for t in lens]
-    assert sum(len(t) for t in traces) >= 8  # several boundary updates happened
+    assert sum(len(t) for t in traces) >= 2  # boundary updates happened
 
 
 def test_decode_adopts_reference_eager_cache():
