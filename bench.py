@@ -255,9 +255,9 @@ def run_b200(args):
     pairs = attention_pairs(T, C, W, plan)
     attn_flops = 4.0 * D * pairs * B * h_loc          # QK^T and PV of this rank's heads
     achieved = attn_flops / (attn_ms * 1e-3) / 1e12
-    roofline = {"bound": "tensor", "kernel": "kvm_attn_prefill_kernel", "achieved": round(achieved, 2),
+    roofline = {"bound": "tensor", "kernel": "kvm_attn_prefill_tc_kernel", "achieved": round(achieved, 2),
                 "peak": peaks["bf16_tflops"], "unit": "TFLOP/s", "frac": round(achieved / peaks["bf16_tflops"], 4),
-                "peak_source": peaks["source"], "traffic": _traffic("attn_prefill", B * h_loc * T),
+                "peak_source": peaks["source"], "traffic": _traffic("kvm_attn_prefill_tc_kernel", B * h_loc * T),
                 "ms": round(attn_ms, 4), "chain_ms": round(chain_ms, 4),
                 "algorithmic_flops": attn_flops}
 
@@ -321,16 +321,20 @@ def run_b200(args):
         dist.destroy_process_group()
 
 
+# DRAM traffic of the dominant kernels from ncu captures (dram__bytes_read.sum + dram__bytes_write.sum of one
+# launch), scaled to this run's launch by the units it processes; the captures and their commands are the
+# summaries under profiles/ named after these kernels.
+NCU_TRAFFIC = {
+    # B1 x T16384 x 16 heads: 289.0 MB + 61.8 MB per launch -> bytes per (head, token)
+    "kvm_attn_prefill_tc_kernel": (289.0e6 + 61.8e6) / (16 * 16384),
+    # decode workload of this bench: 399.0 MB + 3.6 MB per launch for 397 MB of algorithmic K/V rows
+    "kvm_decode_attn_kernel": (399.0e6 + 3.6e6) / 397.0e6,
+}
+
+
 def _traffic(kernel, units):
-    """DRAM bytes per launch from the committed ncu summary (bytes per unit x units), or None."""
-    path = os.path.join(ROOT, "profiles", "traffic.json")
-    if not os.path.exists(path):
-        return None
-    with open(path) as f:
-        t = json.load(f)
-    if kernel not in t:
-        return None
-    return t[kernel]["dram_bytes_per_unit"] * units
+    """DRAM bytes per launch: ncu bytes per unit (see NCU_TRAFFIC) x the units of one launch."""
+    return round(NCU_TRAFFIC[kernel] * units) if kernel in NCU_TRAFFIC else None
 
 
 def run_decode(args, dev, rank, world, peaks):
@@ -435,7 +439,9 @@ def run_decode(args, dev, rank, world, peaks):
             "roofline": {"bound": "hbm", "kernel": "kvm_decode_attn_kernel", "achieved": round(gbs, 1),
                          "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": round(gbs / peaks["hbm_gbs"], 4),
                          "peak_source": peaks["source"],
-                         "note": "algorithmic K/V bytes of all steps / whole-step device time (ring write, boundary updates and combine included)"}}
+                         "traffic": _traffic("kvm_decode_attn_kernel", float(nb.item()) / world / steps),
+                         "note": "algorithmic K/V bytes of all steps / whole-step device time (ring write, boundary updates "
+                                 "and combine included); achieved, traffic per token"}}
 
 
 # ------------------------------------------------------------------------------------ CPU oracle
