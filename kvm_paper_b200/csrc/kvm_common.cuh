@@ -217,14 +217,28 @@ __device__ __forceinline__ float row_norm(const RowVec<D, GL>& r) {
   return sqrtf(group_sum<GL>(s));
 }
 
+// x[i] / n for one shared divisor: one refined reciprocal, then per element a product and one residual
+// correction (the textbook correctly-rounded division with the reciprocal shared across the row).
+template <int N>
+__device__ __forceinline__ void divide_by(float (&x)[N], float n) {
+  const float r0 = __frcp_rn(n);
+  const float r = fmaf(fmaf(-n, r0, 1.0f), r0, r0);
+#pragma unroll
+  for (int i = 0; i < N; ++i) {
+    const float q = x[i] * r;
+    x[i] = fmaf(fmaf(-q, n, x[i]), r, q);
+  }
+}
+
 // Attention view of one memory row: k_attn = LN(k_sum), v_attn = v_sum / max(|v_sum|, 1e-12) * vlen.
 template <int D, int GL = 32>
 __device__ __forceinline__ void refresh_memory_row(const LayerDev& L, RowVec<D, GL> ks, RowVec<D, GL> vs, float vlen,
                                                    bf16* k_attn_row, bf16* v_attn_row, int gl, bool do_store = true) {
   layer_norm_row<D, GL>(ks, L.ln_w, L.ln_b, L.ln_eps, gl);
   float n = fmaxf(row_norm<D, GL>(vs), 1e-12f);
+  divide_by(vs.x, n);
 #pragma unroll
-  for (int i = 0; i < D / GL; ++i) vs.x[i] = __fdiv_rn(vs.x[i], n) * vlen;
+  for (int i = 0; i < D / GL; ++i) vs.x[i] *= vlen;
   if (do_store) {
     store_row<D, GL>(ks, k_attn_row, gl);
     store_row<D, GL>(vs, v_attn_row, gl);

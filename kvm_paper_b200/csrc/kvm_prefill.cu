@@ -32,10 +32,21 @@ kvm_prepare_keys_kernel(LayerDev L, Tensor4 k, bf16* __restrict__ pk_all, long l
 // after the last update the final view is gathered into `mem.k_attn` / `mem.v_attn`.
 template <int D, int NT, bool SB>
 __global__ void __launch_bounds__(NT, 1)
-kvm_chain_kernel(LayerDev L, long long T, Tensor4 k, Tensor4 v, Tensor4 gate, const kvm_update_plan* __restrict__ plan,
+kvm_chain_kernel(LayerDev L_in, long long T, Tensor4 k, Tensor4 v, Tensor4 gate, const kvm_update_plan* __restrict__ plan,
                  int n_plan, MemoryDev mem, bf16* pool_k, bf16* pool_v, long long pool_rows, int* ver_idx,
                  long long ver_rows, bf16* pk_scr, const bf16* __restrict__ pk_all, int* route, int nc) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
+  // LayerNorm weights in shared memory: almost all of the SM's L1 is carved out as shared memory, so every
+  // LayerNorm of the chain would otherwise pay an L2 round trip for them
+  __shared__ float ln_s[2 * D];
+  for (int i = threadIdx.x; i < D; i += NT) {
+    ln_s[i] = L_in.ln_w[i];
+    ln_s[D + i] = L_in.ln_b[i];
+  }
+  LayerDev L = L_in;
+  L.ln_w = ln_s;
+  L.ln_b = ln_s + D;
+  __syncthreads();
   UpdateSmem<D> s;
   s.carve(smem_raw, L.C, mem.capacity, SB);
   const int row = blockIdx.x / nc;     // the nc CTAs of a cluster share one kv row

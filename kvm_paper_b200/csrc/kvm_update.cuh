@@ -40,6 +40,7 @@ __device__ long long g_phase_cycles[16];
 #endif
 
 constexpr int kScanTile = 64;  // memory rows per shared-memory tile of the routing GEMM
+constexpr int kDirectRows = 4; // up to this many appended rows are scored with plain dot products
 
 struct TokenSrc {  // the C tokens consumed by one update; token t at base + t*stride
   const bf16* k;
@@ -126,7 +127,7 @@ struct UpdateSmem {
   }
 };
 
-constexpr size_t kSmemLimit = 227 * 1024;
+constexpr size_t kSmemLimit = 225 * 1024;  // dynamic part: the kernels also hold ~1 KB of static shared memory
 
 template <int D>
 __host__ __device__ inline bool update_block_fits_smem(int C, int capacity) {
@@ -156,6 +157,35 @@ __device__ __forceinline__ uint32_t mul_bf16x2(uint32_t a, __nv_bfloat162 g2) {
   __nv_bfloat162 x = *reinterpret_cast<__nv_bfloat162*>(&a);
   x = __hmul2(x, g2);
   return *reinterpret_cast<uint32_t*>(&x);
+}
+
+// acc += row (optionally times the gate, rounded to bf16 first) for the EPL elements of this lane; the gated
+// product is formed on packed bf16 pairs (the product of two bf16 numbers rounds the same way everywhere).
+template <int D, int GL>
+__device__ __forceinline__ void accumulate_row(RowVec<D, GL>& acc, const bf16* row, int gl, bool gated, float gate) {
+  constexpr int EPL = D / GL;
+  const bf16* p = row + gl * EPL;
+  const __nv_bfloat162 g2 = __float2bfloat162_rn(gate);
+  if constexpr (EPL % 8 == 0) {
+#pragma unroll
+    for (int c = 0; c < EPL / 8; ++c) {
+      uint4 u = *reinterpret_cast<const uint4*>(p + c * 8);
+      if (gated) {
+        u.x = mul_bf16x2(u.x, g2);
+        u.y = mul_bf16x2(u.y, g2);
+        u.z = mul_bf16x2(u.z, g2);
+        u.w = mul_bf16x2(u.w, g2);
+      }
+      const float2 a = unpack_bf16(u.x), b = unpack_bf16(u.y), d = unpack_bf16(u.z), e = unpack_bf16(u.w);
+      acc.x[c * 8 + 0] += a.x; acc.x[c * 8 + 1] += a.y; acc.x[c * 8 + 2] += b.x; acc.x[c * 8 + 3] += b.y;
+      acc.x[c * 8 + 4] += d.x; acc.x[c * 8 + 5] += d.y; acc.x[c * 8 + 6] += e.x; acc.x[c * 8 + 7] += e.y;
+    }
+  } else {
+    RowVec<D, GL> r;
+    load_row<D, GL>(r, row, gl);
+#pragma unroll
+    for (int e = 0; e < EPL; ++e) acc.x[e] += gated ? bf16_round(r.x[e] * gate) : r.x[e];
+  }
 }
 
 // Issue the cp.async copies of one tile of memory rows [row0, row0+kScanTile) (rows >= n_end zero-filled).
@@ -236,27 +266,42 @@ __device__ __noinline__ void scan_memory(const BlockView& blk, bool gate_keys, i
       if (active) {
         const bf16* bt = s.btile + (size_t)cur * kScanTile * STR;
         const int tile_base = n_begin + it * kScanTile;
+        // two 8-row groups of the tile at a time: four independent accumulation chains keep the MMA pipe fed
 #pragma unroll
-        for (int nt = 0; nt < kScanTile / 8; ++nt) {
+        for (int nt = 0; nt < kScanTile / 8; nt += 2) {
           if (tile_base + nt * 8 >= n_end) break;
-          float cg[4] = {0.f, 0.f, 0.f, 0.f}, cp[4] = {0.f, 0.f, 0.f, 0.f};
-          const bf16* brow = bt + (size_t)(nt * 8 + g) * STR + t * 2;
+          float cg[2][4], cp[2][4];
+#pragma unroll
+          for (int h = 0; h < 2; ++h)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) cg[h][e] = cp[h][e] = 0.f;
+          const bf16* brow0 = bt + (size_t)(nt * 8 + g) * STR + t * 2;
+          const bf16* brow1 = brow0 + (size_t)8 * STR;
 #pragma unroll
           for (int ks = 0; ks < KS; ++ks) {
-            uint32_t b0 = *reinterpret_cast<const uint32_t*>(brow + ks * 16);
-            uint32_t b1 = *reinterpret_cast<const uint32_t*>(brow + ks * 16 + 8);
-            mma_bf16_16816(cg, ag[ks], b0, b1);
-            if (want_app) mma_bf16_16816(cp, ap[ks], b0, b1);
+            const uint32_t b00 = *reinterpret_cast<const uint32_t*>(brow0 + ks * 16);
+            const uint32_t b01 = *reinterpret_cast<const uint32_t*>(brow0 + ks * 16 + 8);
+            const uint32_t b10 = *reinterpret_cast<const uint32_t*>(brow1 + ks * 16);
+            const uint32_t b11 = *reinterpret_cast<const uint32_t*>(brow1 + ks * 16 + 8);
+            mma_bf16_16816(cg[0], ag[ks], b00, b01);
+            mma_bf16_16816(cg[1], ag[ks], b10, b11);
+            if (want_app) {
+              mma_bf16_16816(cp[0], ap[ks], b00, b01);
+              mma_bf16_16816(cp[1], ap[ks], b10, b11);
+            }
           }
 #pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            const int r = e >> 1;
-            const int n = tile_base + nt * 8 + t * 2 + (e & 1);
-            if (n < n_end) {
-              if (want_app) amax[r] = fmaxf(amax[r], bf16_round(cp[e]));
-              if (n >= protected_rows && (cg[e] > bbest[r] || bidx[r] < 0)) {
-                bbest[r] = cg[e];
-                bidx[r] = n;
+          for (int h = 0; h < 2; ++h) {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              const int r = e >> 1;
+              const int n = tile_base + (nt + h) * 8 + t * 2 + (e & 1);
+              if (n < n_end) {
+                if (want_app) amax[r] = fmaxf(amax[r], bf16_round(cp[h][e]));
+                if (n >= protected_rows && (cg[h][e] > bbest[r] || bidx[r] < 0)) {
+                  bbest[r] = cg[h][e];
+                  bidx[r] = n;
+                }
               }
             }
           }
@@ -421,7 +466,36 @@ __device__ void memory_update(const LayerDev& L, const TokenSrc& src, const Memo
     }
   }
   KVM_PHASE_MARK(2);
-  if (n_append > 0 && n_merge > 0) {
+  if (n_append == 1 && n_merge > 0) {
+    // one append: the token with the lowest novelty score, lowest index among equals (= rank 0 of the
+    // stable ranking below), found by a block-wide reduction instead of the O(C) count per token
+    float bv = tid < C ? s.app[tid] : INFINITY;
+    int bt = tid < C ? tid : 0x7fffffff;
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, bv, off);
+      const int ot = __shfl_xor_sync(0xffffffffu, bt, off);
+      if (ov < bv || (ov == bv && ot < bt)) { bv = ov; bt = ot; }
+    }
+    float* red_v = reinterpret_cast<float*>(s.counters + 4);   // [32] per-warp candidates (reused right below)
+    int* red_t = s.tstart;                                      // [C] scratch at this point of the update
+    if (lane == 0) { red_v[warp] = bv; red_t[warp] = bt; }
+    __syncthreads();
+    if (warp == 0) {
+      bv = lane < NT / 32 ? red_v[lane] : INFINITY;
+      bt = lane < NT / 32 ? red_t[lane] : 0x7fffffff;
+#pragma unroll
+      for (int off = 16; off > 0; off >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, bv, off);
+        const int ot = __shfl_xor_sync(0xffffffffu, bt, off);
+        if (ov < bv || (ov == bv && ot < bt)) { bv = ov; bt = ot; }
+      }
+      if (lane == 0) s.counters[2] = bt;
+    }
+    __syncthreads();
+    if (tid < C) s.flag[tid] = tid == s.counters[2] ? 1 : 0;
+    __syncthreads();
+  } else if (n_append > 0 && n_merge > 0) {
     if (tid < C) {
       const float si = s.app[tid];
       int rank = 0;
@@ -456,6 +530,7 @@ __device__ void memory_update(const LayerDev& L, const TokenSrc& src, const Memo
     for (int base = 0; base < n_append; base += GROUPS) {
       const int p_ = base + grp;
       const bool act = p_ < n_append && (S_before + p_) < capacity && (p_ % nc == crank);
+      if (!__any_sync(0xffffffffu, act)) continue;  // no row for this warp (the refresh uses group shuffles: whole warps only)
       const int t_ = s.list[p_ < n_append ? p_ : 0];
       const int row = act ? S_before + p_ : 0;
       RowVec<D, GL> kr, vr;
@@ -499,35 +574,81 @@ __device__ void memory_update(const LayerDev& L, const TokenSrc& src, const Memo
   KVM_PHASE_MARK(4);
 
   // ---- 3. merge targets among the rows that were just appended (append-before-merge)
-  if (n_append > 0)
+  if (n_append > 0 && n_append <= kDirectRows) {
+    // few new rows: fp32 dot products of every token's gated key with them, 8 lanes per token (fixed
+    // summation order), instead of a tensor-core pass; a new row wins only with a strictly larger logit
+    for (int r = max(S_before, protected_rows); r < S_after; ++r) {
+      const int slot = pool ? view.cur[r] : r;
+      RowVec<D, GL> mr;  // this lane's 16 elements of the new row (one global read per row)
+      load_row<D, GL>(mr, view.k + (size_t)slot * D, gl);
+      for (int base = 0; base < C; base += GROUPS) {
+        const int tkn = base + grp;
+        const bool act = tkn < C;
+        const int t_ = act ? tkn : 0;
+        RowVec<D, GL> kr;
+        load_row<D, GL>(kr, blk.pk + (size_t)t_ * blk.pk_st, gl);
+        float acc = 0.f;
+        if (L.gate_keys) {
+          const float gt = s.g_s[t_];
+#pragma unroll
+          for (int i = 0; i < D / GL; ++i) acc = fmaf(bf16_round(kr.x[i] * gt), mr.x[i], acc);
+        } else {
+#pragma unroll
+          for (int i = 0; i < D / GL; ++i) acc = fmaf(kr.x[i], mr.x[i], acc);
+        }
+        acc = group_sum<GL>(acc);
+        if (act && gl == 0 && (s.idx[t_] < 0 || acc > s.best[t_])) {
+          s.best[t_] = acc;
+          s.idx[t_] = r;
+        }
+      }
+    }
+    __syncthreads();
+  } else if (n_append > 0) {
     scan_memory<D, NT>(blk, L.gate_keys != 0, C, view.k, view.cur, S_before, S_after, false, protected_rows, s);
+  }
   KVM_PHASE_MARK(5);
 
   // ---- 4. group the merged tokens by target row, token order inside a group
   if (tid < C && s.flag[tid]) s.idx[tid] = -1;
   __syncthreads();
   bool is_leader = false;
-  if (tid < C) {
-    const int mine = s.idx[tid];
+  int ltok = 0;  // the token this thread leads (valid if is_leader)
+  {
+    // per merged token: how many tokens with the same target come before it, how many there are, which is
+    // the first.  With 2C <= NT two threads share a token, each counting over one half of the block.
+    const bool pair = 2 * C <= NT;
+    const int tok = pair ? tid >> 1 : tid;
+    const int half = pair ? tid & 1 : 0;
+    const int lo = pair ? half * (C / 2) : 0, hi = pair ? lo + C / 2 : C;
+    const int mine = tok < C ? s.idx[tok] : -1;
+    int before = 0, total = 0, first = C;
     if (mine >= 0) {
-      int before = 0, total = 0, first = tid;
 #pragma unroll 4
-      for (int u0 = 0; u0 < C; u0 += 4) {
+      for (int u0 = lo; u0 < hi; u0 += 4) {
         const int4 a = *reinterpret_cast<const int4*>(s.idx + u0);
         const int e0 = a.x == mine, e1 = a.y == mine, e2 = a.z == mine, e3 = a.w == mine;
         total += e0 + e1 + e2 + e3;
-        before += (e0 & (u0 + 0 < tid)) + (e1 & (u0 + 1 < tid)) + (e2 & (u0 + 2 < tid)) + (e3 & (u0 + 3 < tid));
+        before += (e0 & (u0 + 0 < tok)) + (e1 & (u0 + 1 < tok)) + (e2 & (u0 + 2 < tok)) + (e3 & (u0 + 3 < tok));
         if (e3 && u0 + 3 < first) first = u0 + 3;
         if (e2 && u0 + 2 < first) first = u0 + 2;
         if (e1 && u0 + 1 < first) first = u0 + 1;
         if (e0 && u0 + 0 < first) first = u0 + 0;
       }
-      s.ord[tid] = before;
-      s.lead[tid] = first;
+    }
+    if (pair) {
+      total += __shfl_xor_sync(0xffffffffu, total, 1);
+      before += __shfl_xor_sync(0xffffffffu, before, 1);
+      first = min(first, __shfl_xor_sync(0xffffffffu, first, 1));
+    }
+    if (mine >= 0 && half == 0) {
+      s.ord[tok] = before;
+      s.lead[tok] = first;
       if (before == 0) {
-        s.tcnt[tid] = total;
-        s.tstart[tid] = atomicAdd(&s.counters[0], total);
+        s.tcnt[tok] = total;
+        s.tstart[tok] = atomicAdd(&s.counters[0], total);
         is_leader = true;
+        ltok = tok;
       }
     }
   }
@@ -541,7 +662,7 @@ __device__ void memory_update(const LayerDev& L, const TokenSrc& src, const Memo
       if (w < warp) p += c;
       tot += c;
     }
-    if (is_leader) s.touched[p] = tid;
+    if (is_leader) s.touched[p] = ltok;
     if (tid == 0) s.counters[1] = tot;
   }
   __syncthreads();
@@ -570,25 +691,18 @@ __device__ void memory_update(const LayerDev& L, const TokenSrc& src, const Memo
       bf16* sum_row = (is_v ? mem.v_sum : mem.k_sum) + (size_t)row * D;
       RowVec<D, GL> sum, acc;
       load_row<D, GL>(sum, sum_row, gl);  // issued first: its latency hides behind the accumulation
+      const float vl = is_v ? mem.vlen[row] : 0.f;
 #pragma unroll
       for (int e = 0; e < D / GL; ++e) acc.x[e] = 0.f;
       if (!is_v) {
         for (int j = 0; j < n; ++j) {
           const int tkn = s.list[b0 + j];
-          const float gt = s.g_s[tkn];
-          RowVec<D, GL> kr;
-          load_row<D, GL>(kr, blk.pk + (size_t)tkn * blk.pk_st, gl);
-#pragma unroll
-          for (int e = 0; e < D / GL; ++e) acc.x[e] += L.gate_keys ? bf16_round(kr.x[e] * gt) : kr.x[e];
+          accumulate_row<D, GL>(acc, blk.pk + (size_t)tkn * blk.pk_st, gl, L.gate_keys != 0, s.g_s[tkn]);
         }
       } else {
         for (int j = 0; j < n; ++j) {
           const int tkn = s.list[b0 + j];
-          const float gt = s.g_s[tkn];
-          RowVec<D, GL> vr;
-          load_row<D, GL>(vr, blk.v + (long long)tkn * blk.v_st, gl);
-#pragma unroll
-          for (int e = 0; e < D / GL; ++e) acc.x[e] += L.gate_values ? bf16_round(vr.x[e] * gt) : vr.x[e];
+          accumulate_row<D, GL>(acc, blk.v + (long long)tkn * blk.v_st, gl, L.gate_values != 0, s.g_s[tkn]);
         }
       }
 #pragma unroll
@@ -599,9 +713,9 @@ __device__ void memory_update(const LayerDev& L, const TokenSrc& src, const Memo
         if (act) store_row<D, GL>(sum, view.k + (size_t)slot * D, gl);
       } else {
         const float nrm = fmaxf(row_norm<D, GL>(sum), 1e-12f);
-        const float vl = mem.vlen[row];
+        divide_by(sum.x, nrm);
 #pragma unroll
-        for (int e = 0; e < D / GL; ++e) sum.x[e] = __fdiv_rn(sum.x[e], nrm) * vl;
+        for (int e = 0; e < D / GL; ++e) sum.x[e] *= vl;
         if (act) store_row<D, GL>(sum, view.v + (size_t)slot * D, gl);
       }
     }
