@@ -34,8 +34,9 @@ template <int D, int NT, bool SB>
 __global__ void __launch_bounds__(NT, 1)
 kvm_chain_kernel(LayerDev L_in, long long T, Tensor4 k, Tensor4 v, Tensor4 gate, const kvm_update_plan* __restrict__ plan,
                  int n_plan, MemoryDev mem, bf16* pool_k, bf16* pool_v, long long pool_rows, int* ver_idx,
-                 long long ver_rows, bf16* pk_scr, const bf16* __restrict__ pk_all, int* route, int nc) {
-  extern __shared__ __align__(16) unsigned char smem_raw[];
+                 long long ver_rows, bf16* pk_scr, const bf16* __restrict__ pk_all, int* route, int nc, int* status) {
+  extern __shared__ __align__(1024) unsigned char chain_smem[];
+  unsigned char* smem_raw = chain_smem;
   // LayerNorm weights in shared memory: almost all of the SM's L1 is carved out as shared memory, so every
   // LayerNorm of the chain would otherwise pay an L2 round trip for them
   __shared__ float ln_s[2 * D];
@@ -49,6 +50,24 @@ kvm_chain_kernel(LayerDev L_in, long long T, Tensor4 k, Tensor4 v, Tensor4 gate,
   __syncthreads();
   UpdateSmem<D> s;
   s.carve(smem_raw, L.C, mem.capacity, SB);
+  s.status = status;
+  bool has_tmem = false;
+  if constexpr (SB && D == 128 && NT == 512) {
+    if (L.C == 128 || L.C == 256) {  // tcgen05 routing scan: its two barriers and tensor memory, once per kernel
+      if (threadIdx.x == 0) {
+        tc::mbar_init(&s.bars[0], 1);
+        tc::mbar_init(&s.bars[1], 1);
+        tc::fence_barrier_init();
+      }
+      if (threadIdx.x < 32) tc::tmem_alloc(reinterpret_cast<uint32_t*>(s.bars + 2), kTcTmemCols);
+      has_tmem = true;
+      tc::tc_fence_before_sync();
+      __syncthreads();
+      tc::tc_fence_after_sync();
+      s.tmem = *reinterpret_cast<volatile uint32_t*>(s.bars + 2);
+      s.use_tc = true;
+    }
+  }
   const int row = blockIdx.x / nc;     // the nc CTAs of a cluster share one kv row
   const int crank = blockIdx.x % nc;
   const int b = row / L.Hkv, h = row % L.Hkv;
@@ -136,6 +155,11 @@ kvm_chain_kernel(LayerDev L_in, long long T, Tensor4 k, Tensor4 v, Tensor4 gate,
       *reinterpret_cast<uint4*>(m.k_attn + (size_t)r * D + cc * 8) = *reinterpret_cast<const uint4*>(view.k + src_off);
       *reinterpret_cast<uint4*>(m.v_attn + (size_t)r * D + cc * 8) = *reinterpret_cast<const uint4*>(view.v + src_off);
     }
+  }
+  if (has_tmem) {
+    tc::tc_fence_before_sync();
+    __syncthreads();
+    if (threadIdx.x < 32) tc::tmem_dealloc(s.tmem, kTcTmemCols);
   }
 }
 
@@ -429,7 +453,7 @@ static cudaError_t launch_prefill(const LayerDev& L, int batch, long long T, Ten
     cfg.numAttrs = 1;
     int* ver_arg = versions ? ver_idx : nullptr;
     e = cudaLaunchKernelEx(&cfg, kern, L, T, k, v, gate, plan_dev, n_plan, mem, pool_k, pool_v, pool_rows, ver_arg, ver_rows,
-                           pk_scr, (const bf16*)pk_all, route, nc);
+                           pk_scr, (const bf16*)pk_all, route, nc, status);
     if (e != cudaSuccess) return e;
   }
   if (!(phases & KVM_PREFILL_ATTENTION)) return cudaSuccess;

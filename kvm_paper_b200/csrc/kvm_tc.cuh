@@ -142,6 +142,23 @@ __device__ __forceinline__ void mma_commit(uint64_t* bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
 
+// Same for a kernel that may run as a thread-block cluster: the barrier is named by its address in the
+// cluster's shared-memory window, formed explicitly for this CTA's own rank.
+__device__ __forceinline__ void mma_commit_own_cta(uint64_t* bar) {
+  uint32_t rank, addr;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(rank));
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(addr) : "r"(smem_u32(bar)), "r"(rank));
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(addr) : "memory");
+}
+// Bounded wait with its own limit (for waits that are known to be short).
+__device__ __forceinline__ bool mbar_wait_limit(uint64_t* bar, uint32_t parity, uint32_t limit) {
+  for (uint32_t i = 0; i < limit; ++i) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if (i >= 4) __nanosleep(i < 64 ? 40 : 200);
+  }
+  return false;
+}
+
 // byte offset of element (row, col) inside one [rows][64] SW128 block (col in elements, bf16)
 __device__ __forceinline__ uint32_t sw128_offset(int row, int col) {
   return (uint32_t)(row * 128 + ((((col >> 3) ^ (row & 7)) & 7) << 4) + ((col & 7) << 1));

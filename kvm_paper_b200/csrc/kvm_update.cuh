@@ -19,6 +19,7 @@
 #pragma once
 
 #include "kvm_common.cuh"
+#include "kvm_tc.cuh"
 
 namespace kvm {
 
@@ -62,8 +63,17 @@ struct MemoryRowPtrs {  // the memory of one kv row
 };
 
 struct BlockView {  // where the phases after the load find the block's data
-  const bf16* pk;   // prepared keys, row stride pk_st elements
+  const bf16* pk;   // prepared keys, row stride pk_st elements ...
   int pk_st;
+  int swz_rows;     // ... or, if non-zero (D = 128): two blocks of [swz_rows][64 elements] in the 128-byte swizzle
+                    // (16-byte piece c of row r at position c ^ (r % 8)), the tcgen05 operand layout
+  // 16-byte piece c (elements 8c .. 8c+7) of row r
+  __device__ __forceinline__ const bf16* pk_piece(int r, int c) const {
+    if (swz_rows)
+      return reinterpret_cast<const bf16*>(reinterpret_cast<const unsigned char*>(pk) + (size_t)(c >> 3) * swz_rows * 128 +
+                                           r * 128 + (((c & 7) ^ (r & 7)) << 4));
+    return pk + (size_t)r * pk_st + c * 8;
+  }
   const bf16* v;    // values, row stride v_st elements
   long long v_st;
   const float* g;   // gates [C] (shared memory)
@@ -95,13 +105,18 @@ struct UpdateSmem {
   float* xapp;   // [kMaxCluster][C] partial novelty maxima of the CTAs of a cluster
   float* xbest;  // [kMaxCluster][C] partial best logits
   int* xidx;     // [kMaxCluster][C] partial best rows
+  uint64_t* bars;  // [2] mbarriers of the tcgen05 routing scan, [2] = slot for the tensor-memory base address
+  uint32_t tmem;   // tensor-memory base (valid when use_tc)
+  bool use_tc;     // the tcgen05 routing scan is available (tensor memory allocated, barriers initialised once)
+  uint32_t tc_tiles;  // tiles issued so far by the tcgen05 scan: tile n signals barrier n%2 with phase parity (n/2)%2
+  int* status;     // device status word (a bounded wait that ran out is reported here), or null
   static constexpr int kTokenArrays = 13 + 3 * 4;
   __host__ __device__ static size_t bytes(int C, int capacity, bool sb) {
     size_t b = (size_t)2 * kScanTile * scan_tile_stride<D>() * sizeof(bf16);
     if (sb) b += (size_t)C * (D + 8) * sizeof(bf16) + (size_t)C * D * sizeof(bf16);
     b += (size_t)C * 4 * kTokenArrays;
     b += (size_t)((capacity + 3) / 4 * 4) * 4;
-    b += 36 * 4;
+    b += 36 * 4 + 32;
     return b;
   }
   __device__ void carve(unsigned char* base, int C, int capacity, bool sb) {
@@ -123,7 +138,12 @@ struct UpdateSmem {
     xbest = reinterpret_cast<float*>(base); base += (size_t)4 * C * 4;
     xidx = reinterpret_cast<int*>(base); base += (size_t)4 * C * 4;
     cur = reinterpret_cast<int*>(base); base += (size_t)((capacity + 3) / 4 * 4) * 4;
-    counters = reinterpret_cast<int*>(base);
+    counters = reinterpret_cast<int*>(base); base += 36 * 4;
+    bars = reinterpret_cast<uint64_t*>(base);
+    tmem = 0;
+    use_tc = false;
+    tc_tiles = 0;
+    status = nullptr;
   }
 };
 
@@ -188,6 +208,46 @@ __device__ __forceinline__ void accumulate_row(RowVec<D, GL>& acc, const bf16* r
   }
 }
 
+// The EPL elements of this lane of prepared-key row `row` (either layout of the block view).
+template <int D, int GL>
+__device__ __forceinline__ void load_pk_row(RowVec<D, GL>& r, const BlockView& blk, int row, int gl) {
+  constexpr int EPL = D / GL;
+  if constexpr (EPL % 8 == 0) {
+#pragma unroll
+    for (int c = 0; c < EPL / 8; ++c) {
+      const uint4 u = *reinterpret_cast<const uint4*>(blk.pk_piece(row, gl * (EPL / 8) + c));
+      const float2 a = unpack_bf16(u.x), b = unpack_bf16(u.y), d = unpack_bf16(u.z), e = unpack_bf16(u.w);
+      r.x[c * 8 + 0] = a.x; r.x[c * 8 + 1] = a.y; r.x[c * 8 + 2] = b.x; r.x[c * 8 + 3] = b.y;
+      r.x[c * 8 + 4] = d.x; r.x[c * 8 + 5] = d.y; r.x[c * 8 + 6] = e.x; r.x[c * 8 + 7] = e.y;
+    }
+  } else {
+    load_row<D, GL>(r, blk.pk + (size_t)row * blk.pk_st, gl);
+  }
+}
+// accumulate_row for a prepared-key row of the block view
+template <int D, int GL>
+__device__ __forceinline__ void accumulate_pk_row(RowVec<D, GL>& acc, const BlockView& blk, int row, int gl, bool gated, float gate) {
+  constexpr int EPL = D / GL;
+  if constexpr (EPL % 8 == 0) {
+    const __nv_bfloat162 g2 = __float2bfloat162_rn(gate);
+#pragma unroll
+    for (int c = 0; c < EPL / 8; ++c) {
+      uint4 u = *reinterpret_cast<const uint4*>(blk.pk_piece(row, gl * (EPL / 8) + c));
+      if (gated) {
+        u.x = mul_bf16x2(u.x, g2);
+        u.y = mul_bf16x2(u.y, g2);
+        u.z = mul_bf16x2(u.z, g2);
+        u.w = mul_bf16x2(u.w, g2);
+      }
+      const float2 a = unpack_bf16(u.x), b = unpack_bf16(u.y), d = unpack_bf16(u.z), e = unpack_bf16(u.w);
+      acc.x[c * 8 + 0] += a.x; acc.x[c * 8 + 1] += a.y; acc.x[c * 8 + 2] += b.x; acc.x[c * 8 + 3] += b.y;
+      acc.x[c * 8 + 4] += d.x; acc.x[c * 8 + 5] += d.y; acc.x[c * 8 + 6] += e.x; acc.x[c * 8 + 7] += e.y;
+    }
+  } else {
+    accumulate_row<D, GL>(acc, blk.pk + (size_t)row * blk.pk_st, gl, gated, gate);
+  }
+}
+
 // Issue the cp.async copies of one tile of memory rows [row0, row0+kScanTile) (rows >= n_end zero-filled).
 // `slots` (shared memory, may be null = identity) maps a memory row to the row of `k_attn` that holds it.
 template <int D, int NT>
@@ -225,16 +285,14 @@ __device__ __noinline__ void scan_memory(const BlockView& blk, bool gate_keys, i
     uint32_t ap[KS][4], ag[KS][4];
     if (active) {
       const int r0 = mt * 16 + g, r1 = r0 + 8;
-      const bf16* p0 = blk.pk + (size_t)r0 * blk.pk_st + t * 2;
-      const bf16* p1 = blk.pk + (size_t)r1 * blk.pk_st + t * 2;
       const __nv_bfloat162 g0 = __float2bfloat162_rn(blk.g[r0]);
       const __nv_bfloat162 g1 = __float2bfloat162_rn(blk.g[r1]);
 #pragma unroll
       for (int ks = 0; ks < KS; ++ks) {
-        ap[ks][0] = *reinterpret_cast<const uint32_t*>(p0 + ks * 16);
-        ap[ks][1] = *reinterpret_cast<const uint32_t*>(p1 + ks * 16);
-        ap[ks][2] = *reinterpret_cast<const uint32_t*>(p0 + ks * 16 + 8);
-        ap[ks][3] = *reinterpret_cast<const uint32_t*>(p1 + ks * 16 + 8);
+        ap[ks][0] = *reinterpret_cast<const uint32_t*>(blk.pk_piece(r0, ks * 2) + t * 2);
+        ap[ks][1] = *reinterpret_cast<const uint32_t*>(blk.pk_piece(r1, ks * 2) + t * 2);
+        ap[ks][2] = *reinterpret_cast<const uint32_t*>(blk.pk_piece(r0, ks * 2 + 1) + t * 2);
+        ap[ks][3] = *reinterpret_cast<const uint32_t*>(blk.pk_piece(r1, ks * 2 + 1) + t * 2);
         if (gate_keys) {
           ag[ks][0] = mul_bf16x2(ap[ks][0], g0);
           ag[ks][1] = mul_bf16x2(ap[ks][1], g1);
@@ -337,6 +395,207 @@ __device__ __noinline__ void scan_memory(const BlockView& blk, bool gate_keys, i
   __syncthreads();
 }
 
+// ---------------------------------------------------------------------------------------------------
+// Routing GEMM on the 5th-generation tensor cores (tcgen05 + tensor memory), for D = 128 and blocks of 128
+// or 256 tokens whose prepared keys sit in shared memory in the 128-byte-swizzled K-major operand layout.
+// Same contract as scan_memory.  Per tile of 64 memory rows one elected thread issues two groups of MMAs
+// (M = 128 tokens each): prepared keys x tile (novelty) and gated keys x tile (merge logits), into one of
+// two accumulator buffers in tensor memory; warps 0..7 read back the novelty accumulators (running maximum
+// of the bf16-rounded scores), warps 8..15 the merge logits (running fp32 first-argmax), one token row per
+// thread and four independent partial results per thread.  The gated keys (A operand of the second group)
+// are built once into the shared-memory region that later holds the block's values (fetched after the
+// scan) while the first novelty MMAs run.  The first two memory tiles are already in flight when the
+// function is entered (`tiles_in_flight`), issued next to the block load.
+// Returns false (for every thread) if a bounded wait ran out; nothing has been merged into s.app / s.best /
+// s.idx in that case.
+constexpr int kTcTile = 64;                       // memory rows per tile of the tcgen05 scan
+constexpr uint32_t kTcTmemCols = 512;             // two buffers x (novelty, logits) x two 128-token accumulators x 64
+
+template <int D, int NT>
+__device__ __forceinline__ void scan_tc_load_tile(UpdateSmem<D>& s, const bf16* __restrict__ k_attn, const int* slots, int n_begin,
+                                                  int n_end, int it) {
+  unsigned char* dst = reinterpret_cast<unsigned char*>(s.btile) + (size_t)(it & 1) * (2 * kTcTile * 128);
+  const int row0 = n_begin + it * kTcTile;
+  for (int c = threadIdx.x; c < kTcTile * 16; c += NT) {
+    const int r = c >> 4, cc = c & 15;
+    const int row = row0 + r;
+    const bool in = row < n_end;
+    const int slot = in ? (slots ? slots[row] : row) : 0;
+    cp_async16(dst + (cc >> 3) * (kTcTile * 128) + r * 128 + (((cc & 7) ^ (r & 7)) << 4), k_attn + (size_t)slot * D + cc * 8,
+               in ? 16 : 0);
+  }
+}
+
+template <int D, int NT>
+__device__ __noinline__ bool scan_memory_tc(const BlockView& blk, bool gate_keys, int C, const bf16* __restrict__ k_attn,
+                                            const int* slots, int n_begin, int n_end, bool want_app, int protected_rows,
+                                            UpdateSmem<D>& s, int tiles_in_flight) {
+  static_assert(D == 128 && NT == 512, "tcgen05 routing scan: head dimension 128, 16 warps");
+  constexpr int TN = kTcTile;
+  constexpr uint32_t kWaitLimit = 1u << 12;  // the MMAs of one tile take well under a microsecond
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int n_tiles = (n_end - n_begin + TN - 1) / TN;
+  if (n_tiles <= 0) return true;
+  const int n_mt = C / 128;                                              // accumulators of 128 tokens per operand
+  const unsigned char* A_pk = reinterpret_cast<const unsigned char*>(blk.pk);   // [2 k-halves][C][128 B], swizzled
+  unsigned char* A_gk = reinterpret_cast<unsigned char*>(s.v_s);                 // same layout, gated
+  uint64_t* mbar = s.bars;
+  constexpr uint32_t idesc = tc::make_idesc(128, TN, 0, 0);
+  const uint32_t pk_addr = tc::smem_u32(A_pk), gk_addr = gate_keys ? tc::smem_u32(A_gk) : pk_addr;
+  const uint32_t b_addr = tc::smem_u32(s.btile);
+  const bool issuer = tid == NT - 32;
+  // read-back roles: warps 0..7 novelty (operand 0), warps 8..15 logits (operand 1); warp w -> accumulator (w%8)/4, lanes 32*(w%4)..
+  const int op = warp >> 3, mt = (warp >> 2) & 1;
+  const bool epi = mt < n_mt && (op == 1 || want_app);
+  const uint32_t t_lane = s.tmem + ((uint32_t)((warp & 3) * 32) << 16) + (uint32_t)(op * 128 + mt * TN);
+  const uint32_t g0 = s.tc_tiles;  // global index of this call's first tile (barriers are initialised once per kernel)
+  bool ok = true;
+
+  // D[buffer it%2][operand][m] += A_operand[m] x tile it
+  auto issue_mmas = [&](int it, int operand) {
+    const uint32_t a_addr = operand ? gk_addr : pk_addr;
+    const uint64_t db0 = tc::make_desc(b_addr + (uint32_t)((it & 1) * (2 * TN * 128)), 16, 1024);
+    for (int m = 0; m < n_mt; ++m) {
+      const uint64_t da0 = tc::make_desc(a_addr + (uint32_t)(m * 128 * 128), 16, 1024);
+#pragma unroll
+      for (int ks = 0; ks < D / 16; ++ks) {
+        const uint64_t da = da0 + (uint64_t)(((uint32_t)(ks >> 2) * (uint32_t)(C * 128) + (uint32_t)(ks & 3) * 32u) >> 4);
+        const uint64_t db = db0 + (uint64_t)(((uint32_t)(ks >> 2) * (uint32_t)(TN * 128) + (uint32_t)(ks & 3) * 32u) >> 4);
+        tc::mma_ss(s.tmem + (uint32_t)((it & 1) * 256 + operand * 128 + m * TN), da, db, idesc, ks > 0);
+      }
+    }
+  };
+  // four independent running results per thread (columns c % 4), folded at the end: short dependency chains
+  float am[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+  float bb[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+  int bi[4] = {-1, -1, -1, -1};
+  auto epilogue = [&](int it) {
+    const int tile_base = n_begin + it * TN;
+    const int ncols = min(TN, n_end - tile_base);
+    const bool full = ncols == TN && tile_base >= protected_rows;  // no column of this tile is masked
+    tc::tc_fence_after_sync();
+#pragma unroll
+    for (int half = 0; half < TN / 32; ++half) {
+      if (half * 32 < ncols) {
+        uint32_t r[32];
+        tc::tmem_ld32(t_lane + (uint32_t)((it & 1) * 256 + half * 32), r);
+        tc::tmem_ld_wait();
+        const int n0 = tile_base + half * 32;
+        if (op == 0) {
+          if (full) {
+#pragma unroll
+            for (int c = 0; c < 32; ++c) am[c & 3] = fmaxf(am[c & 3], bf16_round(__uint_as_float(r[c])));
+          } else {
+#pragma unroll
+            for (int c = 0; c < 32; ++c)
+              if (n0 + c < n_end) am[c & 3] = fmaxf(am[c & 3], bf16_round(__uint_as_float(r[c])));
+          }
+        } else {
+          if (full) {
+#pragma unroll
+            for (int c = 0; c < 32; ++c) {
+              const float x = __uint_as_float(r[c]);
+              if (x > bb[c & 3] || bi[c & 3] < 0) {
+                bb[c & 3] = x;
+                bi[c & 3] = n0 + c;
+              }
+            }
+          } else {
+#pragma unroll
+            for (int c = 0; c < 32; ++c) {
+              const float x = __uint_as_float(r[c]);
+              const int n = n0 + c;
+              if (n < n_end && n >= protected_rows && (x > bb[c & 3] || bi[c & 3] < 0)) {
+                bb[c & 3] = x;
+                bi[c & 3] = n;
+              }
+            }
+          }
+        }
+      }
+    }
+    tc::tc_fence_before_sync();
+  };
+
+  // tiles not yet in flight among the first two
+  for (int it = tiles_in_flight; it < 2 && it < n_tiles; ++it) scan_tc_load_tile<D, NT>(s, k_attn, slots, n_begin, n_end, it);
+  cp_async_commit();
+  cp_async_wait<0>();
+  tc::fence_proxy_async();
+  __syncthreads();  // prepared keys (A operand 0) and the first tiles are in shared memory
+  if (issuer && want_app) {  // novelty MMAs of the first tiles run while the gated operand is built
+    tc::tc_fence_after_sync();
+    for (int it = 0; it < 2 && it < n_tiles; ++it) issue_mmas(it, 0);
+  }
+  if (gate_keys) {
+    // gated keys: the swizzle is a permutation inside 1024-byte groups of 8 rows, so the operand is copied
+    // 16-byte unit by unit; unit u of a k-half block belongs to row u / 8
+    // (the issuing thread's warp stays out of the copy: its MMAs go out while the others build)
+    for (int u = tid; u < C * 16 && warp < NT / 32 - 1; u += NT - 32) {
+      const int r = (u & (C * 8 - 1)) >> 3;
+      uint4 v = *reinterpret_cast<const uint4*>(A_pk + (size_t)u * 16);
+      const __nv_bfloat162 g2 = __float2bfloat162_rn(blk.g[r]);
+      v.x = mul_bf16x2(v.x, g2);
+      v.y = mul_bf16x2(v.y, g2);
+      v.z = mul_bf16x2(v.z, g2);
+      v.w = mul_bf16x2(v.w, g2);
+      *reinterpret_cast<uint4*>(A_gk + (size_t)u * 16) = v;
+    }
+    tc::fence_proxy_async();
+    __syncthreads();
+  }
+  if (issuer) {
+    tc::tc_fence_after_sync();
+    for (int it = 0; it < 2 && it < n_tiles; ++it) {
+      issue_mmas(it, 1);
+      tc::mma_commit_own_cta(&mbar[(g0 + it) & 1]);  // covers the novelty MMAs of the tile as well (issued earlier)
+    }
+  }
+  for (int it = 0; it < n_tiles; ++it) {
+    ok = ok && tc::mbar_wait_limit(&mbar[(g0 + it) & 1], ((g0 + it) >> 1) & 1, kWaitLimit);
+    const bool more = it + 2 < n_tiles;
+    if (more) {  // the MMAs of tile `it` are done: its operand buffer may be refilled
+      scan_tc_load_tile<D, NT>(s, k_attn, slots, n_begin, n_end, it + 2);
+      cp_async_commit();
+    }
+    if (epi) epilogue(it);
+    if (more) {
+      cp_async_wait<0>();
+      tc::fence_proxy_async();
+      __syncthreads();  // tile it+2 complete; accumulator buffer it%2 has been read back
+      if (issuer) {
+        tc::tc_fence_after_sync();
+        if (want_app) issue_mmas(it + 2, 0);
+        issue_mmas(it + 2, 1);
+        tc::mma_commit_own_cta(&mbar[(g0 + it + 2) & 1]);
+      }
+      }
+  }
+  s.tc_tiles = g0 + (uint32_t)n_tiles;
+  if (!__syncthreads_and(ok ? 1 : 0)) return false;
+  if (epi) {
+    const int row = mt * 128 + (warp & 3) * 32 + lane;
+    if (op == 0) {
+      s.app[row] = fmaxf(fmaxf(am[0], am[1]), fmaxf(am[2], am[3]));
+    } else {
+      float bbest = bb[0];
+      int bidx = bi[0];
+#pragma unroll
+      for (int j = 1; j < 4; ++j)  // first maximum in row order: larger logit, or equal logit at a lower row
+        if (bi[j] >= 0 && (bidx < 0 || bb[j] > bbest || (bb[j] == bbest && bi[j] < bidx))) {
+          bbest = bb[j];
+          bidx = bi[j];
+        }
+      if (bidx >= 0 && (s.idx[row] < 0 || bbest > s.best[row])) {
+        s.best[row] = bbest;
+        s.idx[row] = bidx;
+      }
+    }
+  }
+  __syncthreads();
+  return true;
+}
+
 // Where the attention view (k_attn / v_attn rows) of the memory lives.
 //   in place (decode, short prompts): row r of the memory is row r of `k` / `v`;  `cur` == nullptr
 //   pool (prefill): every refreshed or appended row is written to a fresh pool row, `cur[r]` (shared
@@ -370,22 +629,50 @@ __device__ void memory_update(const LayerDev& L, const TokenSrc& src, const Memo
   const int S_after = S_before + n_append;
   const int n_merge = C - n_append;
   const bool pool = view.cur != nullptr;
+  // this CTA scans the tiles [crank, crank+1) * n_tiles / nc of the old memory
+  const int n_tiles_all = (S_before + kScanTile - 1) / kScanTile;
+  const int scan_b = min(S_before, (crank * n_tiles_all / nc) * kScanTile);
+  const int scan_e = min(S_before, ((crank + 1) * n_tiles_all / nc) * kScanTile);
+  // routing scan of the old memory on tcgen05: the prepared keys are staged in the swizzled operand layout, the
+  // gated operand borrows the value staging area (the values are fetched after the scan)
+  bool use_tc = false;
+  if constexpr (SB && PKR && D == 128 && NT == 512) use_tc = s.use_tc && (C == 128 || C == 256) && n_merge > 0;
+  const bool defer_v = use_tc;
+  int tiles_in_flight = 0;
 
   KVM_PHASE_BEGIN();
   // ---- 0. bring the block in: keys first (needed at once), values behind them
   BlockView blk;
   blk.g = s.g_s;
+  blk.swz_rows = 0;
   if constexpr (SB) {
-    for (int c = tid; c < C * CPR; c += NT) {
-      const int r = c / CPR, cc = c % CPR;
-      cp_async16(s.pk_s + (size_t)r * PST + cc * 8, src.k + (long long)r * src.k_st + cc * 8, 16);
+    if (use_tc) {
+      unsigned char* dst = reinterpret_cast<unsigned char*>(s.pk_s);
+      for (int c = tid; c < C * CPR; c += NT) {
+        const int r = c / CPR, cc = c % CPR;
+        cp_async16(dst + (size_t)(cc >> 3) * C * 128 + r * 128 + (((cc & 7) ^ (r & 7)) << 4),
+                   src.k + (long long)r * src.k_st + cc * 8, 16);
+      }
+      cp_async_commit();
+      if constexpr (D == 128 && NT == 512) {  // the first two memory tiles of the scan travel behind the keys
+        const int n_t = (scan_e - scan_b + kTcTile - 1) / kTcTile;
+        tiles_in_flight = min(2, max(n_t, 0));
+        for (int it = 0; it < tiles_in_flight; ++it) scan_tc_load_tile<D, NT>(s, view.k, view.cur, scan_b, scan_e, it);
+      }
+      cp_async_commit();
+      blk.swz_rows = C;
+    } else {
+      for (int c = tid; c < C * CPR; c += NT) {
+        const int r = c / CPR, cc = c % CPR;
+        cp_async16(s.pk_s + (size_t)r * PST + cc * 8, src.k + (long long)r * src.k_st + cc * 8, 16);
+      }
+      cp_async_commit();
+      for (int c = tid; c < C * CPR; c += NT) {
+        const int r = c / CPR, cc = c % CPR;
+        cp_async16(s.v_s + (size_t)r * D + cc * 8, src.v + (long long)r * src.v_st + cc * 8, 16);
+      }
+      cp_async_commit();
     }
-    cp_async_commit();
-    for (int c = tid; c < C * CPR; c += NT) {
-      const int r = c / CPR, cc = c % CPR;
-      cp_async16(s.v_s + (size_t)r * D + cc * 8, src.v + (long long)r * src.v_st + cc * 8, 16);
-    }
-    cp_async_commit();
     blk.pk = s.pk_s; blk.pk_st = PST; blk.v = s.v_s; blk.v_st = D;
   } else {
     blk.pk = pk_scr; blk.pk_st = D; blk.v = src.v; blk.v_st = src.v_st;
@@ -437,11 +724,28 @@ __device__ void memory_update(const LayerDev& L, const TokenSrc& src, const Memo
 
   // ---- 2. scores against the old memory, append selection
   if (n_merge > 0) {
-    // this CTA scans the tiles [crank, crank+1) * n_tiles / nc of the old memory
-    const int n_tiles_all = (S_before + kScanTile - 1) / kScanTile;
-    const int nb = min(S_before, (crank * n_tiles_all / nc) * kScanTile);
-    const int ne = min(S_before, ((crank + 1) * n_tiles_all / nc) * kScanTile);
-    scan_memory<D, NT>(blk, L.gate_keys != 0, C, view.k, view.cur, nb, ne, n_append > 0, protected_rows, s);
+    bool scanned = false;
+    if constexpr (SB && PKR && D == 128 && NT == 512) {
+      if (use_tc) {
+        scanned = scan_memory_tc<D, NT>(blk, L.gate_keys != 0, C, view.k, view.cur, scan_b, scan_e, n_append > 0, protected_rows,
+                                        s, tiles_in_flight);
+        if (!scanned) {  // report, and stay on the warp-level path for the rest of this kernel
+          if (tid == 0 && s.status) atomicExch(s.status, KVM_ERR_DEVICE_TIMEOUT);
+          s.use_tc = false;
+        }
+      }
+    }
+    if (!scanned)
+      scan_memory<D, NT>(blk, L.gate_keys != 0, C, view.k, view.cur, scan_b, scan_e, n_append > 0, protected_rows, s);
+    if constexpr (SB) {
+      if (defer_v) {  // the value staging area is free again: fetch the block's values behind the ranking
+        for (int c = tid; c < C * CPR; c += NT) {
+          const int r = c / CPR, cc = c % CPR;
+          cp_async16(s.v_s + (size_t)r * D + cc * 8, src.v + (long long)r * src.v_st + cc * 8, 16);
+        }
+        cp_async_commit();
+      }
+    }
     if (nc > 1) {
       // all-gather of the partial results through distributed shared memory, then a local combine
       for (int i = tid; i < C * nc; i += NT) {
@@ -534,7 +838,7 @@ __device__ void memory_update(const LayerDev& L, const TokenSrc& src, const Memo
       const int t_ = s.list[p_ < n_append ? p_ : 0];
       const int row = act ? S_before + p_ : 0;
       RowVec<D, GL> kr, vr;
-      load_row<D, GL>(kr, blk.pk + (size_t)t_ * blk.pk_st, gl);
+      load_pk_row<D, GL>(kr, blk, t_, gl);
       load_row<D, GL>(vr, blk.v + (long long)t_ * blk.v_st, gl);
       if (L.gate_appends) {
         const float gt = s.g_s[t_];
@@ -586,7 +890,7 @@ __device__ void memory_update(const LayerDev& L, const TokenSrc& src, const Memo
         const bool act = tkn < C;
         const int t_ = act ? tkn : 0;
         RowVec<D, GL> kr;
-        load_row<D, GL>(kr, blk.pk + (size_t)t_ * blk.pk_st, gl);
+        load_pk_row<D, GL>(kr, blk, t_, gl);
         float acc = 0.f;
         if (L.gate_keys) {
           const float gt = s.g_s[t_];
@@ -697,7 +1001,7 @@ __device__ void memory_update(const LayerDev& L, const TokenSrc& src, const Memo
       if (!is_v) {
         for (int j = 0; j < n; ++j) {
           const int tkn = s.list[b0 + j];
-          accumulate_row<D, GL>(acc, blk.pk + (size_t)tkn * blk.pk_st, gl, L.gate_keys != 0, s.g_s[tkn]);
+          accumulate_pk_row<D, GL>(acc, blk, tkn, gl, L.gate_keys != 0, s.g_s[tkn]);
         }
       } else {
         for (int j = 0; j < n; ++j) {
