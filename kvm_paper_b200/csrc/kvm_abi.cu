@@ -15,7 +15,7 @@ cudaError_t prefill_dispatch(int D, const LayerDev& L, int batch, long long T, T
 size_t update_smem_bytes(int D, int C, int capacity);
 cudaError_t decode_dispatch(int D, const LayerDev& L, int batch, const DecodeCacheDev& cache, Tensor4 q, Tensor4 k,
                             Tensor4 v, Tensor4 gate, const int* n_append, int any_update, int max_rows, bf16* out,
-                            int* route, bf16* pk_scr, bf16* gk_scr, float* partial, int* counters, int overlap,
+                            int* route, bf16* pk_scr, float* partial, int* counters, int nslots, int overlap,
                             cudaStream_t stream);
 cudaError_t refresh_dispatch(int D, const LayerDev& L, int batch, MemoryDev mem, const int* state_len,
                              cudaStream_t stream);
@@ -130,7 +130,7 @@ PrefillWs prefill_ws(const kvm_layer* l, int batch, long long seq_len, long long
 }
 
 struct DecodeWs {
-  size_t pk, gk, partial, counters, total;
+  size_t pk, partial, counters, total;
   int nsplit_max;
 };
 DecodeWs decode_ws(const kvm_layer* l, int batch, int max_rows) {
@@ -139,9 +139,8 @@ DecodeWs decode_ws(const kvm_layer* l, int batch, int max_rows) {
   DecodeWs w;
   w.nsplit_max = (max_rows + kDecodeRowsPerSplit - 1) / kDecodeRowsPerSplit + 2;  // memory / window / wrapped window runs
   size_t off = 0;
-  w.counters = off; off = align_up(off + (rows + batch + 1) * 4, 256);  // split counters, sequence counters, status word
+  w.counters = off; off = align_up(off + (rows + batch + 1) * 4, 256);  // row counters, launch counter (+ spare), status word
   w.pk = off; off = align_up(off + rows * (size_t)l->chunk_len * D * 2, 256);
-  w.gk = off; off = align_up(off + rows * (size_t)l->chunk_len * D * 2, 256);
   w.partial = off; off = align_up(off + (size_t)batch * l->n_q_heads * w.nsplit_max * (D + 2) * 4, 256);
   w.total = off;
   return w;
@@ -292,9 +291,9 @@ static int decode_step_impl(const kvm_layer* layer, int32_t batch, const kvm_dec
   if (any_update < 0 || any_update > batch) any_update = batch;  // count unknown: no overlap
   cudaError_t e = decode_dispatch(D, to_dev(layer), batch, c, to_dev(q), to_dev(k), to_dev(v), to_dev(gate), n_append_dev,
                                   any_update, max_rows, static_cast<bf16*>(out), route_dev,
-                                  reinterpret_cast<bf16*>(wsb + ws.pk), reinterpret_cast<bf16*>(wsb + ws.gk),
-                                  reinterpret_cast<float*>(wsb + ws.partial), reinterpret_cast<int*>(wsb + ws.counters),
-                                  overlap, static_cast<cudaStream_t>(stream));
+                                  reinterpret_cast<bf16*>(wsb + ws.pk), reinterpret_cast<float*>(wsb + ws.partial),
+                                  reinterpret_cast<int*>(wsb + ws.counters), ws.nsplit_max, overlap,
+                                  static_cast<cudaStream_t>(stream));
   if (e != cudaSuccess) return cuda_fail(e, who);
   return KVM_OK;
 }

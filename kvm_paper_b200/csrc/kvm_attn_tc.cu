@@ -18,6 +18,7 @@
 // exit, frees its tensor memory and returns.
 #include "kvm_common.cuh"
 #include "kvm_tc.cuh"
+#include "kvm_tma_host.cuh"
 
 namespace kvm {
 
@@ -90,24 +91,35 @@ struct Slice {
 };
 
 // ------------------------------------------------------------------------------------------ loaders
-// Loader `lw` brings the key/value tiles t = lw, lw+4, ... into stage lw; loaders 0..NQ-1 also bring
-// query tile `lw` together with their first tile.  Returns false if a bounded wait expired.
+// The q, k, v inputs as 4-D tensors [batch][head][token][D] (any strides): boxes of 64 elements x 128 tokens
+// (queries) or 64 tokens (keys, values) land in the 128-byte-swizzled operand layout.
+struct AttnMaps {
+  CUtensorMap q, k, v;
+  int q_head_inner, kv_head_inner;  // the head dimension has the smaller stride ([B,T,H,D] storage): it comes second
+};
+// box at (element x, token t, head h, batch b) of a tensor whose dimensions are ordered by stride
+__device__ __forceinline__ void attn_tma(void* dst, const CUtensorMap* m, bool head_inner, int x, int t, int h, int b,
+                                         uint64_t* bar) {
+  if (head_inner) tc::tma_load_4d(dst, m, x, h, t, b, bar);
+  else tc::tma_load_4d(dst, m, x, t, h, b, bar);
+}
+
+// Loader `lw` brings the key/value tiles t = lw, lw+4, ... into stage lw; loaders 0..NQ-1 first fetch query
+// tile `lw`.  Query tiles and window tiles are contiguous token ranges: one thread issues tiled TMA copies
+// (two per operand, one per 64-element half of the head dimension) that signal the stage's barrier with
+// their byte count.  Memory tiles are gathered row by row through the version table with 16-byte cp.async.
+// Rows past the end of the sequence read as zeros; rows past the query block are real tokens that the causal
+// mask hides.  Returns false if a bounded wait expired.
 template <int NQ>
 __device__ __forceinline__ bool loader_role(const Slice<NQ>& sl, unsigned char* smem, Bars* bars, int lw, int lane,
-                                            const Tensor4& q, const Tensor4& k, const Tensor4& v) {
+                                            const AttnMaps* maps) {
   using CF = Cfg<NQ>;
-  const bf16* kbase = k.row(sl.b, sl.hkv, 0);
-  const bf16* vbase = v.row(sl.b, sl.hkv, 0);
-  const bool has_q = lw < NQ && sl.n_tiles[lw < NQ ? lw : 0] > 0;
-  if (has_q) {
-    const long long qs = sl.q0 + (long long)lw * BM;
-    for (int c = lane; c < BM * 16; c += 32) {
-      const int r = c >> 4, cc = c & 15;
-      const long long row = qs + r;
-      const bool ok = row < sl.q_end[lw < NQ ? lw : 0];
-      const bf16* src = q.row(sl.b, sl.hq, ok ? row : qs) + cc * 8;
-      cp_async16(smem + CF::kOffQ + lw * 32768 + (cc >> 3) * 16384 + tc::sw128_offset(r, (cc & 7) * 8), src, ok ? 16 : 0);
-    }
+  if (lw < NQ && sl.n_tiles[lw < NQ ? lw : 0] > 0 && lane == 0) {
+    unsigned char* dQ = smem + CF::kOffQ + lw * 32768;
+    const int qs = (int)(sl.q0 + (long long)lw * BM);
+    tc::mbar_arrive_expect_tx(&bars->q_full[lw], 2u * BM * 128u);
+    attn_tma(dQ, &maps->q, maps->q_head_inner != 0, 0, qs, sl.hq, sl.b, &bars->q_full[lw]);
+    attn_tma(dQ + 16384, &maps->q, maps->q_head_inner != 0, 64, qs, sl.hq, sl.b, &bars->q_full[lw]);
   }
   const int stage = lw;
   unsigned char* dK = smem + CF::kOffK + stage * 16384;
@@ -115,56 +127,47 @@ __device__ __forceinline__ bool loader_role(const Slice<NQ>& sl, unsigned char* 
   // lane -> fixed 16-byte column chunk cc and row parity; iteration `it` covers rows 2*it and 2*it+1
   const int cc = lane & 15, rh = lane >> 4;
   const uint32_t col_off = (uint32_t)(cc >> 3) * 8192u;
-  bool first = true;
   const bool prof = blockIdx.x == 0 && blockIdx.y == 0 && lane == 0 && lw == 0;
   (void)prof;
   TC_T0();
-  for (int t = lw; t < sl.n_max || first; t += kLoaders) {
-    const bool have_tile = t < sl.n_max;
-    if (have_tile) {
-      if (t >= kStages && !warp_wait(&bars->kv_empty[stage], ((t / kStages) - 1) & 1)) return false;
-      TC_MARK(0, prof);
-      if (t < sl.n_mem_tiles) {
-        const int row0 = t * BN;
-        const int i0 = row0 + lane < sl.S ? __ldg(sl.midx + row0 + lane) : 0;
-        const int i1 = row0 + 32 + lane < sl.S ? __ldg(sl.midx + row0 + 32 + lane) : 0;
-#pragma unroll
-        for (int it = 0; it < BN / 2; ++it) {
-          const int r = it * 2 + rh;
-          const int a0 = __shfl_sync(0xffffffffu, it < 16 ? i0 : i1, r & 31);
-          const bool ok = row0 + r < sl.S;
-          const uint32_t off = col_off + (uint32_t)(r * 128) + (uint32_t)((((cc & 7) ^ (r & 7)) & 7) << 4);
-          const size_t src = (size_t)a0 * HD + cc * 8;
-          cp_async16(dK + off, sl.mk + src, ok ? 16 : 0);
-          cp_async16(dV + off, sl.mv + src, ok ? 16 : 0);
-        }
-      } else {
-        const long long r0 = sl.bb + (long long)(t - sl.n_mem_tiles) * BN;
-        const bf16* pk = kbase + (r0 + rh) * k.st + cc * 8;
-        const bf16* pv = vbase + (r0 + rh) * v.st + cc * 8;
-        const int n_ok = (int)min((long long)BN, sl.q_end_all - r0);  // rows of this tile that exist
-#pragma unroll
-        for (int it = 0; it < BN / 2; ++it) {
-          const int r = it * 2 + rh;
-          const bool ok = r < n_ok;
-          const uint32_t off = col_off + (uint32_t)(r * 128) + (uint32_t)((((cc & 7) ^ (r & 7)) & 7) << 4);
-          cp_async16(dK + off, ok ? pk + (long long)it * 2 * k.st : kbase, ok ? 16 : 0);
-          cp_async16(dV + off, ok ? pv + (long long)it * 2 * v.st : vbase, ok ? 16 : 0);
-        }
+  for (int t = lw; t < sl.n_max; t += kLoaders) {
+    if (t >= kStages && !warp_wait(&bars->kv_empty[stage], ((t / kStages) - 1) & 1)) return false;
+    TC_MARK(0, prof);
+    if (t >= sl.n_mem_tiles) {
+      if (lane == 0) {
+        const int r0 = (int)(sl.bb + (long long)(t - sl.n_mem_tiles) * BN);
+        tc::mbar_arrive_expect_tx(&bars->kv_full[stage], 4u * BN * 128u);
+        const bool hi = maps->kv_head_inner != 0;
+        attn_tma(dK, &maps->k, hi, 0, r0, sl.hkv, sl.b, &bars->kv_full[stage]);
+        attn_tma(dK + 8192, &maps->k, hi, 64, r0, sl.hkv, sl.b, &bars->kv_full[stage]);
+        attn_tma(dV, &maps->v, hi, 0, r0, sl.hkv, sl.b, &bars->kv_full[stage]);
+        attn_tma(dV + 8192, &maps->v, hi, 64, r0, sl.hkv, sl.b, &bars->kv_full[stage]);
       }
+      __syncwarp();
+      TC_MARK(1, prof);
+      continue;
+    }
+    const int row0 = t * BN;
+    const int i0 = row0 + lane < sl.S ? __ldg(sl.midx + row0 + lane) : 0;
+    const int i1 = row0 + 32 + lane < sl.S ? __ldg(sl.midx + row0 + 32 + lane) : 0;
+#pragma unroll
+    for (int it = 0; it < BN / 2; ++it) {
+      const int r = it * 2 + rh;
+      const int a0 = __shfl_sync(0xffffffffu, it < 16 ? i0 : i1, r & 31);
+      const bool ok = row0 + r < sl.S;
+      const uint32_t off = col_off + (uint32_t)(r * 128) + (uint32_t)((((cc & 7) ^ (r & 7)) & 7) << 4);
+      const size_t src = (size_t)a0 * HD + cc * 8;
+      cp_async16(dK + off, sl.mk + src, ok ? 16 : 0);
+      cp_async16(dV + off, sl.mv + src, ok ? 16 : 0);
     }
     cp_async_commit();
     TC_MARK(1, prof);
-    cp_async_wait<0>();       // this warp's tile (and its query tile, the first time) has landed
+    cp_async_wait<0>();       // this warp's tile has landed
     TC_MARK(2, prof);
     tc::fence_proxy_async();  // generic-proxy writes -> visible to the tensor core's operand reads
     __syncwarp();
     TC_MARK(3, prof);
-    if (lane == 0) {
-      if (first && has_q) tc::mbar_arrive(&bars->q_full[lw]);
-      if (have_tile) tc::mbar_arrive(&bars->kv_full[stage]);
-    }
-    first = false;
+    if (lane == 0) tc::mbar_arrive(&bars->kv_full[stage]);
   }
   return true;
 }
@@ -369,7 +372,7 @@ kvm_attn_prefill_tc_kernel(LayerDev L, long long T, Tensor4 q, Tensor4 k, Tensor
                            const kvm_update_plan* __restrict__ plan, const bf16* __restrict__ pool_k,
                            const bf16* __restrict__ pool_v, long long pool_rows, const int* __restrict__ ver_idx,
                            long long ver_rows, bf16* __restrict__ out, int ctas_per_block, float sm_scale,
-                           int* __restrict__ status) {
+                           int* __restrict__ status, const __grid_constant__ AttnMaps maps) {
   using CF = Cfg<NQ>;
   extern __shared__ __align__(1024) unsigned char smem[];
   Bars* bars = reinterpret_cast<Bars*>(smem + CF::kOffBar);
@@ -437,7 +440,7 @@ kvm_attn_prefill_tc_kernel(LayerDev L, long long T, Tensor4 q, Tensor4 k, Tensor
   if (warp < CF::kSoftmaxWarps) {
     ok = softmax_role<NQ>(sl, L, smem, bars, tmem, warp >> 2, tid & 127, warp & 3, lane, T, out, sm_scale);
   } else if (warp < CF::kMmaWarp) {
-    ok = loader_role<NQ>(sl, smem, bars, warp - CF::kSoftmaxWarps, lane, q, k, v);
+    ok = loader_role<NQ>(sl, smem, bars, warp - CF::kSoftmaxWarps, lane, &maps);
     cp_async_wait<0>();
   } else {
     if (lane == 0) ok = mma_role<NQ>(sl, smem, bars, tmem);
@@ -459,10 +462,30 @@ static cudaError_t launch_nq(const LayerDev& L, int batch, long long T, Tensor4 
   cudaError_t e = cudaFuncSetAttribute(kvm_attn_prefill_tc_kernel<NQ>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                        (int)CF::kSmemBytes);
   if (e != cudaSuccess) return e;
+  AttnMaps maps;
+  // dimensions ordered by stride: [B,T,H,D] storage (heads inside tokens) or [B,H,T,D] storage
+  auto encode = [&](CUtensorMap* m, const Tensor4& t, int heads, int box_rows, bool head_inner) {
+    if (head_inner) {
+      const cuuint64_t dims[4] = {(cuuint64_t)HD, (cuuint64_t)heads, (cuuint64_t)T, (cuuint64_t)batch};
+      const cuuint64_t strides[3] = {(cuuint64_t)t.sh * 2, (cuuint64_t)t.st * 2, (cuuint64_t)t.sb * 2};
+      const cuuint32_t box[4] = {64, 1, (cuuint32_t)box_rows, 1};
+      return encode_bf16_map(m, t.ptr, 4, dims, strides, box);
+    }
+    const cuuint64_t dims[4] = {(cuuint64_t)HD, (cuuint64_t)T, (cuuint64_t)heads, (cuuint64_t)batch};
+    const cuuint64_t strides[3] = {(cuuint64_t)t.st * 2, (cuuint64_t)t.sh * 2, (cuuint64_t)t.sb * 2};
+    const cuuint32_t box[4] = {64, (cuuint32_t)box_rows, 1, 1};
+    return encode_bf16_map(m, t.ptr, 4, dims, strides, box);
+  };
+  maps.q_head_inner = q.sh < q.st ? 1 : 0;
+  maps.kv_head_inner = k.sh < k.st ? 1 : 0;
+  if ((v.sh < v.st) != (k.sh < k.st)) return cudaErrorInvalidValue;  // keys and values share one layout
+  if (!encode(&maps.q, q, L.Hq, BM, maps.q_head_inner != 0) || !encode(&maps.k, k, L.Hkv, BN, maps.kv_head_inner != 0) ||
+      !encode(&maps.v, v, L.Hkv, BN, maps.kv_head_inner != 0))
+    return cudaErrorInvalidValue;
   dim3 grid(n_qblocks * ctas_per_block, batch * L.Hq);
   kvm_attn_prefill_tc_kernel<NQ><<<grid, CF::kThreads, CF::kSmemBytes, stream>>>(
       L, T, q, k, v, plan_dev, pool_k, pool_v, pool_rows, ver_idx, ver_rows, out, ctas_per_block,
-      1.0f / sqrtf((float)HD), status);
+      1.0f / sqrtf((float)HD), status, maps);
   return cudaGetLastError();
 }
 

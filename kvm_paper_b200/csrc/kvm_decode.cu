@@ -14,6 +14,7 @@
 
 #include "kvm_update.cuh"
 #include "kvm_tc.cuh"
+#include "kvm_tma_host.cuh"
 
 namespace kvm {
 
@@ -110,7 +111,6 @@ constexpr int kDecThreads = (kDecConsumers + 1) * 32;      // + one producer war
 constexpr int kDecChunk = kDecConsumers * 16;              // rows per pipeline stage
 constexpr int kDecBoxRows = 16;                            // rows per TMA box: the fetch granularity of a run's tail
 constexpr int kDecMaxBatch = 1024;                         // sequences per launch (their chunk table lives in shared memory)
-constexpr int kDecodeRowsPerSplit = 128;  // the workspace holds ceil(max_rows / 128) + 2 partials per query head
 constexpr int kDecMaxSmem = 227 * 1024;   // dynamic shared memory one CTA may use (one CTA per SM)
 
 // Shared-memory layout of the attention kernel (byte offsets), for G query heads per kv head.
@@ -667,26 +667,12 @@ static int device_sm_count() {
   return n_sm;
 }
 
-typedef CUresult (*TensorMapEncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
-                                      const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
-                                      CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
 // [rows][D] bf16 row array -> tensor map with boxes of kDecBoxRows rows x min(D, 64) elements
 static bool encode_rows_map(CUtensorMap* m, const void* base, uint64_t rows, int D) {
-  static TensorMapEncodeFn enc = nullptr;
-  if (!enc) {
-    void* fn = nullptr;
-    cudaDriverEntryPointQueryResult qres;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres) != cudaSuccess || !fn) return false;
-    enc = reinterpret_cast<TensorMapEncodeFn>(fn);
-  }
   const cuuint64_t gdim[2] = {(cuuint64_t)D, rows};
   const cuuint64_t gstr[1] = {(cuuint64_t)D * 2};
   const cuuint32_t box[2] = {(cuuint32_t)(D >= 64 ? 64 : D), (cuuint32_t)kDecBoxRows};
-  const cuuint32_t es[2] = {1, 1};
-  return enc(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), gdim, gstr, box, es,
-             CU_TENSOR_MAP_INTERLEAVE_NONE, D >= 64 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
-             CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+  return encode_bf16_map(m, base, 2, gdim, gstr, box);
 }
 
 // The tensor maps of a decode cache (small cache keyed by the array addresses and sizes: a serving loop
@@ -768,11 +754,10 @@ static cudaError_t launch_pdl(void (*kern)(KArgs...), dim3 grid, dim3 block, siz
 template <int D, int ST, int NH>
 static cudaError_t launch_decode_attn(const LayerDev& L, int batch, const DecodeCacheDev& cache, Tensor4 q,
                                       const int* n_append, int max_rows, bf16* out, float* partial, int* counters,
-                                      int mode, int grid, const DecMaps& maps, bool pdl, cudaStream_t stream) {
+                                      int nslots, int mode, int grid, const DecMaps& maps, bool pdl, cudaStream_t stream) {
   // The workspace holds `nslots` partial results per query head; a kv row of at most max_chunks chunks cut
   // into ranges of at least per_min chunks never needs more.
   const int G = L.Hq / L.Hkv, rows = batch * L.Hkv;
-  const int nslots = (max_rows + kDecodeRowsPerSplit - 1) / kDecodeRowsPerSplit + 2;
   const int max_chunks = (max_rows + kDecChunk - 1) / kDecChunk + 3;
   const int per_min = (max_chunks + nslots - 2) / (nslots - 1);
   auto kern = kvm_decode_attn_kernel<D, ST, NH>;
@@ -806,10 +791,9 @@ static cudaError_t launch_decode_attn(const LayerDev& L, int batch, const Decode
 template <int D>
 static cudaError_t launch_decode(const LayerDev& L, int batch, const DecodeCacheDev& cache, Tensor4 q, Tensor4 k,
                                  Tensor4 v, Tensor4 gate, const int* n_append, int any_update, int max_rows, bf16* out,
-                                 int* route, bf16* pk_scr, bf16* gk_scr, float* partial, int* counters,
+                                 int* route, bf16* pk_scr, float* partial, int* counters, int nslots,
                                  int overlap, cudaStream_t stream) {
   constexpr int NT = 512;
-  (void)gk_scr;
   const int rows = batch * L.Hkv, G = L.Hq / L.Hkv;
   if (G > 16) return cudaErrorInvalidValue;  // the query heads of a kv head form one M=16 MMA tile
   const int n_sm = device_sm_count();
@@ -819,10 +803,10 @@ static cudaError_t launch_decode(const LayerDev& L, int batch, const DecodeCache
   if (!decode_maps(cache, (uint64_t)rows, cache.mem.capacity, L.W * L.C, D, &maps)) return cudaErrorInvalidValue;
   auto attn = [&](int mode, int grid, const int* na, bool pdl = false) {
     if (G <= 8)
-      return st3 ? launch_decode_attn<D, 3, 1>(L, batch, cache, q, na, max_rows, out, partial, counters, mode, grid, maps, pdl, stream)
-                 : launch_decode_attn<D, 2, 1>(L, batch, cache, q, na, max_rows, out, partial, counters, mode, grid, maps, pdl, stream);
-    return st3 ? launch_decode_attn<D, 3, 2>(L, batch, cache, q, na, max_rows, out, partial, counters, mode, grid, maps, pdl, stream)
-               : launch_decode_attn<D, 2, 2>(L, batch, cache, q, na, max_rows, out, partial, counters, mode, grid, maps, pdl, stream);
+      return st3 ? launch_decode_attn<D, 3, 1>(L, batch, cache, q, na, max_rows, out, partial, counters, nslots, mode, grid, maps, pdl, stream)
+                 : launch_decode_attn<D, 2, 1>(L, batch, cache, q, na, max_rows, out, partial, counters, nslots, mode, grid, maps, pdl, stream);
+    return st3 ? launch_decode_attn<D, 3, 2>(L, batch, cache, q, na, max_rows, out, partial, counters, nslots, mode, grid, maps, pdl, stream)
+               : launch_decode_attn<D, 2, 2>(L, batch, cache, q, na, max_rows, out, partial, counters, nslots, mode, grid, maps, pdl, stream);
   };
   cudaError_t e;
   {
@@ -875,12 +859,12 @@ static cudaError_t launch_decode(const LayerDev& L, int batch, const DecodeCache
 
 cudaError_t decode_dispatch(int D, const LayerDev& L, int batch, const DecodeCacheDev& cache, Tensor4 q, Tensor4 k,
                             Tensor4 v, Tensor4 gate, const int* n_append, int any_update, int max_rows, bf16* out,
-                            int* route, bf16* pk_scr, bf16* gk_scr, float* partial, int* counters, int overlap,
+                            int* route, bf16* pk_scr, float* partial, int* counters, int nslots, int overlap,
                             cudaStream_t stream) {
   switch (D) {
-    case 32: return launch_decode<32>(L, batch, cache, q, k, v, gate, n_append, any_update, max_rows, out, route, pk_scr, gk_scr, partial, counters, overlap, stream);
-    case 64: return launch_decode<64>(L, batch, cache, q, k, v, gate, n_append, any_update, max_rows, out, route, pk_scr, gk_scr, partial, counters, overlap, stream);
-    case 128: return launch_decode<128>(L, batch, cache, q, k, v, gate, n_append, any_update, max_rows, out, route, pk_scr, gk_scr, partial, counters, overlap, stream);
+    case 32: return launch_decode<32>(L, batch, cache, q, k, v, gate, n_append, any_update, max_rows, out, route, pk_scr, partial, counters, nslots, overlap, stream);
+    case 64: return launch_decode<64>(L, batch, cache, q, k, v, gate, n_append, any_update, max_rows, out, route, pk_scr, partial, counters, nslots, overlap, stream);
+    case 128: return launch_decode<128>(L, batch, cache, q, k, v, gate, n_append, any_update, max_rows, out, route, pk_scr, partial, counters, nslots, overlap, stream);
   }
   return cudaErrorInvalidValue;
 }
