@@ -49,8 +49,8 @@ constexpr float kRescaleThreshold = 8.0f;  // log2 units
 template <int NQ>
 struct Cfg {
   static constexpr int kSoftmaxWarps = NQ * 4;
-  static constexpr int kThreads = (kSoftmaxWarps + kLoaders + 1) * 32;
-  static constexpr int kMmaWarp = kSoftmaxWarps + kLoaders;
+  static constexpr int kThreads = (kSoftmaxWarps + kLoaders + NQ) * 32;
+  static constexpr int kMmaWarp = kSoftmaxWarps + kLoaders;    // first of NQ MMA-issuing warps
   static constexpr uint32_t kTmemCols = NQ == 2 ? 512 : 256;
   static constexpr uint32_t kColO = NQ * 128;                  // first column of the output accumulators
   static constexpr uint32_t kOffQ = 0;                         // NQ x 2 x [128][64] bf16
@@ -72,10 +72,17 @@ __device__ __forceinline__ bool warp_wait(uint64_t* bar, uint32_t parity) {
   return __all_sync(0xffffffffu, ok);
 }
 
+#ifndef KVM_ATT_EXP
+#define KVM_ATT_EXP 0
+#endif
 __device__ __forceinline__ float ex2(float x) {
+#if KVM_ATT_EXP == 1
+  return fmaf(x, 0.001f, 0.5f);
+#else
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
+#endif
 }
 
 // Geometry of one CTA, computed identically by every role.
@@ -147,6 +154,10 @@ __device__ __forceinline__ bool loader_role(const Slice<NQ>& sl, unsigned char* 
       TC_MARK(1, prof);
       continue;
     }
+#if KVM_ATT_EXP == 3
+    if (lane == 0) tc::mbar_arrive(&bars->kv_full[stage]);
+    continue;
+#endif
     const int row0 = t * BN;
     const int i0 = row0 + lane < sl.S ? __ldg(sl.midx + row0 + lane) : 0;
     const int i1 = row0 + 32 + lane < sl.S ? __ldg(sl.midx + row0 + 32 + lane) : 0;
@@ -173,69 +184,66 @@ __device__ __forceinline__ bool loader_role(const Slice<NQ>& sl, unsigned char* 
 }
 
 // ------------------------------------------------------------------------------------------ MMA issue
-// Executed by ONE thread.  Order: QK of tiles 0 and 1, then per tile t: P V of every query tile (as its
-// softmax delivers P), release of the stage, QK of tile t+2.
+// One thread per query tile issues that tile's MMAs (a single thread issuing for both query tiles spent
+// more cycles issuing than the tensor core needs to execute).  Order: QK of tiles 0 and 1, then per tile t:
+// P V (as the softmax delivers P), release of the stage, QK of tile t+2.  A stage is released by every
+// issuer: one that does not use a tile (the causal range of its query tile ends earlier) still arrives
+// on the stage's barrier, after the tile has landed, so that arrivals stay in step with the stage's uses.
 template <int NQ>
-__device__ __forceinline__ bool mma_role(const Slice<NQ>& sl, unsigned char* smem, Bars* bars, uint32_t tmem) {
+__device__ __forceinline__ bool mma_role(const Slice<NQ>& sl, unsigned char* smem, Bars* bars, uint32_t tmem, int qi) {
   using CF = Cfg<NQ>;
   constexpr uint32_t idesc_qk = tc::make_idesc(BM, BN, 0, 0);
   constexpr uint32_t idesc_pv = tc::make_idesc(BM, HD, 0, 1);
   const uint32_t sQ = tc::smem_u32(smem + CF::kOffQ), sK = tc::smem_u32(smem + CF::kOffK);
   const uint32_t sV = tc::smem_u32(smem + CF::kOffV), sP = tc::smem_u32(smem + CF::kOffP);
   // descriptors differ only in their 14-bit start-address field: build each base once, then add offsets
-  const uint64_t dQ = tc::make_desc(sQ, 16, 1024), dK = tc::make_desc(sK, 16, 1024);
-  const uint64_t dP = tc::make_desc(sP, 16, 1024), dV = tc::make_desc(sV, 8192, 1024);
-  auto issue_qk = [&](int qi, int t) {
+  const uint64_t dQ = tc::make_desc(sQ, 16, 1024) + (uint64_t)((qi * 32768) >> 4), dK = tc::make_desc(sK, 16, 1024);
+  const uint64_t dP = tc::make_desc(sP, 16, 1024) + (uint64_t)((qi * 16384) >> 4), dV = tc::make_desc(sV, 8192, 1024);
+  const int nt = sl.n_tiles[qi];
+  auto issue_qk = [&](int t) {
     const int stage = t % kStages, sbuf = t & 1;
     const uint32_t d = tmem + (uint32_t)((qi * 2 + sbuf) * BN);
-    const uint64_t da0 = dQ + (uint64_t)((qi * 32768) >> 4);
     const uint64_t db0 = dK + (uint64_t)((stage * 16384) >> 4);
 #pragma unroll
     for (int ks = 0; ks < HD / 16; ++ks) {
-      const uint64_t da = da0 + (uint64_t)(((ks >> 2) * 16384 + (ks & 3) * 32) >> 4);
+      const uint64_t da = dQ + (uint64_t)(((ks >> 2) * 16384 + (ks & 3) * 32) >> 4);
       const uint64_t db = db0 + (uint64_t)(((ks >> 2) * 8192 + (ks & 3) * 32) >> 4);
       tc::mma_ss(d, da, db, idesc_qk, ks > 0);
     }
     tc::mma_commit(&bars->s_full[qi][sbuf]);
   };
-#pragma unroll
-  for (int qi = 0; qi < NQ; ++qi)
-    if (sl.n_tiles[qi] > 0 && !tc::mbar_wait(&bars->q_full[qi], 0)) return false;
-  for (int t = 0; t < 2 && t < sl.n_max; ++t) {
+  if (nt > 0 && !tc::mbar_wait(&bars->q_full[qi], 0)) return false;
+  for (int t = 0; t < 2 && t < nt; ++t) {
     if (!tc::mbar_wait(&bars->kv_full[t % kStages], 0)) return false;
     tc::tc_fence_after_sync();
-#pragma unroll
-    for (int qi = 0; qi < NQ; ++qi)
-      if (t < sl.n_tiles[qi]) issue_qk(qi, t);
+    issue_qk(t);
   }
-  const bool prof = blockIdx.x == 0 && blockIdx.y == 0;
+  const bool prof = blockIdx.x == 0 && blockIdx.y == 0 && qi == NQ - 1;
   (void)prof;
   TC_T0();
   for (int t = 0; t < sl.n_max; ++t) {
     const int stage = t % kStages;
-#pragma unroll
-    for (int qi = 0; qi < NQ; ++qi) {
-      if (t >= sl.n_tiles[qi]) continue;
+    if (t < nt) {
       if (!tc::mbar_wait(&bars->p_full[qi], t & 1)) return false;
-      TC_MARK(4 + qi, prof);
+      TC_MARK(4, prof);
       tc::tc_fence_after_sync();
-      const uint64_t da0 = dP + (uint64_t)((qi * 16384) >> 4);
       const uint64_t db0 = dV + (uint64_t)((stage * 16384) >> 4);
 #pragma unroll
       for (int ks = 0; ks < BN / 16; ++ks)
-        tc::mma_ss(tmem + CF::kColO + qi * 128, da0 + (uint64_t)((ks * 32) >> 4), db0 + (uint64_t)((ks * 2048) >> 4),
-                   idesc_pv, (t > 0) || (ks > 0));
+        tc::mma_ss(tmem + CF::kColO + qi * 128, dP + (uint64_t)((ks * 32) >> 4), db0 + (uint64_t)((ks * 2048) >> 4), idesc_pv,
+                   (t > 0) || (ks > 0));
       tc::mma_commit(&bars->pv_done[qi]);
+      tc::mma_commit(&bars->kv_empty[stage]);
+      TC_MARK(6, prof);
+    } else {
+      if (!tc::mbar_wait(&bars->kv_full[stage], (t / kStages) & 1)) return false;
+      tc::mbar_arrive(&bars->kv_empty[stage]);
     }
-    tc::mma_commit(&bars->kv_empty[stage]);
-    TC_MARK(6, prof);
-    if (t + 2 < sl.n_max) {
+    if (t + 2 < nt) {
       if (!tc::mbar_wait(&bars->kv_full[(t + 2) % kStages], ((t + 2) / kStages) & 1)) return false;
       TC_MARK(7, prof);
       tc::tc_fence_after_sync();
-#pragma unroll
-      for (int qi = 0; qi < NQ; ++qi)
-        if (t + 2 < sl.n_tiles[qi]) issue_qk(qi, t + 2);
+      issue_qk(t + 2);
       TC_MARK(8, prof);
     }
   }
@@ -267,6 +275,14 @@ __device__ __forceinline__ bool softmax_role(const Slice<NQ>& sl, const LayerDev
     if (!warp_wait(&bars->s_full[qi][sbuf], (t >> 1) & 1)) return false;
     TC_MARK(10, prof);
     tc::tc_fence_after_sync();
+#if KVM_ATT_EXP == 2
+    if (t > 0 && !warp_wait(&bars->pv_done[qi], (t - 1) & 1)) return false;
+    tc::fence_proxy_async();
+    tc::tc_fence_before_sync();
+    __syncwarp();
+    if (lane == 0) tc::mbar_arrive(&bars->p_full[qi]);
+    continue;
+#endif
     uint32_t sr[2][32];
     tc::tmem_ld32(lane_addr + (uint32_t)((qi * 2 + sbuf) * BN), sr[0]);
     tc::tmem_ld32(lane_addr + (uint32_t)((qi * 2 + sbuf) * BN + 32), sr[1]);
@@ -426,7 +442,7 @@ kvm_attn_prefill_tc_kernel(LayerDev L, long long T, Tensor4 q, Tensor4 k, Tensor
     }
     for (int i = 0; i < kStages; ++i) {
       tc::mbar_init(&bars->kv_full[i], 1);
-      tc::mbar_init(&bars->kv_empty[i], 1);
+      tc::mbar_init(&bars->kv_empty[i], NQ);
     }
     tc::fence_barrier_init();
   }
@@ -443,7 +459,7 @@ kvm_attn_prefill_tc_kernel(LayerDev L, long long T, Tensor4 q, Tensor4 k, Tensor
     ok = loader_role<NQ>(sl, smem, bars, warp - CF::kSoftmaxWarps, lane, &maps);
     cp_async_wait<0>();
   } else {
-    if (lane == 0) ok = mma_role<NQ>(sl, smem, bars, tmem);
+    if (lane == 0) ok = mma_role<NQ>(sl, smem, bars, tmem, warp - CF::kMmaWarp);
     __syncwarp();
   }
   if (!ok) atomicExch(status, KVM_ERR_DEVICE_TIMEOUT);
