@@ -72,17 +72,10 @@ __device__ __forceinline__ bool warp_wait(uint64_t* bar, uint32_t parity) {
   return __all_sync(0xffffffffu, ok);
 }
 
-#ifndef KVM_ATT_EXP
-#define KVM_ATT_EXP 0
-#endif
 __device__ __forceinline__ float ex2(float x) {
-#if KVM_ATT_EXP == 1
-  return fmaf(x, 0.001f, 0.5f);
-#else
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
-#endif
 }
 
 // Geometry of one CTA, computed identically by every role.
@@ -154,10 +147,6 @@ __device__ __forceinline__ bool loader_role(const Slice<NQ>& sl, unsigned char* 
       TC_MARK(1, prof);
       continue;
     }
-#if KVM_ATT_EXP == 3
-    if (lane == 0) tc::mbar_arrive(&bars->kv_full[stage]);
-    continue;
-#endif
     const int row0 = t * BN;
     const int i0 = row0 + lane < sl.S ? __ldg(sl.midx + row0 + lane) : 0;
     const int i1 = row0 + 32 + lane < sl.S ? __ldg(sl.midx + row0 + 32 + lane) : 0;
@@ -275,14 +264,6 @@ __device__ __forceinline__ bool softmax_role(const Slice<NQ>& sl, const LayerDev
     if (!warp_wait(&bars->s_full[qi][sbuf], (t >> 1) & 1)) return false;
     TC_MARK(10, prof);
     tc::tc_fence_after_sync();
-#if KVM_ATT_EXP == 2
-    if (t > 0 && !warp_wait(&bars->pv_done[qi], (t - 1) & 1)) return false;
-    tc::fence_proxy_async();
-    tc::tc_fence_before_sync();
-    __syncwarp();
-    if (lane == 0) tc::mbar_arrive(&bars->p_full[qi]);
-    continue;
-#endif
     uint32_t sr[2][32];
     tc::tmem_ld32(lane_addr + (uint32_t)((qi * 2 + sbuf) * BN), sr[0]);
     tc::tmem_ld32(lane_addr + (uint32_t)((qi * 2 + sbuf) * BN + 32), sr[1]);
