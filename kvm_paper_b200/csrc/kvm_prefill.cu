@@ -433,24 +433,49 @@ static cudaError_t launch_prefill(const LayerDev& L, int batch, long long T, Ten
     auto kern = sb ? kvm_chain_kernel<D, NT, true> : kvm_chain_kernel<D, NT, false>;
     e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_u);
     if (e != cudaSuccess) return e;
-    // a cluster of CTAs per kv row when the GPU has more SMs than rows (the chain is latency-bound per row)
-    int dev = 0, n_sm = 0;
-    cudaGetDevice(&dev);
-    cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, dev);
-    int nc = 1;
-    while (nc * 2 <= kMaxCluster && rows * nc * 2 <= n_sm && n_plan > 1) nc *= 2;
+    // A cluster of CTAs per kv row when the GPU has room for it (the chain is latency-bound per row): the largest
+    // cluster size for which every row's cluster is resident at once.  A cluster must fit inside one GPC, so the
+    // count of co-resident clusters comes from the occupancy query, not from the SM count alone (16 clusters of 8
+    // do not fit 148 SMs: a second wave would double the time).
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(rows * nc);
     cfg.blockDim = dim3(NT);
     cfg.dynamicSmemBytes = smem_u;
     cfg.stream = stream;
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeClusterDimension;
-    attr[0].val.clusterDim.x = nc;
     attr[0].val.clusterDim.y = 1;
     attr[0].val.clusterDim.z = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
+    int nc = 1;
+    if (n_plan > 1) {
+      static int fit_rows[4] = {-1, -1, -1, -1};  // co-resident clusters of 1, 2, 4, 8 CTAs (cached occupancy queries)
+      static size_t fit_smem = 0;
+      if (fit_smem != smem_u) {
+        fit_rows[0] = fit_rows[1] = fit_rows[2] = fit_rows[3] = -1;
+        fit_smem = smem_u;
+      }
+      for (int lg = 3; lg >= 1; --lg) {
+        const int c = 1 << lg;
+        if (c > kMaxCluster) continue;
+        if (fit_rows[lg] < 0) {
+          int n_clusters = 0;
+          cfg.gridDim = dim3(c * 64);
+          attr[0].val.clusterDim.x = c;
+          if (cudaOccupancyMaxActiveClusters(&n_clusters, kern, &cfg) != cudaSuccess) {
+            (void)cudaGetLastError();
+            n_clusters = 0;
+          }
+          fit_rows[lg] = n_clusters;
+        }
+        if (fit_rows[lg] >= rows) {
+          nc = c;
+          break;
+        }
+      }
+    }
+    cfg.gridDim = dim3(rows * nc);
+    attr[0].val.clusterDim.x = nc;
     int* ver_arg = versions ? ver_idx : nullptr;
     e = cudaLaunchKernelEx(&cfg, kern, L, T, k, v, gate, plan_dev, n_plan, mem, pool_k, pool_v, pool_rows, ver_arg, ver_rows,
                            pk_scr, (const bf16*)pk_all, route, nc, status);

@@ -41,6 +41,7 @@ __device__ long long g_phase_cycles[16];
 #endif
 
 constexpr int kScanTile = 64;  // memory rows per shared-memory tile of the routing GEMM
+constexpr int kMaxCluster = 8; // CTAs that may share one kv row (the portable cluster size limit)
 constexpr int kDirectRows = 4; // up to this many appended rows are scored with plain dot products
 
 struct TokenSrc {  // the C tokens consumed by one update; token t at base + t*stride
@@ -110,7 +111,7 @@ struct UpdateSmem {
   bool use_tc;     // the tcgen05 routing scan is available (tensor memory allocated, barriers initialised once)
   uint32_t tc_tiles;  // tiles issued so far by the tcgen05 scan: tile n signals barrier n%2 with phase parity (n/2)%2
   int* status;     // device status word (a bounded wait that ran out is reported here), or null
-  static constexpr int kTokenArrays = 13 + 3 * 4;
+  static constexpr int kTokenArrays = 13 + 3 * kMaxCluster;
   __host__ __device__ static size_t bytes(int C, int capacity, bool sb) {
     size_t b = (size_t)2 * kScanTile * scan_tile_stride<D>() * sizeof(bf16);
     if (sb) b += (size_t)C * (D + 8) * sizeof(bf16) + (size_t)C * D * sizeof(bf16);
@@ -134,9 +135,9 @@ struct UpdateSmem {
       base += (size_t)C * 4;
     }
     base += (size_t)C * 4;  // spare
-    xapp = reinterpret_cast<float*>(base); base += (size_t)4 * C * 4;
-    xbest = reinterpret_cast<float*>(base); base += (size_t)4 * C * 4;
-    xidx = reinterpret_cast<int*>(base); base += (size_t)4 * C * 4;
+    xapp = reinterpret_cast<float*>(base); base += (size_t)kMaxCluster * C * 4;
+    xbest = reinterpret_cast<float*>(base); base += (size_t)kMaxCluster * C * 4;
+    xidx = reinterpret_cast<int*>(base); base += (size_t)kMaxCluster * C * 4;
     cur = reinterpret_cast<int*>(base); base += (size_t)((capacity + 3) / 4 * 4) * 4;
     counters = reinterpret_cast<int*>(base); base += 36 * 4;
     bars = reinterpret_cast<uint64_t*>(base);
@@ -157,7 +158,6 @@ __host__ __device__ inline bool update_block_fits_smem(int C, int capacity) {
 // A cluster of up to kMaxCluster CTAs may share one kv row: the memory rows of the routing scan and the
 // touched rows of the scatter are split between them, partial routing results are exchanged through
 // distributed shared memory, everything else is computed redundantly (it is deterministic).
-constexpr int kMaxCluster = 4;
 __device__ __forceinline__ void cluster_sync_all() {
   asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
