@@ -41,7 +41,7 @@ __device__ long long g_phase_cycles[16];
 #endif
 
 constexpr int kScanTile = 64;  // memory rows per shared-memory tile of the routing GEMM
-constexpr int kMaxCluster = 8; // CTAs that may share one kv row (the portable cluster size limit)
+constexpr int kMaxCluster = 4; // CTAs that may share one kv row
 constexpr int kDirectRows = 4; // up to this many appended rows are scored with plain dot products
 
 struct TokenSrc {  // the C tokens consumed by one update; token t at base + t*stride
