@@ -294,14 +294,12 @@ def run_b200(args):
                           (q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2), gate.transpose(1, 2)))
         for h_, d_ in ((hq, q), (hk, k), (hv, v), (hg, gate)):
             h_.copy_(d_.transpose(1, 2))
-        dq, dk, dv, dg = (torch.empty_like(h_, device=dev) for h_ in (hq, hk, hv, hg))
         h_out = torch.empty(B, T, h_loc * D, dtype=torch.bfloat16).pin_memory()
+        # the package's host-buffer entry point: copy-in, kernels and copy-out of consecutive sequences overlap
+        host_prefill = ops.HostPrefill(runner.params, B, plan, slice_batch=1)
 
         def e2e_step():
-            dq.copy_(hq, non_blocking=True); dk.copy_(hk, non_blocking=True)
-            dv.copy_(hv, non_blocking=True); dg.copy_(hg, non_blocking=True)
-            out = runner.run(dq.transpose(1, 2), dk.transpose(1, 2), dv.transpose(1, 2), dg.transpose(1, 2))
-            h_out.copy_(out, non_blocking=True)
+            host_prefill.run(hq, hk, hv, hg, h_out)
 
         n_e2e = max(2, min(args.steps, 5))
         e2e_step()
@@ -318,7 +316,7 @@ def run_b200(args):
         h2d = sum(t_.numel() * t_.element_size() for t_ in (hq, hk, hv, hg))
         e2e = {"value": round(B * T / (float(t2.item()) * 1e-3), 1), "unit": UNIT, "ms_per_step": round(float(t2.item()), 3),
                "h2d_bytes_per_step": h2d * world, "d2h_bytes_per_step": h_out.numel() * 2 * world}
-        del hq, hk, hv, hg, dq, dk, dv, dg, h_out
+        del hq, hk, hv, hg, h_out, host_prefill
 
     del runner, q, k, v, gate
     torch.cuda.empty_cache()

@@ -246,6 +246,62 @@ class PrefillRunner:
         _lib.check(rc)
 
 
+class HostPrefill:
+    """Prefill whose inputs and output live in pinned host memory (a serving front end that receives the
+    post-QKV tensors of a request batch on the host): the batch is cut into slices of sequences and slice
+    i+1 is copied in while slice i is computed and slice i-1 is copied out, on three streams (copy-in,
+    the caller's current stream, copy-out) with two sets of device buffers.
+
+    Host tensors are laid out as the projections produce them: q [B,T,Hq,D], k/v [B,T,Hkv,D],
+    gate [B,T,Hkv,1], out [B,T,Hq*D], all bf16 and pinned."""
+
+    def __init__(self, params: LayerParams, batch: int, plan: PrefillPlan, slice_batch: int = 1):
+        cfg = params.cfg
+        if batch % slice_batch:
+            raise ValueError(f"batch {batch} is not a multiple of the slice size {slice_batch}")
+        dev = params.device
+        self.params, self.plan, self.batch, self.bs = params, plan, int(batch), int(slice_batch)
+        T, D = plan.seq_len, cfg.head_dim
+        kw = dict(device=dev, dtype=torch.bfloat16)
+        self.runners = [PrefillRunner(params, self.bs, plan) for _ in range(2)]
+        self.dev_in = [(torch.empty(self.bs, T, cfg.n_q_heads, D, **kw), torch.empty(self.bs, T, cfg.n_kv_heads, D, **kw),
+                        torch.empty(self.bs, T, cfg.n_kv_heads, D, **kw), torch.empty(self.bs, T, cfg.n_kv_heads, 1, **kw))
+                       for _ in range(2)]
+        self.s_in, self.s_out = torch.cuda.Stream(device=dev), torch.cuda.Stream(device=dev)
+        self.ev_in = [torch.cuda.Event() for _ in range(2)]      # inputs of the slot have arrived
+        self.ev_comp = [torch.cuda.Event() for _ in range(2)]    # the slot's kernels are done (inputs free, output ready)
+        self.ev_out = [torch.cuda.Event() for _ in range(2)]     # the slot's output has left the device
+
+    def run(self, hq: torch.Tensor, hk: torch.Tensor, hv: torch.Tensor, hg: torch.Tensor, h_out: torch.Tensor) -> torch.Tensor:
+        for name, t in (("q", hq), ("k", hk), ("v", hv), ("gate", hg), ("out", h_out)):
+            if t.is_cuda or not t.is_pinned() or t.dtype != torch.bfloat16 or t.size(0) != self.batch:
+                raise ValueError(f"{name} must be a pinned bf16 host tensor with batch {self.batch}")
+        cur = torch.cuda.current_stream(self.params.device)
+        self.s_in.wait_stream(cur)  # whatever produced the host buffers' contents is ordered before the copies
+        n = self.batch // self.bs
+        for i in range(n):
+            slot, lo = i % 2, i * self.bs
+            with torch.cuda.stream(self.s_in):
+                if i >= 2:
+                    self.s_in.wait_event(self.ev_comp[slot])  # slice i-2 no longer reads these device buffers
+                for d, h in zip(self.dev_in[slot], (hq, hk, hv, hg)):
+                    d.copy_(h[lo:lo + self.bs], non_blocking=True)
+                self.ev_in[slot].record(self.s_in)
+            cur.wait_event(self.ev_in[slot])
+            if i >= 2:
+                cur.wait_event(self.ev_out[slot])  # the slot's output buffer has been copied out
+            dq, dk, dv, dg = (t.transpose(1, 2) for t in self.dev_in[slot])
+            out = self.runners[slot].run(dq, dk, dv, dg)
+            self.ev_comp[slot].record(cur)
+            with torch.cuda.stream(self.s_out):
+                self.s_out.wait_event(self.ev_comp[slot])
+                h_out[lo:lo + self.bs].copy_(out, non_blocking=True)
+                self.ev_out[slot].record(self.s_out)
+        for slot in range(min(2, n)):
+            cur.wait_event(self.ev_out[slot])  # the call is complete, in stream order, when the output is on the host
+        return h_out
+
+
 def prefill_forward(params: LayerParams, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, gate: torch.Tensor,
                     plan: PrefillPlan, *, memory_capacity: int | None = None, want_route: bool = False,
                     phases: int = _lib.PREFILL_CHAIN | _lib.PREFILL_ATTENTION, check: bool = False) -> PrefillResult:
