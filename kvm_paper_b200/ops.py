@@ -268,7 +268,8 @@ class HostPrefill:
                         torch.empty(self.bs, T, cfg.n_kv_heads, D, **kw), torch.empty(self.bs, T, cfg.n_kv_heads, 1, **kw))
                        for _ in range(2)]
         self.s_in, self.s_out = torch.cuda.Stream(device=dev), torch.cuda.Stream(device=dev)
-        self.ev_in = [torch.cuda.Event() for _ in range(2)]      # inputs of the slot have arrived
+        self.ev_kv = [torch.cuda.Event() for _ in range(2)]      # keys, values and gates of the slot have arrived
+        self.ev_in = [torch.cuda.Event() for _ in range(2)]      # ... and the queries
         self.ev_comp = [torch.cuda.Event() for _ in range(2)]    # the slot's kernels are done (inputs free, output ready)
         self.ev_out = [torch.cuda.Event() for _ in range(2)]     # the slot's output has left the device
 
@@ -284,14 +285,19 @@ class HostPrefill:
             with torch.cuda.stream(self.s_in):
                 if i >= 2:
                     self.s_in.wait_event(self.ev_comp[slot])  # slice i-2 no longer reads these device buffers
-                for d, h in zip(self.dev_in[slot], (hq, hk, hv, hg)):
+                # keys, values and gates first: the memory trajectory does not need the queries
+                for d, h in zip(self.dev_in[slot][1:], (hk, hv, hg)):
                     d.copy_(h[lo:lo + self.bs], non_blocking=True)
+                self.ev_kv[slot].record(self.s_in)
+                self.dev_in[slot][0].copy_(hq[lo:lo + self.bs], non_blocking=True)
                 self.ev_in[slot].record(self.s_in)
+            dq, dk, dv, dg = (t.transpose(1, 2) for t in self.dev_in[slot])
+            cur.wait_event(self.ev_kv[slot])
+            self.runners[slot].run(dq, dk, dv, dg, phases=_lib.PREFILL_CHAIN)
             cur.wait_event(self.ev_in[slot])
             if i >= 2:
                 cur.wait_event(self.ev_out[slot])  # the slot's output buffer has been copied out
-            dq, dk, dv, dg = (t.transpose(1, 2) for t in self.dev_in[slot])
-            out = self.runners[slot].run(dq, dk, dv, dg)
+            out = self.runners[slot].run(dq, dk, dv, dg, phases=_lib.PREFILL_ATTENTION)
             self.ev_comp[slot].record(cur)
             with torch.cuda.stream(self.s_out):
                 self.s_out.wait_event(self.ev_comp[slot])
