@@ -75,11 +75,13 @@ typedef struct kvm_memory {
 typedef struct kvm_update_plan {
   int32_t state_before;  /* rows before the update */
   int32_t n_append;      /* 0..C rows appended (the least similar tokens), the rest are merged */
-  int32_t version_row;   /* first row of the version written after this update inside the version store */
+  int32_t version_row;   /* first entry of the version written after this update inside the version tables
+                            (one table entry per memory row: its row in the workspace's row pool) */
   int32_t reserved;
 } kvm_update_plan;
 
-/* Bytes of scratch kvm_prefill_forward needs for the given shape (versions + routing scratch).
+/* Bytes of scratch kvm_prefill_forward needs for the given shape (row pool, version tables, prepared keys,
+ * routing scratch, status word).
  * Replaces the workspace allocation inside build_prefill_forward
  * (model/kernels/kvm_triton_training_kernels.py:3416-3448). */
 size_t kvm_prefill_workspace_bytes(const kvm_layer* layer, int32_t batch, int64_t seq_len,

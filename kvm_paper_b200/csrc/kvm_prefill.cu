@@ -1,5 +1,5 @@
 // Prefill kernels: (1) the memory chain -- initial memory, then one block-recurrent update per
-// token block, each followed by a snapshot ("version") of the attention view of the memory;
+// token block, each leaving a "version" of the attention view of the memory (an index table into a row pool);
 // (2) block attention -- every query tile attends jointly to [memory version ; sliding window]
 // with one online softmax (front blocks: plain causal attention over the window only).
 //
@@ -27,7 +27,7 @@ kvm_prepare_keys_kernel(LayerDev L, Tensor4 k, bf16* __restrict__ pk_all, long l
 }
 
 // ------------------------------------------------------------------------------------------ chain
-// One CTA per kv row walks the whole prompt: initial memory, then one update per token block.  The
+// One CTA (or a cluster of up to 4 CTAs) per kv row walks the whole prompt: initial memory, then one update per token block.  The
 // attention view of the memory is kept in a row pool with per-version index tables (see ViewStore);
 // after the last update the final view is gathered into `mem.k_attn` / `mem.v_attn`.
 template <int D, int NT, bool SB>

@@ -19,7 +19,6 @@ from . import _lib
 from ._lib import KvmDecodeCache as _CCache
 from ._lib import KvmLayer, KvmMemory, KvmTensor4, KvmUpdatePlan
 
-DECODE_ROWS_PER_SPLIT = 128
 
 
 def _ptr(t: torch.Tensor | None) -> int | None:
@@ -200,7 +199,7 @@ class PrefillResult:
 
 
 class PrefillRunner:
-    """Preallocated buffers for repeated prefills of one shape (memory, version store, output).
+    """Preallocated buffers for repeated prefills of one shape (memory, workspace with the row pool and version tables, output).
 
     ``run`` only enqueues kernels on the current stream; nothing is allocated per call."""
 
