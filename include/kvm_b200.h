@@ -145,10 +145,10 @@ size_t kvm_decode_workspace_bytes(const kvm_layer* layer, int32_t batch, int32_t
  *                 any_update == 0
  *   any_update    host count of sequences with n_append_dev[b] >= 0 (0: launch no update kernel; a
  *                 negative value or one above batch means "some, count unknown").  With a known
- *                 count the update runs on a stream owned by the library, next to the attention of
- *                 the other sequences, and is joined back into `stream` before the call's last
- *                 kernel; all work of the call is ordered after prior work in `stream` and before
- *                 later work in it
+ *                 count the update (and the attention of the updated sequences behind it) runs on a
+ *                 stream owned by the library, next to the attention of the other sequences, and is
+ *                 joined back into `stream` at the end of the call; all work of the call is ordered
+ *                 after prior work in `stream` and before later work in it
  *   max_rows      upper bound of (memory rows + window rows) over the batch (launch geometry)
  *   out           [B,1,Hq*D] bf16
  *   route_dev     optional [batch*Hkv, C] int32, written for updated sequences (see prefill)

@@ -754,7 +754,8 @@ static cudaError_t launch_pdl(void (*kern)(KArgs...), dim3 grid, dim3 block, siz
 template <int D, int ST, int NH>
 static cudaError_t launch_decode_attn(const LayerDev& L, int batch, const DecodeCacheDev& cache, Tensor4 q,
                                       const int* n_append, int max_rows, bf16* out, float* partial, int* counters,
-                                      int nslots, int mode, int grid, const DecMaps& maps, bool pdl, cudaStream_t stream) {
+                                      int nslots, int mode, int grid, const DecMaps& maps, bool pdl, int done_slot,
+                                      cudaStream_t stream) {
   // The workspace holds `nslots` partial results per query head; a kv row of at most max_chunks chunks cut
   // into ranges of at least per_min chunks never needs more.
   const int G = L.Hq / L.Hkv, rows = batch * L.Hkv;
@@ -778,7 +779,7 @@ static cudaError_t launch_decode_attn(const LayerDev& L, int batch, const Decode
       smem_set = lay.total;
     }
     cudaError_t e = launch_pdl(kern, dim3(grid), dim3(kDecThreads), lay.total, stream, pdl && batch <= kDecMaxBatch, L, cache, q,
-                               n_append, partial, counters, counters + rows, counters + rows + batch, out,
+                               n_append, partial, counters, counters + rows + done_slot, counters + rows + batch, out,
                                1.0f / sqrtf((float)D), b0, nb, nslots, per_min, mode, maps);
     if (e != cudaSuccess) return e;
   }
@@ -801,12 +802,15 @@ static cudaError_t launch_decode(const LayerDev& L, int batch, const DecodeCache
   const bool st3 = DecSmem(D, G, L.Hq, std::min(batch, kDecMaxBatch), 3).total <= (size_t)kDecMaxSmem;
   DecMaps maps;
   if (!decode_maps(cache, (uint64_t)rows, cache.mem.capacity, L.W * L.C, D, &maps)) return cudaErrorInvalidValue;
-  auto attn = [&](int mode, int grid, const int* na, bool pdl = false) {
+  // `done_slot`: which launch counter of the workspace the launch uses (two launches that may run at the same
+  // time need one each); `st`: the stream it goes to
+  auto attn = [&](int mode, int grid, const int* na, bool pdl = false, int done_slot = 0, cudaStream_t st = nullptr) {
+    if (st == nullptr) st = stream;
     if (G <= 8)
-      return st3 ? launch_decode_attn<D, 3, 1>(L, batch, cache, q, na, max_rows, out, partial, counters, nslots, mode, grid, maps, pdl, stream)
-                 : launch_decode_attn<D, 2, 1>(L, batch, cache, q, na, max_rows, out, partial, counters, nslots, mode, grid, maps, pdl, stream);
-    return st3 ? launch_decode_attn<D, 3, 2>(L, batch, cache, q, na, max_rows, out, partial, counters, nslots, mode, grid, maps, pdl, stream)
-               : launch_decode_attn<D, 2, 2>(L, batch, cache, q, na, max_rows, out, partial, counters, nslots, mode, grid, maps, pdl, stream);
+      return st3 ? launch_decode_attn<D, 3, 1>(L, batch, cache, q, na, max_rows, out, partial, counters, nslots, mode, grid, maps, pdl, done_slot, st)
+                 : launch_decode_attn<D, 2, 1>(L, batch, cache, q, na, max_rows, out, partial, counters, nslots, mode, grid, maps, pdl, done_slot, st);
+    return st3 ? launch_decode_attn<D, 3, 2>(L, batch, cache, q, na, max_rows, out, partial, counters, nslots, mode, grid, maps, pdl, done_slot, st)
+               : launch_decode_attn<D, 2, 2>(L, batch, cache, q, na, max_rows, out, partial, counters, nslots, mode, grid, maps, pdl, done_slot, st);
   };
   cudaError_t e;
   {
@@ -847,14 +851,16 @@ static cudaError_t launch_decode(const LayerDev& L, int batch, const DecodeCache
   if ((e = cudaStreamWaitEvent(side->stream, side->fork, 0)) != cudaSuccess) return e;
   upd<<<rows, NT, smem_u, side->stream>>>(L, cache, k, v, gate, n_append, pk_scr, route, 2);
   if ((e = cudaGetLastError()) != cudaSuccess) return e;
+  // ... followed there by their attention, on the SMs the update leaves (second launch counter of the workspace;
+  // the two attention launches touch disjoint sequences, rows, partial slots and outputs)
+  if ((e = attn(2, upd_sms, n_append, false, 1, side->stream)) != cudaSuccess) return e;
   if ((e = cudaEventRecord(side->join, side->stream)) != cudaSuccess) return e;
   // ... next to the ring write and the attention of all others, which leave those SMs free
   kvm_decode_pre_kernel<D, 32, false, false><<<rows, 32, 0, stream>>>(L, cache, k, v, gate, n_append, pk_scr, route, 1);
   if ((e = cudaGetLastError()) != cudaSuccess) return e;
   if ((e = attn(1, n_sm - upd_sms, n_append)) != cudaSuccess) return e;
-  // join: attention of the updated sequences
-  if ((e = cudaStreamWaitEvent(stream, side->join, 0)) != cudaSuccess) return e;
-  return attn(2, n_sm, n_append);
+  // join
+  return cudaStreamWaitEvent(stream, side->join, 0);
 }
 
 cudaError_t decode_dispatch(int D, const LayerDev& L, int batch, const DecodeCacheDev& cache, Tensor4 q, Tensor4 k,
