@@ -432,7 +432,7 @@ __device__ __noinline__ bool scan_memory_tc(const BlockView& blk, bool gate_keys
                                             UpdateSmem<D>& s, int tiles_in_flight) {
   static_assert(D == 128 && NT == 512, "tcgen05 routing scan: head dimension 128, 16 warps");
   constexpr int TN = kTcTile;
-  constexpr uint32_t kWaitLimit = 1u << 12;  // the MMAs of one tile take well under a microsecond
+  constexpr uint32_t kWaitLimit = 1u << 16;  // the MMAs of one tile take well under a microsecond; ~13 ms before giving up
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int n_tiles = (n_end - n_begin + TN - 1) / TN;
   if (n_tiles <= 0) return true;
