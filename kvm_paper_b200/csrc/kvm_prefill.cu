@@ -12,18 +12,30 @@ namespace kvm {
 // ------------------------------------------------------------------------------------ prepared keys
 // Parallel pre-pass: prepared key (rotary dims zeroed, LayerNorm, bf16) of every token an update will
 // consume, written as [kv row][token][D].  Takes the LayerNorm off the sequential chain.
+constexpr int kPrepUnroll = 4;  // tokens per lane group: their loads are issued before the first LayerNorm
 template <int D>
 __global__ void __launch_bounds__(256)
 kvm_prepare_keys_kernel(LayerDev L, Tensor4 k, bf16* __restrict__ pk_all, long long n_tok) {
-  constexpr int GL = 8;
+  constexpr int GL = 8, TPB = 256 / GL;
   const int gl = threadIdx.x % GL;
-  const long long tkn = (long long)blockIdx.x * (256 / GL) + threadIdx.x / GL;
+  const long long base = (long long)blockIdx.x * (TPB * kPrepUnroll) + threadIdx.x / GL;
   const int row = blockIdx.y;
   const int b = row / L.Hkv, h = row % L.Hkv;
-  const bool act = tkn < n_tok;
-  RowVec<D, GL> r;
-  prepare_key_row<D, GL>(L, r, k.row(b, h, act ? tkn : 0), gl);
-  if (act) store_row<D, GL>(r, pk_all + ((size_t)row * n_tok + tkn) * D, gl);
+  RowVec<D, GL> r[kPrepUnroll];
+#pragma unroll
+  for (int u = 0; u < kPrepUnroll; ++u) {
+    const long long tkn = base + (long long)u * TPB;
+    load_row<D, GL>(r[u], k.row(b, h, tkn < n_tok ? tkn : 0), gl);
+  }
+#pragma unroll
+  for (int u = 0; u < kPrepUnroll; ++u) {
+    const long long tkn = base + (long long)u * TPB;
+#pragma unroll
+    for (int i = 0; i < D / GL; ++i)
+      if (gl * (D / GL) + i < L.rope_dim) r[u].x[i] = 0.f;
+    layer_norm_row<D, GL>(r[u], L.ln_w, L.ln_b, L.ln_eps, gl);
+    if (tkn < n_tok) store_row<D, GL>(r[u], pk_all + ((size_t)row * n_tok + tkn) * D, gl);
+  }
 }
 
 // ------------------------------------------------------------------------------------------ chain
@@ -425,7 +437,7 @@ static cudaError_t launch_prefill(const LayerDev& L, int batch, long long T, Ten
     const size_t smem_u = UpdateSmem<D>::bytes(L.C, mem.capacity, sb);
     if (n_plan > 1) {
       const long long n_tok = (long long)n_plan * L.C;
-      dim3 pgrid((unsigned)((n_tok + 31) / 32), rows);
+      dim3 pgrid((unsigned)((n_tok + 32 * kPrepUnroll - 1) / (32 * kPrepUnroll)), rows);
       kvm_prepare_keys_kernel<D><<<pgrid, 256, 0, stream>>>(L, k, pk_all, n_tok);
       e = cudaGetLastError();
       if (e != cudaSuccess) return e;
