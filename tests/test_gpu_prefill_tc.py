@@ -27,6 +27,7 @@ def _inputs(B, Hq, Hkv, T, seed):
     (128, 128 * 3, 4, 2, "fixed"),               # grouped queries share a kv row
     (256, 256 * 4 + 130, 2, 2, "power_law"),     # two query tiles per block, memory with a partial last tile
     (128, 100, 2, 2, "fixed"),                   # shorter than one block: front attention only
+    (512, 512 * 4 + 77, 2, 1, "power_law"),      # block of 512: the update reads the block from global memory (not staged)
 ])
 def test_tc_attention_matches_oracle(C, T, Hq, Hkv, mode):
     temps = dict(front_head_temp=torch.linspace(0.9, 1.2, Hq), state_head_temp=torch.linspace(1.1, 0.8, Hq))
