@@ -56,8 +56,7 @@ struct Cfg {
   static constexpr uint32_t kOffQ = 0;                         // NQ x 2 x [128][64] bf16
   static constexpr uint32_t kOffK = NQ * 32768;                // kStages x 2 x [64][64]
   static constexpr uint32_t kOffV = kOffK + kStages * 16384;   // kStages x 2 x [64 keys][64]
-  static constexpr uint32_t kOffP = kOffV + kStages * 16384;   // NQ x [128][64]
-  static constexpr uint32_t kOffBar = kOffP + NQ * 16384;
+  static constexpr uint32_t kOffBar = kOffV + kStages * 16384;
   static constexpr uint32_t kSmemBytes = kOffBar + 256;
 };
 
@@ -184,10 +183,10 @@ __device__ __forceinline__ bool mma_role(const Slice<NQ>& sl, unsigned char* sme
   constexpr uint32_t idesc_qk = tc::make_idesc(BM, BN, 0, 0);
   constexpr uint32_t idesc_pv = tc::make_idesc(BM, HD, 0, 1);
   const uint32_t sQ = tc::smem_u32(smem + CF::kOffQ), sK = tc::smem_u32(smem + CF::kOffK);
-  const uint32_t sV = tc::smem_u32(smem + CF::kOffV), sP = tc::smem_u32(smem + CF::kOffP);
+  const uint32_t sV = tc::smem_u32(smem + CF::kOffV);
   // descriptors differ only in their 14-bit start-address field: build each base once, then add offsets
   const uint64_t dQ = tc::make_desc(sQ, 16, 1024) + (uint64_t)((qi * 32768) >> 4), dK = tc::make_desc(sK, 16, 1024);
-  const uint64_t dP = tc::make_desc(sP, 16, 1024) + (uint64_t)((qi * 16384) >> 4), dV = tc::make_desc(sV, 8192, 1024);
+  const uint64_t dV = tc::make_desc(sV, 8192, 1024);
   const int nt = sl.n_tiles[qi];
   auto issue_qk = [&](int t) {
     const int stage = t % kStages, sbuf = t & 1;
@@ -217,9 +216,11 @@ __device__ __forceinline__ bool mma_role(const Slice<NQ>& sl, unsigned char* sme
       TC_MARK(4, prof);
       tc::tc_fence_after_sync();
       const uint64_t db0 = dV + (uint64_t)((stage * 16384) >> 4);
+      // P (bf16) lies in the first 32 columns of the score buffer it was computed from: 8 columns per k-step
+      const uint32_t aP = tmem + (uint32_t)((qi * 2 + (t & 1)) * BN);
 #pragma unroll
       for (int ks = 0; ks < BN / 16; ++ks)
-        tc::mma_ss(tmem + CF::kColO + qi * 128, dP + (uint64_t)((ks * 32) >> 4), db0 + (uint64_t)((ks * 2048) >> 4), idesc_pv,
+        tc::mma_ts(tmem + CF::kColO + qi * 128, aP + (uint32_t)(ks * 8), db0 + (uint64_t)((ks * 2048) >> 4), idesc_pv,
                    (t > 0) || (ks > 0));
       tc::mma_commit(&bars->pv_done[qi]);
       tc::mma_commit(&bars->kv_empty[stage]);
@@ -255,7 +256,6 @@ __device__ __forceinline__ bool softmax_role(const Slice<NQ>& sl, const LayerDev
   const float scale_mem = sm_scale * L.state_temp[sl.hq] * kLog2e;
   const float scale_win = sm_scale * L.front_temp[sl.hq] * kLog2e;
   float m_run = -INFINITY, l_run = 0.f;
-  unsigned char* prow = smem + CF::kOffP + qi * 16384 + row * 128;
   const bool prof = blockIdx.x == 0 && blockIdx.y == 0 && row == 0 && qi == NQ - 1;
   (void)prof;
   TC_T0();
@@ -290,9 +290,11 @@ __device__ __forceinline__ bool softmax_role(const Slice<NQ>& sl, const LayerDev
     const bool need = tmax > m_run + kRescaleThreshold || (m_run == -INFINITY && tmax > -INFINITY);
     const bool warp_need = __any_sync(0xffffffffu, need);
     TC_MARK(12, prof);
-    if (t > 0 && !warp_wait(&bars->pv_done[qi], (t - 1) & 1)) return false;
-    TC_MARK(13, prof);
     if (warp_need) {
+      // the running output may only be touched between P V of tile t-1 (complete) and of tile t (not yet issued:
+      // it waits for this warp's arrival below)
+      if (t > 0 && !warp_wait(&bars->pv_done[qi], (t - 1) & 1)) return false;
+      TC_MARK(13, prof);
       const float m_new = fmaxf(m_run, tmax);
       const float alpha = (m_run == -INFINITY) ? 0.f : ex2(m_run - m_new);
       l_run *= alpha;
@@ -314,23 +316,21 @@ __device__ __forceinline__ bool softmax_role(const Slice<NQ>& sl, const LayerDev
     TC_MARK(14, prof);
     const float neg_m = (m_run == -INFINITY) ? 0.f : -m_run;
     float ls0 = 0.f, ls1 = 0.f;
+    uint32_t pk[32];
 #pragma unroll
-    for (int cchunk = 0; cchunk < 8; ++cchunk) {
-      uint32_t pk[4];
-#pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        const int i = cchunk * 8 + e * 2;
-        const float p0 = ex2(fmaf(__uint_as_float(sr[i >> 5][i & 31]), sc, neg_m));
-        const float p1 = ex2(fmaf(__uint_as_float(sr[(i + 1) >> 5][(i + 1) & 31]), sc, neg_m));
-        ls0 += p0;
-        ls1 += p1;
-        pk[e] = pack_bf16(p0, p1);
-      }
-      *reinterpret_cast<uint4*>(prow + (((cchunk ^ (row & 7)) & 7) << 4)) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+    for (int e = 0; e < 32; ++e) {
+      const int i = e * 2;
+      const float p0 = ex2(fmaf(__uint_as_float(sr[i >> 5][i & 31]), sc, neg_m));
+      const float p1 = ex2(fmaf(__uint_as_float(sr[(i + 1) >> 5][(i + 1) & 31]), sc, neg_m));
+      ls0 += p0;
+      ls1 += p1;
+      pk[e] = pack_bf16(p0, p1);
     }
     l_run += ls0 + ls1;
+    // P replaces the scores it came from (all 64 columns of this row are in registers): the A operand of P V
+    tc::tmem_st32(lane_addr + (uint32_t)((qi * 2 + sbuf) * BN), pk);
+    tc::tmem_st_wait();
     TC_MARK(15, prof);
-    tc::fence_proxy_async();
     tc::tc_fence_before_sync();
     __syncwarp();
     if (lane == 0) tc::mbar_arrive(&bars->p_full[qi]);

@@ -74,6 +74,8 @@ RAGGED_CASES = {
     "gqa16_d128": (16, 1, 128, 64, 128, [380, 640, 127, 500], 40),
     # one query head per kv head, head dim 32 (unswizzled TMA boxes)
     "mha_d32": (2, 2, 32, 16, 64, [200, 66, 450], 70),
+    # block of 512 tokens: the boundary update reads the block from global memory instead of staging it
+    "gqa2_c512": (2, 1, 128, 64, 512, [1530, 2040, 1000], 30),
 }
 
 
