@@ -301,13 +301,13 @@ __device__ __forceinline__ bool softmax_role(const Slice<NQ>& sl, const LayerDev
       if (t > 0) {  // rescale the running output of this warp's 32 rows in tensor memory
         tc::tc_fence_after_sync();
 #pragma unroll
-        for (int cb = 0; cb < HD / 32; ++cb) {
-          uint32_t o[32];
-          tc::tmem_ld32(lane_addr + col_o + cb * 32, o);
+        for (int cb = 0; cb < HD / 16; ++cb) {  // 16 columns at a time: the scores of the tile stay in registers
+          uint32_t o[16];
+          tc::tmem_ld16(lane_addr + col_o + cb * 16, o);
           tc::tmem_ld_wait();
 #pragma unroll
-          for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
-          tc::tmem_st32(lane_addr + col_o + cb * 32, o);
+          for (int i = 0; i < 16; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+          tc::tmem_st16(lane_addr + col_o + cb * 16, o);
         }
         tc::tmem_st_wait();
       }
