@@ -87,6 +87,9 @@ struct Slice {
   const bf16* mk;
   const bf16* mv;
   const int* midx;
+  // per-query-tile values picked with compile-time indices, so that the slice stays in registers
+  __device__ __forceinline__ int tiles_of(int qi) const { return (NQ == 1 || qi == 0) ? n_tiles[0] : n_tiles[NQ - 1]; }
+  __device__ __forceinline__ long long q_end_of(int qi) const { return (NQ == 1 || qi == 0) ? q_end[0] : q_end[NQ - 1]; }
 };
 
 // ------------------------------------------------------------------------------------------ loaders
@@ -113,7 +116,7 @@ template <int NQ>
 __device__ __forceinline__ bool loader_role(const Slice<NQ>& sl, unsigned char* smem, Bars* bars, int lw, int lane,
                                             const AttnMaps* maps) {
   using CF = Cfg<NQ>;
-  if (lw < NQ && sl.n_tiles[lw < NQ ? lw : 0] > 0 && lane == 0) {
+  if (lw < NQ && sl.tiles_of(lw) > 0 && lane == 0) {
     unsigned char* dQ = smem + CF::kOffQ + lw * 32768;
     const int qs = (int)(sl.q0 + (long long)lw * BM);
     tc::mbar_arrive_expect_tx(&bars->q_full[lw], 2u * BM * 128u);
@@ -187,7 +190,7 @@ __device__ __forceinline__ bool mma_role(const Slice<NQ>& sl, unsigned char* sme
   // descriptors differ only in their 14-bit start-address field: build each base once, then add offsets
   const uint64_t dQ = tc::make_desc(sQ, 16, 1024) + (uint64_t)((qi * 32768) >> 4), dK = tc::make_desc(sK, 16, 1024);
   const uint64_t dV = tc::make_desc(sV, 8192, 1024);
-  const int nt = sl.n_tiles[qi];
+  const int nt = sl.tiles_of(qi);
   auto issue_qk = [&](int t) {
     const int stage = t % kStages, sbuf = t & 1;
     const uint32_t d = tmem + (uint32_t)((qi * 2 + sbuf) * BN);
@@ -247,10 +250,11 @@ __device__ __forceinline__ bool softmax_role(const Slice<NQ>& sl, const LayerDev
                                              uint32_t tmem, int qi, int row, int wq, int lane, long long T,
                                              bf16* __restrict__ out, float sm_scale) {
   using CF = Cfg<NQ>;
-  const int nt = sl.n_tiles[qi];
+  const int nt = sl.tiles_of(qi);
   if (nt <= 0) return true;
   const long long qs = sl.q0 + (long long)qi * BM;
   const long long qpos = qs + row;
+  const long long q_end = sl.q_end_of(qi);
   const uint32_t lane_addr = tmem + ((uint32_t)(wq * 32) << 16);
   const uint32_t col_o = CF::kColO + qi * 128;
   const float scale_mem = sm_scale * L.state_temp[sl.hq] * kLog2e;
@@ -316,19 +320,22 @@ __device__ __forceinline__ bool softmax_role(const Slice<NQ>& sl, const LayerDev
     TC_MARK(14, prof);
     const float neg_m = (m_run == -INFINITY) ? 0.f : -m_run;
     float ls0 = 0.f, ls1 = 0.f;
-    uint32_t pk[32];
+    // P replaces the scores it came from (all 64 columns of this row are in registers): the A operand of P V,
+    // written in two halves of 16 columns (32 keys) each
 #pragma unroll
-    for (int e = 0; e < 32; ++e) {
-      const int i = e * 2;
-      const float p0 = ex2(fmaf(__uint_as_float(sr[i >> 5][i & 31]), sc, neg_m));
-      const float p1 = ex2(fmaf(__uint_as_float(sr[(i + 1) >> 5][(i + 1) & 31]), sc, neg_m));
-      ls0 += p0;
-      ls1 += p1;
-      pk[e] = pack_bf16(p0, p1);
+    for (int half = 0; half < 2; ++half) {
+      uint32_t pk[16];
+#pragma unroll
+      for (int e = 0; e < 16; ++e) {
+        const float p0 = ex2(fmaf(__uint_as_float(sr[half][e * 2]), sc, neg_m));
+        const float p1 = ex2(fmaf(__uint_as_float(sr[half][e * 2 + 1]), sc, neg_m));
+        ls0 += p0;
+        ls1 += p1;
+        pk[e] = pack_bf16(p0, p1);
+      }
+      tc::tmem_st16(lane_addr + (uint32_t)((qi * 2 + sbuf) * BN + half * 16), pk);
     }
     l_run += ls0 + ls1;
-    // P replaces the scores it came from (all 64 columns of this row are in registers): the A operand of P V
-    tc::tmem_st32(lane_addr + (uint32_t)((qi * 2 + sbuf) * BN), pk);
     tc::tmem_st_wait();
     TC_MARK(15, prof);
     tc::tc_fence_before_sync();
@@ -346,7 +353,7 @@ __device__ __forceinline__ bool softmax_role(const Slice<NQ>& sl, const LayerDev
     uint32_t o[32];
     tc::tmem_ld32(lane_addr + col_o + cb * 32, o);
     tc::tmem_ld_wait();
-    if (qpos < sl.q_end[qi]) {
+    if (qpos < q_end) {
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
         uint4 w;
