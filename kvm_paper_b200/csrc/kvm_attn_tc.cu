@@ -252,9 +252,9 @@ __device__ __forceinline__ bool softmax_role(const Slice<NQ>& sl, const LayerDev
   using CF = Cfg<NQ>;
   const int nt = sl.tiles_of(qi);
   if (nt <= 0) return true;
-  const long long qs = sl.q0 + (long long)qi * BM;
-  const long long qpos = qs + row;
-  const long long q_end = sl.q_end_of(qi);
+  // positions relative to the first window token (32-bit: the window is a few blocks long)
+  const int qs_rel = (int)(sl.q0 - sl.bb) + qi * BM, q_rel = qs_rel + row;
+  const int S = sl.S, nm = sl.n_mem_tiles;
   const uint32_t lane_addr = tmem + ((uint32_t)(wq * 32) << 16);
   const uint32_t col_o = CF::kColO + qi * 128;
   const float scale_mem = sm_scale * L.state_temp[sl.hq] * kLog2e;
@@ -273,12 +273,12 @@ __device__ __forceinline__ bool softmax_role(const Slice<NQ>& sl, const LayerDev
     tc::tmem_ld32(lane_addr + (uint32_t)((qi * 2 + sbuf) * BN + 32), sr[1]);
     tc::tmem_ld_wait();
     TC_MARK(11, prof);
-    const bool is_mem = t < sl.n_mem_tiles;
-    const long long base = is_mem ? (long long)t * BN : sl.bb + (long long)(t - sl.n_mem_tiles) * BN;
+    const bool is_mem = t < nm;
+    const int base = (is_mem ? t : t - nm) * BN;  // first key of the tile within its segment (memory / window)
     const float sc = is_mem ? scale_mem : scale_win;
     // keys [0, n_ok) of this tile are visible to this row (memory: rows below S; window: causal)
-    const int n_ok = (int)max(0LL, min((long long)BN, (is_mem ? (long long)sl.S : qpos + 1) - base));
-    const bool tile_masked = is_mem ? (base + BN > sl.S) : (base + BN > qs + 1);  // uniform over the warpgroup
+    const int n_ok = max(0, min(BN, (is_mem ? S : q_rel + 1) - base));
+    const bool tile_masked = base + BN > (is_mem ? S : qs_rel + 1);  // uniform over the warpgroup
     if (tile_masked) {
 #pragma unroll
       for (int i = 0; i < 64; ++i)
@@ -347,6 +347,7 @@ __device__ __forceinline__ bool softmax_role(const Slice<NQ>& sl, const LayerDev
   if (!warp_wait(&bars->pv_done[qi], (nt - 1) & 1)) return false;
   tc::tc_fence_after_sync();
   const float inv = l_run > 0.f ? 1.0f / l_run : 0.f;
+  const long long qpos = sl.q0 + (long long)(qi * BM + row), q_end = sl.q_end_of(qi);
   bf16* orow = out + ((long long)sl.b * T + qpos) * ((long long)L.Hq * HD) + (long long)sl.hq * HD;
 #pragma unroll
   for (int cb = 0; cb < HD / 32; ++cb) {
