@@ -45,6 +45,14 @@ constexpr int HD = 128;  // head dim
 constexpr int kStages = 4;
 constexpr int kLoaders = 4;
 constexpr float kRescaleThreshold = 8.0f;  // log2 units
+#ifndef KVM_ATTN_LEAD
+#define KVM_ATTN_LEAD 2
+#endif
+// Tile order of a CTA: `lead` window tiles (they arrive by TMA right after the CTA starts, while the first memory
+// tiles still wait for the plan entry, the version table and the row gather), then the memory tiles, then the
+// remaining window tiles.  `lead` is at most the number of window tiles that every query tile of the CTA uses,
+// so each query tile still consumes a prefix of the order.
+constexpr int kLeadWindowTiles = KVM_ATTN_LEAD;
 
 template <int NQ>
 struct Cfg {
@@ -80,7 +88,7 @@ __device__ __forceinline__ float ex2(float x) {
 // Geometry of one CTA, computed identically by every role.
 template <int NQ>
 struct Slice {
-  int b, hq, hkv, S, n_mem_tiles, n_max;
+  int b, hq, hkv, S, n_mem_tiles, n_max, lead;
   long long q0, bb, q_end_all;
   long long q_end[NQ];
   int n_tiles[NQ];
@@ -135,9 +143,10 @@ __device__ __forceinline__ bool loader_role(const Slice<NQ>& sl, unsigned char* 
   for (int t = lw; t < sl.n_max; t += kLoaders) {
     if (t >= kStages && !warp_wait(&bars->kv_empty[stage], ((t / kStages) - 1) & 1)) return false;
     TC_MARK(0, prof);
-    if (t >= sl.n_mem_tiles) {
+    const bool is_mem = t >= sl.lead && t < sl.lead + sl.n_mem_tiles;
+    if (!is_mem) {
       if (lane == 0) {
-        const int r0 = (int)(sl.bb + (long long)(t - sl.n_mem_tiles) * BN);
+        const int r0 = (int)(sl.bb + (long long)(t < sl.lead ? t : t - sl.n_mem_tiles) * BN);
         tc::mbar_arrive_expect_tx(&bars->kv_full[stage], 4u * BN * 128u);
         const bool hi = maps->kv_head_inner != 0;
         attn_tma(dK, &maps->k, hi, 0, r0, sl.hkv, sl.b, &bars->kv_full[stage]);
@@ -149,7 +158,7 @@ __device__ __forceinline__ bool loader_role(const Slice<NQ>& sl, unsigned char* 
       TC_MARK(1, prof);
       continue;
     }
-    const int row0 = t * BN;
+    const int row0 = (t - sl.lead) * BN;
     const int i0 = row0 + lane < sl.S ? __ldg(sl.midx + row0 + lane) : 0;
     const int i1 = row0 + 32 + lane < sl.S ? __ldg(sl.midx + row0 + 32 + lane) : 0;
 #pragma unroll
@@ -254,7 +263,7 @@ __device__ __forceinline__ bool softmax_role(const Slice<NQ>& sl, const LayerDev
   if (nt <= 0) return true;
   // positions relative to the first window token (32-bit: the window is a few blocks long)
   const int qs_rel = (int)(sl.q0 - sl.bb) + qi * BM, q_rel = qs_rel + row;
-  const int S = sl.S, nm = sl.n_mem_tiles;
+  const int S = sl.S, nm = sl.n_mem_tiles, lead = sl.lead;
   const uint32_t lane_addr = tmem + ((uint32_t)(wq * 32) << 16);
   const uint32_t col_o = CF::kColO + qi * 128;
   const float scale_mem = sm_scale * L.state_temp[sl.hq] * kLog2e;
@@ -273,8 +282,8 @@ __device__ __forceinline__ bool softmax_role(const Slice<NQ>& sl, const LayerDev
     tc::tmem_ld32(lane_addr + (uint32_t)((qi * 2 + sbuf) * BN + 32), sr[1]);
     tc::tmem_ld_wait();
     TC_MARK(11, prof);
-    const bool is_mem = t < nm;
-    const int base = (is_mem ? t : t - nm) * BN;  // first key of the tile within its segment (memory / window)
+    const bool is_mem = t >= lead && t < lead + nm;
+    const int base = (is_mem ? t - lead : (t < lead ? t : t - nm)) * BN;  // first key of the tile within its segment
     const float sc = is_mem ? scale_mem : scale_win;
     // keys [0, n_ok) of this tile are visible to this row (memory: rows below S; window: causal)
     const int n_ok = max(0, min(BN, (is_mem ? S : q_rel + 1) - base));
@@ -412,11 +421,14 @@ kvm_attn_prefill_tc_kernel(LayerDev L, long long T, Tensor4 q, Tensor4 k, Tensor
   sl.bb = max(0LL, (long long)(j + 1 - L.W) * C);
   sl.n_mem_tiles = (sl.S + BN - 1) / BN;
   sl.n_max = 0;
+  sl.lead = kLeadWindowTiles;
 #pragma unroll
   for (int qi = 0; qi < NQ; ++qi) {
     const long long qs = sl.q0 + (long long)qi * BM;
     sl.q_end[qi] = min(q_blk_end, qs + BM);
-    sl.n_tiles[qi] = qs < q_blk_end ? sl.n_mem_tiles + (int)((sl.q_end[qi] - sl.bb + BN - 1) / BN) : 0;
+    const int nw = (int)((sl.q_end[qi] - sl.bb + BN - 1) / BN);
+    sl.n_tiles[qi] = qs < q_blk_end ? sl.n_mem_tiles + nw : 0;
+    if (qs < q_blk_end) sl.lead = min(sl.lead, nw);
     sl.n_max = max(sl.n_max, sl.n_tiles[qi]);
   }
   sl.q_end_all = min(q_blk_end, sl.q0 + (long long)BM * NQ);
