@@ -114,23 +114,40 @@ __device__ __forceinline__ void attn_tma(void* dst, const CUtensorMap* m, bool h
   else tc::tma_load_4d(dst, m, x, t, h, b, bar);
 }
 
-// Loader `lw` brings the key/value tiles t = lw, lw+4, ... into stage lw; loaders 0..NQ-1 first fetch query
-// tile `lw`.  Query tiles and window tiles are contiguous token ranges: one thread issues tiled TMA copies
-// (two per operand, one per 64-element half of the head dimension) that signal the stage's barrier with
-// their byte count.  Memory tiles are gathered row by row through the version table with 16-byte cp.async.
+// Query tiles and window tiles are contiguous token ranges: one thread issues tiled TMA copies (two per operand,
+// one per 64-element half of the head dimension) that signal the destination's barrier with their byte count.
 // Rows past the end of the sequence read as zeros; rows past the query block are real tokens that the causal
-// mask hides.  Returns false if a bounded wait expired.
+// mask hides.
+// One thread: query tile qi (128 tokens from `qs`) -> its operand buffer.
+template <int NQ>
+__device__ __forceinline__ void issue_query_tile(unsigned char* smem, Bars* bars, const AttnMaps* maps, int b, int hq,
+                                                 int qi, int qs) {
+  unsigned char* dQ = smem + Cfg<NQ>::kOffQ + qi * 32768;
+  tc::mbar_arrive_expect_tx(&bars->q_full[qi], 2u * BM * 128u);
+  attn_tma(dQ, &maps->q, maps->q_head_inner != 0, 0, qs, hq, b, &bars->q_full[qi]);
+  attn_tma(dQ + 16384, &maps->q, maps->q_head_inner != 0, 64, qs, hq, b, &bars->q_full[qi]);
+}
+// One thread: 64 window tokens from `r0` (keys and values) -> stage `stage`.
+template <int NQ>
+__device__ __forceinline__ void issue_window_tile(unsigned char* smem, Bars* bars, const AttnMaps* maps, int b, int hkv,
+                                                  int stage, int r0) {
+  unsigned char* dK = smem + Cfg<NQ>::kOffK + stage * 16384;
+  unsigned char* dV = smem + Cfg<NQ>::kOffV + stage * 16384;
+  tc::mbar_arrive_expect_tx(&bars->kv_full[stage], 4u * BN * 128u);
+  const bool hi = maps->kv_head_inner != 0;
+  attn_tma(dK, &maps->k, hi, 0, r0, hkv, b, &bars->kv_full[stage]);
+  attn_tma(dK + 8192, &maps->k, hi, 64, r0, hkv, b, &bars->kv_full[stage]);
+  attn_tma(dV, &maps->v, hi, 0, r0, hkv, b, &bars->kv_full[stage]);
+  attn_tma(dV + 8192, &maps->v, hi, 64, r0, hkv, b, &bars->kv_full[stage]);
+}
+
+// Loader `lw` brings the key/value tiles t = lw, lw+4, ... into stage lw, except the query tiles and the leading
+// window tiles, which thread 0 issues when the CTA starts (they need nothing from the plan).  Memory tiles are
+// gathered row by row through the version table with 16-byte cp.async.  Returns false if a bounded wait expired.
 template <int NQ>
 __device__ __forceinline__ bool loader_role(const Slice<NQ>& sl, unsigned char* smem, Bars* bars, int lw, int lane,
                                             const AttnMaps* maps) {
   using CF = Cfg<NQ>;
-  if (lw < NQ && sl.tiles_of(lw) > 0 && lane == 0) {
-    unsigned char* dQ = smem + CF::kOffQ + lw * 32768;
-    const int qs = (int)(sl.q0 + (long long)lw * BM);
-    tc::mbar_arrive_expect_tx(&bars->q_full[lw], 2u * BM * 128u);
-    attn_tma(dQ, &maps->q, maps->q_head_inner != 0, 0, qs, sl.hq, sl.b, &bars->q_full[lw]);
-    attn_tma(dQ + 16384, &maps->q, maps->q_head_inner != 0, 64, qs, sl.hq, sl.b, &bars->q_full[lw]);
-  }
   const int stage = lw;
   unsigned char* dK = smem + CF::kOffK + stage * 16384;
   unsigned char* dV = smem + CF::kOffV + stage * 16384;
@@ -141,19 +158,12 @@ __device__ __forceinline__ bool loader_role(const Slice<NQ>& sl, unsigned char* 
   (void)prof;
   TC_T0();
   for (int t = lw; t < sl.n_max; t += kLoaders) {
+    if (t < sl.lead) continue;  // issued when the CTA started
     if (t >= kStages && !warp_wait(&bars->kv_empty[stage], ((t / kStages) - 1) & 1)) return false;
     TC_MARK(0, prof);
-    const bool is_mem = t >= sl.lead && t < sl.lead + sl.n_mem_tiles;
+    const bool is_mem = t < sl.lead + sl.n_mem_tiles;
     if (!is_mem) {
-      if (lane == 0) {
-        const int r0 = (int)(sl.bb + (long long)(t < sl.lead ? t : t - sl.n_mem_tiles) * BN);
-        tc::mbar_arrive_expect_tx(&bars->kv_full[stage], 4u * BN * 128u);
-        const bool hi = maps->kv_head_inner != 0;
-        attn_tma(dK, &maps->k, hi, 0, r0, sl.hkv, sl.b, &bars->kv_full[stage]);
-        attn_tma(dK + 8192, &maps->k, hi, 64, r0, sl.hkv, sl.b, &bars->kv_full[stage]);
-        attn_tma(dV, &maps->v, hi, 0, r0, sl.hkv, sl.b, &bars->kv_full[stage]);
-        attn_tma(dV + 8192, &maps->v, hi, 64, r0, sl.hkv, sl.b, &bars->kv_full[stage]);
-      }
+      if (lane == 0) issue_window_tile<NQ>(smem, bars, maps, sl.b, sl.hkv, stage, (int)(sl.bb + (long long)(t - sl.n_mem_tiles) * BN));
       __syncwarp();
       TC_MARK(1, prof);
       continue;
@@ -407,29 +417,16 @@ kvm_attn_prefill_tc_kernel(LayerDev L, long long T, Tensor4 q, Tensor4 k, Tensor
     if (tid == 0) atomicExch(status, KVM_ERR_UNSUPPORTED);
     return;
   }
-  sl.S = 0;
-  sl.mk = sl.mv = nullptr;
-  sl.midx = nullptr;
-  if (j >= L.W) {
-    const kvm_update_plan pl = plan[j - L.W];
-    sl.S = pl.state_before + pl.n_append;
-    const size_t kvrow = (size_t)(sl.b * L.Hkv + sl.hkv);
-    sl.mk = pool_k + kvrow * pool_rows * HD;
-    sl.mv = pool_v + kvrow * pool_rows * HD;
-    sl.midx = ver_idx + kvrow * ver_rows + pl.version_row;
-  }
+  // what does not depend on the plan: window start, window tiles per query tile, leading window tiles
   sl.bb = max(0LL, (long long)(j + 1 - L.W) * C);
-  sl.n_mem_tiles = (sl.S + BN - 1) / BN;
-  sl.n_max = 0;
   sl.lead = kLeadWindowTiles;
+  int nw[NQ];
 #pragma unroll
   for (int qi = 0; qi < NQ; ++qi) {
     const long long qs = sl.q0 + (long long)qi * BM;
     sl.q_end[qi] = min(q_blk_end, qs + BM);
-    const int nw = (int)((sl.q_end[qi] - sl.bb + BN - 1) / BN);
-    sl.n_tiles[qi] = qs < q_blk_end ? sl.n_mem_tiles + nw : 0;
-    if (qs < q_blk_end) sl.lead = min(sl.lead, nw);
-    sl.n_max = max(sl.n_max, sl.n_tiles[qi]);
+    nw[qi] = qs < q_blk_end ? (int)((sl.q_end[qi] - sl.bb + BN - 1) / BN) : 0;
+    if (qs < q_blk_end) sl.lead = min(sl.lead, nw[qi]);
   }
   sl.q_end_all = min(q_blk_end, sl.q0 + (long long)BM * NQ);
 
@@ -446,8 +443,32 @@ kvm_attn_prefill_tc_kernel(LayerDev L, long long T, Tensor4 q, Tensor4 k, Tensor
       tc::mbar_init(&bars->kv_empty[i], NQ);
     }
     tc::fence_barrier_init();
+    // the copies that need nothing from the plan start now; the plan entry is read behind them
+#pragma unroll
+    for (int qi = 0; qi < NQ; ++qi)
+      if (nw[qi] > 0) issue_query_tile<NQ>(smem, bars, &maps, sl.b, sl.hq, qi, (int)(sl.q0 + (long long)qi * BM));
+    for (int t = 0; t < sl.lead; ++t)
+      issue_window_tile<NQ>(smem, bars, &maps, sl.b, sl.hkv, t, (int)(sl.bb + (long long)t * BN));
   }
   if (warp == CF::kMmaWarp) tc::tmem_alloc(&bars->tmem_base, CF::kTmemCols);
+  sl.S = 0;
+  sl.mk = sl.mv = nullptr;
+  sl.midx = nullptr;
+  if (j >= L.W) {
+    const kvm_update_plan pl = plan[j - L.W];
+    sl.S = pl.state_before + pl.n_append;
+    const size_t kvrow = (size_t)(sl.b * L.Hkv + sl.hkv);
+    sl.mk = pool_k + kvrow * pool_rows * HD;
+    sl.mv = pool_v + kvrow * pool_rows * HD;
+    sl.midx = ver_idx + kvrow * ver_rows + pl.version_row;
+  }
+  sl.n_mem_tiles = (sl.S + BN - 1) / BN;
+  sl.n_max = 0;
+#pragma unroll
+  for (int qi = 0; qi < NQ; ++qi) {
+    sl.n_tiles[qi] = nw[qi] > 0 ? sl.n_mem_tiles + nw[qi] : 0;
+    sl.n_max = max(sl.n_max, sl.n_tiles[qi]);
+  }
   tc::tc_fence_before_sync();
   __syncthreads();
   tc::tc_fence_after_sync();
