@@ -69,7 +69,7 @@ struct Cfg {
 };
 
 struct Bars {
-  uint64_t q_full[2], kv_full[kStages], kv_empty[kStages], s_full[2][2], p_full[2], pv_done[2];
+  uint64_t q_full[2], kv_full[kStages], kv_empty[kStages], s_full[2][2], p_full[2], pv_done[2], o_ready[2];
   uint32_t tmem_base;
 };
 
@@ -104,7 +104,7 @@ struct Slice {
 // The q, k, v inputs as 4-D tensors [batch][head][token][D] (any strides): boxes of 64 elements x 128 tokens
 // (queries) or 64 tokens (keys, values) land in the 128-byte-swizzled operand layout.
 struct AttnMaps {
-  CUtensorMap q, k, v;
+  CUtensorMap q, k, v, o;  // o: the output [B, T, Hq, D] with boxes of 64 elements x 128 tokens
   int q_head_inner, kv_head_inner;  // the head dimension has the smaller stride ([B,T,H,D] storage): it comes second
 };
 // box at (element x, token t, head h, batch b) of a tensor whose dimensions are ordered by stride
@@ -266,8 +266,8 @@ __device__ __forceinline__ bool mma_role(const Slice<NQ>& sl, unsigned char* sme
 // One query row per thread of warpgroup qi.  Returns false if a bounded wait expired.
 template <int NQ>
 __device__ __forceinline__ bool softmax_role(const Slice<NQ>& sl, const LayerDev& L, unsigned char* smem, Bars* bars,
-                                             uint32_t tmem, int qi, int row, int wq, int lane, long long T,
-                                             bf16* __restrict__ out, float sm_scale) {
+                                             uint32_t tmem, int qi, int row, int wq, int lane, float sm_scale,
+                                             const AttnMaps* maps) {
   using CF = Cfg<NQ>;
   const int nt = sl.tiles_of(qi);
   if (nt <= 0) return true;
@@ -362,28 +362,42 @@ __device__ __forceinline__ bool softmax_role(const Slice<NQ>& sl, const LayerDev
     if (lane == 0) tc::mbar_arrive(&bars->p_full[qi]);
     TC_MARK(16, prof);
   }
-  // epilogue: O / l -> bf16 -> [B, T, Hq*D]
+  // epilogue: O / l -> bf16 -> the query tile's operand buffer (all QK of this tile have completed), in the
+  // 128-byte-swizzled layout of a [128 tokens][64] box per half of the head dimension -> two TMA stores into
+  // [B, T, Hq*D]; tokens past the end of the sequence are clipped by the tensor map
   if (!warp_wait(&bars->pv_done[qi], (nt - 1) & 1)) return false;
   tc::tc_fence_after_sync();
   const float inv = l_run > 0.f ? 1.0f / l_run : 0.f;
-  const long long qpos = sl.q0 + (long long)(qi * BM + row), q_end = sl.q_end_of(qi);
-  bf16* orow = out + ((long long)sl.b * T + qpos) * ((long long)L.Hq * HD) + (long long)sl.hq * HD;
+  unsigned char* dO = smem + CF::kOffQ + qi * 32768;
 #pragma unroll
-  for (int cb = 0; cb < HD / 32; ++cb) {
-    uint32_t o[32];
-    tc::tmem_ld32(lane_addr + col_o + cb * 32, o);
+  for (int cb = 0; cb < HD / 16; ++cb) {
+    uint32_t o[16];
+    tc::tmem_ld16(lane_addr + col_o + cb * 16, o);
     tc::tmem_ld_wait();
-    if (qpos < q_end) {
 #pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        uint4 w;
-        w.x = pack_bf16(__uint_as_float(o[i * 8 + 0]) * inv, __uint_as_float(o[i * 8 + 1]) * inv);
-        w.y = pack_bf16(__uint_as_float(o[i * 8 + 2]) * inv, __uint_as_float(o[i * 8 + 3]) * inv);
-        w.z = pack_bf16(__uint_as_float(o[i * 8 + 4]) * inv, __uint_as_float(o[i * 8 + 5]) * inv);
-        w.w = pack_bf16(__uint_as_float(o[i * 8 + 6]) * inv, __uint_as_float(o[i * 8 + 7]) * inv);
-        *reinterpret_cast<uint4*>(orow + cb * 32 + i * 8) = w;
-      }
+    for (int i = 0; i < 2; ++i) {
+      uint4 o8;
+      o8.x = pack_bf16(__uint_as_float(o[i * 8 + 0]) * inv, __uint_as_float(o[i * 8 + 1]) * inv);
+      o8.y = pack_bf16(__uint_as_float(o[i * 8 + 2]) * inv, __uint_as_float(o[i * 8 + 3]) * inv);
+      o8.z = pack_bf16(__uint_as_float(o[i * 8 + 4]) * inv, __uint_as_float(o[i * 8 + 5]) * inv);
+      o8.w = pack_bf16(__uint_as_float(o[i * 8 + 6]) * inv, __uint_as_float(o[i * 8 + 7]) * inv);
+      const int c = cb * 2 + i;  // 16-byte chunk of the 256-byte row: half c >> 3, chunk c & 7 within the half
+      *reinterpret_cast<uint4*>(dO + (c >> 3) * 16384 + row * 128 + ((((c & 7) ^ (row & 7)) & 7) << 4)) = o8;
     }
+  }
+  tc::fence_proxy_async();  // generic-proxy writes -> visible to the TMA store
+  __syncwarp();
+  if (lane == 0) tc::mbar_arrive(&bars->o_ready[qi]);
+  if (wq == 0) {
+    if (!warp_wait(&bars->o_ready[qi], 0)) return false;
+    if (lane == 0) {
+      const int qs = (int)(sl.q0 + (long long)qi * BM);
+      tc::tma_store_4d(&maps->o, dO, 0, sl.hq, qs, sl.b);
+      tc::tma_store_4d(&maps->o, dO + 16384, 64, sl.hq, qs, sl.b);
+      tc::bulk_commit_group();
+      tc::bulk_wait_group_read0();  // shared memory must outlive the copy
+    }
+    __syncwarp();
   }
   return true;
 }
@@ -437,6 +451,7 @@ kvm_attn_prefill_tc_kernel(LayerDev L, long long T, Tensor4 q, Tensor4 k, Tensor
       tc::mbar_init(&bars->s_full[i][1], 1);
       tc::mbar_init(&bars->p_full[i], 4);
       tc::mbar_init(&bars->pv_done[i], 1);
+      tc::mbar_init(&bars->o_ready[i], 4);
     }
     for (int i = 0; i < kStages; ++i) {
       tc::mbar_init(&bars->kv_full[i], 1);
@@ -476,7 +491,7 @@ kvm_attn_prefill_tc_kernel(LayerDev L, long long T, Tensor4 q, Tensor4 k, Tensor
 
   bool ok = true;
   if (warp < CF::kSoftmaxWarps) {
-    ok = softmax_role<NQ>(sl, L, smem, bars, tmem, warp >> 2, tid & 127, warp & 3, lane, T, out, sm_scale);
+    ok = softmax_role<NQ>(sl, L, smem, bars, tmem, warp >> 2, tid & 127, warp & 3, lane, sm_scale, &maps);
   } else if (warp < CF::kMmaWarp) {
     ok = loader_role<NQ>(sl, smem, bars, warp - CF::kSoftmaxWarps, lane, &maps);
     cp_async_wait<0>();
@@ -517,8 +532,13 @@ static cudaError_t launch_nq(const LayerDev& L, int batch, long long T, Tensor4 
   maps.q_head_inner = q.sh < q.st ? 1 : 0;
   maps.kv_head_inner = k.sh < k.st ? 1 : 0;
   if ((v.sh < v.st) != (k.sh < k.st)) return cudaErrorInvalidValue;  // keys and values share one layout
+  Tensor4 o4;  // the output [B, T, Hq*D] seen as [batch][head][token][D]
+  o4.ptr = out;
+  o4.sb = T * (long long)L.Hq * HD;
+  o4.st = (long long)L.Hq * HD;
+  o4.sh = HD;
   if (!encode(&maps.q, q, L.Hq, BM, maps.q_head_inner != 0) || !encode(&maps.k, k, L.Hkv, BN, maps.kv_head_inner != 0) ||
-      !encode(&maps.v, v, L.Hkv, BN, maps.kv_head_inner != 0))
+      !encode(&maps.v, v, L.Hkv, BN, maps.kv_head_inner != 0) || !encode(&maps.o, o4, L.Hq, BM, true))
     return cudaErrorInvalidValue;
   dim3 grid(n_qblocks * ctas_per_block, batch * L.Hq);
   kvm_attn_prefill_tc_kernel<NQ><<<grid, CF::kThreads, CF::kSmemBytes, stream>>>(
