@@ -350,8 +350,8 @@ def run_b200(args):
 # launch), scaled to this run's launch by the units it processes; the captures and their commands are the
 # summaries under profiles/ named after these kernels.
 NCU_TRAFFIC = {
-    # B1 x T16384 x 16 heads: 289.0 MB + 64.7 MB per launch -> bytes per (head, token)
-    "kvm_attn_prefill_tc_kernel": (289.0e6 + 64.7e6) / (16 * 16384),
+    # B1 x T16384 x 16 heads: 289.0 MB + 50.9 MB per launch -> bytes per (head, token)
+    "kvm_attn_prefill_tc_kernel": (289.0e6 + 50.9e6) / (16 * 16384),
     # decode workload of this bench: 399.0 MB + 3.6 MB per launch for 397 MB of algorithmic K/V rows
     "kvm_decode_attn_kernel": (399.0e6 + 3.6e6) / 397.0e6,
 }
