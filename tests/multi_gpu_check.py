@@ -38,6 +38,9 @@ def main():
     if rank == 0:
         _, _, ref = gh.device_prefill(full, q, k, v, gate, want_route=False)
         ok = torch.equal(y, ref.out)
+        if not ok:
+            d = (y.float() - ref.out.float()).abs()
+            print("prefill mismatch: max abs", float(d.max()), "first bad index", d.nonzero()[0].tolist(), flush=True)
     # decode: sequences sharded, every rank holds its own cache
     n_seq, n_steps = 4, 20
     spec = gh.bf16_spec(ko.KvmSpec(2, 2, 64, 64, 32, 32, 2, 8, 1, "power_law", state_growth_factor=4.0, state_min_len=32))
@@ -56,7 +59,11 @@ def main():
 
     out = sharding.gather_sequences(decode(sl), world, seq_dim=1)
     if rank == 0:
-        ok = ok and torch.equal(out, decode(slice(0, n_seq)))
+        ref_dec = decode(slice(0, n_seq))
+        if not torch.equal(out, ref_dec):
+            d = (out.float() - ref_dec.float()).abs()
+            print("decode mismatch: max abs", float(d.max()), "first bad index", d.nonzero()[0].tolist(), flush=True)
+            ok = False
     flag = torch.tensor([1 if ok else 0], device="cuda")
     dist.all_reduce(flag, op=dist.ReduceOp.MIN)
     if rank == 0:
