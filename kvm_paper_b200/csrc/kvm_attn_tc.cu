@@ -69,7 +69,7 @@ struct Cfg {
 };
 
 struct Bars {
-  uint64_t q_full[2], kv_full[kStages], kv_empty[kStages], s_full[2][2], p_full[2], pv_done[2], o_ready[2];
+  uint64_t q_full[2], kv_full[kStages], kv_empty[kStages], s_full[2][2], p_full[2], pv_done[2], o_final[2], o_ready[2];
   uint32_t tmem_base;
 };
 
@@ -246,6 +246,9 @@ __device__ __forceinline__ bool mma_role(const Slice<NQ>& sl, unsigned char* sme
                    (t > 0) || (ks > 0));
       tc::mma_commit(&bars->pv_done[qi]);
       tc::mma_commit(&bars->kv_empty[stage]);
+      // The epilogue waits on a barrier of its own: the softmax only waits on pv_done before a rescale, so at
+      // the end of the tile loop pv_done may be two phases behind, which a parity wait cannot tell from done.
+      if (t == nt - 1) tc::mma_commit(&bars->o_final[qi]);
       TC_MARK(6, prof);
     } else {
       if (!tc::mbar_wait(&bars->kv_full[stage], (t / kStages) & 1)) return false;
@@ -365,7 +368,7 @@ __device__ __forceinline__ bool softmax_role(const Slice<NQ>& sl, const LayerDev
   // epilogue: O / l -> bf16 -> the query tile's operand buffer (all QK of this tile have completed), in the
   // 128-byte-swizzled layout of a [128 tokens][64] box per half of the head dimension -> two TMA stores into
   // [B, T, Hq*D]; tokens past the end of the sequence are clipped by the tensor map
-  if (!warp_wait(&bars->pv_done[qi], (nt - 1) & 1)) return false;
+  if (!warp_wait(&bars->o_final[qi], 0)) return false;
   tc::tc_fence_after_sync();
   const float inv = l_run > 0.f ? 1.0f / l_run : 0.f;
   unsigned char* dO = smem + CF::kOffQ + qi * 32768;
@@ -451,6 +454,7 @@ kvm_attn_prefill_tc_kernel(LayerDev L, long long T, Tensor4 q, Tensor4 k, Tensor
       tc::mbar_init(&bars->s_full[i][1], 1);
       tc::mbar_init(&bars->p_full[i], 4);
       tc::mbar_init(&bars->pv_done[i], 1);
+      tc::mbar_init(&bars->o_final[i], 1);
       tc::mbar_init(&bars->o_ready[i], 4);
     }
     for (int i = 0; i < kStages; ++i) {
