@@ -1,19 +1,24 @@
 // Block attention of the prefill on the Blackwell tensor cores (tcgen05 + tensor memory), head_dim 128.
 //
 // One CTA = NQ query tiles of 128 rows (NQ = 2: a whole 256-row slice of a query block) of one
-// (batch, q-head).  Keys/values are consumed in tiles of 64 rows shared by the query tiles: first the
-// memory version of the block (rows gathered from the row pool through the version's index table), then
-// the sliding window up to the diagonal.
+// (batch, q-head).  Keys/values are consumed in tiles of 64 rows shared by the query tiles: two window tiles,
+// then the memory version of the block (rows gathered from the row pool through the version's index table),
+// then the rest of the sliding window up to the diagonal.
 //
 //   softmax warpgroups (NQ x 4 warps)  one query row per thread (= one tensor-memory lane): tcgen05.ld of
-//               the score tile, scale by the segment's temperature, mask, exp2, row sum, bf16 P into
-//               shared memory for the P V product.  The running maximum is only raised (and O in
-//               tensor memory rescaled with tcgen05.ld/st) when a tile exceeds it by more than 2^8.
-//   loader warps (4)   tile t is loaded by loader t % 4 into stage t % 4: cp.async into 128B-swizzled
-//               operand layouts, fence to the async proxy, mbarrier arrive; four tiles are in flight
-//   MMA warp    one thread issues tcgen05.mma:  S = Q K^T into tensor memory (two S buffers per query
-//               tile, so the next score tile is computed while the current one is in softmax), O += P V
-// Tensor memory: NQ x 2 score buffers of 64 columns, NQ output accumulators of 128 columns.
+//               the score tile, scale by the segment's temperature, mask, exp2, row sum, bf16 P written with
+//               tcgen05.st over the columns of the score tile it came from (P never touches shared memory).
+//               The running maximum is only raised (and O in tensor memory rescaled with tcgen05.ld/st, 16
+//               columns at a time) when a tile exceeds it by more than 2^8.  At the end: O / l as bf16 into
+//               the query tile's operand buffer, two TMA stores.
+//   loader warps (4)   tile t is loaded by loader t % 4 into stage t % 4: tiled TMA for window tiles, 16-byte
+//               cp.async through the version table for memory tiles (128B-swizzled operand layouts, fence to
+//               the async proxy, mbarrier arrive); four tiles are in flight.  Query tiles and the two leading
+//               window tiles are issued by thread 0 before the plan entry is read.
+//   MMA warps (NQ)   one thread per query tile issues tcgen05.mma:  S = Q K^T into tensor memory (two S buffers
+//               per query tile, so the next score tile is computed while the current one is in softmax),
+//               O += P V with P as the tensor-memory A operand
+// Tensor memory: NQ x 2 score buffers of 64 columns (P aliases their first 32), NQ output accumulators of 128.
 // Every mbarrier wait is bounded; on expiry the CTA records a status code, falls through to the common
 // exit, frees its tensor memory and returns.
 #include "kvm_common.cuh"
