@@ -7,7 +7,12 @@
  *
  * Conventions
  *   - every pointer named *_dev / documented "device" is a CUDA device pointer owned by the caller;
- *     the library allocates nothing and keeps no state between calls;
+ *     the library allocates no device memory.  What it keeps between calls, per process: the text of the
+ *     calling thread's last error; per device, created on first use and guarded by mutexes so that several
+ *     host threads may drive several GPUs: one side stream with two events (kvm_decode_step's overlapped
+ *     memory update), a small cache of tensor maps keyed by the decode cache's addresses and sizes, the
+ *     shared-memory limits already raised on the kernels, cached occupancy answers, and the device address
+ *     of the built-in scratch of kvm_decode_step_static.  None of it depends on the data of a call;
  *   - all activations and memory rows are bfloat16, lengths/norms fp32, indices int32;
  *   - `stream` is a cudaStream_t passed as void* (NULL = default stream); calls only enqueue work;
  *   - return value 0 = ok, otherwise one of KVM_ERR_*; kvm_last_error_string() describes the last
@@ -114,11 +119,31 @@ int kvm_prefill_forward(const kvm_layer* layer, int32_t batch, int64_t seq_len,
                         kvm_memory memory, void* out, int32_t* route_dev,
                         void* workspace, size_t workspace_bytes, uint32_t phases, void* stream);
 
-/* Waits for `stream` and returns what the kernels of the last kvm_prefill_forward on this workspace
- * reported: KVM_OK, or KVM_ERR_DEVICE_TIMEOUT if a bounded device-side wait (mbarrier / tensor-memory
- * pipeline) expired -- the kernels then leave through their normal exit, nothing hangs, the output is
- * undefined.  No counterpart in the reference (its Triton kernels have no device-side waits). */
-int kvm_prefill_status(const void* workspace, void* stream);
+/* Waits for `stream` and returns what the kernels of the last prefill on this workspace reported (the
+ * status word is opened by a call that includes KVM_PREFILL_CHAIN and collects what that call and later
+ * attention-only calls report): KVM_OK, or KVM_ERR_DEVICE_TIMEOUT if a bounded device-side wait
+ * (mbarrier / tensor-memory pipeline) expired -- the kernels then leave through their normal exit, nothing
+ * hangs, the output is undefined.  A reported status is cleared.  No counterpart in the reference (its
+ * Triton kernels have no device-side waits). */
+int kvm_prefill_status(void* workspace, void* stream);
+
+/* Where kvm_prefill_forward keeps its intermediate results inside `workspace` (byte offsets), for inspection
+ * after a call: the row pool of the memory's attention view ([B*Hkv, pool_rows, D] bf16, keys and values),
+ * the version tables ([B*Hkv, total_version_rows] int32: entry plan[u].version_row + r is the pool row that
+ * holds memory row r after update u) and the prepared keys of all consumed tokens
+ * ([B*Hkv, (n_updates+1)*C, D] bf16; present when n_updates > 0).  Counterpart of the reference's
+ * capture_state_snapshots hook (model/kernels/kvm_triton_training_kernels.py:3518-3524), without copies. */
+typedef struct kvm_prefill_layout {
+  size_t status_offset;
+  size_t pool_k_offset;
+  size_t pool_v_offset;
+  size_t version_table_offset;
+  size_t prepared_keys_offset;
+  int64_t pool_rows;
+  size_t total_bytes;
+} kvm_prefill_layout;
+int kvm_prefill_workspace_layout(const kvm_layer* layer, int32_t batch, int64_t seq_len,
+                                 int64_t total_version_rows, kvm_prefill_layout* out);
 
 /* The decode-time cache of one layer for `batch` sequences with ragged lengths (all device memory,
  * caller-owned).  Replaces TritonKVMDecodeCache (model/kvm_triton_decode.py:34-400); unlike the
@@ -132,6 +157,9 @@ typedef struct kvm_decode_cache {
   int32_t* state_len;     /* [batch] memory rows in use */
 } kvm_decode_cache;
 
+/* Bytes of scratch kvm_decode_step needs.  The first (batch*Hkv + batch + 1) int32 of the workspace -- split
+ * counters, two launch counters and the status word -- must be ZERO before the first step (cudaMemset once
+ * after allocating); the kernels leave the counters at zero, so later steps need no clearing. */
 size_t kvm_decode_workspace_bytes(const kvm_layer* layer, int32_t batch, int32_t max_rows_per_seq);
 
 /* One decode token for every sequence of the batch: append to the ring, run the memory update for
@@ -158,6 +186,14 @@ int kvm_decode_step(const kvm_layer* layer, int32_t batch, kvm_decode_cache cach
                     const int32_t* n_append_dev, int32_t any_update, int32_t max_rows,
                     void* out, int32_t* route_dev, void* workspace, size_t workspace_bytes,
                     void* stream);
+
+/* Waits for `stream` and returns what the decode kernels that used `workspace` have reported since the last
+ * call: KVM_OK or KVM_ERR_DEVICE_TIMEOUT (a bounded wait of the attention kernel's copy pipeline expired; the
+ * kernel drained and returned, that token's output is undefined).  `layer` and `batch` as given to
+ * kvm_decode_step (they locate the word).  workspace == NULL reads the built-in scratch of
+ * kvm_decode_step_static on the current device.  A reported status is cleared.  No counterpart in the
+ * reference. */
+int kvm_decode_status(const kvm_layer* layer, int32_t batch, void* workspace, void* stream);
 
 /* `n_steps` consecutive decode steps whose inputs are already on the device (teacher-forced or synthetic
  * decoding, as in the reference's kernel benchmark, which pre-generates the per-token q/k/v/gate:

@@ -10,8 +10,7 @@ import ctypes as C
 import os
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-# KVM_B200_LIB selects another build of the same library (e.g. an instrumented development build)
-LIB_PATH = os.environ.get("KVM_B200_LIB") or os.path.join(_HERE, "libkvm_b200.so")
+LIB_PATH = os.path.join(_HERE, "libkvm_b200.so")
 
 KVM_OK = 0
 PREFILL_CHAIN, PREFILL_ATTENTION, PREFILL_LEGACY_ATTENTION = 1, 2, 4
@@ -43,6 +42,12 @@ class KvmUpdatePlan(C.Structure):
                 ("reserved", C.c_int32)]
 
 
+class KvmPrefillLayout(C.Structure):
+    _fields_ = [("status_offset", C.c_size_t), ("pool_k_offset", C.c_size_t), ("pool_v_offset", C.c_size_t),
+                ("version_table_offset", C.c_size_t), ("prepared_keys_offset", C.c_size_t),
+                ("pool_rows", C.c_int64), ("total_bytes", C.c_size_t)]
+
+
 class KvmDecodeCache(C.Structure):
     _fields_ = [("memory", KvmMemory), ("ring_k", C.c_void_p), ("ring_v", C.c_void_p),
                 ("ring_gate", C.c_void_p), ("total_len", C.c_void_p), ("state_len", C.c_void_p)]
@@ -51,6 +56,7 @@ class KvmDecodeCache(C.Structure):
 EXPORTS = [
     "kvm_prefill_workspace_bytes", "kvm_prefill_forward", "kvm_decode_workspace_bytes", "kvm_decode_step",
     "kvm_memory_refresh", "kvm_last_error_string", "kvm_abi_version", "kvm_decode_step_static", "kvm_prefill_status", "kvm_decode_run",
+    "kvm_decode_status", "kvm_prefill_workspace_layout",
 ]
 STATIC_SCRATCH_BYTES = 32 << 20
 
@@ -77,6 +83,10 @@ def load():
         C.c_void_p, C.c_size_t, C.c_uint32, C.c_void_p]
     lib.kvm_prefill_status.restype = C.c_int
     lib.kvm_prefill_status.argtypes = [C.c_void_p, C.c_void_p]
+    lib.kvm_prefill_workspace_layout.restype = C.c_int
+    lib.kvm_prefill_workspace_layout.argtypes = [LP(KvmLayer), C.c_int32, C.c_int64, C.c_int64, LP(KvmPrefillLayout)]
+    lib.kvm_decode_status.restype = C.c_int
+    lib.kvm_decode_status.argtypes = [LP(KvmLayer), C.c_int32, C.c_void_p, C.c_void_p]
     lib.kvm_decode_workspace_bytes.restype = C.c_size_t
     lib.kvm_decode_workspace_bytes.argtypes = [LP(KvmLayer), C.c_int32, C.c_int32]
     lib.kvm_decode_step.restype = C.c_int

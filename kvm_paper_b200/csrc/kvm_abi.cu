@@ -1,5 +1,5 @@
 // extern "C" entry points of libkvm_b200: argument validation, workspace carve-up, launches.
-// Nothing here allocates device memory or keeps state between calls.
+// Nothing here allocates device memory.  What the library keeps between calls is listed in the header.
 #include <cstdarg>
 #include <cstdio>
 #include <cstring>
@@ -229,7 +229,10 @@ int kvm_prefill_forward(const kvm_layer* layer, int32_t batch, int64_t seq_len, 
   if (((uintptr_t)workspace) % 256 || ((uintptr_t)out) % 16) return fail(KVM_ERR_BAD_ARGUMENT, "workspace must be 256-byte aligned and out 16-byte aligned");
 
   unsigned char* wsb = static_cast<unsigned char*>(workspace);
-  cudaError_t e = cudaMemsetAsync(wsb + ws.status, 0, sizeof(int), static_cast<cudaStream_t>(stream));
+  cudaError_t e = cudaSuccess;
+  // the status word belongs to a whole prefill: the chain phase opens it, an attention-only call on the same
+  // workspace adds to it (so that a timeout of the chain is still seen after the attention call)
+  if (phases & KVM_PREFILL_CHAIN) e = cudaMemsetAsync(wsb + ws.status, 0, sizeof(int), static_cast<cudaStream_t>(stream));
   if (e != cudaSuccess) return cuda_fail(e, "kvm_prefill_forward: cudaMemsetAsync");
   e = prefill_dispatch(D, to_dev(layer), batch, seq_len, to_dev(q), to_dev(k), to_dev(v), to_dev(gate), plan_dev,
                                    n_updates + 1, total_version_rows, to_dev(memory), static_cast<bf16*>(out), route_dev,
@@ -242,12 +245,31 @@ int kvm_prefill_forward(const kvm_layer* layer, int32_t batch, int64_t seq_len, 
   return KVM_OK;
 }
 
-int kvm_prefill_status(const void* workspace, void* stream) {
+int kvm_prefill_workspace_layout(const kvm_layer* layer, int32_t batch, int64_t seq_len, int64_t total_version_rows,
+                                 kvm_prefill_layout* out) {
+  g_err[0] = 0;
+  if (int rc = check_layer(layer)) return rc;
+  if (batch <= 0 || seq_len <= 0 || total_version_rows < 0 || !out)
+    return fail(KVM_ERR_BAD_ARGUMENT, "batch and seq_len must be positive, total_version_rows not negative, out not NULL");
+  const PrefillWs ws = prefill_ws(layer, batch, seq_len, total_version_rows);
+  out->status_offset = ws.status;
+  out->pool_k_offset = ws.pool_k;
+  out->pool_v_offset = ws.pool_v;
+  out->version_table_offset = ws.ver_idx;
+  out->prepared_keys_offset = ws.pk_all;
+  out->pool_rows = ws.pool_rows;
+  out->total_bytes = ws.total;
+  return KVM_OK;
+}
+
+int kvm_prefill_status(void* workspace, void* stream) {
   g_err[0] = 0;
   if (!workspace) return fail(KVM_ERR_BAD_ARGUMENT, "workspace is NULL");
   int st = 0;
-  cudaError_t e = cudaMemcpyAsync(&st, workspace, sizeof(int), cudaMemcpyDeviceToHost, static_cast<cudaStream_t>(stream));
-  if (e == cudaSuccess) e = cudaStreamSynchronize(static_cast<cudaStream_t>(stream));
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  cudaError_t e = cudaMemcpyAsync(&st, workspace, sizeof(int), cudaMemcpyDeviceToHost, s);
+  if (e == cudaSuccess) e = cudaStreamSynchronize(s);
+  if (e == cudaSuccess && st != 0) e = cudaMemsetAsync(workspace, 0, sizeof(int), s);  // reported once
   if (e != cudaSuccess) return cuda_fail(e, "kvm_prefill_status");
   if (st == KVM_ERR_DEVICE_TIMEOUT) return fail(st, "a bounded wait inside a prefill kernel expired (device-side timeout)");
   if (st != 0) return fail(st, "a prefill kernel reported status %d", st);
@@ -262,7 +284,7 @@ size_t kvm_decode_workspace_bytes(const kvm_layer* layer, int32_t batch, int32_t
 static int decode_step_impl(const kvm_layer* layer, int32_t batch, const kvm_decode_cache& cache, kvm_tensor4 q, kvm_tensor4 k,
                             kvm_tensor4 v, kvm_tensor4 gate, const int32_t* n_append_dev, int32_t any_update, int32_t max_rows,
                             void* out, int32_t* route_dev, void* workspace, size_t workspace_bytes, void* stream,
-                            int overlap, const char* who) {
+                            int overlap, const char* who, bool clear_counters = false) {
   if (int rc = check_layer(layer)) return rc;
   if (batch <= 0) return fail(KVM_ERR_BAD_ARGUMENT, "batch %d must be positive", batch);
   const int D = layer->head_dim;
@@ -289,7 +311,13 @@ static int decode_step_impl(const kvm_layer* layer, int32_t batch, const kvm_dec
   c.ring_g = static_cast<bf16*>(cache.ring_gate); c.total_len = cache.total_len; c.state_len = cache.state_len;
   unsigned char* wsb = static_cast<unsigned char*>(workspace);
   if (any_update < 0 || any_update > batch) any_update = batch;  // count unknown: no overlap
-  cudaError_t e = decode_dispatch(D, to_dev(layer), batch, c, to_dev(q), to_dev(k), to_dev(v), to_dev(gate), n_append_dev,
+  cudaError_t e;
+  if (clear_counters) {  // every argument has been checked: the first thing enqueued is the clearing of the counters
+    e = cudaMemsetAsync(wsb + ws.counters, 0, ((size_t)batch * layer->n_kv_heads + batch + 1) * sizeof(int),
+                        static_cast<cudaStream_t>(stream));
+    if (e != cudaSuccess) return cuda_fail(e, who);
+  }
+  e = decode_dispatch(D, to_dev(layer), batch, c, to_dev(q), to_dev(k), to_dev(v), to_dev(gate), n_append_dev,
                                   any_update, max_rows, static_cast<bf16*>(out), route_dev,
                                   reinterpret_cast<bf16*>(wsb + ws.pk), reinterpret_cast<float*>(wsb + ws.partial),
                                   reinterpret_cast<int*>(wsb + ws.counters), ws.nsplit_max, overlap,
@@ -346,12 +374,28 @@ int kvm_decode_step_static(const kvm_layer* layer, int32_t batch, kvm_decode_cac
                 ws.total, (unsigned)KVM_STATIC_SCRATCH_BYTES, batch, layer->n_kv_heads, layer->chunk_len, layer->head_dim, max_rows);
   void* scratch = nullptr;
   if (int rc = static_scratch_for_current_device(&scratch)) return rc;
-  // the array keeps whatever the previous call left: the split counters must start at zero
-  cudaError_t e = cudaMemsetAsync(static_cast<unsigned char*>(scratch) + ws.counters, 0,
-                                  ((size_t)batch * layer->n_kv_heads + batch + 1) * sizeof(int), static_cast<cudaStream_t>(stream));
-  if (e != cudaSuccess) return cuda_fail(e, "kvm_decode_step_static: cudaMemsetAsync");
+  // the array keeps whatever the previous call left: the split counters (and the status word behind them) must
+  // start at zero; they are cleared on the stream once the remaining arguments have been validated
   return decode_step_impl(layer, batch, cache, q, k, v, gate, n_append_dev, any_update, max_rows, out, route_dev, scratch,
-                          (size_t)KVM_STATIC_SCRATCH_BYTES, stream, 0, "kvm_decode_step_static");
+                          (size_t)KVM_STATIC_SCRATCH_BYTES, stream, 0, "kvm_decode_step_static", true);
+}
+
+int kvm_decode_status(const kvm_layer* layer, int32_t batch, void* workspace, void* stream) {
+  g_err[0] = 0;
+  if (!layer || batch <= 0 || layer->n_kv_heads <= 0) return fail(KVM_ERR_BAD_ARGUMENT, "layer is NULL or batch %d not positive", batch);
+  if (!workspace) {  // the built-in scratch of kvm_decode_step_static
+    if (int rc = static_scratch_for_current_device(&workspace)) return rc;
+  }
+  int* word = reinterpret_cast<int*>(static_cast<unsigned char*>(workspace)) + (size_t)batch * layer->n_kv_heads + batch;
+  int st = 0;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  cudaError_t e = cudaMemcpyAsync(&st, word, sizeof(int), cudaMemcpyDeviceToHost, s);
+  if (e == cudaSuccess) e = cudaStreamSynchronize(s);
+  if (e == cudaSuccess && st != 0) e = cudaMemsetAsync(word, 0, sizeof(int), s);  // reported once
+  if (e != cudaSuccess) return cuda_fail(e, "kvm_decode_status");
+  if (st == KVM_ERR_DEVICE_TIMEOUT) return fail(st, "a bounded wait inside a decode kernel expired (device-side timeout)");
+  if (st != 0) return fail(st, "a decode kernel reported status %d", st);
+  return KVM_OK;
 }
 
 int kvm_memory_refresh(const kvm_layer* layer, int32_t batch, kvm_memory memory, const int32_t* state_len_dev, void* stream) {

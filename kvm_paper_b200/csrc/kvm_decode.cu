@@ -283,13 +283,17 @@ kvm_decode_attn_kernel(LayerDev L, DecodeCacheDev cache, Tensor4 q, const int* _
   const int per = max(per_min, (total_f + (int)gridDim.x - 1) / (int)gridDim.x);
   const int active = (total_f + per - 1) / per;               // CTAs with work
   const int cta = blockIdx.x;
-  if (cta >= active) return;
-  const int f_begin = cta * per, f_end = min(total_f, f_begin + per);
+  // CTAs without a share of the list still take part in the launch counter below: the lengths may only move
+  // once every CTA of the grid has read them
+  const bool has_work = cta < active;
+  const int f_begin = has_work ? cta * per : 0, f_end = has_work ? min(total_f, f_begin + per) : 0;
   const int nloc = f_end - f_begin;
   volatile int* abort_flag = &s_abort;
   pdl_trigger();  // the next token's ring-write kernel may be staged (it waits for this grid to complete)
 
-  if (warp == NW) {
+  if (!has_work) {
+    // nothing to stream
+  } else if (warp == NW) {
     // =============================================================== producer warp (lanes in lockstep)
     int pb, ph, pc, pcb;
     DecGeo pg;
@@ -624,12 +628,13 @@ kvm_decode_attn_kernel(LayerDev L, DecodeCacheDev cache, Tensor4 q, const int* _
     for (int k2 = 0; k2 < 1000; ++k2) __nanosleep(1000);
   }
 
-  // ---- the last CTA of the launch advances the lengths of the sequences in scope
+  // ---- the last CTA of the launch advances the lengths of the sequences in scope: by then every CTA of the
+  //      grid (also those without work) has derived its geometry from the old lengths
   __syncthreads();
   if (tid == 0) {
     __threadfence();
     const int prev = atomicAdd(done_counter, 1);
-    s_flag = (prev == active - 1);
+    s_flag = (prev == (int)gridDim.x - 1);
   }
   __syncthreads();
   if (s_flag) {
@@ -659,6 +664,8 @@ __global__ void kvm_memory_refresh_kernel(LayerDev L, MemoryDev mem, const int* 
 }
 
 // ------------------------------------------------------------------------------------- host side
+constexpr int kMaxDevices = 64;  // device ordinals the per-device caches below cover
+
 static int device_sm_count() {
   int dev = 0, n_sm = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess ||
@@ -719,10 +726,10 @@ struct DecodeSide {
   bool ok = false;
 };
 static DecodeSide* decode_side() {
-  static DecodeSide side[64];
+  static DecodeSide side[kMaxDevices];
   static std::mutex mu;
   int dev = 0;
-  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return nullptr;
   std::lock_guard<std::mutex> lock(mu);
   DecodeSide& d = side[dev];
   if (!d.ok) {
@@ -762,21 +769,20 @@ static cudaError_t launch_decode_attn(const LayerDev& L, int batch, const Decode
   const int max_chunks = (max_rows + kDecChunk - 1) / kDecChunk + 3;
   const int per_min = (max_chunks + nslots - 2) / (nslots - 1);
   auto kern = kvm_decode_attn_kernel<D, ST, NH>;
-  static size_t smem_set = 0;  // largest dynamic shared memory enabled so far on dev_set
-  static int dev_set = -1;
+  static size_t smem_set[kMaxDevices] = {0};  // largest dynamic shared memory enabled so far, per device
+  static std::mutex mu;
   int dev_now = 0;
-  cudaGetDevice(&dev_now);
-  if (dev_now != dev_set) {  // function attributes are per device
-    smem_set = 0;
-    dev_set = dev_now;
-  }
+  if (cudaGetDevice(&dev_now) != cudaSuccess || dev_now < 0 || dev_now >= kMaxDevices) return cudaErrorInvalidDevice;
   for (int b0 = 0; b0 < batch; b0 += kDecMaxBatch) {
     const int nb = std::min(kDecMaxBatch, batch - b0);
     const DecSmem lay(D, G, L.Hq, nb, ST);
-    if (lay.total > smem_set) {
-      cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)lay.total);
-      if (e != cudaSuccess) return e;
-      smem_set = lay.total;
+    {
+      std::lock_guard<std::mutex> lock(mu);  // function attributes are per device
+      if (lay.total > smem_set[dev_now]) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)lay.total);
+        if (e != cudaSuccess) return e;
+        smem_set[dev_now] = lay.total;
+      }
     }
     cudaError_t e = launch_pdl(kern, dim3(grid), dim3(kDecThreads), lay.total, stream, pdl && batch <= kDecMaxBatch, L, cache, q,
                                n_append, partial, counters, counters + rows + done_slot, counters + rows + batch, out,
@@ -816,13 +822,16 @@ static cudaError_t launch_decode(const LayerDev& L, int batch, const DecodeCache
   {
     // The ring-write kernel runs between attention kernels that use nearly all shared memory of an SM:
     // give it the same shared-memory carve-out so that the SMs are not reconfigured twice per token.
-    static int carve_dev = -1;
+    static bool carve_set[kMaxDevices] = {false};
+    static std::mutex mu;
     int dev_now = 0;
-    cudaGetDevice(&dev_now);
-    if (dev_now != carve_dev) {
-      cudaFuncSetAttribute(kvm_decode_pre_kernel<D, 32, false, false>, cudaFuncAttributePreferredSharedMemoryCarveout,
-                           (int)cudaSharedmemCarveoutMaxShared);
-      carve_dev = dev_now;
+    if (cudaGetDevice(&dev_now) == cudaSuccess && dev_now >= 0 && dev_now < kMaxDevices) {
+      std::lock_guard<std::mutex> lock(mu);
+      if (!carve_set[dev_now]) {
+        cudaFuncSetAttribute(kvm_decode_pre_kernel<D, 32, false, false>, cudaFuncAttributePreferredSharedMemoryCarveout,
+                             (int)cudaSharedmemCarveoutMaxShared);
+        carve_set[dev_now] = true;
+      }
     }
   }
   if (!any_update) {

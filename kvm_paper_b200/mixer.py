@@ -86,6 +86,10 @@ class StatesCache:
 class SequenceMixer(nn.Module):
     """KVM mixer; parameter names equal the reference's so its checkpoints load unchanged."""
 
+    # When set, every prefill / decode call synchronises and raises if a kernel reported a device-side timeout
+    # (a bounded wait that ran out).  Off by default: the reference's mixers never synchronise either.
+    check_device_status = False
+
     _CACHE_DECODE = "kvm_b200_decode_cache"
     _CACHE_S_K = "kvm_s_k"
     _CACHE_S_V = "kvm_s_v"
@@ -317,7 +321,7 @@ class SequenceMixer(nn.Module):
         plan = self.make_prefill_plan(int(q.size(2)))
         params = self.layer_params(q.device)
         return ops.prefill_forward(params, q, k, v, merge_gate, plan, want_route=want_route,
-                                   memory_capacity=memory_capacity)
+                                   memory_capacity=memory_capacity, check=self.check_device_status)
 
     def forward_prefill(self, q, k, v, merge_gate, v_first, position_embeddings, attention_mask,
                         past_key_values=None, **kwargs):
@@ -375,6 +379,8 @@ class SequenceMixer(nn.Module):
         if int(cache.total_len_h[0]) != past_len or len(set(cache.total_len_h.tolist())) != 1:
             raise AssertionError(f"KVM decode cache length disagrees with the layer cache: {cache.total_len_h.tolist()} != {past_len}")
         out = cache.step(q, k, v, merge_gate)
+        if self.check_device_status:
+            cache.check_status()
         past_key_values.update(self.layer_idx, offset=1, states_dict={self._CACHE_DECODE: cache})
         return self.c_proj(out.to(q.dtype))
 

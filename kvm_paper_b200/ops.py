@@ -196,6 +196,7 @@ class PrefillResult:
     memory: MemoryBuffers
     plan: PrefillPlan
     route: torch.Tensor | None        # [B*Hkv, n_updates+1, C] int32 if requested
+    runner: Any = None                # the PrefillRunner that produced it (workspace inspection)
 
 
 class PrefillRunner:
@@ -243,6 +244,29 @@ class PrefillRunner:
         """Synchronise and raise if a kernel of the last run reported a device-side timeout."""
         rc = _lib.load().kvm_prefill_status(self.ws.data_ptr(), _stream_ptr(self.params.device))
         _lib.check(rc)
+
+    def workspace_views(self) -> dict[str, torch.Tensor]:
+        """Views (no copies) of what the last run left in the workspace, for inspection: the row pool of the
+        memory's attention view ``pool_k`` / ``pool_v`` [kv rows, pool_rows, D], the version tables
+        ``versions`` [kv rows, total_version_rows] (entry ``plan.version_row[u] + r`` = pool row of memory
+        row ``r`` after update ``u``) and the prepared keys ``prepared_keys`` [kv rows, (n_updates+1)*C, D]."""
+        cfg, plan = self.params.cfg, self.plan
+        lay = _lib.KvmPrefillLayout()
+        _lib.check(_lib.load().kvm_prefill_workspace_layout(C.byref(self.params.c), self.batch, plan.seq_len,
+                                                            plan.total_version_rows, C.byref(lay)))
+        rows, D = self.batch * cfg.n_kv_heads, cfg.head_dim
+
+        def view(offset, shape, dtype):
+            n = math.prod(shape) * torch.empty((), dtype=dtype).element_size()
+            return self.ws[offset:offset + n].view(dtype).view(shape)
+
+        out = {"pool_k": view(lay.pool_k_offset, (rows, lay.pool_rows, D), torch.bfloat16),
+               "pool_v": view(lay.pool_v_offset, (rows, lay.pool_rows, D), torch.bfloat16),
+               "versions": view(lay.version_table_offset, (rows, plan.total_version_rows), torch.int32)}
+        if plan.n_updates > 0:
+            out["prepared_keys"] = view(lay.prepared_keys_offset, (rows, (plan.n_updates + 1) * cfg.chunk_len, D),
+                                        torch.bfloat16)
+        return out
 
 
 class HostPrefill:
@@ -322,7 +346,7 @@ def prefill_forward(params: LayerParams, q: torch.Tensor, k: torch.Tensor, v: to
     if check:
         runner.check_status()
     # buffers are released by the caching allocator in stream order
-    return PrefillResult(out, runner.memory, plan, runner.route)
+    return PrefillResult(out, runner.memory, plan, runner.route, runner)
 
 
 # ------------------------------------------------------------------------------------ decode cache
@@ -359,7 +383,11 @@ class KvmDecodeCache:
         self.route = None
         self._last_any_update, self._last_n_append = False, None
         self._n_append = torch.full((batch,), -1, device=dev, dtype=torch.int32)
-        self._n_append_pinned = torch.full((batch,), -1, dtype=torch.int32).pin_memory()
+        # host staging of the per-step append counts: a small ring of pinned buffers, each guarded by an event
+        # recorded behind its copy, so that a later step never overwrites a buffer the copy engine still reads
+        self._n_append_pinned = [torch.full((batch,), -1, dtype=torch.int32).pin_memory() for _ in range(4)]
+        self._n_append_events = [None] * 4
+        self._n_append_slot = 0
         self._alloc_workspace()
 
     def _alloc_workspace(self):
@@ -459,8 +487,15 @@ class KvmDecodeCache:
         any_update = n_app is not None
         self._last_any_update, self._last_n_append = any_update, n_app
         if any_update:
-            self._n_append_pinned.copy_(torch.from_numpy(n_app))
-            self._n_append.copy_(self._n_append_pinned, non_blocking=True)
+            slot = self._n_append_slot
+            self._n_append_slot = (slot + 1) % len(self._n_append_pinned)
+            if self._n_append_events[slot] is not None:
+                self._n_append_events[slot].synchronize()
+            self._n_append_pinned[slot].copy_(torch.from_numpy(n_app))
+            self._n_append.copy_(self._n_append_pinned[slot], non_blocking=True)
+            ev = self._n_append_events[slot] or torch.cuda.Event()
+            ev.record(torch.cuda.current_stream(self.device))
+            self._n_append_events[slot] = ev
             if want_route:
                 self.route = torch.zeros(self.kv_rows, cfg.chunk_len, device=self.device, dtype=torch.int32)
         ccache = _CCache(self.memory.c(), self.ring_k.data_ptr(), self.ring_v.data_ptr(), self.ring_gate.data_ptr(),
@@ -510,6 +545,11 @@ class KvmDecodeCache:
         _lib.check(rc)
         self._keepalive = (q, k, v, gate, n_app_dev)
         return out
+
+    def check_status(self) -> None:
+        """Synchronise and raise if a decode kernel reported a device-side timeout since the last check."""
+        rc = _lib.load().kvm_decode_status(C.byref(self.params.c), self.batch, self._ws.data_ptr(), _stream_ptr(self.device))
+        _lib.check(rc)
 
     # -- inspection -----------------------------------------------------------------------------
     def logical_state_dict(self, b: int | None = None) -> dict[str, Any]:

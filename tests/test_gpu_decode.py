@@ -87,6 +87,23 @@ def test_decode_ragged_batch_matches_per_sequence_oracle(case):
     torch.manual_seed(21)
     Hq, Hkv, D, rope, C, lens, n_steps = RAGGED_CASES[case]
     spec = ko.KvmSpec(Hq, Hkv, D, D, rope, C, 2, 8, 1, "power_law", state_growth_factor=4.0, state_min_len=C)
+    _ragged_batch_against_oracle(spec, lens, n_steps)
+
+
+def test_decode_benchmark_range_contexts_match_per_sequence_oracle():
+    """Contexts from the range of the decode benchmark (4096 .. 65536 tokens, 16 heads x 128, block 256, one new
+    mean per block: memories of 270 .. 507 rows, rows spanning several 128-row chunks and several CTAs), 260
+    steps so that every sequence crosses a block boundary, each sequence against its own B=1 oracle run."""
+    torch.manual_seed(22)
+    spec = gh.bf16_spec(ko.KvmSpec(16, 16, 128, 128, 64, 256, 2, 4, 1, "plus_one", state_min_len=256))
+    traces = _ragged_batch_against_oracle(spec, [65000, 4100, 33023, 20479, 48000], 260)
+    total = gh.summarize([r for t in traces for r in t])
+    gh.record_counts("decode_benchmark_range", total)
+    assert total["updates"] >= 5 and total["merge_tokens"] >= 5 * 16 * 255
+
+
+def _ragged_batch_against_oracle(spec, lens, n_steps):
+    Hq, Hkv, D, C = spec.num_attention_heads, spec.num_key_value_heads, spec.d_qk_head, spec.chunk_len
     B = len(lens)
     params = gh.layer_params(spec)
     states, inputs = [], []
@@ -125,8 +142,12 @@ def test_decode_ragged_batch_matches_per_sequence_oracle(case):
         sd = cache.logical_state_dict(b)
         assert sd["kvm_s_k"].size(2) == states[b]["kvm_s_k"].size(2)
         assert torch.equal(sd["kvm_bswa_k"].cpu(), states[b]["kvm_bswa_k"])
+        scale = max(1.0, float(states[b]["kvm_s_k"].float().abs().max()))
+        assert_close_bf16(sd["kvm_s_k"].cpu(), states[b]["kvm_s_k"], f"seq {b} kvm_s_k", max_abs_tol=2e-2 * scale)
     assert cache.total_len.cpu().tolist() == [t + n_steps for t in lens]
     assert sum(len(t) for t in traces) >= 2  # boundary updates happened
+    cache.check_status()                     # no kernel reported an expired wait
+    return traces
 
 
 def test_decode_adopts_reference_eager_cache():
@@ -175,3 +196,27 @@ def test_decode_run_equals_step_by_step():
     assert torch.equal(got, want)
     assert torch.equal(c1.memory.k_sum, c2.memory.k_sum) and torch.equal(c1.total_len, c2.total_len)
     assert c1.update_count == c2.update_count and c1.update_count >= 3
+
+
+def test_decode_counters_and_lengths_stay_consistent_when_most_ctas_have_no_work():
+    """One short sequence: the chunk list has one or two entries, so all but one or two CTAs of the persistent
+    grid have no work.  The lengths may only advance once every CTA has read them: after every step the
+    lengths are exact and the workspace counters are back at zero (a CTA that saw advanced lengths would take
+    work of the next token and leave counters behind)."""
+    torch.manual_seed(3)
+    spec = ko.KvmSpec(2, 1, 64, 64, 32, 32, 2, 4, 1, "power_law", state_growth_factor=4.0, state_min_len=32)
+    T, n = 40, 150
+    q = torch.randn(1, 2, T + n, 64).bfloat16().cuda()
+    k = torch.nn.functional.layer_norm(torch.randn(1, 1, T + n, 64), (64,)).bfloat16().cuda()
+    v = torch.randn(1, 1, T + n, 64).bfloat16().cuda()
+    g = (1 + torch.nn.functional.elu(torch.randn(1, 1, T + n, 1))).bfloat16().cuda()
+    params, plan, res = gh.device_prefill(spec, q[:, :, :T], k[:, :, :T], v[:, :, :T], g[:, :, :T])
+    cache = ops.decode_cache_from_prefill(params, res, k[:, :, :T], v[:, :, :T], g[:, :, :T], gh.desired_fn(spec))
+    n_counters = cache.kv_rows + cache.batch + 1
+    for i in range(T, T + n):
+        cache.step(*(t[:, :, i:i + 1] for t in (q, k, v, g)))
+        head = cache._ws[: 4 * n_counters].view(torch.int32)
+        assert cache.total_len.cpu().tolist() == [i + 1], f"step {i - T}"
+        assert cache.state_len.cpu().tolist() == [int(cache.state_len_h[0])]
+        assert int(head.abs().sum()) == 0, f"step {i - T}: counters {head.cpu().tolist()}"
+    cache.check_status()

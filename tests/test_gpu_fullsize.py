@@ -1,15 +1,20 @@
-"""Size-independent properties of the device path at the benchmark's full sequence length (T = 32768,
-16 heads x 128, block 256, one new mean per block): the oracle needs minutes for these sizes, so the
-checks are properties the algorithm guarantees at any size — determinism, causality (a prefix of the
-prompt gives the prefix of the output, bit for bit), conservation of the routed tokens, convexity of the
-attention output, and agreement of the decode path with the prefill path one token later."""
+"""The device path at the benchmark's full sequence length (T = 32768, 16 heads x 128, block 256).
+
+Two kinds of checks.  (1) Against the oracle at this size: the oracle follows the device's routing decisions
+(teacher forcing, after classifying each one) and the activations, the carried memory and every decision are
+compared -- for the benchmark's "one new mean per block" schedule and for the reference's native
+``power_law`` 16*sqrt(T) schedule capped at 1024 means (ranked appends of up to 187 rows per block); the
+decisions are additionally checked for exactness on identical operands (the device's own prepared keys and
+memory versions, scores recomputed in float64).  (2) Size-independent properties: determinism, causality (a
+prefix of the prompt gives the prefix of the output, bit for bit), conservation of the routed tokens,
+convexity of the attention output, agreement of the decode path with the prefill path one token later."""
 
 import pytest
 import torch
 
 from kvm_paper_b200 import ops
 from oracle import kvm_oracle as ko
-from tests.helpers import assert_close_bf16
+from tests.helpers import assert_close_bf16, assert_not_worse_than_reference, max_abs, mean_rel
 from tests import gpu_helpers as gh
 
 pytestmark = pytest.mark.gpu
@@ -39,6 +44,45 @@ def _prefill(spec, q, k, v, gate, T=None, want_route=False):
                               check=True)
     torch.cuda.synchronize()
     return params, plan, res
+
+
+def _spec_for(mode):
+    if mode == "plus_one":
+        return _spec()
+    # the reference's native schedule (configs/prolong/120M/kvm_*_wd.yaml): 16 * sqrt(context), at most 4 blocks of means
+    return gh.bf16_spec(ko.KvmSpec(H, H, D, D, 64, C, 2, 4, 1, "power_law", state_growth_factor=16.0,
+                                   state_growth_exponent=0.5, state_min_len=C))
+
+
+@pytest.mark.parametrize("mode", ["plus_one", "power_law"])
+def test_full_length_prefill_matches_oracle(mode):
+    """B = 1, all 16 heads, T = 32768 through the C ABI against the oracle (a few seconds of CPU time)."""
+    spec = _spec_for(mode)
+    q, k, v, gate = _inputs(1, T_FULL, seed=21)
+    _, plan, res = _prefill(spec, q, k, v, gate, want_route=True)
+    if mode == "power_law":
+        assert plan.final_state_len == 1024 and max(plan.n_append[1:]) == 187
+    forced = [gh.decisions_from_route(res.route[:, u], 1, H) for u in range(1, plan.n_updates + 1)]
+    qc, kc, vc, gc = (t.cpu() for t in (q, k, v, gate))
+    trace = []
+    with torch.no_grad():
+        y, st = ko.prefill(spec, qc, kc, vc, gc, trace=trace, forced=forced)
+        y32, _ = ko.prefill(gh.fp32_spec(spec), qc.float(), kc.float(), vc.float(), gc.float(), forced=forced)
+    summary = gh.summarize(trace)
+    exact = gh.exact_routing_check(spec, res, gate)
+    out = res.out.cpu()
+    gh.record_counts(f"full_length_prefill[{mode}]", dict(
+        teacher_forced=summary, identical_operands=exact, out_max_abs=max_abs(out, y), out_mean_rel=mean_rel(out, y),
+        out_mean_rel_vs_fp32=mean_rel(out, y32), reference_bf16_mean_rel_vs_fp32=mean_rel(y, y32)))
+    # decisions: nothing outside the tie tolerance under teacher forcing; on identical operands nothing outside
+    # fp32 summation noise, and every append set legal
+    assert summary["merge_illegal"] == 0 and summary["append_rows_illegal"] == 0, summary
+    assert exact["merge_beyond_fp32_noise"] == 0 and exact["append_rows_illegal"] == 0, exact
+    assert exact["merge_tokens"] == summary["merge_tokens"] >= 490_000
+    # activations and carried memory
+    assert_close_bf16(out, y, f"full-length prefill ({mode})")
+    assert_not_worse_than_reference(out, y, y32, f"full-length prefill ({mode})")
+    gh.compare_memory(res.memory, st, plan.final_state_len, f"full-length prefill ({mode})")
 
 
 def test_full_length_prefill_is_deterministic_and_causal():

@@ -22,11 +22,20 @@ def _free_port():
 def test_two_gpu_results_equal_single_gpu():
     env = dict(os.environ, NCCL_NVLS_ENABLE="0")
     res = None
-    for _ in range(2):  # a rendezvous that fails to start (port taken, slow first import) is retried once on a new port
+    for _ in range(2):
         cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2", "--master-addr", "127.0.0.1",
                "--master-port", str(_free_port()), os.path.join(ROOT, "tests", "multi_gpu_check.py")]
         res = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env, cwd=ROOT)
-        if res.returncode == 0 or "MULTI_GPU_MISMATCH" in res.stdout:
+        if res.returncode == 0:
+            break
+        # Only a rendezvous that failed to start (port taken between probing and binding) is tried again, on a new
+        # port.  Anything that ran kernels -- a mismatch, a CUDA error, a crash of a rank -- fails at once: the
+        # same job is never run twice on the GPUs.
+        text = res.stdout + res.stderr
+        rendezvous = any(m in text for m in ("Address already in use", "EADDRINUSE", "RendezvousConnectionError",
+                                             "RendezvousTimeoutError", "failed to connect to", "TCPStore"))
+        ran = any(m in text for m in ("MULTI_GPU_", "CUDA error", "cudaError", "mismatch", "Xid", "illegal"))
+        if not rendezvous or ran:
             break
     assert res.returncode == 0, res.stdout[-2000:] + res.stderr[-2000:]
     assert "MULTI_GPU_OK" in res.stdout, res.stdout[-2000:] + res.stderr[-2000:]

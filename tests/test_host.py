@@ -13,50 +13,9 @@ from kvm_paper_b200 import _lib, ops
 from kvm_paper_b200.mixer import SequenceMixer, StatesCache
 from oracle import kvm_oracle as ko
 from tests.helpers import SMALL_FIXTURES, load_fixture, spec_from_fixture
+from tests.helpers import config_from_fixture as _config_from_fixture, mixer_from_fixture as _mixer_from_fixture, rotary_tables as _rotary
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
-
-
-def _config_from_fixture(fix):
-    cfg = dict(
-        num_key_value_heads=None, d_qk_head=None, d_v_head=None, d_head=None, mup_base_dim=768, rope_partial_dim=64,
-        use_value_residual=1, kvm_value_residual_mode="rwkv", kvm_token_shift_mode="rwkv",
-        kvm_apply_merge_gate_to_initial_state=0, kvm_apply_merge_gate_to_appends=0, kvm_use_merge_gate_keys=1,
-        kvm_use_merge_gate_values=1, kvm_use_head_temps=1, kvm_use_vlens=1, use_tokenshift_att=0, sink_len=1,
-        chunk_len=256, n_max_d_chunks=1, n_bswa_chunks=2, state_budget_mode="fixed", state_growth_factor=1.0,
-        state_growth_exponent=0.5, state_round_down=1, state_min_len=-1, state_saturation_n=None)
-    cfg.update(fix["case"]["cfg"])
-    return types.SimpleNamespace(**cfg)
-
-
-def _mixer_from_fixture(fix):
-    cfg = _config_from_fixture(fix)
-    dtype = getattr(torch, fix["case"]["dtype"])
-    old = torch.get_default_dtype()
-    torch.set_default_dtype(dtype)
-    try:
-        m = SequenceMixer(cfg, 1)
-    finally:
-        torch.set_default_dtype(old)
-    missing, unexpected = m.load_state_dict(fix["state_dict"], strict=False)
-    assert not unexpected, unexpected
-    assert set(missing) <= {"c_proj.weight"}, missing  # the fixture's c_proj was replaced by Identity
-    m.eval()
-    if fix["case"].get("plus_one"):
-        m._desired_state_len = lambda ctx, avail, cur, _m=m: max(min(max(int(cur), 0) + 1, max(int(avail), 0), _m.max_state_len), max(int(cur), 0))
-    return cfg, m
-
-
-def _rotary(cfg, d, pos):
-    """cos / signed-sin tables as the reference's RotaryEmbedding builds them (model/rwkv7_backbone.py:34-73)."""
-    partial = cfg.rope_partial_dim
-    freq = (1 / 10000.0) ** torch.linspace(0.0, 1.0, steps=partial // 2, dtype=torch.float32)
-    freq = torch.cat([freq.repeat_interleave(2), freq.new_zeros(d - partial)])
-    B, T = pos.shape
-    theta = pos.float().view(B, T, 1, 1) @ freq.view(1, 1, 1, -1)
-    cos, sin = theta.cos().bfloat16(), theta.sin().bfloat16()
-    sin[..., 1::2] *= -1
-    return cos, sin
 
 
 @pytest.mark.parametrize("name", SMALL_FIXTURES)
