@@ -89,6 +89,12 @@ class SequenceMixer(nn.Module):
     # When set, every prefill / decode call synchronises and raises if a kernel reported a device-side timeout
     # (a bounded wait that ran out).  Off by default: the reference's mixers never synchronise either.
     check_device_status = False
+    # Validation hook (the reference's Triton mixer has ``capture_state_snapshots`` for the same purpose): when
+    # set, every prefill / decode call also records the routing decision of every consumed token in
+    # ``last_route`` ([B*Hkv, n_updates+1, C] after a prefill, [B*Hkv, C] or None after a decode step;
+    # >= 0: memory row merged into, -(1+row): appended as that row).
+    capture_routes = False
+    last_route = None
 
     _CACHE_DECODE = "kvm_b200_decode_cache"
     _CACHE_S_K = "kvm_s_k"
@@ -330,7 +336,9 @@ class SequenceMixer(nn.Module):
         if attention_mask is not None:
             raise ValueError("kvm_b200 mixer does not support attention_mask")
         T = int(q.size(2))
-        res = self.prefill_raw(q, k, v, merge_gate)
+        res = self.prefill_raw(q, k, v, merge_gate, want_route=self.capture_routes)
+        if self.capture_routes:
+            self.last_route = res.route
         y = self.c_proj(res.out.to(q.dtype))
         if past_key_values is not None:
             plan = res.plan
@@ -378,7 +386,9 @@ class SequenceMixer(nn.Module):
             raise RuntimeError("KVM decode cache belongs to another mixer")
         if int(cache.total_len_h[0]) != past_len or len(set(cache.total_len_h.tolist())) != 1:
             raise AssertionError(f"KVM decode cache length disagrees with the layer cache: {cache.total_len_h.tolist()} != {past_len}")
-        out = cache.step(q, k, v, merge_gate)
+        out = cache.step(q, k, v, merge_gate, want_route=self.capture_routes)
+        if self.capture_routes:
+            self.last_route = cache.route if cache._last_any_update else None
         if self.check_device_status:
             cache.check_status()
         past_key_values.update(self.layer_idx, offset=1, states_dict={self._CACHE_DECODE: cache})

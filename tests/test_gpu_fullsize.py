@@ -77,7 +77,9 @@ def test_full_length_prefill_matches_oracle(mode):
     # decisions: nothing outside the tie tolerance under teacher forcing; on identical operands nothing outside
     # fp32 summation noise, and every append set legal
     assert summary["merge_illegal"] == 0 and summary["append_rows_illegal"] == 0, summary
+    assert summary["merge_differ"] == summary["merge_differ_fp32"], summary   # observed on B200: 0 of 510 000 differ
     assert exact["merge_beyond_fp32_noise"] == 0 and exact["append_rows_illegal"] == 0, exact
+    assert exact["append_rows_differ"] <= 2, exact                            # observed: 0
     assert exact["merge_tokens"] == summary["merge_tokens"] >= 490_000
     # activations and carried memory
     assert_close_bf16(out, y, f"full-length prefill ({mode})")
