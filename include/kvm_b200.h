@@ -112,6 +112,13 @@ size_t kvm_prefill_workspace_bytes(const kvm_layer* layer, int32_t batch, int64_
 #define KVM_PREFILL_ATTENTION 2u  /* run block attention (reads the versions in `workspace`, fills out) */
 #define KVM_PREFILL_LEGACY_ATTENTION 4u /* with ATTENTION: use the warp-level mma.sync kernel even where the
                                            tcgen05 kernel applies (head_dim 128, block multiple of 128) */
+#define KVM_PREFILL_LEGACY_CHAIN 8u     /* with CHAIN: use the general chain kernel even where the kernel with the
+                                           resident memory on the tensor cores applies (head_dim 128, block 128/256) */
+#define KVM_PREFILL_TEST_WITHHOLD_ARRIVAL 16u /* test hook, with CHAIN on the tensor-core chain: one barrier arrival of
+                                           the first update is withheld and the wait limit is a fraction of a
+                                           millisecond, so that the bounded wait behind it runs out: the kernel must
+                                           report KVM_ERR_DEVICE_TIMEOUT through kvm_prefill_status and return
+                                           (nothing is in flight, nothing faults); the results are undefined */
 int kvm_prefill_forward(const kvm_layer* layer, int32_t batch, int64_t seq_len,
                         kvm_tensor4 q, kvm_tensor4 k, kvm_tensor4 v, kvm_tensor4 gate,
                         const kvm_update_plan* plan_dev, const kvm_update_plan* plan_host,
@@ -131,7 +138,8 @@ int kvm_prefill_status(void* workspace, void* stream);
  * after a call: the row pool of the memory's attention view ([B*Hkv, pool_rows, D] bf16, keys and values),
  * the version tables ([B*Hkv, total_version_rows] int32: entry plan[u].version_row + r is the pool row that
  * holds memory row r after update u) and the prepared keys of all consumed tokens
- * ([B*Hkv, (n_updates+1)*C, D] bf16; present when n_updates > 0).  Counterpart of the reference's
+ * ([B*Hkv, (n_updates+1)*C, D] bf16; present when n_updates > 0; the gated keys lie in a second array of
+ * the same shape).  Counterpart of the reference's
  * capture_state_snapshots hook (model/kernels/kvm_triton_training_kernels.py:3518-3524), without copies. */
 typedef struct kvm_prefill_layout {
   size_t status_offset;
@@ -139,6 +147,7 @@ typedef struct kvm_prefill_layout {
   size_t pool_v_offset;
   size_t version_table_offset;
   size_t prepared_keys_offset;
+  size_t gated_keys_offset;    /* bf16(prepared key * gate), same shape (head_dim 128 with blocks of 128 / 256 only) */
   int64_t pool_rows;
   size_t total_bytes;
 } kvm_prefill_layout;

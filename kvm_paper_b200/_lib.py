@@ -13,7 +13,8 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_HERE, "libkvm_b200.so")
 
 KVM_OK = 0
-PREFILL_CHAIN, PREFILL_ATTENTION, PREFILL_LEGACY_ATTENTION = 1, 2, 4
+PREFILL_CHAIN, PREFILL_ATTENTION, PREFILL_LEGACY_ATTENTION, PREFILL_LEGACY_CHAIN = 1, 2, 4, 8
+PREFILL_TEST_WITHHOLD_ARRIVAL = 16
 ERROR_NAMES = {1: "bad argument", 2: "capacity", 3: "device timeout", 4: "CUDA error", 5: "unsupported"}
 
 
@@ -45,7 +46,7 @@ class KvmUpdatePlan(C.Structure):
 class KvmPrefillLayout(C.Structure):
     _fields_ = [("status_offset", C.c_size_t), ("pool_k_offset", C.c_size_t), ("pool_v_offset", C.c_size_t),
                 ("version_table_offset", C.c_size_t), ("prepared_keys_offset", C.c_size_t),
-                ("pool_rows", C.c_int64), ("total_bytes", C.c_size_t)]
+                ("gated_keys_offset", C.c_size_t), ("pool_rows", C.c_int64), ("total_bytes", C.c_size_t)]
 
 
 class KvmDecodeCache(C.Structure):

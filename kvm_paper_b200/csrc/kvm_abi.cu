@@ -11,7 +11,8 @@ namespace kvm {
 cudaError_t prefill_dispatch(int D, const LayerDev& L, int batch, long long T, Tensor4 q, Tensor4 k, Tensor4 v,
                              Tensor4 gate, const kvm_update_plan* plan_dev, int n_plan, long long ver_rows,
                              MemoryDev mem, bf16* out, int* route, bf16* pool_k, bf16* pool_v, long long pool_rows,
-                             int* ver_idx, bf16* pk_scr, bf16* pk_all, int* status, unsigned phases, cudaStream_t stream);
+                             int* ver_idx, bf16* pk_scr, bf16* pk_all, bf16* gk_all, int* route_ws, int s_final, int* status,
+                             unsigned phases, cudaStream_t stream);
 size_t update_smem_bytes(int D, int C, int capacity);
 cudaError_t decode_dispatch(int D, const LayerDev& L, int batch, const DecodeCacheDev& cache, Tensor4 q, Tensor4 k,
                             Tensor4 v, Tensor4 gate, const int* n_append, int any_update, int max_rows, bf16* out,
@@ -107,7 +108,7 @@ int check_memory(const kvm_memory& m, const kvm_layer* l) {
 // rows per kv row), the per-version index tables, and the prepared-key scratch of the update variant
 // that cannot stage a block in shared memory.
 struct PrefillWs {
-  size_t status, pool_k, pool_v, ver_idx, pk, pk_all, total;
+  size_t status, pool_k, pool_v, ver_idx, pk, pk_all, gk_all, route, total;
   long long pool_rows;
 };
 PrefillWs prefill_ws(const kvm_layer* l, int batch, long long seq_len, long long ver_rows) {
@@ -125,6 +126,11 @@ PrefillWs prefill_ws(const kvm_layer* l, int batch, long long seq_len, long long
   w.ver_idx = off; off = align_up(off + rows * (size_t)ver_rows * 4, 256);
   w.pk = off; off = align_up(off + rows * (size_t)C * D * 2, 256);
   w.pk_all = off; off = align_up(off + (n_plan > 1 ? rows * (size_t)(n_plan * C) * D * 2 : 0), 256);  // prepared keys of all consumed tokens
+  // gated keys of all consumed tokens and the routing decisions (the chain on the tensor cores reads its operands
+  // from memory and hands the decisions to the value pass)
+  const bool tc = D == 128 && (C == 128 || C == 256) && n_plan > 1;
+  w.gk_all = off; off = align_up(off + (tc ? rows * (size_t)(n_plan * C) * D * 2 : 0), 256);
+  w.route = off; off = align_up(off + (tc ? rows * (size_t)(n_plan * C) * 4 : 0), 256);
   w.total = off;
   return w;
 }
@@ -193,7 +199,7 @@ int kvm_prefill_forward(const kvm_layer* layer, int32_t batch, int64_t seq_len, 
   g_err[0] = 0;
   if (int rc = check_layer(layer)) return rc;
   if (batch <= 0 || seq_len <= 0) return fail(KVM_ERR_BAD_ARGUMENT, "batch %d and seq_len %lld must be positive", batch, (long long)seq_len);
-  if ((phases & 3u) == 0 || (phases & ~7u)) return fail(KVM_ERR_BAD_ARGUMENT, "phases %u must be a combination of KVM_PREFILL_CHAIN and KVM_PREFILL_ATTENTION", phases);
+  if ((phases & 3u) == 0 || (phases & ~31u)) return fail(KVM_ERR_BAD_ARGUMENT, "phases %u must be a combination of KVM_PREFILL_CHAIN and KVM_PREFILL_ATTENTION", phases);
   const int D = layer->head_dim, C = layer->chunk_len, W = layer->n_bswa_chunks;
   if (int rc = check_tensor(q, "q", D)) return rc;
   if (int rc = check_tensor(k, "k", D)) return rc;
@@ -239,6 +245,7 @@ int kvm_prefill_forward(const kvm_layer* layer, int32_t batch, int64_t seq_len, 
                                    reinterpret_cast<bf16*>(wsb + ws.pool_k), reinterpret_cast<bf16*>(wsb + ws.pool_v),
                                    ws.pool_rows, reinterpret_cast<int*>(wsb + ws.ver_idx),
                                    reinterpret_cast<bf16*>(wsb + ws.pk), reinterpret_cast<bf16*>(wsb + ws.pk_all),
+                                   reinterpret_cast<bf16*>(wsb + ws.gk_all), reinterpret_cast<int*>(wsb + ws.route), (int)S,
                                    reinterpret_cast<int*>(wsb + ws.status), phases,
                                    static_cast<cudaStream_t>(stream));
   if (e != cudaSuccess) return cuda_fail(e, "kvm_prefill_forward");
@@ -257,6 +264,7 @@ int kvm_prefill_workspace_layout(const kvm_layer* layer, int32_t batch, int64_t 
   out->pool_v_offset = ws.pool_v;
   out->version_table_offset = ws.ver_idx;
   out->prepared_keys_offset = ws.pk_all;
+  out->gated_keys_offset = ws.gk_all;
   out->pool_rows = ws.pool_rows;
   out->total_bytes = ws.total;
   return KVM_OK;

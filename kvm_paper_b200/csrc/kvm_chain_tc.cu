@@ -1,0 +1,1086 @@
+// The memory chain of the prefill for head_dim 128 and blocks of 128 or 256 tokens, organised for the latency of
+// one update (the updates of a kv row are strictly sequential: block m routes against the memory block m-1 left).
+//
+// Follows the reference's eager update (model/kvm_mixer.py:250-340) with the fp32 merge routing of
+// model/kvm_fp32_routing_reference.py:24-49; what the reference does with 3-5 host-issued launches per block
+// (model/kernels/kvm_triton_training_kernels.py:1606-1747) is one resident step here.
+//
+// Split of the work
+//   kvm_chain_tc_kernel   routing and the KEY side of the memory: a cluster of 1..8 CTAs per kv row walks all
+//                         updates.  Memory row r belongs to CTA r % nc, which keeps the attention view of its
+//                         rows (k_attn) RESIDENT in shared memory in the tensor-core operand layout, so a routing
+//                         pass loads nothing: per update
+//                           1. novelty pass   S = pk x k_attn^T (tcgen05, accumulators in tensor memory), running
+//                                             maximum per token, partial maxima exchanged through distributed
+//                                             shared memory, rounded to bf16; the n_append lowest are appended
+//                           2. logits pass    S = gk x k_attn^T against the memory after the appends, running fp32
+//                                             first-argmax per token (sink rows excluded), partial results
+//                                             exchanged, lowest row wins ties
+//                           3. scatter        delta[rows x D] = onehot[rows x tokens] x gk[tokens x D] on the
+//                                             tensor cores (touched rows compacted onto the 128 accumulator
+//                                             lanes; products are exact, the accumulation order is the hardware's
+//                                             and fixed), then row = bf16(row + bf16(delta)), LayerNorm refresh of
+//                                             the touched rows into shared memory and into the row pool
+//                         Prepared keys pk and gated keys gk = bf16(pk * gate) of every token come from a parallel
+//                         pre-pass and arrive by tiled TMA one update ahead.
+//   kvm_vpass_kernel      the VALUE side, which no later update reads: one warp per memory row walks the routing
+//                         decisions of all updates and accumulates the gated values routed to its row in token
+//                         order (fixed-order, warp-parallel over the head dimension), writing the row's value view
+//                         for every version it changes.  Fully parallel over rows and kv rows.
+// Every wait is bounded; a wait that runs out sets the status word, all roles and all CTAs of the cluster leave
+// through the common exit, tensor memory is freed.
+#include <algorithm>
+#include <mutex>
+
+#include "kvm_common.cuh"
+#include "kvm_tc.cuh"
+#include "kvm_tma_host.cuh"
+
+namespace kvm {
+namespace chain {
+
+constexpr int HD = 128;
+constexpr int kWorkerWarps = 16;
+constexpr int kWorkers = kWorkerWarps * 32;   // threads that do everything but issuing copies and MMAs
+constexpr int kThreads = kWorkers + 32;       // + the issuing warp (one elected thread)
+constexpr int kChunk = 64;                    // memory rows per MMA and per tensor-memory chunk
+constexpr int kTmBufs = 4;                    // chunks in flight: 4 x (2 token tiles x 64 columns) = 512 columns
+constexpr uint32_t kTmemCols = 512;
+constexpr int kMaxSmem = 225 * 1024;           // dynamic part; the kernel also holds 1 KB of static shared memory
+
+__host__ __device__ inline int ceil_div(int a, int b) { return (a + b - 1) / b; }
+
+// Shared-memory carve-up (byte offsets from a 1024-byte aligned base).
+struct Layout {
+  int Rcap;  // resident memory rows per CTA (multiple of 64)
+  uint32_t R, P, G, xbuf, part, tok, rowi, tloc, stat, bars, total;
+  __host__ __device__ Layout(int C, int s_max, int nc) {
+    Rcap = ceil_div(ceil_div(s_max, nc), kChunk) * kChunk;
+    uint32_t off = 0;
+    R = off;    off += 2u * Rcap * 128u;                 // [2 halves of D][Rcap][64] bf16, 128-byte swizzle
+    P = off;    off += (uint32_t)C * 256u;               // prepared keys of the block; later the one-hot operand
+    G = off;    off += (uint32_t)C * 256u;               // gated keys of the block
+    xbuf = off; off += 2u * nc * C * 8u;                 // [parity][source CTA][token] {value, row}
+    part = off; off += 2u * C * 8u;                      // [column half][token] {value, row}: the two halves of a chunk
+    tok = off;  off += 4u * C * 4u;                      // nov[C] f32, idx[C], pos[C], list[C]
+    const uint32_t sp = (uint32_t)((s_max + 63) & ~31);  // padded row count: every region below stays 16-byte aligned
+    rowi = off; off += sp * 8u;                          // cur[sp] i32, gci[sp] i16, lci[sp] i16
+    tloc = off; off += 2u * C * 2u + 2u * sp;            // touched_local[C] u16, spare, tf[sp] u8
+    stat = off; off += 2u * 4u * 128u * 4u;              // LayerNorm partial sums of the scatter epilogue
+    bars = off; off += 512u;
+    total = (off + 15u) & ~15u;
+  }
+};
+
+struct Bars {
+  uint64_t full_p, full_g;              // TMA arrivals of the block's prepared / gated keys
+  uint64_t tm_full[kTmBufs];            // MMAs of a chunk complete
+  uint64_t tm_empty[kTmBufs];           // the chunk has been read back
+  uint64_t w2i;                         // workers -> issuer: shared-memory operands are ready
+  uint64_t sc_done;                     // scatter MMAs complete
+  uint64_t xbar[2];                     // arrivals of the peers' partial results (two in flight)
+  uint32_t tmem_base;
+  int abort;                            // somebody in the cluster gave up
+  int n_pass;                           // scatter passes of the current update (workers -> issuer)
+  float red_v[32];
+  int red_t[32];
+};
+
+static_assert(sizeof(Bars) <= 512, "the barrier block outgrew its shared-memory region");
+
+struct Args {
+  LayerDev L;
+  const kvm_update_plan* plan;
+  int n_plan;
+  int nc;
+  int s_max;             // final number of memory rows
+  long long n_tok;       // tokens per kv row in pk_all / gk_all
+  bf16* k_sum;           // [rows][capacity][D]
+  bf16* k_attn;          // [rows][capacity][D] final view
+  int capacity;
+  bf16* pool_k;          // [rows][pool_rows][D] or null (no versions kept)
+  long long pool_rows;
+  int* ver_idx;          // [rows][ver_rows] or null
+  long long ver_rows;
+  int* route;            // [rows][n_plan][C]
+  int* status;
+  uint32_t wait_limit;
+  uint32_t test_flags;   // bit 0: the issuer withholds one commit (exercises the timeout path)
+};
+
+// ------------------------------------------------------------------------------------------------ primitives
+__device__ __forceinline__ void wsync() { asm volatile("bar.sync 1, %0;" ::"n"(kWorkers) : "memory"); }
+// uniform AND over the worker threads
+__device__ __forceinline__ bool wvote(bool ok) {
+  uint32_t r;
+  asm volatile(
+      "{\n\t.reg .pred p, q;\n\t"
+      "setp.ne.b32 p, %1, 0;\n\t"
+      "barrier.cta.red.and.pred q, 1, %2, p;\n\t"
+      "selp.b32 %0, 1, 0, q;\n\t}"
+      : "=r"(r)
+      : "r"((uint32_t)ok), "n"(kWorkers)
+      : "memory");
+  return r != 0;
+}
+__device__ __forceinline__ bool try_wait_cluster(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.b32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(tc::smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// Bounded wait; also gives up when somebody else has.
+template <bool CLUSTER = false>
+__device__ __forceinline__ bool wait(uint64_t* bar, uint32_t parity, uint32_t limit, volatile int* abort) {
+  for (uint32_t i = 0; i < limit; ++i) {
+    if (CLUSTER ? try_wait_cluster(bar, parity) : tc::mbar_try_wait(bar, parity)) return true;
+    if (i >= 8) {
+      if (*abort) return false;
+      __nanosleep(i < 64 ? 20 : 100);
+    }
+  }
+  return false;
+}
+__device__ __forceinline__ uint32_t peer_addr(const void* local, int peer) {
+  uint32_t a = tc::smem_u32(local), r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(peer));
+  return r;
+}
+__device__ __forceinline__ void st_peer_v2(uint32_t addr, float v, int i) {
+  asm volatile("st.shared::cluster.v2.b32 [%0], {%1, %2};" ::"r"(addr), "r"(__float_as_uint(v)), "r"(i) : "memory");
+}
+__device__ __forceinline__ void st_peer_b32(uint32_t addr, int v) {
+  asm volatile("st.shared::cluster.b32 [%0], %1;" ::"r"(addr), "r"(v) : "memory");
+}
+__device__ __forceinline__ void fence_cluster() { asm volatile("fence.acq_rel.cluster;" ::: "memory"); }
+__device__ __forceinline__ void arrive_peer(uint32_t bar_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(bar_addr) : "memory");
+}
+__device__ __forceinline__ void cluster_barrier() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+
+// 16-byte piece c (elements 8c..8c+7) of row r of an operand stored as [2 halves][rows][64] in the 128-byte swizzle
+__device__ __forceinline__ uint32_t piece(int rows, int r, int c) {
+  return (uint32_t)((c >> 3) * rows * 128 + r * 128 + (((c & 7) ^ (r & 7)) << 4));
+}
+
+// rows r < S owned by CTA `rank` (r % nc == rank)
+__device__ __forceinline__ int n_local(int S, int nc, int rank) { return S > rank ? (S - rank + nc - 1) / nc : 0; }
+
+// ------------------------------------------------------------------------------------------------ the issuer
+// One thread: TMA copies of the next block, the MMAs of the routing passes and of the scatter.
+struct Issuer {
+  const Args& a;
+  unsigned char* smem;
+  const Layout& lay;
+  Bars* bars;
+  uint32_t tmem;
+  int crank, row;
+  const CUtensorMap* map_pk;
+  const CUtensorMap* map_gk;
+  uint32_t g = 0;        // chunks issued so far (buffer g % 4, use g / 4)
+  uint32_t n_w2i = 0, n_sc = 0, n_load = 0;
+  volatile int* abort;
+
+  __device__ __forceinline__ bool wait_workers() {
+    const bool ok = wait(&bars->w2i, n_w2i & 1, a.wait_limit, abort);
+    ++n_w2i;
+    tc::tc_fence_after_sync();
+    return ok;
+  }
+  __device__ __forceinline__ void load_block(int u, bool want_p) {
+    const int C = a.L.C;
+    const int y = (int)((long long)row * a.n_tok + (long long)u * C);
+    if (want_p) {
+      tc::mbar_arrive_expect_tx(&bars->full_p, (uint32_t)C * 256u);
+      tc::tma_load_2d(smem + lay.P, map_pk, 0, y, &bars->full_p);
+      tc::tma_load_2d(smem + lay.P + C * 128, map_pk, 64, y, &bars->full_p);
+    }
+    tc::mbar_arrive_expect_tx(&bars->full_g, (uint32_t)C * 256u);
+    tc::tma_load_2d(smem + lay.G, map_gk, 0, y, &bars->full_g);
+    tc::tma_load_2d(smem + lay.G + C * 128, map_gk, 64, y, &bars->full_g);
+  }
+  // S[tokens x 64 rows] = A[tokens x D] * R[rows l0.. x D]^T for every chunk of the first n_rows local rows
+  __device__ __forceinline__ bool pass(uint32_t a_off, int n_rows, bool withhold_first_commit) {
+    const int C = a.L.C, n_mt = C / 128;
+    constexpr uint32_t idesc = tc::make_idesc(128, kChunk, 0, 0);
+    const uint32_t a_addr = tc::smem_u32(smem + a_off), r_addr = tc::smem_u32(smem + lay.R);
+    const int n_chunks = ceil_div(n_rows, kChunk);
+    for (int c = 0; c < n_chunks; ++c, ++g) {
+      const uint32_t b = g % kTmBufs;
+      if (g >= kTmBufs && !wait(&bars->tm_empty[b], ((g / kTmBufs) - 1) & 1, a.wait_limit, abort)) return false;
+      tc::tc_fence_after_sync();
+      const uint64_t db0 = tc::make_desc(r_addr + (uint32_t)(c * kChunk * 128), 16, 1024);
+      for (int m = 0; m < n_mt; ++m) {
+        const uint64_t da0 = tc::make_desc(a_addr + (uint32_t)(m * 128 * 128), 16, 1024);
+#pragma unroll
+        for (int ks = 0; ks < HD / 16; ++ks) {
+          const uint64_t da = da0 + (uint64_t)(((uint32_t)(ks >> 2) * (uint32_t)(C * 128) + (uint32_t)(ks & 3) * 32u) >> 4);
+          const uint64_t db = db0 + (uint64_t)(((uint32_t)(ks >> 2) * (uint32_t)(lay.Rcap * 128) + (uint32_t)(ks & 3) * 32u) >> 4);
+          tc::mma_ss(tmem + b * 128u + (uint32_t)(m * kChunk), da, db, idesc, ks > 0);
+        }
+      }
+      if (!(withhold_first_commit && c == 0)) tc::mma_commit_own_cta(&bars->tm_full[b]);
+    }
+    return true;
+  }
+  // delta[128 compacted rows x D] = onehot[rows x C tokens] * gk[C tokens x D]
+  __device__ __forceinline__ void scatter() {
+    const int C = a.L.C;
+    constexpr uint32_t idesc = tc::make_idesc(128, HD, 0, 1);
+    const uint64_t da0 = tc::make_desc(tc::smem_u32(smem + lay.P), 16, 1024);             // one-hot, K-major: [C/64][128][64]
+    const uint64_t db0 = tc::make_desc(tc::smem_u32(smem + lay.G), (uint32_t)C * 128u, 1024);  // gated keys, MN-major
+    for (int ks = 0; ks < C / 16; ++ks) {
+      const uint64_t da = da0 + (uint64_t)(((uint32_t)(ks >> 2) * (128u * 128u) + (uint32_t)(ks & 3) * 32u) >> 4);
+      const uint64_t db = db0 + (uint64_t)(((uint32_t)ks * 2048u) >> 4);
+      tc::mma_ss(tmem, da, db, idesc, ks > 0);
+    }
+    tc::mma_commit_own_cta(&bars->sc_done);
+  }
+
+  __device__ bool run() {
+    const int C = a.L.C, nc = a.nc;
+    // block 0 (the initial memory) needs the prepared keys only; the gated keys travel with it to keep the barriers in step
+    load_block(0, true);
+    for (int u = 0; u < a.n_plan; ++u) {
+      const kvm_update_plan pl = a.plan[u];
+      const int S0 = pl.state_before, na = pl.n_append, S1 = S0 + na, nm = C - na;
+      if (u == 0) {
+        // the workers build the initial memory from the prepared keys and report when the block buffers are free
+        if (!wait_workers()) return false;
+        n_load = 1;
+        if (a.n_plan > 1) load_block(1, true);
+        continue;
+      }
+      const bool has_nov = na > 0 && nm > 0;
+      if (has_nov) {
+        if (!wait(&bars->full_p, n_load & 1, a.wait_limit, abort)) return false;
+        if (!pass(lay.P, n_local(S0, nc, crank), false)) return false;
+        if (!wait_workers()) return false;  // the appended rows are in the resident memory
+      }
+      if (nm > 0) {
+        if (!wait(&bars->full_g, n_load & 1, a.wait_limit, abort)) return false;
+        if (!pass(lay.G, n_local(S1, nc, crank), (a.test_flags & 1u) && u == 1)) return false;
+      }
+      // scatter passes (their number is decided by the workers once the routing is final)
+      if (!wait_workers()) return false;
+      const int n_pass = *reinterpret_cast<volatile int*>(&bars->n_pass);
+      for (int p = 0; p < n_pass; ++p) {
+        if (p > 0 && !wait_workers()) return false;
+        scatter();
+        ++n_sc;
+      }
+      if (n_pass == 0) {  // nothing routed to this CTA's rows: the logits MMAs must still be complete before G is overwritten
+        tc::mma_commit_own_cta(&bars->sc_done);
+        ++n_sc;
+      }
+      if (!wait(&bars->sc_done, (n_sc - 1) & 1, a.wait_limit, abort)) return false;
+      ++n_load;  // the loads of this update have been consumed
+      // both operands of every block are loaded (also where an update needs only one): the two barriers stay in step
+      if (u + 1 < a.n_plan) load_block(u + 1, true);
+      // the next routing pass reads the resident memory the workers are refreshing now
+      if (!wait_workers()) return false;
+    }
+    return true;
+  }
+};
+
+// ------------------------------------------------------------------------------------------------ the workers
+struct Workers {
+  const Args& a;
+  unsigned char* smem;
+  const Layout& lay;
+  Bars* bars;
+  uint32_t tmem;
+  int crank, row;
+  const float* ln_w;
+  const float* ln_b;
+  volatile int* abort;
+  int tid, warp, lane;
+  uint32_t g = 0, n_sc = 0, n_x = 0, n_load = 0;
+  int pool_next = 0;
+
+  __device__ __forceinline__ float* nov() const { return reinterpret_cast<float*>(smem + lay.tok); }
+  __device__ __forceinline__ int* idx() const { return reinterpret_cast<int*>(smem + lay.tok) + a.L.C; }
+  __device__ __forceinline__ int* pos() const { return reinterpret_cast<int*>(smem + lay.tok) + 2 * a.L.C; }
+  __device__ __forceinline__ int* list() const { return reinterpret_cast<int*>(smem + lay.tok) + 3 * a.L.C; }
+  __device__ __forceinline__ int* cur() const { return reinterpret_cast<int*>(smem + lay.rowi); }
+  __device__ __forceinline__ int padded_rows() const { return (a.s_max + 63) & ~31; }
+  __device__ __forceinline__ short* gci() const { return reinterpret_cast<short*>(smem + lay.rowi + (uint32_t)padded_rows() * 4u); }
+  __device__ __forceinline__ short* lci() const { return gci() + padded_rows(); }
+  __device__ __forceinline__ unsigned short* tloc() const { return reinterpret_cast<unsigned short*>(smem + lay.tloc); }
+  __device__ __forceinline__ unsigned char* tf() const { return smem + lay.tloc + 2u * a.L.C * 2u; }
+  __device__ __forceinline__ float2* part(int half) const { return reinterpret_cast<float2*>(smem + lay.part) + half * a.L.C; }
+  __device__ __forceinline__ float2* xb(int parity, int src) const { return reinterpret_cast<float2*>(smem + lay.xbuf) + (size_t)(parity * a.nc + src) * a.L.C; }
+  __device__ __forceinline__ float* stat(int which) const { return reinterpret_cast<float*>(smem + lay.stat) + which * 4 * 128; }
+
+  __device__ __forceinline__ void signal_issuer() {
+    tc::fence_proxy_async();   // shared-memory writes of this thread -> visible to the tensor core / TMA
+    tc::tc_fence_before_sync();
+    __syncwarp();
+    if (lane == 0) tc::mbar_arrive(&bars->w2i);
+  }
+
+  // Read back the chunks of a routing pass.  ARG = false: running maximum (novelty); true: running first-argmax of
+  // rows >= `protected_rows`.  Leaves per token the CTA's partial result in part(half)[token].
+  template <bool ARG>
+  __device__ __forceinline__ bool read_pass(int n_rows, int protected_rows) {
+    const int C = a.L.C, nc = a.nc;
+    const int half = warp >> 3, mt = (warp >> 2) & 1, quarter = warp & 3;
+    const bool active = mt * 128 < C;
+    const int token = mt * 128 + quarter * 32 + lane;
+    const int n_chunks = ceil_div(n_rows, kChunk);
+    float bv[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+    int bi[4] = {-1, -1, -1, -1};
+    bool ok = true;
+    for (int c = 0; c < n_chunks; ++c, ++g) {
+      const uint32_t b = g % kTmBufs;
+      if (!active) continue;
+      ok = ok && wait(&bars->tm_full[b], (g / kTmBufs) & 1, a.wait_limit, abort);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;  // the caller aborts
+      {
+        tc::tc_fence_after_sync();
+        uint32_t r[32];
+        tc::tmem_ld32(tmem + ((uint32_t)(quarter * 32) << 16) + b * 128u + (uint32_t)(mt * kChunk + half * 32), r);
+        tc::tmem_ld_wait();
+        const int l0 = c * kChunk + half * 32;  // local row of column 0
+        // first local row that counts: global row l * nc + crank >= protected_rows
+        const int l_min = ARG ? (protected_rows > crank ? (protected_rows - crank + nc - 1) / nc : 0) : 0;
+        const bool full = l0 + 32 <= n_rows && l0 >= l_min;
+        if (!ARG) {
+          if (full) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) bv[j & 3] = fmaxf(bv[j & 3], __uint_as_float(r[j]));
+          } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+              if (l0 + j < n_rows) bv[j & 3] = fmaxf(bv[j & 3], __uint_as_float(r[j]));
+          }
+        } else {
+          if (full) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+              const float x = __uint_as_float(r[j]);
+              if (x > bv[j & 3] || bi[j & 3] < 0) { bv[j & 3] = x; bi[j & 3] = l0 + j; }
+            }
+          } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+              const float x = __uint_as_float(r[j]);
+              const int l = l0 + j;
+              if (l < n_rows && l >= l_min && (x > bv[j & 3] || bi[j & 3] < 0)) { bv[j & 3] = x; bi[j & 3] = l; }
+            }
+          }
+        }
+        tc::tc_fence_before_sync();
+      }
+      __syncwarp();
+      if (lane == 0) tc::mbar_arrive(&bars->tm_empty[b]);
+    }
+    if (active) {
+      float v = bv[0];
+      int i = bi[0];
+      if (!ARG) {
+        v = fmaxf(fmaxf(bv[0], bv[1]), fmaxf(bv[2], bv[3]));
+      } else {
+#pragma unroll
+        for (int j = 1; j < 4; ++j)  // first maximum in row order: larger value, or equal value at a lower row
+          if (bi[j] >= 0 && (i < 0 || bv[j] > v || (bv[j] == v && bi[j] < i))) { v = bv[j]; i = bi[j]; }
+        if (i >= 0) i = i * nc + crank;  // local -> global row
+      }
+      part(half)[token] = make_float2(v, __int_as_float(i));
+    }
+    return wvote(ok);
+  }
+
+  // Merge the two column halves, exchange the CTA's partial results with the peers, combine.
+  // ARG = false: nov()[t] = bf16(max); true: idx()[t] = first row with the largest logit.
+  template <bool ARG>
+  __device__ __forceinline__ bool exchange() {
+    const int C = a.L.C, nc = a.nc;
+    const int parity = n_x & 1;
+    float v = -INFINITY;
+    int i = -1;
+    if (tid < C) {
+      const float2 p0 = part(0)[tid], p1 = part(1)[tid];
+      v = p0.x;
+      i = __float_as_int(p0.y);
+      const int i1 = __float_as_int(p1.y);
+      if (!ARG) {
+        v = fmaxf(p0.x, p1.x);
+      } else if (i1 >= 0 && (i < 0 || p1.x > v || (p1.x == v && i1 < i))) {
+        v = p1.x;
+        i = i1;
+      }
+    }
+    bool ok = true;
+    if (nc > 1) {
+      if (tid < C) {
+        xb(parity, crank)[tid] = make_float2(v, __int_as_float(i));
+        for (int p = 0; p < nc; ++p)
+          if (p != crank) st_peer_v2(peer_addr(&xb(parity, crank)[tid], p), v, i);
+        fence_cluster();
+      }
+      __syncwarp();
+      if (lane == 0 && warp * 32 < C)
+        for (int p = 0; p < nc; ++p)
+          if (p != crank) arrive_peer(peer_addr(&bars->xbar[parity], p));
+      ok = wait<true>(&bars->xbar[parity], (n_x >> 1) & 1, a.wait_limit, abort);
+      wsync();  // this CTA's own partial results are visible, too
+      if (ok && tid < C) {
+        v = -INFINITY;
+        i = -1;
+        for (int p = 0; p < nc; ++p) {
+          const float2 q = xb(parity, p)[tid];
+          const int qi = __float_as_int(q.y);
+          if (!ARG) v = fmaxf(v, q.x);
+          else if (qi >= 0 && (i < 0 || q.x > v || (q.x == v && qi < i))) { v = q.x; i = qi; }
+        }
+      }
+    }
+    ++n_x;
+    if (tid < C) {
+      if (!ARG) nov()[tid] = bf16_round(v);
+      else idx()[tid] = i;
+    }
+    return wvote(ok);
+  }
+
+  // LayerNorm view of one memory row (8 lanes per row): source `x`, written to the resident memory (if local) and
+  // to a pool row / the carried sums.
+  __device__ __forceinline__ void store_key_row(RowVec<HD, 8>& x, int r, int slot, int gl, bool mine) {
+    const size_t grow = (size_t)row * a.capacity + r;
+    if (mine) store_row<HD, 8>(x, a.k_sum + grow * HD, gl);
+    layer_norm_row<HD, 8>(x, ln_w, ln_b, a.L.ln_eps, gl);
+    if (mine) {
+      const int l = r / a.nc;
+      uint4 u0, u1;
+      u0.x = pack_bf16(x.x[0], x.x[1]); u0.y = pack_bf16(x.x[2], x.x[3]); u0.z = pack_bf16(x.x[4], x.x[5]); u0.w = pack_bf16(x.x[6], x.x[7]);
+      u1.x = pack_bf16(x.x[8], x.x[9]); u1.y = pack_bf16(x.x[10], x.x[11]); u1.z = pack_bf16(x.x[12], x.x[13]); u1.w = pack_bf16(x.x[14], x.x[15]);
+      *reinterpret_cast<uint4*>(smem + lay.R + piece(lay.Rcap, l, 2 * gl)) = u0;
+      *reinterpret_cast<uint4*>(smem + lay.R + piece(lay.Rcap, l, 2 * gl + 1)) = u1;
+      if (a.pool_k) {
+        bf16* dst = a.pool_k + ((size_t)row * a.pool_rows + slot) * HD + gl * 16;
+        *reinterpret_cast<uint4*>(dst) = u0;
+        *reinterpret_cast<uint4*>(dst + 8) = u1;
+      }
+    }
+  }
+  // the 16 elements of lane gl of row t of a block operand (prepared or gated keys)
+  __device__ __forceinline__ void load_block_row(RowVec<HD, 8>& x, uint32_t off, int t, int gl) {
+    const int C = a.L.C;
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      const uint4 u = *reinterpret_cast<const uint4*>(smem + off + piece(C, t, 2 * gl + h));
+      const float2 p0 = unpack_bf16(u.x), p1 = unpack_bf16(u.y), p2 = unpack_bf16(u.z), p3 = unpack_bf16(u.w);
+      x.x[h * 8 + 0] = p0.x; x.x[h * 8 + 1] = p0.y; x.x[h * 8 + 2] = p1.x; x.x[h * 8 + 3] = p1.y;
+      x.x[h * 8 + 4] = p2.x; x.x[h * 8 + 5] = p2.y; x.x[h * 8 + 6] = p3.x; x.x[h * 8 + 7] = p3.y;
+    }
+  }
+
+  // rows [S0, S0 + na) from the tokens list()[0..na): `src_off` = operand holding what is stored (prepared or gated keys)
+  __device__ __forceinline__ void append_rows(int S0, int na, uint32_t src_off) {
+    const int gl = tid & 7, grp = tid >> 3;
+    for (int base = 0; base < na; base += kWorkers / 8) {  // whole warps stay together: the LayerNorm uses group shuffles
+      const int p = base + grp;
+      const bool act = p < na;
+      const int r = S0 + (act ? p : 0);
+      const int t = list()[act ? p : 0];
+      RowVec<HD, 8> x;
+      load_block_row(x, src_off, t, gl);
+      store_key_row(x, r, pool_next + p, gl, act && (r % a.nc == crank));
+    }
+    for (int i = tid; i < na; i += kWorkers) cur()[S0 + i] = pool_next + i;
+    pool_next += na;
+  }
+
+  __device__ bool run() {
+    const int C = a.L.C, nc = a.nc;
+    int* route_row = a.route + (size_t)row * a.n_plan * C;
+    for (int u = 0; u < a.n_plan; ++u) {
+      const kvm_update_plan pl = a.plan[u];
+      const int S0 = pl.state_before, na = pl.n_append, S1 = S0 + na, nm = C - na;
+      int* ver = (a.ver_idx && pl.version_row >= 0) ? a.ver_idx + (size_t)row * a.ver_rows + pl.version_row : nullptr;
+      bool ok = true;
+      if (u == 0) {
+        // ---- initial memory: the first C tokens row for row (model/kvm_mixer.py:434-447)
+        ok = wait(&bars->full_p, 0, a.wait_limit, abort) && wait(&bars->full_g, 0, a.wait_limit, abort);
+        if (!wvote(ok)) return false;
+        if (tid < C) list()[tid] = tid;
+        wsync();
+        append_rows(0, na, (a.L.gate_initial && a.L.gate_keys) ? lay.G : lay.P);
+        if (crank == 0)
+          for (int i = tid; i < C; i += kWorkers) route_row[i] = i < na ? -(1 + i) : 0;
+        wsync();
+        if (ver)
+          for (int i = tid + crank * kWorkers; i < S1; i += kWorkers * nc) ver[i] = cur()[i];
+        n_load = 1;
+        signal_issuer();
+        continue;
+      }
+      const bool has_nov = na > 0 && nm > 0;
+      const int protected_rows = min(a.L.sink_len, S1);
+      // ---- 1. novelty of every token against the old memory; the n_append least similar tokens are appended
+      if (has_nov) {
+        if (!read_pass<false>(n_local(S0, nc, crank), 0)) return false;
+        if (!exchange<false>()) return false;
+      }
+      if (na > 0) {
+        if (!has_nov) {  // the whole block is appended
+          ok = wait(&bars->full_p, n_load & 1, a.wait_limit, abort);
+          if (!wvote(ok)) return false;
+          if (tid < C) { pos()[tid] = tid; list()[tid] = tid; idx()[tid] = -1; }
+        } else if (na == 1) {
+          // the token with the lowest novelty, lowest index among equals
+          float bv = tid < C ? nov()[tid] : INFINITY;
+          int bt = tid < C ? tid : 0x7fffffff;
+#pragma unroll
+          for (int off = 16; off > 0; off >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, bv, off);
+            const int ot = __shfl_xor_sync(0xffffffffu, bt, off);
+            if (ov < bv || (ov == bv && ot < bt)) { bv = ov; bt = ot; }
+          }
+          if (lane == 0) { bars->red_v[warp] = bv; bars->red_t[warp] = bt; }
+          wsync();
+          bv = bars->red_v[0];
+          bt = bars->red_t[0];
+          for (int w = 1; w < kWorkerWarps; ++w) {
+            const float ov = bars->red_v[w];
+            const int ot = bars->red_t[w];
+            if (ov < bv || (ov == bv && ot < bt)) { bv = ov; bt = ot; }
+          }
+          if (tid < C) pos()[tid] = tid == bt ? 0 : -1;
+          if (tid == 0) list()[0] = bt;
+        } else {
+          // stable rank of the novelty scores: the na lowest are appended, in token order
+          int f = 0;
+          if (tid < C) {
+            const float si = nov()[tid];
+            int rank = 0;
+#pragma unroll 4
+            for (int u0 = 0; u0 < C; u0 += 4) {
+              const float4 q = *reinterpret_cast<const float4*>(nov() + u0);
+              rank += (q.x < si || (q.x == si && u0 + 0 < tid)) ? 1 : 0;
+              rank += (q.y < si || (q.y == si && u0 + 1 < tid)) ? 1 : 0;
+              rank += (q.z < si || (q.z == si && u0 + 2 < tid)) ? 1 : 0;
+              rank += (q.w < si || (q.w == si && u0 + 3 < tid)) ? 1 : 0;
+            }
+            f = rank < na ? 1 : 0;
+          }
+          const unsigned bal = __ballot_sync(0xffffffffu, f != 0);
+          if (lane == 0) bars->red_t[warp] = __popc(bal);
+          wsync();
+          if (tid < C) {
+            int p = __popc(bal & ((1u << lane) - 1u));
+            for (int w = 0; w < warp; ++w) p += bars->red_t[w];
+            pos()[tid] = f ? p : -1;
+            if (f) list()[p] = tid;
+          }
+        }
+        wsync();
+        append_rows(S0, na, (a.L.gate_appends && a.L.gate_keys) ? lay.G : lay.P);
+        if (has_nov) signal_issuer();  // the appended rows are in the resident memory: the logits pass may start
+      } else if (tid < C) {
+        pos()[tid] = -1;
+      }
+      // ---- 2. merge target of every token: first argmax of the fp32 logits over the memory after the appends
+      if (nm > 0) {
+        if (!read_pass<true>(n_local(S1, nc, crank), protected_rows)) return false;
+        if (!exchange<true>()) return false;
+      }
+      // ---- 3. routing table, touched rows and their pool slots
+      int my = -1;
+      if (tid < C) {
+        const int p = pos()[tid];
+        my = p >= 0 ? -1 : idx()[tid];
+        if (crank == 0) route_row[(size_t)u * C + tid] = p >= 0 ? -(1 + S0 + p) : my;
+      }
+      for (int i = tid; i < S1; i += kWorkers) tf()[i] = 0;
+      wsync();
+      if (my >= 0) tf()[my] = 1;
+      wsync();
+      int n_touched = 0, n_touched_local = 0;
+      {
+        // compact index of every touched row among all touched rows (pool slot) and among this CTA's (accumulator lane)
+        const unsigned mine_mask = [&]() {  // lanes whose row (base + lane, base a multiple of 32) belongs to this CTA
+          unsigned m = 0;
+          for (int l = 0; l < 32; ++l)
+            if (l % nc == crank) m |= 1u << l;
+          return m;
+        }();
+        int base_all = 0, base_loc = 0;
+        for (int r0 = 0; r0 < S1; r0 += kWorkers) {
+          const int r = r0 + tid;
+          const bool t = r < S1 && tf()[r];
+          const unsigned bal = __ballot_sync(0xffffffffu, t);
+          if (lane == 0) {
+            bars->red_t[warp] = __popc(bal);
+            bars->red_t[16 + warp] = __popc(bal & mine_mask);
+          }
+          wsync();
+          int pa = base_all, pl_ = base_loc, ta = 0, tl = 0;
+          for (int w = 0; w < kWorkerWarps; ++w) {
+            const int ca = bars->red_t[w], cl = bars->red_t[16 + w];
+            if (w < warp) { pa += ca; pl_ += cl; }
+            ta += ca;
+            tl += cl;
+          }
+          if (t) {
+            const unsigned lt = (1u << lane) - 1u;
+            const int ga = pa + __popc(bal & lt);
+            gci()[r] = (short)ga;
+            if (r % nc == crank) {
+              const int ll = pl_ + __popc(bal & mine_mask & lt);
+              lci()[r] = (short)ll;
+              tloc()[ll] = (unsigned short)r;
+            }
+          }
+          base_all += ta;
+          base_loc += tl;
+          wsync();
+        }
+        n_touched = base_all;
+        n_touched_local = base_loc;
+      }
+      // ---- 4. scatter: delta of the touched rows on the tensor cores, 128 compacted rows per pass
+      const int n_pass = ceil_div(n_touched_local, 128);
+      if (tid == 0) bars->n_pass = n_pass;
+      if (n_pass == 0) {
+        signal_issuer();
+        ++n_sc;  // the issuer still commits once (it waits for the logits MMAs before the block buffers are reused)
+      }
+      for (int p = 0; p < n_pass; ++p) {
+        {  // one-hot operand [C/64][128 rows][64 tokens] (in the buffer of the prepared keys, which are dead by now)
+          uint4* o = reinterpret_cast<uint4*>(smem + lay.P);
+          for (int i = tid; i < C * 16; i += kWorkers) o[i] = make_uint4(0, 0, 0, 0);
+          wsync();
+          if (my >= 0 && my % nc == crank) {
+            const int ll = lci()[my] - p * 128;
+            if (ll >= 0 && ll < 128) {
+              const uint32_t off = (uint32_t)(tid >> 6) * (128u * 128u) + tc::sw128_offset(ll, tid & 63);
+              *reinterpret_cast<unsigned short*>(smem + lay.P + off) = 0x3F80;  // bf16 1.0
+            }
+          }
+        }
+        signal_issuer();
+        // this thread's share of the epilogue: row = accumulator lane quarter*32 + lane, 32 of its 128 elements
+        const int quarter = warp & 3, colq = warp >> 2;
+        const int ci = quarter * 32 + lane;
+        const bool act = p * 128 + ci < n_touched_local;
+        const int r = act ? tloc()[p * 128 + ci] : 0;
+        const size_t grow = (size_t)row * a.capacity + r;
+        uint4 old[4];
+        if (act) {
+#pragma unroll
+          for (int j = 0; j < 4; ++j) old[j] = *reinterpret_cast<const uint4*>(a.k_sum + grow * HD + colq * 32 + j * 8);
+        }
+        ok = wait(&bars->sc_done, n_sc & 1, a.wait_limit, abort);
+        ++n_sc;
+        if (!wvote(ok)) return false;
+        tc::tc_fence_after_sync();
+        float x[32];
+        {
+          uint32_t d[32];
+          tc::tmem_ld32(tmem + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(colq * 32), d);
+          tc::tmem_ld_wait();
+          tc::tc_fence_before_sync();
+          float s1 = 0.f;
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const uint32_t w4[4] = {old[j].x, old[j].y, old[j].z, old[j].w};
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              const float2 o2 = act ? unpack_bf16(w4[e]) : make_float2(0.f, 0.f);
+              const int c = j * 8 + e * 2;
+              x[c] = bf16_round(o2.x + bf16_round(__uint_as_float(d[c])));
+              x[c + 1] = bf16_round(o2.y + bf16_round(__uint_as_float(d[c + 1])));
+              s1 += x[c] + x[c + 1];
+            }
+          }
+          stat(0)[colq * 128 + ci] = s1;
+        }
+        if (act) {  // the carried sums
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            uint4 o;
+            o.x = pack_bf16(x[j * 8 + 0], x[j * 8 + 1]); o.y = pack_bf16(x[j * 8 + 2], x[j * 8 + 3]);
+            o.z = pack_bf16(x[j * 8 + 4], x[j * 8 + 5]); o.w = pack_bf16(x[j * 8 + 6], x[j * 8 + 7]);
+            *reinterpret_cast<uint4*>(a.k_sum + grow * HD + colq * 32 + j * 8) = o;
+          }
+        }
+        wsync();
+        const float mean = (stat(0)[ci] + stat(0)[128 + ci] + stat(0)[256 + ci] + stat(0)[384 + ci]) * (1.0f / HD);
+        float s2 = 0.f;
+#pragma unroll
+        for (int c = 0; c < 32; ++c) {
+          x[c] -= mean;
+          s2 += x[c] * x[c];
+        }
+        stat(1)[colq * 128 + ci] = s2;
+        wsync();
+        const float var = (stat(1)[ci] + stat(1)[128 + ci] + stat(1)[256 + ci] + stat(1)[384 + ci]) * (1.0f / HD);
+        const float rstd = 1.0f / sqrtf(var + a.L.ln_eps);
+        if (act) {
+          const int l = r / nc;
+          const int slot = pool_next + gci()[r];
+          bf16* pdst = a.pool_k ? a.pool_k + ((size_t)row * a.pool_rows + slot) * HD + colq * 32 : nullptr;
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            float y[8];
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+              const int dcol = colq * 32 + j * 8 + e;
+              y[e] = x[j * 8 + e] * rstd * ln_w[dcol] + ln_b[dcol];
+            }
+            uint4 o;
+            o.x = pack_bf16(y[0], y[1]); o.y = pack_bf16(y[2], y[3]); o.z = pack_bf16(y[4], y[5]); o.w = pack_bf16(y[6], y[7]);
+            *reinterpret_cast<uint4*>(smem + lay.R + piece(lay.Rcap, l, colq * 4 + j)) = o;
+            if (pdst) *reinterpret_cast<uint4*>(pdst + j * 8) = o;
+          }
+        }
+      }
+      // ---- 5. the version: every touched row moved to a fresh pool row
+      for (int i = tid; i < S1; i += kWorkers)
+        if (tf()[i]) cur()[i] = pool_next + gci()[i];
+      pool_next += n_touched;
+      wsync();
+      if (ver)
+        for (int i = tid + crank * kWorkers; i < S1; i += kWorkers * nc) ver[i] = cur()[i];
+      ++n_load;
+      signal_issuer();  // the resident memory is final for the next update
+    }
+    // final attention view of the keys, row order, for whoever continues from this memory (the decode cache)
+    {
+      const kvm_update_plan pl = a.plan[a.n_plan - 1];
+      const int S = pl.state_before + pl.n_append;
+      for (int i = tid; i < n_local(S, nc, crank) * 16; i += kWorkers) {
+        const int l = i >> 4, c = i & 15;
+        const int r = l * nc + crank;
+        *reinterpret_cast<uint4*>(a.k_attn + ((size_t)row * a.capacity + r) * HD + c * 8) =
+            *reinterpret_cast<const uint4*>(smem + lay.R + piece(lay.Rcap, l, c));
+      }
+    }
+    return true;
+  }
+};
+
+struct Maps {
+  CUtensorMap pk, gk;  // [rows * n_tok][D] bf16, boxes of 64 elements x C tokens
+};
+
+__global__ void __launch_bounds__(kThreads, 1)
+kvm_chain_tc_kernel(const __grid_constant__ Args a, const __grid_constant__ Maps maps) {
+  extern __shared__ __align__(1024) unsigned char smem[];
+  __shared__ float ln_s[2 * HD];
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int nc = a.nc;
+  const int row = blockIdx.x / nc, crank = blockIdx.x % nc;
+  const Layout lay(a.L.C, a.s_max, nc);
+  Bars* bars = reinterpret_cast<Bars*>(smem + lay.bars);
+  const bool aligned = (tc::smem_u32(smem) & 1023u) == 0;  // operand tiles need 1024-byte alignment (uniform over the grid)
+  if (!aligned) {
+    if (tid == 0) atomicExch(a.status, KVM_ERR_UNSUPPORTED);
+    return;
+  }
+  for (int i = tid; i < HD; i += kThreads) {
+    ln_s[i] = a.L.ln_w[i];
+    ln_s[HD + i] = a.L.ln_b[i];
+  }
+  {  // resident memory starts as zeros: rows past the live ones feed the MMAs, too (their scores are masked)
+    uint4* r4 = reinterpret_cast<uint4*>(smem + lay.R);
+    for (int i = tid; i < lay.Rcap * 16; i += kThreads) r4[i] = make_uint4(0, 0, 0, 0);
+    for (int i = tid; i < a.s_max; i += kThreads) reinterpret_cast<int*>(smem + lay.rowi)[i] = 0;
+  }
+  if (tid == 0) {
+    const int n_epi = (a.L.C / 128) * 8;  // worker warps that read back a chunk
+    tc::mbar_init(&bars->full_p, 1);
+    tc::mbar_init(&bars->full_g, 1);
+    for (int i = 0; i < kTmBufs; ++i) {
+      tc::mbar_init(&bars->tm_full[i], 1);
+      tc::mbar_init(&bars->tm_empty[i], n_epi);
+    }
+    tc::mbar_init(&bars->w2i, kWorkerWarps);
+    tc::mbar_init(&bars->sc_done, 1);
+    tc::mbar_init(&bars->xbar[0], max(1, (nc - 1) * (a.L.C / 32)));  // one arrival per sending warp of every peer
+    tc::mbar_init(&bars->xbar[1], max(1, (nc - 1) * (a.L.C / 32)));
+    bars->abort = 0;
+    bars->n_pass = 0;
+    tc::fence_barrier_init();
+  }
+  if (warp == kWorkerWarps) tc::tmem_alloc(&bars->tmem_base, kTmemCols);
+  tc::fence_proxy_async();
+  tc::tc_fence_before_sync();
+  __syncthreads();
+  tc::tc_fence_after_sync();
+  if (nc > 1) cluster_barrier();  // the peers' barriers exist before anybody arrives on them
+  const uint32_t tmem = bars->tmem_base;
+  volatile int* abort = &bars->abort;
+
+  bool ok = true;
+  if (warp == kWorkerWarps) {
+    if (lane == 0) {
+      Issuer is{a, smem, lay, bars, tmem, crank, row, &maps.pk, &maps.gk};
+      is.abort = abort;
+      ok = is.run();
+    }
+  } else {
+    Workers w{a, smem, lay, bars, tmem, crank, row, ln_s, ln_s + HD, abort, tid, warp, lane};
+    ok = w.run();
+  }
+  if (!ok) {
+    // report, tell everybody in the cluster, then leave through the common exit
+    atomicExch(a.status, KVM_ERR_DEVICE_TIMEOUT);
+    *abort = 1;
+    if (nc > 1 && lane == 0)
+      for (int p = 0; p < nc; ++p)
+        if (p != crank) st_peer_b32(peer_addr(&bars->abort, p), 1);
+  }
+  __syncwarp();
+  __syncthreads();
+  if (*abort) {
+    // copies and MMAs of this CTA may still be in flight: they complete on their own within microseconds
+    for (int k2 = 0; k2 < 64; ++k2) __nanosleep(1000);
+  }
+  tc::tc_fence_before_sync();
+  __syncthreads();
+  if (warp == kWorkerWarps) tc::tmem_dealloc(tmem, kTmemCols);
+  if (nc > 1) cluster_barrier();  // nobody leaves while a peer may still write into its shared memory
+}
+
+// ------------------------------------------------------------------------------------------------ value side
+constexpr int kVpWarps = 32;
+
+// One warp per memory row.  route: [rows][n_plan][C] (>= 0: merged into that row, -(1+r): appended as row r).
+__global__ void __launch_bounds__(kVpWarps * 32)
+kvm_vpass_kernel(LayerDev L, Tensor4 v, Tensor4 gate, const kvm_update_plan* __restrict__ plan, int n_plan,
+                 const int* __restrict__ route, MemoryDev mem, bf16* __restrict__ pool_v, long long pool_rows,
+                 const int* __restrict__ ver_idx, long long ver_rows, int s_final, int tile_updates) {
+  extern __shared__ __align__(16) unsigned char vsm[];
+  short* rt = reinterpret_cast<short*>(vsm);  // [tile_updates][C] routing decisions of the current tile
+  const int C = L.C, EPL = C / 32;            // EPL tokens per lane: 4 or 8
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int row = blockIdx.y;
+  const int b = row / L.Hkv, h = row % L.Hkv;
+  const int r = blockIdx.x * kVpWarps + warp;  // this warp's memory row
+  const bool live = r < s_final;
+  const int* route_row = route + (size_t)row * n_plan * C;
+  float x[4] = {0.f, 0.f, 0.f, 0.f};           // carried value sum of the row (bf16 values), elements 4*lane..
+  float vl = 0.f;
+  bool born = false;
+
+  auto load_v = [&](long long t, float (&o)[4], float& g) {
+    const uint2 u = *reinterpret_cast<const uint2*>(v.row(b, h, t) + lane * 4);
+    const float2 p0 = unpack_bf16(u.x), p1 = unpack_bf16(u.y);
+    o[0] = p0.x; o[1] = p0.y; o[2] = p1.x; o[3] = p1.y;
+    g = __bfloat162float(*gate.row(b, h, t));
+  };
+
+  for (int u0 = 0; u0 < n_plan; u0 += tile_updates) {
+    const int nu = min(tile_updates, n_plan - u0);
+    __syncthreads();
+    for (int i = tid; i < nu * C; i += kVpWarps * 32) rt[i] = (short)route_row[(size_t)u0 * C + i];
+    __syncthreads();
+    if (!live) continue;
+    for (int uu = 0; uu < nu; ++uu) {
+      const int u = u0 + uu;
+      // which of this lane's tokens were appended as / merged into row r
+      unsigned m_app = 0, m_mrg = 0;
+      for (int j = 0; j < EPL; ++j) {
+        const int e = rt[uu * C + lane * EPL + j];
+        if (e == r && u > 0) m_mrg |= 1u << j;
+        if (e == -(1 + r)) m_app |= 1u << j;
+      }
+      unsigned any_app = __ballot_sync(0xffffffffu, m_app != 0);
+      unsigned any_mrg = __ballot_sync(0xffffffffu, m_mrg != 0);
+      if (!any_app && !any_mrg) continue;
+      if (any_app) {  // the row is born from one token: value (gated where the layer says so), magnitude
+        const int src = __ffs(any_app) - 1;
+        const unsigned mm = __shfl_sync(0xffffffffu, m_app, src);
+        const long long t = (long long)u * C + src * EPL + (__ffs(mm) - 1);
+        float g;
+        load_v(t, x, g);
+        const bool gated = u == 0 ? (L.gate_initial != 0) : (L.gate_appends != 0 && L.gate_values != 0);
+        float n2 = 0.f;
+        if (u > 0 && gated) {
+#pragma unroll
+          for (int i = 0; i < 4; ++i) x[i] = bf16_round(x[i] * g);
+        }
+#pragma unroll
+        for (int i = 0; i < 4; ++i) n2 += x[i] * x[i];
+        vl = sqrtf(warp_sum(n2));  // the initial rows keep the magnitude of the ungated value
+        if (u == 0 && gated) {
+#pragma unroll
+          for (int i = 0; i < 4; ++i) x[i] = bf16_round(x[i] * g);
+        }
+        born = true;
+      }
+      if (any_mrg) {  // gated values routed to the row, summed in token order
+        float acc[4] = {0.f, 0.f, 0.f, 0.f};
+        while (any_mrg) {
+          const int src = __ffs(any_mrg) - 1;
+          any_mrg &= any_mrg - 1;
+          unsigned mm = __shfl_sync(0xffffffffu, m_mrg, src);
+          while (mm) {
+            const int j = __ffs(mm) - 1;
+            mm &= mm - 1;
+            float o[4], g;
+            load_v((long long)u * C + src * EPL + j, o, g);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) acc[i] += L.gate_values ? bf16_round(o[i] * g) : o[i];
+          }
+        }
+#pragma unroll
+        for (int i = 0; i < 4; ++i) x[i] = bf16_round(x[i] + bf16_round(acc[i]));
+      }
+      // the value view of the row in this version
+      const kvm_update_plan pl = plan[u];
+      if (born && pool_v && ver_idx && pl.version_row >= 0) {
+        const int slot = ver_idx[(size_t)row * ver_rows + pl.version_row + r];
+        float n2 = 0.f;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) n2 += x[i] * x[i];
+        const float nrm = fmaxf(sqrtf(warp_sum(n2)), 1e-12f);
+        float y[4] = {x[0], x[1], x[2], x[3]};
+        divide_by(y, nrm);
+        uint2 o;
+        o.x = pack_bf16(y[0] * vl, y[1] * vl);
+        o.y = pack_bf16(y[2] * vl, y[3] * vl);
+        *reinterpret_cast<uint2*>(pool_v + ((size_t)row * pool_rows + slot) * HD + lane * 4) = o;
+      }
+    }
+  }
+  if (live && born) {  // the carried state and its final view
+    const size_t off = ((size_t)row * mem.capacity + r) * HD + lane * 4;
+    uint2 s;
+    s.x = pack_bf16(x[0], x[1]);
+    s.y = pack_bf16(x[2], x[3]);
+    *reinterpret_cast<uint2*>(mem.v_sum + off) = s;
+    if (lane == 0) mem.vlen[(size_t)row * mem.capacity + r] = vl;
+    float n2 = 0.f;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) n2 += x[i] * x[i];
+    const float nrm = fmaxf(sqrtf(warp_sum(n2)), 1e-12f);
+    float y[4] = {x[0], x[1], x[2], x[3]};
+    divide_by(y, nrm);
+    uint2 o;
+    o.x = pack_bf16(y[0] * vl, y[1] * vl);
+    o.y = pack_bf16(y[2] * vl, y[3] * vl);
+    *reinterpret_cast<uint2*>(mem.v_attn + off) = o;
+  }
+}
+
+}  // namespace chain
+
+// ------------------------------------------------------------------------------------------------ host side
+// Cluster size for `rows` kv rows: the largest size (<= 8) that fits shared memory and whose clusters are all
+// resident at once; if none is, the smallest that fits (the rows then run in waves).  0: the shape does not fit.
+static int chain_tc_cluster_size(int C, int s_max, int rows) {
+  using namespace chain;
+  static std::mutex mu;
+  static int fit[64][4][2];      // [device][log2 nc][C == 256]: co-resident clusters, 0 = not asked yet
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 0;
+  int smallest = 0, best = 0;
+  for (int lg = 0; lg <= 3; ++lg) {
+    const int nc = 1 << lg;
+    const Layout lay(C, s_max, nc);
+    if (lay.total > (uint32_t)kMaxSmem) continue;
+    if (!smallest) smallest = nc;
+    int n_clusters;
+    {
+      std::lock_guard<std::mutex> lock(mu);
+      n_clusters = fit[dev][lg][C == 256];
+    }
+    if (n_clusters == 0) {
+      // the answer depends on the shared-memory size only through "one CTA per SM": ask with the largest size
+      cudaLaunchConfig_t cfg = {};
+      cfg.blockDim = dim3(kThreads);
+      cfg.gridDim = dim3(nc * 64);
+      cfg.dynamicSmemBytes = 200 * 1024;
+      cudaLaunchAttribute attr[1];
+      attr[0].id = cudaLaunchAttributeClusterDimension;
+      attr[0].val.clusterDim.x = nc;
+      attr[0].val.clusterDim.y = 1;
+      attr[0].val.clusterDim.z = 1;
+      cfg.attrs = attr;
+      cfg.numAttrs = 1;
+      if (cudaFuncSetAttribute(kvm_chain_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxSmem) != cudaSuccess ||
+          cudaOccupancyMaxActiveClusters(&n_clusters, kvm_chain_tc_kernel, &cfg) != cudaSuccess) {
+        (void)cudaGetLastError();
+        n_clusters = -1;
+      }
+      if (n_clusters == 0) n_clusters = -1;
+      std::lock_guard<std::mutex> lock(mu);
+      fit[dev][lg][C == 256] = n_clusters;
+    }
+    if (n_clusters >= rows) best = nc;
+  }
+  return best ? best : smallest;
+}
+
+bool chain_tc_supported(int D, const LayerDev& L, int n_plan, int s_max, int rows) {
+  if (D != 128 || (L.C != 128 && L.C != 256) || n_plan < 2 || s_max >= 32000) return false;
+  if (L.gate_initial && !L.gate_keys) return false;  // the pre-pass only writes gated keys for layers that gate keys
+  return chain_tc_cluster_size(L.C, s_max, rows) > 0;
+}
+
+// The chain for one batch: routing + key side, then the value side.  pk_all / gk_all: [rows][n_plan*C][D] from the
+// pre-pass; route: [rows][n_plan][C].
+cudaError_t launch_chain_tc(const LayerDev& L, int batch, Tensor4 v, Tensor4 gate, const kvm_update_plan* plan_dev, int n_plan,
+                            int s_max, MemoryDev mem, bf16* pool_k, bf16* pool_v, long long pool_rows, int* ver_idx,
+                            long long ver_rows, const bf16* pk_all, const bf16* gk_all, int* route, int* status,
+                            uint32_t wait_limit, uint32_t test_flags, cudaStream_t stream) {
+  using namespace chain;
+  const int rows = batch * L.Hkv, C = L.C;
+  const int nc = chain_tc_cluster_size(C, s_max, rows);
+  if (nc <= 0) return cudaErrorInvalidConfiguration;
+  const Layout lay(C, s_max, nc);
+  const long long n_tok = (long long)n_plan * C;
+  Maps maps;
+  {
+    const cuuint64_t dims[2] = {(cuuint64_t)HD, (cuuint64_t)((long long)rows * n_tok)};
+    const cuuint64_t strides[1] = {(cuuint64_t)HD * 2};
+    const cuuint32_t box[2] = {64, (cuuint32_t)C};
+    if (!encode_bf16_map(&maps.pk, pk_all, 2, dims, strides, box) || !encode_bf16_map(&maps.gk, gk_all, 2, dims, strides, box))
+      return cudaErrorInvalidValue;
+  }
+  Args a;
+  a.L = L; a.plan = plan_dev; a.n_plan = n_plan; a.nc = nc; a.s_max = s_max; a.n_tok = n_tok;
+  a.k_sum = mem.k_sum; a.k_attn = mem.k_attn; a.capacity = mem.capacity;
+  a.pool_k = ver_idx ? pool_k : nullptr; a.pool_rows = pool_rows; a.ver_idx = ver_idx; a.ver_rows = ver_rows;
+  a.route = route; a.status = status; a.wait_limit = wait_limit; a.test_flags = test_flags;
+  cudaError_t e = cudaFuncSetAttribute(kvm_chain_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxSmem);
+  if (e != cudaSuccess) return e;
+  cudaLaunchConfig_t cfg = {};
+  cfg.blockDim = dim3(kThreads);
+  cfg.gridDim = dim3(rows * nc);
+  cfg.dynamicSmemBytes = lay.total;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = nc;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  e = cudaLaunchKernelEx(&cfg, kvm_chain_tc_kernel, a, maps);
+  if (e != cudaSuccess) return e;
+  // value side: one warp per memory row, the routing decisions of as many updates as fit 64 KB per tile
+  const int tile_updates = std::max(1, std::min(n_plan, (64 * 1024) / (C * 2)));
+  const size_t vsmem = (size_t)tile_updates * C * 2;
+  e = cudaFuncSetAttribute(kvm_vpass_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)vsmem);
+  if (e != cudaSuccess) return e;
+  dim3 vgrid((unsigned)ceil_div(s_max, kVpWarps), rows);
+  kvm_vpass_kernel<<<vgrid, kVpWarps * 32, vsmem, stream>>>(L, v, gate, plan_dev, n_plan, route, mem, ver_idx ? pool_v : nullptr,
+                                                            pool_rows, ver_idx, ver_rows, s_max, tile_updates);
+  return cudaGetLastError();
+}
+
+}  // namespace kvm

@@ -12,10 +12,12 @@ namespace kvm {
 // ------------------------------------------------------------------------------------ prepared keys
 // Parallel pre-pass: prepared key (rotary dims zeroed, LayerNorm, bf16) of every token an update will
 // consume, written as [kv row][token][D].  Takes the LayerNorm off the sequential chain.
+// With `gk_all` it also writes the gated key bf16(pk * gate) of every token (a copy of pk for layers that do not
+// gate keys): the tensor-core chain takes both operands of its routing passes from memory.
 constexpr int kPrepUnroll = 4;  // tokens per lane group: their loads are issued before the first LayerNorm
 template <int D>
 __global__ void __launch_bounds__(256)
-kvm_prepare_keys_kernel(LayerDev L, Tensor4 k, bf16* __restrict__ pk_all, long long n_tok) {
+kvm_prepare_keys_kernel(LayerDev L, Tensor4 k, Tensor4 gate, bf16* __restrict__ pk_all, bf16* __restrict__ gk_all, long long n_tok) {
   constexpr int GL = 8, TPB = 256 / GL;
   const int gl = threadIdx.x % GL;
   const long long base = (long long)blockIdx.x * (TPB * kPrepUnroll) + threadIdx.x / GL;
@@ -34,7 +36,17 @@ kvm_prepare_keys_kernel(LayerDev L, Tensor4 k, bf16* __restrict__ pk_all, long l
     for (int i = 0; i < D / GL; ++i)
       if (gl * (D / GL) + i < L.rope_dim) r[u].x[i] = 0.f;
     layer_norm_row<D, GL>(r[u], L.ln_w, L.ln_b, L.ln_eps, gl);
-    if (tkn < n_tok) store_row<D, GL>(r[u], pk_all + ((size_t)row * n_tok + tkn) * D, gl);
+    if (tkn < n_tok) {
+      store_row<D, GL>(r[u], pk_all + ((size_t)row * n_tok + tkn) * D, gl);
+      if (gk_all) {
+        if (L.gate_keys) {
+          const float g = __bfloat162float(*gate.row(b, h, tkn));
+#pragma unroll
+          for (int i = 0; i < D / GL; ++i) r[u].x[i] = bf16_round(r[u].x[i] * g);
+        }
+        store_row<D, GL>(r[u], gk_all + ((size_t)row * n_tok + tkn) * D, gl);
+      }
+    }
   }
 }
 
@@ -418,6 +430,11 @@ kvm_attn_prefill_kernel(LayerDev L, long long T, Tensor4 q, Tensor4 k, Tensor4 v
 }
 
 // ------------------------------------------------------------------------------------- host side
+bool chain_tc_supported(int D, const LayerDev& L, int n_plan, int s_max, int rows);
+cudaError_t launch_chain_tc(const LayerDev& L, int batch, Tensor4 v, Tensor4 gate, const kvm_update_plan* plan_dev, int n_plan,
+                            int s_max, MemoryDev mem, bf16* pool_k, bf16* pool_v, long long pool_rows, int* ver_idx,
+                            long long ver_rows, const bf16* pk_all, const bf16* gk_all, int* route, int* status,
+                            uint32_t wait_limit, uint32_t test_flags, cudaStream_t stream);
 cudaError_t launch_attn_tc(const LayerDev& L, int batch, long long T, Tensor4 q, Tensor4 k, Tensor4 v,
                            const kvm_update_plan* plan_dev, const bf16* pool_k, const bf16* pool_v, long long pool_rows,
                            const int* ver_idx, long long ver_rows, bf16* out, int* status, cudaStream_t stream);
@@ -426,22 +443,31 @@ template <int D>
 static cudaError_t launch_prefill(const LayerDev& L, int batch, long long T, Tensor4 q, Tensor4 k, Tensor4 v, Tensor4 gate,
                                   const kvm_update_plan* plan_dev, int n_plan, long long ver_rows, MemoryDev mem,
                                   bf16* out, int* route, bf16* pool_k, bf16* pool_v, long long pool_rows, int* ver_idx,
-                                  bf16* pk_scr, bf16* pk_all, int* status, unsigned phases, cudaStream_t stream) {
+                                  bf16* pk_scr, bf16* pk_all, bf16* gk_all, int* route_ws, int s_final, int* status,
+                                  unsigned phases, cudaStream_t stream) {
   constexpr int NT = 512;
   const int rows = batch * L.Hkv;
   const int n_qblocks = (int)((T + L.C - 1) / L.C);
   const bool versions = n_qblocks > L.W && ver_rows > 0;
   cudaError_t e;
-  if (phases & KVM_PREFILL_CHAIN) {
+  // head_dim 128 and blocks of 128 / 256 tokens: the chain with the resident memory on the tensor cores
+  const bool tc_chain = !(phases & KVM_PREFILL_LEGACY_CHAIN) && chain_tc_supported(D, L, n_plan, s_final, rows);
+  if ((phases & KVM_PREFILL_CHAIN) && n_plan > 1) {
+    const long long n_tok = (long long)n_plan * L.C;
+    dim3 pgrid((unsigned)((n_tok + 32 * kPrepUnroll - 1) / (32 * kPrepUnroll)), rows);
+    kvm_prepare_keys_kernel<D><<<pgrid, 256, 0, stream>>>(L, k, gate, pk_all, tc_chain ? gk_all : nullptr, n_tok);
+    e = cudaGetLastError();
+    if (e != cudaSuccess) return e;
+  }
+  if ((phases & KVM_PREFILL_CHAIN) && tc_chain) {
+    const bool test = (phases & KVM_PREFILL_TEST_WITHHOLD_ARRIVAL) != 0;
+    e = launch_chain_tc(L, batch, v, gate, plan_dev, n_plan, s_final, mem, pool_k, pool_v, pool_rows, versions ? ver_idx : nullptr,
+                        ver_rows, pk_all, gk_all, route ? route : route_ws, status, test ? (1u << 11) : tc::kSpinLimit,
+                        test ? 1u : 0u, stream);
+    if (e != cudaSuccess) return e;
+  } else if (phases & KVM_PREFILL_CHAIN) {
     const bool sb = update_block_fits_smem<D>(L.C, mem.capacity);
     const size_t smem_u = UpdateSmem<D>::bytes(L.C, mem.capacity, sb);
-    if (n_plan > 1) {
-      const long long n_tok = (long long)n_plan * L.C;
-      dim3 pgrid((unsigned)((n_tok + 32 * kPrepUnroll - 1) / (32 * kPrepUnroll)), rows);
-      kvm_prepare_keys_kernel<D><<<pgrid, 256, 0, stream>>>(L, k, pk_all, n_tok);
-      e = cudaGetLastError();
-      if (e != cudaSuccess) return e;
-    }
     auto kern = sb ? kvm_chain_kernel<D, NT, true> : kvm_chain_kernel<D, NT, false>;
     e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_u);
     if (e != cudaSuccess) return e;
@@ -461,26 +487,19 @@ static cudaError_t launch_prefill(const LayerDev& L, int batch, long long T, Ten
     cfg.numAttrs = 1;
     int nc = 1;
     if (n_plan > 1) {
-      static int fit_rows[4] = {-1, -1, -1, -1};  // co-resident clusters of 1, 2, 4, 8 CTAs (cached occupancy queries)
-      static size_t fit_smem = 0;
-      if (fit_smem != smem_u) {
-        fit_rows[0] = fit_rows[1] = fit_rows[2] = fit_rows[3] = -1;
-        fit_smem = smem_u;
-      }
-      for (int lg = 3; lg >= 1; --lg) {
+      // co-resident clusters of 2 and 4 CTAs (the answer depends on the kernel and its shared memory; asked per call:
+      // this path serves the less common shapes)
+      for (int lg = 2; lg >= 1; --lg) {
         const int c = 1 << lg;
         if (c > kMaxCluster) continue;
-        if (fit_rows[lg] < 0) {
-          int n_clusters = 0;
-          cfg.gridDim = dim3(c * 64);
-          attr[0].val.clusterDim.x = c;
-          if (cudaOccupancyMaxActiveClusters(&n_clusters, kern, &cfg) != cudaSuccess) {
-            (void)cudaGetLastError();
-            n_clusters = 0;
-          }
-          fit_rows[lg] = n_clusters;
+        int n_clusters = 0;
+        cfg.gridDim = dim3(c * 64);
+        attr[0].val.clusterDim.x = c;
+        if (cudaOccupancyMaxActiveClusters(&n_clusters, kern, &cfg) != cudaSuccess) {
+          (void)cudaGetLastError();
+          n_clusters = 0;
         }
-        if (fit_rows[lg] >= rows) {
+        if (n_clusters >= rows) {
           nc = c;
           break;
         }
@@ -514,11 +533,12 @@ static cudaError_t launch_prefill(const LayerDev& L, int batch, long long T, Ten
 cudaError_t prefill_dispatch(int D, const LayerDev& L, int batch, long long T, Tensor4 q, Tensor4 k, Tensor4 v,
                              Tensor4 gate, const kvm_update_plan* plan_dev, int n_plan, long long ver_rows,
                              MemoryDev mem, bf16* out, int* route, bf16* pool_k, bf16* pool_v, long long pool_rows,
-                             int* ver_idx, bf16* pk_scr, bf16* pk_all, int* status, unsigned phases, cudaStream_t stream) {
+                             int* ver_idx, bf16* pk_scr, bf16* pk_all, bf16* gk_all, int* route_ws, int s_final, int* status,
+                             unsigned phases, cudaStream_t stream) {
   switch (D) {
-    case 32: return launch_prefill<32>(L, batch, T, q, k, v, gate, plan_dev, n_plan, ver_rows, mem, out, route, pool_k, pool_v, pool_rows, ver_idx, pk_scr, pk_all, status, phases, stream);
-    case 64: return launch_prefill<64>(L, batch, T, q, k, v, gate, plan_dev, n_plan, ver_rows, mem, out, route, pool_k, pool_v, pool_rows, ver_idx, pk_scr, pk_all, status, phases, stream);
-    case 128: return launch_prefill<128>(L, batch, T, q, k, v, gate, plan_dev, n_plan, ver_rows, mem, out, route, pool_k, pool_v, pool_rows, ver_idx, pk_scr, pk_all, status, phases, stream);
+    case 32: return launch_prefill<32>(L, batch, T, q, k, v, gate, plan_dev, n_plan, ver_rows, mem, out, route, pool_k, pool_v, pool_rows, ver_idx, pk_scr, pk_all, gk_all, route_ws, s_final, status, phases, stream);
+    case 64: return launch_prefill<64>(L, batch, T, q, k, v, gate, plan_dev, n_plan, ver_rows, mem, out, route, pool_k, pool_v, pool_rows, ver_idx, pk_scr, pk_all, gk_all, route_ws, s_final, status, phases, stream);
+    case 128: return launch_prefill<128>(L, batch, T, q, k, v, gate, plan_dev, n_plan, ver_rows, mem, out, route, pool_k, pool_v, pool_rows, ver_idx, pk_scr, pk_all, gk_all, route_ws, s_final, status, phases, stream);
   }
   return cudaErrorInvalidValue;
 }
