@@ -43,8 +43,8 @@ constexpr int HD = 128;
 constexpr int kWorkerWarps = 16;
 constexpr int kWorkers = kWorkerWarps * 32;   // threads that do everything but issuing copies and MMAs
 constexpr int kThreads = kWorkers + 32;       // + the issuing warp (one elected thread)
-constexpr int kChunk = 64;                    // memory rows per MMA and per tensor-memory chunk
-constexpr int kTmBufs = 4;                    // chunks in flight: 4 x (2 token tiles x 64 columns) = 512 columns
+constexpr int kChunk = 256;                   // memory rows per MMA instruction and per tensor-memory chunk (the N limit)
+constexpr int kRowPad = 64;                   // granularity of the resident rows per CTA
 constexpr uint32_t kTmemCols = 512;
 constexpr int kMaxSmem = 225 * 1024;           // dynamic part; the kernel also holds 1 KB of static shared memory
 
@@ -55,7 +55,7 @@ struct Layout {
   int Rcap;  // resident memory rows per CTA (multiple of 64)
   uint32_t R, P, G, xbuf, part, tok, rowi, tloc, stat, bars, total;
   __host__ __device__ Layout(int C, int s_max, int nc) {
-    Rcap = ceil_div(ceil_div(s_max, nc), kChunk) * kChunk;
+    Rcap = ceil_div(ceil_div(s_max, nc), kRowPad) * kRowPad;
     uint32_t off = 0;
     R = off;    off += 2u * Rcap * 128u;                 // [2 halves of D][Rcap][64] bf16, 128-byte swizzle
     P = off;    off += (uint32_t)C * 256u;               // prepared keys of the block; later the one-hot operand
@@ -65,7 +65,7 @@ struct Layout {
     tok = off;  off += 4u * C * 4u;                      // nov[C] f32, idx[C], pos[C], list[C]
     const uint32_t sp = (uint32_t)((s_max + 63) & ~31);  // padded row count: every region below stays 16-byte aligned
     rowi = off; off += sp * 8u;                          // cur[sp] i32, gci[sp] i16, lci[sp] i16
-    tloc = off; off += 2u * C * 2u + 2u * sp;            // touched_local[C] u16, spare, tf[sp] u8
+    tloc = off; off += 2u * C * 2u + 2u * sp;            // touched_local[C] u16, spare, stamps[sp] u16 (update that last touched the row)
     stat = off; off += 2u * 4u * 128u * 4u;              // LayerNorm partial sums of the scatter epilogue
     bars = off; off += 512u;
     total = (off + 15u) & ~15u;
@@ -74,8 +74,8 @@ struct Layout {
 
 struct Bars {
   uint64_t full_p, full_g;              // TMA arrivals of the block's prepared / gated keys
-  uint64_t tm_full[kTmBufs];            // MMAs of a chunk complete
-  uint64_t tm_empty[kTmBufs];           // the chunk has been read back
+  uint64_t tm_full[2];                  // MMAs of a chunk complete, per tile of 128 tokens
+  uint64_t tm_empty[2];                 // ... and read back
   uint64_t w2i;                         // workers -> issuer: shared-memory operands are ready
   uint64_t sc_done;                     // scatter MMAs complete
   uint64_t xbar[2];                     // arrivals of the peers' partial results (two in flight)
@@ -139,9 +139,9 @@ template <bool CLUSTER = false>
 __device__ __forceinline__ bool wait(uint64_t* bar, uint32_t parity, uint32_t limit, volatile int* abort) {
   for (uint32_t i = 0; i < limit; ++i) {
     if (CLUSTER ? try_wait_cluster(bar, parity) : tc::mbar_try_wait(bar, parity)) return true;
-    if (i >= 8) {
+    if ((i & 63) == 63) {  // try_wait suspends the thread for a while by itself; look at the abort flag now and then
       if (*abort) return false;
-      __nanosleep(i < 64 ? 20 : 100);
+      if (i >= 4096) __nanosleep(100);
     }
   }
   return false;
@@ -151,15 +151,15 @@ __device__ __forceinline__ uint32_t peer_addr(const void* local, int peer) {
   asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(peer));
   return r;
 }
-__device__ __forceinline__ void st_peer_v2(uint32_t addr, float v, int i) {
-  asm volatile("st.shared::cluster.v2.b32 [%0], {%1, %2};" ::"r"(addr), "r"(__float_as_uint(v)), "r"(i) : "memory");
+// 8-byte store into a peer's shared memory that completes 8 bytes of the transaction count of the peer's barrier:
+// the data is visible to whoever has waited for that barrier phase (no fence, no separate arrival)
+__device__ __forceinline__ void st_async_v2(uint32_t addr, float v, int i, uint32_t bar_addr) {
+  asm volatile("st.async.weak.shared::cluster.mbarrier::complete_tx::bytes.v2.b32 [%0], {%1, %2}, [%3];" ::"r"(addr),
+               "r"(__float_as_uint(v)), "r"(i), "r"(bar_addr)
+               : "memory");
 }
 __device__ __forceinline__ void st_peer_b32(uint32_t addr, int v) {
   asm volatile("st.shared::cluster.b32 [%0], %1;" ::"r"(addr), "r"(v) : "memory");
-}
-__device__ __forceinline__ void fence_cluster() { asm volatile("fence.acq_rel.cluster;" ::: "memory"); }
-__device__ __forceinline__ void arrive_peer(uint32_t bar_addr) {
-  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(bar_addr) : "memory");
 }
 __device__ __forceinline__ void cluster_barrier() {
   asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
@@ -194,6 +194,16 @@ struct Issuer {
     tc::tc_fence_after_sync();
     return ok;
   }
+  // warm L2 with a later block (the copy into shared memory then does not wait for DRAM)
+  __device__ __forceinline__ void prefetch_block(int u) {
+    const int C = a.L.C;
+    const int y = (int)((long long)row * a.n_tok + (long long)u * C);
+#pragma unroll
+    for (int x = 0; x < 128; x += 64) {
+      asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global.tile [%0, {%1, %2}];" ::"l"(map_pk), "r"(x), "r"(y) : "memory");
+      asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global.tile [%0, {%1, %2}];" ::"l"(map_gk), "r"(x), "r"(y) : "memory");
+    }
+  }
   __device__ __forceinline__ void load_block(int u, bool want_p) {
     const int C = a.L.C;
     const int y = (int)((long long)row * a.n_tok + (long long)u * C);
@@ -206,27 +216,30 @@ struct Issuer {
     tc::tma_load_2d(smem + lay.G, map_gk, 0, y, &bars->full_g);
     tc::tma_load_2d(smem + lay.G + C * 128, map_gk, 64, y, &bars->full_g);
   }
-  // S[tokens x 64 rows] = A[tokens x D] * R[rows l0.. x D]^T for every chunk of the first n_rows local rows
+  // S[tokens x rows] = A[tokens x D] * R[rows x D]^T over the first n_rows local rows, up to 256 rows per chunk: one
+  // MMA per token tile and k-step covers the whole chunk (issuing an MMA costs about as much as executing a small
+  // one), the accumulators of token tile m live in tensor-memory columns [256 m, 256 m + N).  One commit per token
+  // tile, so that the first tile is read back while the second is computed.
   __device__ __forceinline__ bool pass(uint32_t a_off, int n_rows, bool withhold_first_commit) {
     const int C = a.L.C, n_mt = C / 128;
-    constexpr uint32_t idesc = tc::make_idesc(128, kChunk, 0, 0);
     const uint32_t a_addr = tc::smem_u32(smem + a_off), r_addr = tc::smem_u32(smem + lay.R);
     const int n_chunks = ceil_div(n_rows, kChunk);
     for (int c = 0; c < n_chunks; ++c, ++g) {
-      const uint32_t b = g % kTmBufs;
-      if (g >= kTmBufs && !wait(&bars->tm_empty[b], ((g / kTmBufs) - 1) & 1, a.wait_limit, abort)) return false;
-      tc::tc_fence_after_sync();
+      const int n = min(kChunk, n_rows - c * kChunk);
+      const uint32_t idesc = tc::make_idesc(128, (n + 15) & ~15, 0, 0);
       const uint64_t db0 = tc::make_desc(r_addr + (uint32_t)(c * kChunk * 128), 16, 1024);
       for (int m = 0; m < n_mt; ++m) {
+        if (g >= 1 && !wait(&bars->tm_empty[m], (g - 1) & 1, a.wait_limit, abort)) return false;
+        tc::tc_fence_after_sync();
         const uint64_t da0 = tc::make_desc(a_addr + (uint32_t)(m * 128 * 128), 16, 1024);
 #pragma unroll
         for (int ks = 0; ks < HD / 16; ++ks) {
           const uint64_t da = da0 + (uint64_t)(((uint32_t)(ks >> 2) * (uint32_t)(C * 128) + (uint32_t)(ks & 3) * 32u) >> 4);
           const uint64_t db = db0 + (uint64_t)(((uint32_t)(ks >> 2) * (uint32_t)(lay.Rcap * 128) + (uint32_t)(ks & 3) * 32u) >> 4);
-          tc::mma_ss(tmem + b * 128u + (uint32_t)(m * kChunk), da, db, idesc, ks > 0);
+          tc::mma_ss(tmem + (uint32_t)(m * kChunk), da, db, idesc, ks > 0);
         }
+        if (!(withhold_first_commit && c == 0 && m == 0)) tc::mma_commit_own_cta(&bars->tm_full[m]);
       }
-      if (!(withhold_first_commit && c == 0)) tc::mma_commit_own_cta(&bars->tm_full[b]);
     }
     return true;
   }
@@ -256,9 +269,11 @@ struct Issuer {
         if (!wait_workers()) return false;
         n_load = 1;
         if (a.n_plan > 1) load_block(1, true);
+        if (a.n_plan > 2 && crank == 0) prefetch_block(2);
         continue;
       }
       const bool has_nov = na > 0 && nm > 0;
+      if (u + 2 < a.n_plan && crank == (u & (nc - 1))) prefetch_block(u + 2);  // one CTA of the cluster asks, all profit
       if (has_nov) {
         if (!wait(&bars->full_p, n_load & 1, a.wait_limit, abort)) return false;
         if (!pass(lay.P, n_local(S0, nc, crank), false)) return false;
@@ -305,6 +320,8 @@ struct Workers {
   int tid, warp, lane;
   uint32_t g = 0, n_sc = 0, n_x = 0, n_load = 0;
   int pool_next = 0;
+  unsigned mine_mask = 0;  // lanes whose row (a multiple of 32 + lane) belongs to this CTA
+  bool pend_ok = true;     // result of a wait that the next vote still has to take into account
 
   __device__ __forceinline__ float* nov() const { return reinterpret_cast<float*>(smem + lay.tok); }
   __device__ __forceinline__ int* idx() const { return reinterpret_cast<int*>(smem + lay.tok) + a.L.C; }
@@ -315,7 +332,7 @@ struct Workers {
   __device__ __forceinline__ short* gci() const { return reinterpret_cast<short*>(smem + lay.rowi + (uint32_t)padded_rows() * 4u); }
   __device__ __forceinline__ short* lci() const { return gci() + padded_rows(); }
   __device__ __forceinline__ unsigned short* tloc() const { return reinterpret_cast<unsigned short*>(smem + lay.tloc); }
-  __device__ __forceinline__ unsigned char* tf() const { return smem + lay.tloc + 2u * a.L.C * 2u; }
+  __device__ __forceinline__ unsigned short* tf() const { return reinterpret_cast<unsigned short*>(smem + lay.tloc + 2u * a.L.C * 2u); }
   __device__ __forceinline__ float2* part(int half) const { return reinterpret_cast<float2*>(smem + lay.part) + half * a.L.C; }
   __device__ __forceinline__ float2* xb(int parity, int src) const { return reinterpret_cast<float2*>(smem + lay.xbuf) + (size_t)(parity * a.nc + src) * a.L.C; }
   __device__ __forceinline__ float* stat(int which) const { return reinterpret_cast<float*>(smem + lay.stat) + which * 4 * 128; }
@@ -328,7 +345,8 @@ struct Workers {
   }
 
   // Read back the chunks of a routing pass.  ARG = false: running maximum (novelty); true: running first-argmax of
-  // rows >= `protected_rows`.  Leaves per token the CTA's partial result in part(half)[token].
+  // rows >= `protected_rows`.  Warp w reads token tile (w / 4) % 2, lanes 32 (w % 4).., and one half of the chunk's
+  // 32-column groups; leaves per token the CTA's partial result in part(half)[token].
   template <bool ARG>
   __device__ __forceinline__ bool read_pass(int n_rows, int protected_rows) {
     const int C = a.L.C, nc = a.nc;
@@ -336,23 +354,26 @@ struct Workers {
     const bool active = mt * 128 < C;
     const int token = mt * 128 + quarter * 32 + lane;
     const int n_chunks = ceil_div(n_rows, kChunk);
+    // first local row that counts: global row l * nc + crank >= protected_rows
+    const int l_min = ARG ? (protected_rows > crank ? (protected_rows - crank + nc - 1) / nc : 0) : 0;
     float bv[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
     int bi[4] = {-1, -1, -1, -1};
-    bool ok = true;
+    bool ok = pend_ok;
+    pend_ok = true;
     for (int c = 0; c < n_chunks; ++c, ++g) {
-      const uint32_t b = g % kTmBufs;
       if (!active) continue;
-      ok = ok && wait(&bars->tm_full[b], (g / kTmBufs) & 1, a.wait_limit, abort);
+      ok = ok && wait(&bars->tm_full[mt], g & 1, a.wait_limit, abort);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;  // the caller aborts
-      {
-        tc::tc_fence_after_sync();
+      tc::tc_fence_after_sync();
+      const int n = min(kChunk, n_rows - c * kChunk);
+      const int n_groups = ceil_div(n, 32), g_half = (n_groups + 1) / 2;
+      const int g_begin = half ? g_half : 0, g_end = half ? n_groups : g_half;
+      for (int gi = g_begin; gi < g_end; ++gi) {
         uint32_t r[32];
-        tc::tmem_ld32(tmem + ((uint32_t)(quarter * 32) << 16) + b * 128u + (uint32_t)(mt * kChunk + half * 32), r);
+        tc::tmem_ld32(tmem + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(mt * kChunk + gi * 32), r);
         tc::tmem_ld_wait();
-        const int l0 = c * kChunk + half * 32;  // local row of column 0
-        // first local row that counts: global row l * nc + crank >= protected_rows
-        const int l_min = ARG ? (protected_rows > crank ? (protected_rows - crank + nc - 1) / nc : 0) : 0;
+        const int l0 = c * kChunk + gi * 32;  // local row of column 0
         const bool full = l0 + 32 <= n_rows && l0 >= l_min;
         if (!ARG) {
           if (full) {
@@ -379,10 +400,10 @@ struct Workers {
             }
           }
         }
-        tc::tc_fence_before_sync();
       }
+      tc::tc_fence_before_sync();
       __syncwarp();
-      if (lane == 0) tc::mbar_arrive(&bars->tm_empty[b]);
+      if (lane == 0) tc::mbar_arrive(&bars->tm_empty[mt]);
     }
     if (active) {
       float v = bv[0];
@@ -422,22 +443,17 @@ struct Workers {
     }
     bool ok = true;
     if (nc > 1) {
+      // every token's partial result goes to the same token's slot in every peer; this CTA expects the peers' bytes
+      if (tid == 0) tc::mbar_arrive_expect_tx(&bars->xbar[parity], (uint32_t)((nc - 1) * C * 8));
       if (tid < C) {
-        xb(parity, crank)[tid] = make_float2(v, __int_as_float(i));
+        const float2* slot = &xb(parity, crank)[tid];
         for (int p = 0; p < nc; ++p)
-          if (p != crank) st_peer_v2(peer_addr(&xb(parity, crank)[tid], p), v, i);
-        fence_cluster();
+          if (p != crank) st_async_v2(peer_addr(slot, p), v, i, peer_addr(&bars->xbar[parity], p));
       }
-      __syncwarp();
-      if (lane == 0 && warp * 32 < C)
-        for (int p = 0; p < nc; ++p)
-          if (p != crank) arrive_peer(peer_addr(&bars->xbar[parity], p));
-      ok = wait<true>(&bars->xbar[parity], (n_x >> 1) & 1, a.wait_limit, abort);
-      wsync();  // this CTA's own partial results are visible, too
+      ok = tid < C ? wait<true>(&bars->xbar[parity], (n_x >> 1) & 1, a.wait_limit, abort) : true;
       if (ok && tid < C) {
-        v = -INFINITY;
-        i = -1;
         for (int p = 0; p < nc; ++p) {
+          if (p == crank) continue;
           const float2 q = xb(parity, p)[tid];
           const int qi = __float_as_int(q.y);
           if (!ARG) v = fmaxf(v, q.x);
@@ -491,6 +507,7 @@ struct Workers {
     for (int base = 0; base < na; base += kWorkers / 8) {  // whole warps stay together: the LayerNorm uses group shuffles
       const int p = base + grp;
       const bool act = p < na;
+      if (!__any_sync(0xffffffffu, act && ((S0 + p) % a.nc == crank))) continue;  // nothing for this warp to store
       const int r = S0 + (act ? p : 0);
       const int t = list()[act ? p : 0];
       RowVec<HD, 8> x;
@@ -503,6 +520,7 @@ struct Workers {
 
   __device__ bool run() {
     const int C = a.L.C, nc = a.nc;
+    for (int l = crank; l < 32; l += nc) mine_mask |= 1u << l;
     int* route_row = a.route + (size_t)row * a.n_plan * C;
     for (int u = 0; u < a.n_plan; ++u) {
       const kvm_update_plan pl = a.plan[u];
@@ -549,11 +567,12 @@ struct Workers {
           }
           if (lane == 0) { bars->red_v[warp] = bv; bars->red_t[warp] = bt; }
           wsync();
-          bv = bars->red_v[0];
-          bt = bars->red_t[0];
-          for (int w = 1; w < kWorkerWarps; ++w) {
-            const float ov = bars->red_v[w];
-            const int ot = bars->red_t[w];
+          bv = bars->red_v[lane & 15];
+          bt = bars->red_t[lane & 15];
+#pragma unroll
+          for (int off = 8; off > 0; off >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, bv, off);
+            const int ot = __shfl_xor_sync(0xffffffffu, bt, off);
             if (ov < bv || (ov == bv && ot < bt)) { bv = ov; bt = ot; }
           }
           if (tid < C) pos()[tid] = tid == bt ? 0 : -1;
@@ -590,6 +609,15 @@ struct Workers {
       } else if (tid < C) {
         pos()[tid] = -1;
       }
+      if (nm > 0) {
+        // the prepared keys are dead from here on: their buffer becomes the one-hot operand of the scatter; it is
+        // cleared now, while the tensor core works on the logits
+        // (an update without appends never looked at them: their copy must have landed before the buffer is reused)
+        if (na == 0) pend_ok = wait(&bars->full_p, n_load & 1, a.wait_limit, abort);
+        else wsync();  // the warps that store appended rows have read their prepared keys
+        uint4* o = reinterpret_cast<uint4*>(smem + lay.P);
+        for (int i = tid; i < C * 16; i += kWorkers) o[i] = make_uint4(0, 0, 0, 0);
+      }
       // ---- 2. merge target of every token: first argmax of the fp32 logits over the memory after the appends
       if (nm > 0) {
         if (!read_pass<true>(n_local(S1, nc, crank), protected_rows)) return false;
@@ -602,36 +630,32 @@ struct Workers {
         my = p >= 0 ? -1 : idx()[tid];
         if (crank == 0) route_row[(size_t)u * C + tid] = p >= 0 ? -(1 + S0 + p) : my;
       }
-      for (int i = tid; i < S1; i += kWorkers) tf()[i] = 0;
-      wsync();
-      if (my >= 0) tf()[my] = 1;
+      // a row is touched in this update iff its stamp equals the update's number (no clearing between updates)
+      if (my >= 0) tf()[my] = (unsigned short)u;
       wsync();
       int n_touched = 0, n_touched_local = 0;
       {
         // compact index of every touched row among all touched rows (pool slot) and among this CTA's (accumulator lane)
-        const unsigned mine_mask = [&]() {  // lanes whose row (base + lane, base a multiple of 32) belongs to this CTA
-          unsigned m = 0;
-          for (int l = 0; l < 32; ++l)
-            if (l % nc == crank) m |= 1u << l;
-          return m;
-        }();
         int base_all = 0, base_loc = 0;
         for (int r0 = 0; r0 < S1; r0 += kWorkers) {
           const int r = r0 + tid;
-          const bool t = r < S1 && tf()[r];
+          const bool t = r < S1 && tf()[r] == (unsigned short)u;
           const unsigned bal = __ballot_sync(0xffffffffu, t);
           if (lane == 0) {
             bars->red_t[warp] = __popc(bal);
             bars->red_t[16 + warp] = __popc(bal & mine_mask);
           }
           wsync();
-          int pa = base_all, pl_ = base_loc, ta = 0, tl = 0;
-          for (int w = 0; w < kWorkerWarps; ++w) {
-            const int ca = bars->red_t[w], cl = bars->red_t[16 + w];
-            if (w < warp) { pa += ca; pl_ += cl; }
-            ta += ca;
-            tl += cl;
+          // lanes 0..15 hold the counts of all rows, lanes 16..31 of this CTA's rows: inclusive scan over each half
+          int cnt = bars->red_t[lane];
+#pragma unroll
+          for (int d = 1; d < 16; d <<= 1) {
+            const int y = __shfl_up_sync(0xffffffffu, cnt, d, 16);
+            if ((lane & 15) >= d) cnt += y;
           }
+          const int ta = __shfl_sync(0xffffffffu, cnt, 15), tl = __shfl_sync(0xffffffffu, cnt, 31);
+          const int ea = __shfl_sync(0xffffffffu, cnt, max(warp - 1, 0)), el = __shfl_sync(0xffffffffu, cnt, 16 + max(warp - 1, 0));
+          const int pa = base_all + (warp > 0 ? ea : 0), pl_ = base_loc + (warp > 0 ? el : 0);
           if (t) {
             const unsigned lt = (1u << lane) - 1u;
             const int ga = pa + __popc(bal & lt);
@@ -658,9 +682,11 @@ struct Workers {
       }
       for (int p = 0; p < n_pass; ++p) {
         {  // one-hot operand [C/64][128 rows][64 tokens] (in the buffer of the prepared keys, which are dead by now)
-          uint4* o = reinterpret_cast<uint4*>(smem + lay.P);
-          for (int i = tid; i < C * 16; i += kWorkers) o[i] = make_uint4(0, 0, 0, 0);
-          wsync();
+          if (p > 0) {  // a further pass: clear what the previous one set
+            uint4* o = reinterpret_cast<uint4*>(smem + lay.P);
+            for (int i = tid; i < C * 16; i += kWorkers) o[i] = make_uint4(0, 0, 0, 0);
+            wsync();
+          }
           if (my >= 0 && my % nc == crank) {
             const int ll = lci()[my] - p * 128;
             if (ll >= 0 && ll < 128) {
@@ -691,17 +717,22 @@ struct Workers {
           tc::tmem_ld32(tmem + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(colq * 32), d);
           tc::tmem_ld_wait();
           tc::tc_fence_before_sync();
+          // row = bf16(row + bf16(delta)) on packed pairs: one conversion per two elements (conversions are the
+          // slowest instructions of this loop), the sum of two bf16 numbers rounded once
           float s1 = 0.f;
 #pragma unroll
           for (int j = 0; j < 4; ++j) {
             const uint32_t w4[4] = {old[j].x, old[j].y, old[j].z, old[j].w};
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
-              const float2 o2 = act ? unpack_bf16(w4[e]) : make_float2(0.f, 0.f);
               const int c = j * 8 + e * 2;
-              x[c] = bf16_round(o2.x + bf16_round(__uint_as_float(d[c])));
-              x[c + 1] = bf16_round(o2.y + bf16_round(__uint_as_float(d[c + 1])));
-              s1 += x[c] + x[c + 1];
+              const __nv_bfloat162 dl = __floats2bfloat162_rn(__uint_as_float(d[c]), __uint_as_float(d[c + 1]));
+              uint32_t ow = act ? w4[e] : 0u;
+              const __nv_bfloat162 sum = __hadd2(*reinterpret_cast<const __nv_bfloat162*>(&ow), dl);
+              const float2 f2 = __bfloat1622float2(sum);
+              x[c] = f2.x;
+              x[c + 1] = f2.y;
+              s1 += f2.x + f2.y;
             }
           }
           stat(0)[colq * 128 + ci] = s1;
@@ -734,11 +765,11 @@ struct Workers {
 #pragma unroll
           for (int j = 0; j < 4; ++j) {
             float y[8];
+            const float4 w0 = *reinterpret_cast<const float4*>(ln_w + colq * 32 + j * 8), w1 = *reinterpret_cast<const float4*>(ln_w + colq * 32 + j * 8 + 4);
+            const float4 b0 = *reinterpret_cast<const float4*>(ln_b + colq * 32 + j * 8), b1 = *reinterpret_cast<const float4*>(ln_b + colq * 32 + j * 8 + 4);
+            const float wv[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w}, bv8[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
 #pragma unroll
-            for (int e = 0; e < 8; ++e) {
-              const int dcol = colq * 32 + j * 8 + e;
-              y[e] = x[j * 8 + e] * rstd * ln_w[dcol] + ln_b[dcol];
-            }
+            for (int e = 0; e < 8; ++e) y[e] = x[j * 8 + e] * rstd * wv[e] + bv8[e];
             uint4 o;
             o.x = pack_bf16(y[0], y[1]); o.y = pack_bf16(y[2], y[3]); o.z = pack_bf16(y[4], y[5]); o.w = pack_bf16(y[6], y[7]);
             *reinterpret_cast<uint4*>(smem + lay.R + piece(lay.Rcap, l, colq * 4 + j)) = o;
@@ -748,7 +779,7 @@ struct Workers {
       }
       // ---- 5. the version: every touched row moved to a fresh pool row
       for (int i = tid; i < S1; i += kWorkers)
-        if (tf()[i]) cur()[i] = pool_next + gci()[i];
+        if (tf()[i] == (unsigned short)u) cur()[i] = pool_next + gci()[i];
       pool_next += n_touched;
       wsync();
       if (ver)
@@ -778,7 +809,7 @@ struct Maps {
 __global__ void __launch_bounds__(kThreads, 1)
 kvm_chain_tc_kernel(const __grid_constant__ Args a, const __grid_constant__ Maps maps) {
   extern __shared__ __align__(1024) unsigned char smem[];
-  __shared__ float ln_s[2 * HD];
+  __shared__ __align__(16) float ln_s[2 * HD];
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int nc = a.nc;
   const int row = blockIdx.x / nc, crank = blockIdx.x % nc;
@@ -797,19 +828,20 @@ kvm_chain_tc_kernel(const __grid_constant__ Args a, const __grid_constant__ Maps
     uint4* r4 = reinterpret_cast<uint4*>(smem + lay.R);
     for (int i = tid; i < lay.Rcap * 16; i += kThreads) r4[i] = make_uint4(0, 0, 0, 0);
     for (int i = tid; i < a.s_max; i += kThreads) reinterpret_cast<int*>(smem + lay.rowi)[i] = 0;
+    unsigned short* stamps = reinterpret_cast<unsigned short*>(smem + lay.tloc + 2u * a.L.C * 2u);
+    for (int i = tid; i < a.s_max; i += kThreads) stamps[i] = 0;  // update numbers start at 1
   }
   if (tid == 0) {
-    const int n_epi = (a.L.C / 128) * 8;  // worker warps that read back a chunk
     tc::mbar_init(&bars->full_p, 1);
     tc::mbar_init(&bars->full_g, 1);
-    for (int i = 0; i < kTmBufs; ++i) {
+    for (int i = 0; i < 2; ++i) {
       tc::mbar_init(&bars->tm_full[i], 1);
-      tc::mbar_init(&bars->tm_empty[i], n_epi);
+      tc::mbar_init(&bars->tm_empty[i], 8);  // the eight warps that read a token tile
     }
     tc::mbar_init(&bars->w2i, kWorkerWarps);
     tc::mbar_init(&bars->sc_done, 1);
-    tc::mbar_init(&bars->xbar[0], max(1, (nc - 1) * (a.L.C / 32)));  // one arrival per sending warp of every peer
-    tc::mbar_init(&bars->xbar[1], max(1, (nc - 1) * (a.L.C / 32)));
+    tc::mbar_init(&bars->xbar[0], 1);  // one local arrival that states the bytes the peers will store
+    tc::mbar_init(&bars->xbar[1], 1);
     bars->abort = 0;
     bars->n_pass = 0;
     tc::fence_barrier_init();
@@ -855,31 +887,104 @@ kvm_chain_tc_kernel(const __grid_constant__ Args a, const __grid_constant__ Maps
 }
 
 // ------------------------------------------------------------------------------------------------ value side
-constexpr int kVpWarps = 32;
+constexpr int kVpWarps = 16;
+constexpr int kVpQueue = 4;  // routed tokens of a row whose value rows are fetched together
 
 // One warp per memory row.  route: [rows][n_plan][C] (>= 0: merged into that row, -(1+r): appended as row r).
-__global__ void __launch_bounds__(kVpWarps * 32)
+// The warp walks the decisions of all updates (a tile of them at a time in shared memory), queues the tokens that
+// concern its row and fetches their value rows kVpQueue at a time (the loads are independent, the sums are formed
+// afterwards in token order), so that the walk is bound by throughput and not by the latency of one row.
+__global__ void __launch_bounds__(kVpWarps * 32, 2)
 kvm_vpass_kernel(LayerDev L, Tensor4 v, Tensor4 gate, const kvm_update_plan* __restrict__ plan, int n_plan,
                  const int* __restrict__ route, MemoryDev mem, bf16* __restrict__ pool_v, long long pool_rows,
                  const int* __restrict__ ver_idx, long long ver_rows, int s_final, int tile_updates) {
   extern __shared__ __align__(16) unsigned char vsm[];
-  short* rt = reinterpret_cast<short*>(vsm);  // [tile_updates][C] routing decisions of the current tile
+  short* rt = reinterpret_cast<short*>(vsm);                                        // [tile_updates][C] decisions of the tile
+  int* vrow = reinterpret_cast<int*>(vsm + (size_t)tile_updates * L.C * 2);         // [n_plan] version_row of every update
+  int* queue = vrow + ((n_plan + 3) & ~3);                                          // [warps][kVpQueue] token (bit 30: appended)
   const int C = L.C, EPL = C / 32;            // EPL tokens per lane: 4 or 8
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int row = blockIdx.y;
   const int b = row / L.Hkv, h = row % L.Hkv;
   const int r = blockIdx.x * kVpWarps + warp;  // this warp's memory row
   const bool live = r < s_final;
+  const bool versions = pool_v != nullptr && ver_idx != nullptr;
   const int* route_row = route + (size_t)row * n_plan * C;
+  const int* ver_row = ver_idx + (size_t)row * ver_rows;
+  int* q = queue + warp * kVpQueue;
   float x[4] = {0.f, 0.f, 0.f, 0.f};           // carried value sum of the row (bf16 values), elements 4*lane..
+  float acc[4] = {0.f, 0.f, 0.f, 0.f};         // sum of the gated values of the update being collected
   float vl = 0.f;
+  int acc_u = -1, acc_slot = -1, nq = 0;
   bool born = false;
+  for (int i = tid; i < n_plan; i += kVpWarps * 32) vrow[i] = plan[i].version_row;
 
-  auto load_v = [&](long long t, float (&o)[4], float& g) {
-    const uint2 u = *reinterpret_cast<const uint2*>(v.row(b, h, t) + lane * 4);
-    const float2 p0 = unpack_bf16(u.x), p1 = unpack_bf16(u.y);
-    o[0] = p0.x; o[1] = p0.y; o[2] = p1.x; o[3] = p1.y;
-    g = __bfloat162float(*gate.row(b, h, t));
+  // the value view of the row after update u: normalize(sum) * magnitude, into the pool row of that version
+  auto finalize = [&]() {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      x[i] = bf16_round(x[i] + bf16_round(acc[i]));
+      acc[i] = 0.f;
+    }
+    if (versions && acc_slot >= 0) {
+      float n2 = 0.f;
+#pragma unroll
+      for (int i = 0; i < 4; ++i) n2 += x[i] * x[i];
+      const float nrm = fmaxf(sqrtf(warp_sum(n2)), 1e-12f);
+      float y[4] = {x[0], x[1], x[2], x[3]};
+      divide_by(y, nrm);
+      uint2 o;
+      o.x = pack_bf16(y[0] * vl, y[1] * vl);
+      o.y = pack_bf16(y[2] * vl, y[3] * vl);
+      *reinterpret_cast<uint2*>(pool_v + ((size_t)row * pool_rows + acc_slot) * HD + lane * 4) = o;
+    }
+    acc_u = -1;
+  };
+  // fetch the queued tokens' value rows (and gates, and the pool slots of their updates) together, then apply in order
+  auto flush = [&]() {
+    uint2 raw[kVpQueue];
+    float g[kVpQueue];
+    int slot[kVpQueue], item[kVpQueue];
+#pragma unroll
+    for (int i = 0; i < kVpQueue; ++i) {
+      item[i] = i < nq ? q[i] : 0;
+      const long long t = item[i] & 0x3fffffff;
+      if (i < nq) {
+        raw[i] = *reinterpret_cast<const uint2*>(v.row(b, h, t) + lane * 4);
+        g[i] = __bfloat162float(*gate.row(b, h, t));
+        const int vr = vrow[(int)(t / C)];
+        slot[i] = (versions && vr >= 0) ? ver_row[vr + r] : -1;
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < kVpQueue; ++i) {
+      if (i >= nq) break;
+      const int u = (item[i] & 0x3fffffff) / C;
+      if (acc_u >= 0 && acc_u != u) finalize();
+      const float2 p0 = unpack_bf16(raw[i].x), p1 = unpack_bf16(raw[i].y);
+      float o[4] = {p0.x, p0.y, p1.x, p1.y};
+      if (item[i] & 0x40000000) {
+        // the row is born from this token: value (gated where the layer says so) and magnitude
+        const bool gated = u == 0 ? (L.gate_initial != 0) : (L.gate_appends != 0 && L.gate_values != 0);
+        if (u > 0 && gated) {
+#pragma unroll
+          for (int e = 0; e < 4; ++e) o[e] = bf16_round(o[e] * g[i]);
+        }
+        float n2 = 0.f;
+#pragma unroll
+        for (int e = 0; e < 4; ++e) n2 += o[e] * o[e];
+        vl = sqrtf(warp_sum(n2));  // the initial rows keep the magnitude of the ungated value
+#pragma unroll
+        for (int e = 0; e < 4; ++e) x[e] = (u == 0 && gated) ? bf16_round(o[e] * g[i]) : o[e];
+        born = true;
+      } else {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) acc[e] += L.gate_values ? bf16_round(o[e] * g[i]) : o[e];
+      }
+      acc_u = u;
+      acc_slot = slot[i];
+    }
+    nq = 0;
   };
 
   for (int u0 = 0; u0 < n_plan; u0 += tile_updates) {
@@ -888,73 +993,54 @@ kvm_vpass_kernel(LayerDev L, Tensor4 v, Tensor4 gate, const kvm_update_plan* __r
     for (int i = tid; i < nu * C; i += kVpWarps * 32) rt[i] = (short)route_row[(size_t)u0 * C + i];
     __syncthreads();
     if (!live) continue;
+    const unsigned want_m = (unsigned)(r & 0xffff) * 0x10001u, want_a = (unsigned)((-(1 + r)) & 0xffff) * 0x10001u;
     for (int uu = 0; uu < nu; ++uu) {
       const int u = u0 + uu;
-      // which of this lane's tokens were appended as / merged into row r
+      // which of this lane's tokens were appended as / merged into row r (two decisions per 32-bit word)
+      const unsigned* w = reinterpret_cast<const unsigned*>(rt + uu * C + lane * EPL);
+      unsigned e4[4] = {0u, 0u, 0u, 0u}, hit = 0;
+      if (EPL == 8) {
+        const uint4 q4 = *reinterpret_cast<const uint4*>(w);
+        e4[0] = q4.x; e4[1] = q4.y; e4[2] = q4.z; e4[3] = q4.w;
+      } else {
+        const uint2 q2 = *reinterpret_cast<const uint2*>(w);
+        e4[0] = q2.x; e4[1] = q2.y;
+        e4[2] = e4[3] = 0x80008000u;  // matches no row
+      }
+#pragma unroll
+      for (int j = 0; j < 4; ++j) hit |= __vcmpeq2(e4[j], want_a) | (u > 0 ? __vcmpeq2(e4[j], want_m) : 0u);
+      unsigned any = __ballot_sync(0xffffffffu, hit != 0);
+      if (!any) continue;  // the common case: nothing of this update concerns the row
       unsigned m_app = 0, m_mrg = 0;
-      for (int j = 0; j < EPL; ++j) {
-        const int e = rt[uu * C + lane * EPL + j];
-        if (e == r && u > 0) m_mrg |= 1u << j;
-        if (e == -(1 + r)) m_app |= 1u << j;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const unsigned ca = __vcmpeq2(e4[j], want_a), cm = u > 0 ? __vcmpeq2(e4[j], want_m) : 0u;
+        m_app |= ((ca & 1u) | ((ca >> 15) & 2u)) << (2 * j);
+        m_mrg |= ((cm & 1u) | ((cm >> 15) & 2u)) << (2 * j);
       }
-      unsigned any_app = __ballot_sync(0xffffffffu, m_app != 0);
-      unsigned any_mrg = __ballot_sync(0xffffffffu, m_mrg != 0);
-      if (!any_app && !any_mrg) continue;
-      if (any_app) {  // the row is born from one token: value (gated where the layer says so), magnitude
-        const int src = __ffs(any_app) - 1;
-        const unsigned mm = __shfl_sync(0xffffffffu, m_app, src);
-        const long long t = (long long)u * C + src * EPL + (__ffs(mm) - 1);
-        float g;
-        load_v(t, x, g);
-        const bool gated = u == 0 ? (L.gate_initial != 0) : (L.gate_appends != 0 && L.gate_values != 0);
-        float n2 = 0.f;
-        if (u > 0 && gated) {
-#pragma unroll
-          for (int i = 0; i < 4; ++i) x[i] = bf16_round(x[i] * g);
-        }
-#pragma unroll
-        for (int i = 0; i < 4; ++i) n2 += x[i] * x[i];
-        vl = sqrtf(warp_sum(n2));  // the initial rows keep the magnitude of the ungated value
-        if (u == 0 && gated) {
-#pragma unroll
-          for (int i = 0; i < 4; ++i) x[i] = bf16_round(x[i] * g);
-        }
-        born = true;
-      }
-      if (any_mrg) {  // gated values routed to the row, summed in token order
-        float acc[4] = {0.f, 0.f, 0.f, 0.f};
-        while (any_mrg) {
-          const int src = __ffs(any_mrg) - 1;
-          any_mrg &= any_mrg - 1;
-          unsigned mm = __shfl_sync(0xffffffffu, m_mrg, src);
-          while (mm) {
-            const int j = __ffs(mm) - 1;
-            mm &= mm - 1;
-            float o[4], g;
-            load_v((long long)u * C + src * EPL + j, o, g);
-#pragma unroll
-            for (int i = 0; i < 4; ++i) acc[i] += L.gate_values ? bf16_round(o[i] * g) : o[i];
+      while (any) {  // lanes in order = tokens in order
+        const int src = __ffs(any) - 1;
+        any &= any - 1;
+        const unsigned ma = __shfl_sync(0xffffffffu, m_app, src);
+        unsigned mm = __shfl_sync(0xffffffffu, m_mrg, src) | ma;
+        while (mm) {
+          const int j = __ffs(mm) - 1;
+          mm &= mm - 1;
+          if (lane == 0) q[nq] = (u * C + src * EPL + j) | (((ma >> j) & 1u) ? 0x40000000 : 0);
+          ++nq;
+          if (nq == kVpQueue) {
+            __syncwarp();
+            flush();
+            __syncwarp();
           }
         }
-#pragma unroll
-        for (int i = 0; i < 4; ++i) x[i] = bf16_round(x[i] + bf16_round(acc[i]));
-      }
-      // the value view of the row in this version
-      const kvm_update_plan pl = plan[u];
-      if (born && pool_v && ver_idx && pl.version_row >= 0) {
-        const int slot = ver_idx[(size_t)row * ver_rows + pl.version_row + r];
-        float n2 = 0.f;
-#pragma unroll
-        for (int i = 0; i < 4; ++i) n2 += x[i] * x[i];
-        const float nrm = fmaxf(sqrtf(warp_sum(n2)), 1e-12f);
-        float y[4] = {x[0], x[1], x[2], x[3]};
-        divide_by(y, nrm);
-        uint2 o;
-        o.x = pack_bf16(y[0] * vl, y[1] * vl);
-        o.y = pack_bf16(y[2] * vl, y[3] * vl);
-        *reinterpret_cast<uint2*>(pool_v + ((size_t)row * pool_rows + slot) * HD + lane * 4) = o;
       }
     }
+  }
+  if (live) {
+    __syncwarp();
+    flush();
+    if (acc_u >= 0) finalize();
   }
   if (live && born) {  // the carried state and its final view
     const size_t off = ((size_t)row * mem.capacity + r) * HD + lane * 4;
@@ -1074,7 +1160,7 @@ cudaError_t launch_chain_tc(const LayerDev& L, int batch, Tensor4 v, Tensor4 gat
   if (e != cudaSuccess) return e;
   // value side: one warp per memory row, the routing decisions of as many updates as fit 64 KB per tile
   const int tile_updates = std::max(1, std::min(n_plan, (64 * 1024) / (C * 2)));
-  const size_t vsmem = (size_t)tile_updates * C * 2;
+  const size_t vsmem = (size_t)tile_updates * C * 2 + (size_t)((n_plan + 3) & ~3) * 4 + (size_t)kVpWarps * kVpQueue * 4;
   e = cudaFuncSetAttribute(kvm_vpass_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)vsmem);
   if (e != cudaSuccess) return e;
   dim3 vgrid((unsigned)ceil_div(s_max, kVpWarps), rows);
