@@ -388,15 +388,15 @@ struct Workers {
           if (full) {
 #pragma unroll
             for (int j = 0; j < 32; ++j) {
-              const float x = __uint_as_float(r[j]);
-              if (x > bv[j & 3] || bi[j & 3] < 0) { bv[j & 3] = x; bi[j & 3] = l0 + j; }
+              const float x = __uint_as_float(r[j]);  // strictly greater replaces: the first of equal values stays
+              if (x > bv[j & 3]) { bv[j & 3] = x; bi[j & 3] = l0 + j; }
             }
           } else {
 #pragma unroll
             for (int j = 0; j < 32; ++j) {
               const float x = __uint_as_float(r[j]);
               const int l = l0 + j;
-              if (l < n_rows && l >= l_min && (x > bv[j & 3] || bi[j & 3] < 0)) { bv[j & 3] = x; bi[j & 3] = l; }
+              if (l < n_rows && l >= l_min && x > bv[j & 3]) { bv[j & 3] = x; bi[j & 3] = l; }
             }
           }
         }
@@ -901,8 +901,8 @@ kvm_vpass_kernel(LayerDev L, Tensor4 v, Tensor4 gate, const kvm_update_plan* __r
   extern __shared__ __align__(16) unsigned char vsm[];
   short* rt = reinterpret_cast<short*>(vsm);                                        // [tile_updates][C] decisions of the tile
   int* vrow = reinterpret_cast<int*>(vsm + (size_t)tile_updates * L.C * 2);         // [n_plan] version_row of every update
-  int* queue = vrow + ((n_plan + 3) & ~3);                                          // [warps][kVpQueue] token (bit 30: appended)
   const int C = L.C, EPL = C / 32;            // EPL tokens per lane: 4 or 8
+  const int log2c = C == 256 ? 8 : 7;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int row = blockIdx.y;
   const int b = row / L.Hkv, h = row % L.Hkv;
@@ -910,81 +910,89 @@ kvm_vpass_kernel(LayerDev L, Tensor4 v, Tensor4 gate, const kvm_update_plan* __r
   const bool live = r < s_final;
   const bool versions = pool_v != nullptr && ver_idx != nullptr;
   const int* route_row = route + (size_t)row * n_plan * C;
-  const int* ver_row = ver_idx + (size_t)row * ver_rows;
-  int* q = queue + warp * kVpQueue;
+  const int* ver_row = ver_idx + (size_t)row * ver_rows + r;
+  const bf16* v_base = v.row(b, h, 0) + lane * 4;
+  const bf16* g_base = gate.row(b, h, 0);
+  bf16* pool_row = pool_v + (size_t)row * pool_rows * HD + lane * 4;
+  const bool gate_values = L.gate_values != 0;
   float x[4] = {0.f, 0.f, 0.f, 0.f};           // carried value sum of the row (bf16 values), elements 4*lane..
   float acc[4] = {0.f, 0.f, 0.f, 0.f};         // sum of the gated values of the update being collected
   float vl = 0.f;
   int acc_u = -1, acc_slot = -1, nq = 0;
+  int q0 = 0, q1 = 0, q2 = 0, q3 = 0;          // queued tokens (bit 30: appended); the same in every lane
   bool born = false;
   for (int i = tid; i < n_plan; i += kVpWarps * 32) vrow[i] = plan[i].version_row;
 
-  // the value view of the row after update u: normalize(sum) * magnitude, into the pool row of that version
+  // the value view of the row after the update being collected: normalize(sum) * magnitude, into the pool row of that version
   auto finalize = [&]() {
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
       x[i] = bf16_round(x[i] + bf16_round(acc[i]));
       acc[i] = 0.f;
     }
-    if (versions && acc_slot >= 0) {
-      float n2 = 0.f;
-#pragma unroll
-      for (int i = 0; i < 4; ++i) n2 += x[i] * x[i];
+    if (acc_slot >= 0) {
+      const float n2 = x[0] * x[0] + x[1] * x[1] + x[2] * x[2] + x[3] * x[3];
       const float nrm = fmaxf(sqrtf(warp_sum(n2)), 1e-12f);
       float y[4] = {x[0], x[1], x[2], x[3]};
       divide_by(y, nrm);
       uint2 o;
       o.x = pack_bf16(y[0] * vl, y[1] * vl);
       o.y = pack_bf16(y[2] * vl, y[3] * vl);
-      *reinterpret_cast<uint2*>(pool_v + ((size_t)row * pool_rows + acc_slot) * HD + lane * 4) = o;
+      *reinterpret_cast<uint2*>(pool_row + (size_t)acc_slot * HD) = o;
     }
     acc_u = -1;
   };
   // fetch the queued tokens' value rows (and gates, and the pool slots of their updates) together, then apply in order
   auto flush = [&]() {
+    const int item[kVpQueue] = {q0, q1, q2, q3};
     uint2 raw[kVpQueue];
-    float g[kVpQueue];
-    int slot[kVpQueue], item[kVpQueue];
+    bf16 g[kVpQueue];
+    int slot[kVpQueue];
 #pragma unroll
     for (int i = 0; i < kVpQueue; ++i) {
-      item[i] = i < nq ? q[i] : 0;
-      const long long t = item[i] & 0x3fffffff;
       if (i < nq) {
-        raw[i] = *reinterpret_cast<const uint2*>(v.row(b, h, t) + lane * 4);
-        g[i] = __bfloat162float(*gate.row(b, h, t));
-        const int vr = vrow[(int)(t / C)];
-        slot[i] = (versions && vr >= 0) ? ver_row[vr + r] : -1;
+        const int t = item[i] & 0x3fffffff;
+        raw[i] = *reinterpret_cast<const uint2*>(v_base + (long long)t * v.st);
+        g[i] = g_base[(long long)t * gate.st];
+        const int vr = vrow[t >> log2c];
+        slot[i] = (versions && vr >= 0) ? ver_row[vr] : -1;
       }
     }
 #pragma unroll
     for (int i = 0; i < kVpQueue; ++i) {
-      if (i >= nq) break;
-      const int u = (item[i] & 0x3fffffff) / C;
-      if (acc_u >= 0 && acc_u != u) finalize();
-      const float2 p0 = unpack_bf16(raw[i].x), p1 = unpack_bf16(raw[i].y);
-      float o[4] = {p0.x, p0.y, p1.x, p1.y};
-      if (item[i] & 0x40000000) {
-        // the row is born from this token: value (gated where the layer says so) and magnitude
-        const bool gated = u == 0 ? (L.gate_initial != 0) : (L.gate_appends != 0 && L.gate_values != 0);
-        if (u > 0 && gated) {
+      if (i < nq) {
+        const int u = (item[i] & 0x3fffffff) >> log2c;
+        if (acc_u >= 0 && acc_u != u) finalize();
+        const float2 p0 = unpack_bf16(raw[i].x), p1 = unpack_bf16(raw[i].y);
+        float o[4] = {p0.x, p0.y, p1.x, p1.y};
+        const float gf = __bfloat162float(g[i]);
+        if (item[i] & 0x40000000) {
+          // the row is born from this token: value (gated where the layer says so) and magnitude
+          const bool gated = u == 0 ? (L.gate_initial != 0) : (L.gate_appends != 0 && gate_values);
+          if (u > 0 && gated) {
 #pragma unroll
-          for (int e = 0; e < 4; ++e) o[e] = bf16_round(o[e] * g[i]);
+            for (int e = 0; e < 4; ++e) o[e] = bf16_round(o[e] * gf);
+          }
+          vl = sqrtf(warp_sum(o[0] * o[0] + o[1] * o[1] + o[2] * o[2] + o[3] * o[3]));  // initial rows: of the ungated value
+#pragma unroll
+          for (int e = 0; e < 4; ++e) x[e] = (u == 0 && gated) ? bf16_round(o[e] * gf) : o[e];
+          born = true;
+        } else {
+#pragma unroll
+          for (int e = 0; e < 4; ++e) acc[e] += gate_values ? bf16_round(o[e] * gf) : o[e];
         }
-        float n2 = 0.f;
-#pragma unroll
-        for (int e = 0; e < 4; ++e) n2 += o[e] * o[e];
-        vl = sqrtf(warp_sum(n2));  // the initial rows keep the magnitude of the ungated value
-#pragma unroll
-        for (int e = 0; e < 4; ++e) x[e] = (u == 0 && gated) ? bf16_round(o[e] * g[i]) : o[e];
-        born = true;
-      } else {
-#pragma unroll
-        for (int e = 0; e < 4; ++e) acc[e] += L.gate_values ? bf16_round(o[e] * g[i]) : o[e];
+        acc_u = u;
+        acc_slot = slot[i];
       }
-      acc_u = u;
-      acc_slot = slot[i];
     }
     nq = 0;
+  };
+  auto push = [&](int item) {
+    if (nq == 0) q0 = item;
+    else if (nq == 1) q1 = item;
+    else if (nq == 2) q2 = item;
+    else q3 = item;
+    if (++nq == kVpQueue) flush();
   };
 
   for (int u0 = 0; u0 < n_plan; u0 += tile_updates) {
@@ -996,49 +1004,44 @@ kvm_vpass_kernel(LayerDev L, Tensor4 v, Tensor4 gate, const kvm_update_plan* __r
     const unsigned want_m = (unsigned)(r & 0xffff) * 0x10001u, want_a = (unsigned)((-(1 + r)) & 0xffff) * 0x10001u;
     for (int uu = 0; uu < nu; ++uu) {
       const int u = u0 + uu;
-      // which of this lane's tokens were appended as / merged into row r (two decisions per 32-bit word)
+      // two decisions per 32-bit word; token 2j of this lane's share in the low half of word j
       const unsigned* w = reinterpret_cast<const unsigned*>(rt + uu * C + lane * EPL);
-      unsigned e4[4] = {0u, 0u, 0u, 0u}, hit = 0;
+      unsigned e4[4];
       if (EPL == 8) {
         const uint4 q4 = *reinterpret_cast<const uint4*>(w);
         e4[0] = q4.x; e4[1] = q4.y; e4[2] = q4.z; e4[3] = q4.w;
       } else {
-        const uint2 q2 = *reinterpret_cast<const uint2*>(w);
-        e4[0] = q2.x; e4[1] = q2.y;
+        const uint2 q2w = *reinterpret_cast<const uint2*>(w);
+        e4[0] = q2w.x; e4[1] = q2w.y;
         e4[2] = e4[3] = 0x80008000u;  // matches no row
       }
-#pragma unroll
-      for (int j = 0; j < 4; ++j) hit |= __vcmpeq2(e4[j], want_a) | (u > 0 ? __vcmpeq2(e4[j], want_m) : 0u);
-      unsigned any = __ballot_sync(0xffffffffu, hit != 0);
-      if (!any) continue;  // the common case: nothing of this update concerns the row
+      // bit j: token 2j, bit 16 + j: token 2j + 1
       unsigned m_app = 0, m_mrg = 0;
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
-        const unsigned ca = __vcmpeq2(e4[j], want_a), cm = u > 0 ? __vcmpeq2(e4[j], want_m) : 0u;
-        m_app |= ((ca & 1u) | ((ca >> 15) & 2u)) << (2 * j);
-        m_mrg |= ((cm & 1u) | ((cm >> 15) & 2u)) << (2 * j);
+        m_app |= (__vcmpeq2(e4[j], want_a) & 0x00010001u) << j;
+        m_mrg |= (__vcmpeq2(e4[j], want_m) & 0x00010001u) << j;
       }
+      if (u == 0) m_mrg = 0;
+      unsigned any = __ballot_sync(0xffffffffu, (m_app | m_mrg) != 0);
       while (any) {  // lanes in order = tokens in order
         const int src = __ffs(any) - 1;
         any &= any - 1;
         const unsigned ma = __shfl_sync(0xffffffffu, m_app, src);
         unsigned mm = __shfl_sync(0xffffffffu, m_mrg, src) | ma;
-        while (mm) {
-          const int j = __ffs(mm) - 1;
-          mm &= mm - 1;
-          if (lane == 0) q[nq] = (u * C + src * EPL + j) | (((ma >> j) & 1u) ? 0x40000000 : 0);
-          ++nq;
-          if (nq == kVpQueue) {
-            __syncwarp();
-            flush();
-            __syncwarp();
-          }
+        const int t0 = (u << log2c) + src * EPL;
+        while (mm) {  // next token of the lane: the lower of (2 * first low bit, 2 * first high bit + 1)
+          const unsigned lo = mm & 0xffffu, hi = mm >> 16;
+          const int jl = lo ? 2 * (__ffs(lo) - 1) : 64, jh = hi ? 2 * (__ffs(hi) - 1) + 1 : 64;
+          const int j = min(jl, jh);
+          const unsigned bit = 1u << ((j >> 1) + ((j & 1) << 4));
+          mm &= ~bit;
+          push((t0 + j) | ((ma & bit) ? 0x40000000 : 0));
         }
       }
     }
   }
   if (live) {
-    __syncwarp();
     flush();
     if (acc_u >= 0) finalize();
   }
@@ -1049,9 +1052,7 @@ kvm_vpass_kernel(LayerDev L, Tensor4 v, Tensor4 gate, const kvm_update_plan* __r
     s.y = pack_bf16(x[2], x[3]);
     *reinterpret_cast<uint2*>(mem.v_sum + off) = s;
     if (lane == 0) mem.vlen[(size_t)row * mem.capacity + r] = vl;
-    float n2 = 0.f;
-#pragma unroll
-    for (int i = 0; i < 4; ++i) n2 += x[i] * x[i];
+    const float n2 = x[0] * x[0] + x[1] * x[1] + x[2] * x[2] + x[3] * x[3];
     const float nrm = fmaxf(sqrtf(warp_sum(n2)), 1e-12f);
     float y[4] = {x[0], x[1], x[2], x[3]};
     divide_by(y, nrm);
@@ -1160,7 +1161,7 @@ cudaError_t launch_chain_tc(const LayerDev& L, int batch, Tensor4 v, Tensor4 gat
   if (e != cudaSuccess) return e;
   // value side: one warp per memory row, the routing decisions of as many updates as fit 64 KB per tile
   const int tile_updates = std::max(1, std::min(n_plan, (64 * 1024) / (C * 2)));
-  const size_t vsmem = (size_t)tile_updates * C * 2 + (size_t)((n_plan + 3) & ~3) * 4 + (size_t)kVpWarps * kVpQueue * 4;
+  const size_t vsmem = (size_t)tile_updates * C * 2 + (size_t)((n_plan + 3) & ~3) * 4;
   e = cudaFuncSetAttribute(kvm_vpass_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)vsmem);
   if (e != cudaSuccess) return e;
   dim3 vgrid((unsigned)ceil_div(s_max, kVpWarps), rows);
