@@ -14,7 +14,9 @@ One JSON line is printed by rank 0:  value = prefill tokens/s (inputs resident i
 through the public operator call with pinned HOST buffers (H2D of q,k,v,gate and D2H of the output inside
 the timed region), roofline = block-attention kernel against the measured bf16 tensor peak,
 cpu_baseline = the CPU oracle (a port of the reference's eager mixer) on a bounded sample,
-decode = decode tokens/s of 64 ragged sequences (the second half of the metric).
+decode = decode tokens/s of 64 ragged sequences (the second half of the metric), power_law = the same prefill
+with the reference's native 16*sqrt(T) schedule (cap 1024), check = the kernels' status words after the timed
+loops and one head of the timed output against the oracle.
 """
 
 from __future__ import annotations
@@ -277,6 +279,7 @@ def run_b200(args):
     n_rep = 1 if args.prefill_only else max(3, args.steps // 2)
     chain_ms = time_phase(_lib.PREFILL_CHAIN, n_rep)
     attn_ms = time_phase(_lib.PREFILL_ATTENTION, n_rep)
+    runner.run(q, k, v, gate)  # leave a whole prefill in the buffers (the status word belongs to a whole prefill)
     peaks = _peaks()
     pairs = attention_pairs(T, C, W, plan)
     attn_flops = 4.0 * D * pairs * B * h_loc          # QK^T and PV of this rank's heads
@@ -287,6 +290,20 @@ def run_b200(args):
                 "ms": round(attn_ms, 4), "chain_ms": round(chain_ms, 4),
                 "algorithmic_flops": attn_flops}
 
+    # ---- the timed kernels reported nothing, and what they computed is what the oracle computes (one head)
+    check = {"prefill_status": "ok"}
+    try:
+        runner.check_status()
+    except Exception as exc:  # a bounded device-side wait ran out: the number above is not a measurement
+        check["prefill_status"] = str(exc)
+    if rank == 0 and not args.no_cpu:
+        check["oracle_head0"] = oracle_check(mixer, params, plan, q, k, v, gate, runner.out)
+
+    # ---- the reference's native schedule on the same inputs: 16 * sqrt(context), at most 1024 means
+    power_law = None
+    if not args.prefill_only:
+        power_law = run_power_law(mixer, params, q, k, v, gate, B, T, C, W, D, h_loc, peaks, max(3, args.steps // 2))
+
     # ---- end to end through the operator call with host buffers
     e2e = None
     if not args.prefill_only:
@@ -296,7 +313,10 @@ def run_b200(args):
             h_.copy_(d_.transpose(1, 2))
         h_out = torch.empty(B, T, h_loc * D, dtype=torch.bfloat16).pin_memory()
         # the package's host-buffer entry point: copy-in, kernels and copy-out of consecutive sequences overlap
-        host_prefill = ops.HostPrefill(runner.params, B, plan, slice_batch=1)
+        # sequences per slice: as many as keep every kv row's cluster of 8 CTAs resident (16 kv rows), so that ranks
+        # with few heads do not run one chain per sequence
+        slice_batch = max(d for d in range(1, B + 1) if B % d == 0 and (d == 1 or d * h_loc <= 16))
+        host_prefill = ops.HostPrefill(runner.params, B, plan, slice_batch=slice_batch)
 
         def e2e_step():
             host_prefill.run(hq, hk, hv, hg, h_out)
@@ -315,7 +335,8 @@ def run_b200(args):
             dist.all_reduce(t2, op=dist.ReduceOp.MAX)
         h2d = sum(t_.numel() * t_.element_size() for t_ in (hq, hk, hv, hg))
         e2e = {"value": round(B * T / (float(t2.item()) * 1e-3), 1), "unit": UNIT, "ms_per_step": round(float(t2.item()), 3),
-               "h2d_bytes_per_step": h2d * world, "d2h_bytes_per_step": h_out.numel() * 2 * world}
+               "h2d_bytes_per_step": h2d * world, "d2h_bytes_per_step": h_out.numel() * 2 * world,
+               "sequences_per_slice": slice_batch}
         del hq, hk, hv, hg, h_out, host_prefill
 
     del runner, q, k, v, gate
@@ -339,11 +360,87 @@ def run_b200(args):
                        "l2": "inputs (1.6 GB) larger than L2, no flush needed"},
             "e2e": e2e, "gpu_launches": 4 * args.steps,  # per step: prepared + gated keys, chain (routing and keys), value pass, block attention
             "roofline": roofline, "cpu_baseline": cpu,
-            "clocks": clocks.summary(), "decode": decode,
+            "clocks": clocks.summary(), "decode": decode, "power_law": power_law, "check": check,
         }
         print(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()
+
+
+def oracle_check(mixer, params, plan, q, k, v, gate, out):
+    """Batch row 0, head 0 of the timed configuration against the CPU oracle: the device prefill is repeated once
+    with its routing decisions recorded (it must give the timed output bit for bit), the oracle follows those
+    decisions after classifying them, activations are compared."""
+    from kvm_paper_b200 import ops
+    from oracle import kvm_oracle as ko
+    from tests import gpu_helpers as gh
+
+    cfg = params.cfg
+    D = cfg.head_dim
+    one = ops.LayerConfig(1, 1, D, cfg.chunk_len, cfg.n_bswa_chunks, cfg.rope_dim, cfg.sink_len, cfg.gate_keys,
+                          cfg.gate_values, cfg.gate_appends, cfg.gate_initial, cfg.ln_eps)
+    p1 = ops.LayerParams(one, params.ln_w, params.ln_b, params.front[:1], params.state[:1], params.device)
+    sl = [t[:1, :1] for t in (q, k, v, gate)]
+    res = ops.prefill_forward(p1, *sl, plan, want_route=True, check=True)
+    same_bits = bool(torch.equal(res.out[0, :, :D], out[0, :, :D]))
+    spec = ko.KvmSpec(1, 1, D, D, cfg.rope_dim, cfg.chunk_len, cfg.n_bswa_chunks, mixer.n_max_d_chunks, cfg.sink_len, "plus_one",
+                      state_min_len=cfg.chunk_len, ln_weight=params.ln_w.cpu().bfloat16(), ln_bias=params.ln_b.cpu().bfloat16(),
+                      front_head_temp=params.front[:1].cpu().bfloat16(), state_head_temp=params.state[:1].cpu().bfloat16())
+    forced = [gh.decisions_from_route(res.route[:, u], 1, 1) for u in range(1, plan.n_updates + 1)]
+    trace = []
+    with torch.no_grad():
+        y, _ = ko.prefill(spec, *(t.cpu() for t in sl), trace=trace, forced=forced)
+    summ = gh.summarize(trace)
+    d = (res.out.float().cpu() - y.float()).abs()
+    return {"same_bits_as_timed_output": same_bits, "max_abs": round(float(d.max()), 5),
+            "mean_rel": round(float(d.mean() / y.float().abs().mean()), 5), "merge_decisions": summ["merge_tokens"],
+            "merge_differ": summ["merge_differ"], "merge_illegal": summ["merge_illegal"],
+            "append_rows_illegal": summ["append_rows_illegal"],
+            "ok": bool(same_bits and float(d.max()) <= 2e-2 and summ["merge_illegal"] == 0 and summ["append_rows_illegal"] == 0)}
+
+
+def run_power_law(mixer, params, q, k, v, gate, B, T, C, W, D, h_loc, peaks, reps):
+    """Prefill tokens/s with the reference's native schedule (power_law, factor 16, exponent 0.5, cap 1024 means)."""
+    import math as _m
+
+    from kvm_paper_b200 import _lib, ops
+
+    cap = mixer.max_state_len
+
+    def desired(ctx_len, available_context, current):
+        target = max(int(_m.floor(16.0 * (float(max(int(ctx_len), 0)) ** 0.5))), C)
+        return max(min(target, max(int(available_context), 0), cap), max(int(current), 0))
+
+    plan = ops.build_prefill_plan(T, C, W, desired)
+    runner = ops.PrefillRunner(params, B, plan)
+
+    def timed(phases):
+        runner.run(q, k, v, gate, phases=phases)
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(reps):
+            runner.run(q, k, v, gate, phases=phases)
+        b.record()
+        torch.cuda.synchronize()
+        return a.elapsed_time(b) / reps
+
+    total = timed(_lib.PREFILL_CHAIN | _lib.PREFILL_ATTENTION)
+    chain = timed(_lib.PREFILL_CHAIN)
+    attn = timed(_lib.PREFILL_ATTENTION)
+    status = "ok"
+    try:
+        runner.run(q, k, v, gate)
+        runner.check_status()
+    except Exception as exc:
+        status = str(exc)
+    flops = 4.0 * D * attention_pairs(T, C, W, plan) * B * h_loc
+    tf = flops / (attn * 1e-3) / 1e12
+    return {"schedule": "power_law 16*sqrt(context), cap 1024 means", "final_means": plan.final_state_len,
+            "max_appends_per_block": max(plan.n_append[1:]), "value": round(B * T / (total * 1e-3), 1), "unit": UNIT,
+            "ms_per_step": round(total, 4), "chain_ms": round(chain, 4), "attention_ms": round(attn, 4),
+            "attention_tflops": round(tf, 1), "attention_frac": round(tf / peaks["bf16_tflops"], 4),
+            "algorithmic_flops": flops, "status": status}
 
 
 # DRAM traffic of the dominant kernels from ncu captures (dram__bytes_read.sum + dram__bytes_write.sum of one
@@ -456,9 +553,27 @@ def run_decode(args, dev, rank, world, peaks):
         dist.all_reduce(nb, op=dist.ReduceOp.SUM)
     ms = float(t.item())
     gbs = float(nb.item()) / world / (ms * 1e-3) / 1e9  # per GPU
+    status = "ok"
+    try:
+        cache.check_status()
+    except Exception as exc:
+        status = str(exc)
+    n_memory_updates = int(cache.update_count)
+    # the drop-in route: one call of KvmDecodeCache.step per token (what forward_single does), host bookkeeping,
+    # pinned copy and ctypes call included
+    restore()
+    n_api = min(steps, 256)
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    for i in range(n_api):
+        cache.step(q[i], k[i], v[i], g[i])
+    torch.cuda.synchronize()
+    api_ms = (time.perf_counter() - t0) * 1e3 / n_api
     return {"metric": "kvm_decode_tokens_per_s", "value": round(c["n_seq"] * steps / (ms * 1e-3), 1), "unit": UNIT,
             "sequences": c["n_seq"], "steps": steps, "ms_per_step": round(ms / steps, 4),
-            "host_wall_ms_per_step": round(wall * 1e3 / steps, 4), "memory_updates": int(cache.update_count),
+            "host_wall_ms_per_step": round(wall * 1e3 / steps, 4), "memory_updates": n_memory_updates,
+            "status": status, "step_api_ms_per_token": round(api_ms, 4),
+            "step_api_tokens_per_s": round(n_loc * world / (api_ms * 1e-3), 1),
             "workload": "BASELINE configs[2]: 64 ragged sequences, contexts U[4096,65536] (seed 3), 16 heads x 128, "
                         "block 256, +1 mean per block; sequences sharded over ranks",
             "roofline": {"bound": "hbm", "kernel": "kvm_decode_attn_kernel", "achieved": round(gbs, 1),

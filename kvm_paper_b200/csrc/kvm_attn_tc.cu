@@ -421,6 +421,7 @@ kvm_attn_prefill_tc_kernel(LayerDev L, long long T, Tensor4 q, Tensor4 k, Tensor
                            int* __restrict__ status, const __grid_constant__ AttnMaps maps) {
   using CF = Cfg<NQ>;
   extern __shared__ __align__(1024) unsigned char smem[];
+  if (*status != 0) return;  // an earlier kernel of this prefill gave up: the version tables are not to be trusted
   Bars* bars = reinterpret_cast<Bars*>(smem + CF::kOffBar);
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int C = L.C;

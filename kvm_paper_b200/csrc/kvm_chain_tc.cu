@@ -897,7 +897,9 @@ constexpr int kVpQueue = 4;  // routed tokens of a row whose value rows are fetc
 __global__ void __launch_bounds__(kVpWarps * 32, 2)
 kvm_vpass_kernel(LayerDev L, Tensor4 v, Tensor4 gate, const kvm_update_plan* __restrict__ plan, int n_plan,
                  const int* __restrict__ route, MemoryDev mem, bf16* __restrict__ pool_v, long long pool_rows,
-                 const int* __restrict__ ver_idx, long long ver_rows, int s_final, int tile_updates) {
+                 const int* __restrict__ ver_idx, long long ver_rows, int s_final, int tile_updates,
+                 const int* __restrict__ status) {
+  if (*status != 0) return;  // the chain gave up: its routing decisions and version tables are not to be trusted
   extern __shared__ __align__(16) unsigned char vsm[];
   short* rt = reinterpret_cast<short*>(vsm);                                        // [tile_updates][C] decisions of the tile
   int* vrow = reinterpret_cast<int*>(vsm + (size_t)tile_updates * L.C * 2);         // [n_plan] version_row of every update
@@ -1166,7 +1168,7 @@ cudaError_t launch_chain_tc(const LayerDev& L, int batch, Tensor4 v, Tensor4 gat
   if (e != cudaSuccess) return e;
   dim3 vgrid((unsigned)ceil_div(s_max, kVpWarps), rows);
   kvm_vpass_kernel<<<vgrid, kVpWarps * 32, vsmem, stream>>>(L, v, gate, plan_dev, n_plan, route, mem, ver_idx ? pool_v : nullptr,
-                                                            pool_rows, ver_idx, ver_rows, s_max, tile_updates);
+                                                            pool_rows, ver_idx, ver_rows, s_max, tile_updates, status);
   return cudaGetLastError();
 }
 

@@ -233,7 +233,9 @@ __global__ void __launch_bounds__(BM * 2)
 kvm_attn_prefill_kernel(LayerDev L, long long T, Tensor4 q, Tensor4 k, Tensor4 v,
                         const kvm_update_plan* __restrict__ plan, const bf16* __restrict__ pool_k,
                         const bf16* __restrict__ pool_v, long long pool_rows, const int* __restrict__ ver_idx,
-                        long long ver_rows, bf16* __restrict__ out, int tiles_per_block, int j_begin, float sm_scale) {
+                        long long ver_rows, bf16* __restrict__ out, int tiles_per_block, int j_begin, float sm_scale,
+                        const int* __restrict__ status) {
+  if (*status != 0) return;  // an earlier kernel of this prefill gave up: the version tables are not to be trusted
   constexpr int NT = BM * 2;
   constexpr int KS = D / 16;       // k-steps of QK^T
   constexpr int NT8 = kAttnBN / 8; // n8 tiles of a score tile
@@ -526,7 +528,7 @@ static cudaError_t launch_prefill(const LayerDev& L, int batch, long long T, Ten
   if (e != cudaSuccess) return e;
   dim3 grid(n_qblocks * tiles_per_block, batch * L.Hq);
   kvm_attn_prefill_kernel<D, BM><<<grid, BM * 2, smem_a, stream>>>(L, T, q, k, v, plan_dev, pool_k, pool_v, pool_rows, ver_idx,
-                                                                  ver_rows, out, tiles_per_block, 0, 1.0f / sqrtf((float)D));
+                                                                  ver_rows, out, tiles_per_block, 0, 1.0f / sqrtf((float)D), status);
   return cudaGetLastError();
 }
 

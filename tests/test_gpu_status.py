@@ -61,3 +61,33 @@ def test_decode_status_word_is_reported_once():
     cache.check_status()
     cache.step(*step)
     cache.check_status()
+
+
+def test_a_withheld_arrival_runs_a_bounded_wait_out_and_the_kernel_returns():
+    """The device half of the path.  With the test hook of the ABI the chain kernel's issuing thread withholds one
+    barrier arrival of the first update and the wait limit is a fraction of a millisecond: the warps that wait for
+    that arrival give up, every role of every CTA of the cluster leaves through the common exit (tensor memory
+    freed, nothing in flight), the kernels behind it see the status and do nothing, and the host reads
+    KVM_ERR_DEVICE_TIMEOUT.  Nothing faults and nothing hangs: the next ordinary run on the same buffers is clean
+    and gives the bits of an undisturbed run."""
+    torch.manual_seed(2)
+    C, H, T = 128, 2, 128 * 5 + 9
+    spec = gh.bf16_spec(ko.KvmSpec(H, H, 128, 128, 64, C, 2, 4, 1, "plus_one", state_min_len=C))
+    q = torch.nn.functional.layer_norm(torch.randn(1, T, H, 128), (128,)).bfloat16().transpose(1, 2).cuda()
+    k = torch.nn.functional.layer_norm(torch.randn(1, T, H, 128), (128,)).bfloat16().transpose(1, 2).cuda()
+    v = torch.randn(1, T, H, 128).bfloat16().transpose(1, 2).cuda()
+    g = (1 + torch.nn.functional.elu(0.5 * torch.randn(1, T, H, 1))).bfloat16().transpose(1, 2).cuda()
+    params = gh.layer_params(spec)
+    plan = ops.build_prefill_plan(T, C, 2, gh.desired_fn(spec))
+    want = ops.prefill_forward(params, q, k, v, g, plan, check=True)
+    want_out, want_k = want.out.clone(), want.memory.k_sum.clone()
+    runner = ops.PrefillRunner(params, 1, plan)
+    runner.ws.zero_()
+    runner.run(q, k, v, g, phases=_lib.PREFILL_CHAIN | _lib.PREFILL_ATTENTION | _lib.PREFILL_TEST_WITHHOLD_ARRIVAL)
+    with pytest.raises(_lib.KvmError) as err:
+        runner.check_status()
+    assert err.value.code == 3
+    runner.check_status()               # reported once
+    out = runner.run(q, k, v, g)        # the device and the buffers are fine
+    runner.check_status()
+    assert torch.equal(out, want_out) and torch.equal(runner.memory.k_sum, want_k)
