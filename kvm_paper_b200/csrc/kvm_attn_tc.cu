@@ -27,21 +27,6 @@
 
 namespace kvm {
 
-// Optional wait/compute cycle counters per role (development builds with -DKVM_PROFILE_PHASES only).
-#ifdef KVM_PROFILE_PHASES
-__device__ long long g_tc_cycles[32];
-#define TC_T0() long long _tc_t = clock64()
-#define TC_MARK(i, cond)                                      \
-  do {                                                        \
-    long long _n = clock64();                                 \
-    if (cond) atomicAdd((unsigned long long*)&g_tc_cycles[i], (unsigned long long)(_n - _tc_t)); \
-    _tc_t = _n;                                               \
-  } while (0)
-#else
-#define TC_T0() do {} while (0)
-#define TC_MARK(i, cond) do {} while (0)
-#endif
-
 namespace {
 
 constexpr int BM = 128;  // rows per query tile
@@ -50,14 +35,11 @@ constexpr int HD = 128;  // head dim
 constexpr int kStages = 4;
 constexpr int kLoaders = 4;
 constexpr float kRescaleThreshold = 8.0f;  // log2 units
-#ifndef KVM_ATTN_LEAD
-#define KVM_ATTN_LEAD 2
-#endif
 // Tile order of a CTA: `lead` window tiles (they arrive by TMA right after the CTA starts, while the first memory
 // tiles still wait for the plan entry, the version table and the row gather), then the memory tiles, then the
 // remaining window tiles.  `lead` is at most the number of window tiles that every query tile of the CTA uses,
 // so each query tile still consumes a prefix of the order.
-constexpr int kLeadWindowTiles = KVM_ATTN_LEAD;
+constexpr int kLeadWindowTiles = 2;
 
 template <int NQ>
 struct Cfg {
@@ -159,18 +141,13 @@ __device__ __forceinline__ bool loader_role(const Slice<NQ>& sl, unsigned char* 
   // lane -> fixed 16-byte column chunk cc and row parity; iteration `it` covers rows 2*it and 2*it+1
   const int cc = lane & 15, rh = lane >> 4;
   const uint32_t col_off = (uint32_t)(cc >> 3) * 8192u;
-  const bool prof = blockIdx.x == 0 && blockIdx.y == 0 && lane == 0 && lw == 0;
-  (void)prof;
-  TC_T0();
   for (int t = lw; t < sl.n_max; t += kLoaders) {
     if (t < sl.lead) continue;  // issued when the CTA started
     if (t >= kStages && !warp_wait(&bars->kv_empty[stage], ((t / kStages) - 1) & 1)) return false;
-    TC_MARK(0, prof);
     const bool is_mem = t < sl.lead + sl.n_mem_tiles;
     if (!is_mem) {
       if (lane == 0) issue_window_tile<NQ>(smem, bars, maps, sl.b, sl.hkv, stage, (int)(sl.bb + (long long)(t - sl.n_mem_tiles) * BN));
       __syncwarp();
-      TC_MARK(1, prof);
       continue;
     }
     const int row0 = (t - sl.lead) * BN;
@@ -187,12 +164,9 @@ __device__ __forceinline__ bool loader_role(const Slice<NQ>& sl, unsigned char* 
       cp_async16(dV + off, sl.mv + src, ok ? 16 : 0);
     }
     cp_async_commit();
-    TC_MARK(1, prof);
     cp_async_wait<0>();       // this warp's tile has landed
-    TC_MARK(2, prof);
     tc::fence_proxy_async();  // generic-proxy writes -> visible to the tensor core's operand reads
     __syncwarp();
-    TC_MARK(3, prof);
     if (lane == 0) tc::mbar_arrive(&bars->kv_full[stage]);
   }
   return true;
@@ -233,14 +207,10 @@ __device__ __forceinline__ bool mma_role(const Slice<NQ>& sl, unsigned char* sme
     tc::tc_fence_after_sync();
     issue_qk(t);
   }
-  const bool prof = blockIdx.x == 0 && blockIdx.y == 0 && qi == NQ - 1;
-  (void)prof;
-  TC_T0();
   for (int t = 0; t < sl.n_max; ++t) {
     const int stage = t % kStages;
     if (t < nt) {
       if (!tc::mbar_wait(&bars->p_full[qi], t & 1)) return false;
-      TC_MARK(4, prof);
       tc::tc_fence_after_sync();
       const uint64_t db0 = dV + (uint64_t)((stage * 16384) >> 4);
       // P (bf16) lies in the first 32 columns of the score buffer it was computed from: 8 columns per k-step
@@ -254,17 +224,14 @@ __device__ __forceinline__ bool mma_role(const Slice<NQ>& sl, unsigned char* sme
       // The epilogue waits on a barrier of its own: the softmax only waits on pv_done before a rescale, so at
       // the end of the tile loop pv_done may be two phases behind, which a parity wait cannot tell from done.
       if (t == nt - 1) tc::mma_commit(&bars->o_final[qi]);
-      TC_MARK(6, prof);
     } else {
       if (!tc::mbar_wait(&bars->kv_full[stage], (t / kStages) & 1)) return false;
       tc::mbar_arrive(&bars->kv_empty[stage]);
     }
     if (t + 2 < nt) {
       if (!tc::mbar_wait(&bars->kv_full[(t + 2) % kStages], ((t + 2) / kStages) & 1)) return false;
-      TC_MARK(7, prof);
       tc::tc_fence_after_sync();
       issue_qk(t + 2);
-      TC_MARK(8, prof);
     }
   }
   return true;
@@ -287,19 +254,14 @@ __device__ __forceinline__ bool softmax_role(const Slice<NQ>& sl, const LayerDev
   const float scale_mem = sm_scale * L.state_temp[sl.hq] * kLog2e;
   const float scale_win = sm_scale * L.front_temp[sl.hq] * kLog2e;
   float m_run = -INFINITY, l_run = 0.f;
-  const bool prof = blockIdx.x == 0 && blockIdx.y == 0 && row == 0 && qi == NQ - 1;
-  (void)prof;
-  TC_T0();
   for (int t = 0; t < nt; ++t) {
     const int sbuf = t & 1;
     if (!warp_wait(&bars->s_full[qi][sbuf], (t >> 1) & 1)) return false;
-    TC_MARK(10, prof);
     tc::tc_fence_after_sync();
     uint32_t sr[2][32];
     tc::tmem_ld32(lane_addr + (uint32_t)((qi * 2 + sbuf) * BN), sr[0]);
     tc::tmem_ld32(lane_addr + (uint32_t)((qi * 2 + sbuf) * BN + 32), sr[1]);
     tc::tmem_ld_wait();
-    TC_MARK(11, prof);
     const bool is_mem = t >= lead && t < lead + nm;
     const int base = (is_mem ? t - lead : (t < lead ? t : t - nm)) * BN;  // first key of the tile within its segment
     const float sc = is_mem ? scale_mem : scale_win;
@@ -320,12 +282,10 @@ __device__ __forceinline__ bool softmax_role(const Slice<NQ>& sl, const LayerDev
     const float tmax = fmaxf(tm0, tm1) * sc;  // sc > 0
     const bool need = tmax > m_run + kRescaleThreshold || (m_run == -INFINITY && tmax > -INFINITY);
     const bool warp_need = __any_sync(0xffffffffu, need);
-    TC_MARK(12, prof);
     if (warp_need) {
       // the running output may only be touched between P V of tile t-1 (complete) and of tile t (not yet issued:
       // it waits for this warp's arrival below)
       if (t > 0 && !warp_wait(&bars->pv_done[qi], (t - 1) & 1)) return false;
-      TC_MARK(13, prof);
       const float m_new = fmaxf(m_run, tmax);
       const float alpha = (m_run == -INFINITY) ? 0.f : ex2(m_run - m_new);
       l_run *= alpha;
@@ -344,7 +304,6 @@ __device__ __forceinline__ bool softmax_role(const Slice<NQ>& sl, const LayerDev
       }
       m_run = m_new;
     }
-    TC_MARK(14, prof);
     const float neg_m = (m_run == -INFINITY) ? 0.f : -m_run;
     float ls0 = 0.f, ls1 = 0.f;
     // P replaces the scores it came from (all 64 columns of this row are in registers): the A operand of P V,
@@ -364,11 +323,9 @@ __device__ __forceinline__ bool softmax_role(const Slice<NQ>& sl, const LayerDev
     }
     l_run += ls0 + ls1;
     tc::tmem_st_wait();
-    TC_MARK(15, prof);
     tc::tc_fence_before_sync();
     __syncwarp();
     if (lane == 0) tc::mbar_arrive(&bars->p_full[qi]);
-    TC_MARK(16, prof);
   }
   // epilogue: O / l -> bf16 -> the query tile's operand buffer (all QK of this tile have completed), in the
   // 128-byte-swizzled layout of a [128 tokens][64] box per half of the head dimension -> two TMA stores into
@@ -557,16 +514,6 @@ static cudaError_t launch_nq(const LayerDev& L, int batch, long long T, Tensor4 
   return cudaGetLastError();
 }
 
-#ifdef KVM_PROFILE_PHASES
-extern "C" int kvm_debug_tc_cycles(long long* out32, int reset) {
-  cudaError_t e = cudaMemcpyFromSymbol(out32, g_tc_cycles, sizeof(long long) * 32);
-  if (e == cudaSuccess && reset) {
-    long long z[32] = {0};
-    e = cudaMemcpyToSymbol(g_tc_cycles, z, sizeof(z));
-  }
-  return (int)e;
-}
-#endif
 
 cudaError_t launch_attn_tc(const LayerDev& L, int batch, long long T, Tensor4 q, Tensor4 k, Tensor4 v,
                            const kvm_update_plan* plan_dev, const bf16* pool_k, const bf16* pool_v, long long pool_rows,

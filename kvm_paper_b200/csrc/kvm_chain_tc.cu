@@ -46,7 +46,7 @@ constexpr int kThreads = kWorkers + 32;       // + the issuing warp (one elected
 constexpr int kChunk = 256;                   // memory rows per MMA instruction and per tensor-memory chunk (the N limit)
 constexpr int kRowPad = 64;                   // granularity of the resident rows per CTA
 constexpr uint32_t kTmemCols = 512;
-constexpr int kMaxSmem = 225 * 1024;           // dynamic part; the kernel also holds 1 KB of static shared memory
+constexpr int kMaxSmem = 226 * 1024;          // dynamic part; the kernel also holds 1 KB of static shared memory
 
 __host__ __device__ inline int ceil_div(int a, int b) { return (a + b - 1) / b; }
 
@@ -61,13 +61,13 @@ struct Layout {
     P = off;    off += (uint32_t)C * 256u;               // prepared keys of the block; later the one-hot operand
     G = off;    off += (uint32_t)C * 256u;               // gated keys of the block
     xbuf = off; off += 2u * nc * C * 8u;                 // [parity][source CTA][token] {value, row}
-    part = off; off += 2u * C * 8u;                      // [column half][token] {value, row}: the two halves of a chunk
+    part = off; off += (2u * C * 8u > 4096u ? 2u * C * 8u : 4096u);                      // [column half][token] {value, row}: the two halves of a chunk (4 KB at least: see stat)
     tok = off;  off += 4u * C * 4u;                      // nov[C] f32, idx[C], pos[C], list[C]
     const uint32_t sp = (uint32_t)((s_max + 63) & ~31);  // padded row count: every region below stays 16-byte aligned
-    rowi = off; off += sp * 8u;                          // cur[sp] i32, gci[sp] i16, lci[sp] i16
-    tloc = off; off += 2u * C * 2u + 2u * sp;            // touched_local[C] u16, spare, stamps[sp] u16 (update that last touched the row)
-    stat = off; off += 2u * 4u * 128u * 4u;              // LayerNorm partial sums of the scatter epilogue
-    bars = off; off += 512u;
+    rowi = off; off += sp * 4u + sp * 2u + ((2u * Rcap + 15u) & ~15u);  // cur[sp] i32, gci[sp] i16, lci[Rcap] i16 (by local row)
+    tloc = off; off += ((2u * C + 15u) & ~15u) + 2u * sp;  // touched_local[C] u16, stamps[sp] u16 (update that last touched the row)
+    stat = part;                                         // LayerNorm partial sums of the scatter epilogue (the routing partials are dead by then)
+    bars = off; off += 384u;
     total = (off + 15u) & ~15u;
   }
 };
@@ -86,7 +86,7 @@ struct Bars {
   int red_t[32];
 };
 
-static_assert(sizeof(Bars) <= 512, "the barrier block outgrew its shared-memory region");
+static_assert(sizeof(Bars) <= 384, "the barrier block outgrew its shared-memory region");
 
 struct Args {
   LayerDev L;
@@ -330,9 +330,9 @@ struct Workers {
   __device__ __forceinline__ int* cur() const { return reinterpret_cast<int*>(smem + lay.rowi); }
   __device__ __forceinline__ int padded_rows() const { return (a.s_max + 63) & ~31; }
   __device__ __forceinline__ short* gci() const { return reinterpret_cast<short*>(smem + lay.rowi + (uint32_t)padded_rows() * 4u); }
-  __device__ __forceinline__ short* lci() const { return gci() + padded_rows(); }
+  __device__ __forceinline__ short* lci() const { return gci() + padded_rows(); }  // indexed by the local row r / nc
   __device__ __forceinline__ unsigned short* tloc() const { return reinterpret_cast<unsigned short*>(smem + lay.tloc); }
-  __device__ __forceinline__ unsigned short* tf() const { return reinterpret_cast<unsigned short*>(smem + lay.tloc + 2u * a.L.C * 2u); }
+  __device__ __forceinline__ unsigned short* tf() const { return reinterpret_cast<unsigned short*>(smem + lay.tloc + ((2u * a.L.C + 15u) & ~15u)); }
   __device__ __forceinline__ float2* part(int half) const { return reinterpret_cast<float2*>(smem + lay.part) + half * a.L.C; }
   __device__ __forceinline__ float2* xb(int parity, int src) const { return reinterpret_cast<float2*>(smem + lay.xbuf) + (size_t)(parity * a.nc + src) * a.L.C; }
   __device__ __forceinline__ float* stat(int which) const { return reinterpret_cast<float*>(smem + lay.stat) + which * 4 * 128; }
@@ -662,7 +662,7 @@ struct Workers {
             gci()[r] = (short)ga;
             if (r % nc == crank) {
               const int ll = pl_ + __popc(bal & mine_mask & lt);
-              lci()[r] = (short)ll;
+              lci()[r / nc] = (short)ll;
               tloc()[ll] = (unsigned short)r;
             }
           }
@@ -688,7 +688,7 @@ struct Workers {
             wsync();
           }
           if (my >= 0 && my % nc == crank) {
-            const int ll = lci()[my] - p * 128;
+            const int ll = lci()[my / nc] - p * 128;
             if (ll >= 0 && ll < 128) {
               const uint32_t off = (uint32_t)(tid >> 6) * (128u * 128u) + tc::sw128_offset(ll, tid & 63);
               *reinterpret_cast<unsigned short*>(smem + lay.P + off) = 0x3F80;  // bf16 1.0
@@ -828,7 +828,7 @@ kvm_chain_tc_kernel(const __grid_constant__ Args a, const __grid_constant__ Maps
     uint4* r4 = reinterpret_cast<uint4*>(smem + lay.R);
     for (int i = tid; i < lay.Rcap * 16; i += kThreads) r4[i] = make_uint4(0, 0, 0, 0);
     for (int i = tid; i < a.s_max; i += kThreads) reinterpret_cast<int*>(smem + lay.rowi)[i] = 0;
-    unsigned short* stamps = reinterpret_cast<unsigned short*>(smem + lay.tloc + 2u * a.L.C * 2u);
+    unsigned short* stamps = reinterpret_cast<unsigned short*>(smem + lay.tloc + ((2u * a.L.C + 15u) & ~15u));
     for (int i = tid; i < a.s_max; i += kThreads) stamps[i] = 0;  // update numbers start at 1
   }
   if (tid == 0) {

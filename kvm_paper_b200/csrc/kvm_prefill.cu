@@ -545,16 +545,6 @@ cudaError_t prefill_dispatch(int D, const LayerDev& L, int batch, long long T, T
   return cudaErrorInvalidValue;
 }
 
-#ifdef KVM_PROFILE_PHASES
-extern "C" int kvm_debug_phase_cycles(long long* out16, int reset) {
-  cudaError_t e = cudaMemcpyFromSymbol(out16, g_phase_cycles, sizeof(long long) * 16);
-  if (e == cudaSuccess && reset) {
-    long long z[16] = {0};
-    e = cudaMemcpyToSymbol(g_phase_cycles, z, sizeof(z));
-  }
-  return (int)e;
-}
-#endif
 
 size_t update_smem_bytes(int D, int C, int capacity) {  // of the variant without the staged block
   switch (D) {

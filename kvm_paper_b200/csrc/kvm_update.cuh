@@ -23,23 +23,6 @@
 
 namespace kvm {
 
-// Optional per-phase cycle counters of the update (development builds with -DKVM_PROFILE_PHASES only).
-#ifdef KVM_PROFILE_PHASES
-__device__ long long g_phase_cycles[16];
-#define KVM_PHASE_BEGIN() long long _t_prev = clock64()
-#define KVM_PHASE_MARK(i)                                                  \
-  do {                                                                     \
-    if (blockIdx.x == 0 && threadIdx.x == 0) {                             \
-      long long _t = clock64();                                            \
-      g_phase_cycles[i] += _t - _t_prev;                                   \
-      _t_prev = _t;                                                        \
-    }                                                                      \
-  } while (0)
-#else
-#define KVM_PHASE_BEGIN() do {} while (0)
-#define KVM_PHASE_MARK(i) do {} while (0)
-#endif
-
 constexpr int kScanTile = 64;  // memory rows per shared-memory tile of the routing GEMM
 constexpr int kMaxCluster = 4; // CTAs that may share one kv row
 constexpr int kDirectRows = 4; // up to this many appended rows are scored with plain dot products
@@ -639,8 +622,6 @@ __device__ void memory_update(const LayerDev& L, const TokenSrc& src, const Memo
   if constexpr (SB && PKR && D == 128 && NT == 512) use_tc = s.use_tc && (C == 128 || C == 256) && n_merge > 0;
   const bool defer_v = use_tc;
   int tiles_in_flight = 0;
-
-  KVM_PHASE_BEGIN();
   // ---- 0. bring the block in: keys first (needed at once), values behind them
   BlockView blk;
   blk.g = s.g_s;
@@ -696,7 +677,6 @@ __device__ void memory_update(const LayerDev& L, const TokenSrc& src, const Memo
   }
   if constexpr (SB) cp_async_wait<1>();
   __syncthreads();
-  KVM_PHASE_MARK(0);
 
   // ---- 1. prepared keys (in place in shared memory, or into the global scratch); 8 lanes per token
   if constexpr (PKR && !SB) {
@@ -718,7 +698,6 @@ __device__ void memory_update(const LayerDev& L, const TokenSrc& src, const Memo
     }
   }
   __syncthreads();
-  KVM_PHASE_MARK(1);
 
   const int protected_rows = min(L.sink_len, S_after);
 
@@ -769,7 +748,6 @@ __device__ void memory_update(const LayerDev& L, const TokenSrc& src, const Memo
       __syncthreads();
     }
   }
-  KVM_PHASE_MARK(2);
   if (n_append == 1 && n_merge > 0) {
     // one append: the token with the lowest novelty score, lowest index among equals (= rank 0 of the
     // stable ranking below), found by a block-wide reduction instead of the O(C) count per token
@@ -815,7 +793,6 @@ __device__ void memory_update(const LayerDev& L, const TokenSrc& src, const Memo
     }
     __syncthreads();
   }
-  KVM_PHASE_MARK(3);
   if (n_append > 0) {
     // position of every appended token among the appended ones (token order): ballot prefix
     const int f = tid < C ? s.flag[tid] : 0;
@@ -875,7 +852,6 @@ __device__ void memory_update(const LayerDev& L, const TokenSrc& src, const Memo
     __syncthreads();
     return;
   }
-  KVM_PHASE_MARK(4);
 
   // ---- 3. merge targets among the rows that were just appended (append-before-merge)
   if (n_append > 0 && n_append <= kDirectRows) {
@@ -911,7 +887,6 @@ __device__ void memory_update(const LayerDev& L, const TokenSrc& src, const Memo
   } else if (n_append > 0) {
     scan_memory<D, NT>(blk, L.gate_keys != 0, C, view.k, view.cur, S_before, S_after, false, protected_rows, s);
   }
-  KVM_PHASE_MARK(5);
 
   // ---- 4. group the merged tokens by target row, token order inside a group
   if (tid < C && s.flag[tid]) s.idx[tid] = -1;
@@ -975,7 +950,6 @@ __device__ void memory_update(const LayerDev& L, const TokenSrc& src, const Memo
     if (route_out && crank == 0) route_out[tid] = s.flag[tid] ? -(1 + S_before + s.pos[tid]) : s.idx[tid];
   }
   __syncthreads();
-  KVM_PHASE_MARK(6);
 
   // ---- 5. fixed-order accumulation into the touched rows and refresh of their attention view;
   //         eight lanes per row; the first half of the block does the key rows, the second half the values
@@ -1034,7 +1008,6 @@ __device__ void memory_update(const LayerDev& L, const TokenSrc& src, const Memo
   }
   __syncthreads();
   if (nc > 1) cluster_sync_all();  // rows refreshed by the other CTAs are visible before the next update scans them
-  KVM_PHASE_MARK(7);
 }
 
 }  // namespace kvm
