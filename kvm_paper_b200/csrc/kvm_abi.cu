@@ -11,8 +11,8 @@ namespace kvm {
 cudaError_t prefill_dispatch(int D, const LayerDev& L, int batch, long long T, Tensor4 q, Tensor4 k, Tensor4 v,
                              Tensor4 gate, const kvm_update_plan* plan_dev, int n_plan, long long ver_rows,
                              MemoryDev mem, bf16* out, int* route, bf16* pool_k, bf16* pool_v, long long pool_rows,
-                             int* ver_idx, bf16* pk_scr, bf16* pk_all, bf16* gk_all, int* route_ws, int s_final, int* status,
-                             unsigned phases, cudaStream_t stream);
+                             int* ver_idx, bf16* pk_scr, bf16* pk_all, bf16* gk_all, int* route_ws, int* born_ws, unsigned* tbits_ws,
+                             int s_final, int* status, unsigned phases, cudaStream_t stream);
 size_t update_smem_bytes(int D, int C, int capacity);
 cudaError_t decode_dispatch(int D, const LayerDev& L, int batch, const DecodeCacheDev& cache, Tensor4 q, Tensor4 k,
                             Tensor4 v, Tensor4 gate, const int* n_append, int any_update, int max_rows, bf16* out,
@@ -108,7 +108,7 @@ int check_memory(const kvm_memory& m, const kvm_layer* l) {
 // rows per kv row), the per-version index tables, and the prepared-key scratch of the update variant
 // that cannot stage a block in shared memory.
 struct PrefillWs {
-  size_t status, pool_k, pool_v, ver_idx, pk, pk_all, gk_all, route, total;
+  size_t status, pool_k, pool_v, ver_idx, pk, pk_all, gk_all, route, born, tbits, total;
   long long pool_rows;
 };
 PrefillWs prefill_ws(const kvm_layer* l, int batch, long long seq_len, long long ver_rows) {
@@ -131,6 +131,10 @@ PrefillWs prefill_ws(const kvm_layer* l, int batch, long long seq_len, long long
   const bool tc = D == 128 && (C == 128 || C == 256) && n_plan > 1;
   w.gk_all = off; off = align_up(off + (tc ? rows * (size_t)(n_plan * C) * D * 2 : 0), 256);
   w.route = off; off = align_up(off + (tc ? rows * (size_t)(n_plan * C) * 4 : 0), 256);
+  // for the value side: the token that created each memory row (at most C * n_plan rows), one bit per (update, row)
+  const size_t max_rows = (size_t)C * n_plan;
+  w.born = off; off = align_up(off + (tc ? rows * max_rows * 4 : 0), 256);
+  w.tbits = off; off = align_up(off + (tc ? rows * (size_t)n_plan * ((max_rows + 31) / 32) * 4 : 0), 256);
   w.total = off;
   return w;
 }
@@ -245,7 +249,8 @@ int kvm_prefill_forward(const kvm_layer* layer, int32_t batch, int64_t seq_len, 
                                    reinterpret_cast<bf16*>(wsb + ws.pool_k), reinterpret_cast<bf16*>(wsb + ws.pool_v),
                                    ws.pool_rows, reinterpret_cast<int*>(wsb + ws.ver_idx),
                                    reinterpret_cast<bf16*>(wsb + ws.pk), reinterpret_cast<bf16*>(wsb + ws.pk_all),
-                                   reinterpret_cast<bf16*>(wsb + ws.gk_all), reinterpret_cast<int*>(wsb + ws.route), (int)S,
+                                   reinterpret_cast<bf16*>(wsb + ws.gk_all), reinterpret_cast<int*>(wsb + ws.route),
+                                   reinterpret_cast<int*>(wsb + ws.born), reinterpret_cast<unsigned*>(wsb + ws.tbits), (int)S,
                                    reinterpret_cast<int*>(wsb + ws.status), phases,
                                    static_cast<cudaStream_t>(stream));
   if (e != cudaSuccess) return cuda_fail(e, "kvm_prefill_forward");

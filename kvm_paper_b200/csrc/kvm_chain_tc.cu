@@ -103,6 +103,7 @@ struct Args {
   int* ver_idx;          // [rows][ver_rows] or null
   long long ver_rows;
   int* route;            // [rows][n_plan][C]
+  int* born;             // [rows][s_max] token that created each memory row, or null
   int* status;
   uint32_t wait_limit;
   uint32_t test_flags;   // bit 0: the issuer withholds one commit (exercises the timeout path)
@@ -502,7 +503,7 @@ struct Workers {
   }
 
   // rows [S0, S0 + na) from the tokens list()[0..na): `src_off` = operand holding what is stored (prepared or gated keys)
-  __device__ __forceinline__ void append_rows(int S0, int na, uint32_t src_off) {
+  __device__ __forceinline__ void append_rows(int S0, int na, uint32_t src_off, int u) {
     const int gl = tid & 7, grp = tid >> 3;
     for (int base = 0; base < na; base += kWorkers / 8) {  // whole warps stay together: the LayerNorm uses group shuffles
       const int p = base + grp;
@@ -512,7 +513,9 @@ struct Workers {
       const int t = list()[act ? p : 0];
       RowVec<HD, 8> x;
       load_block_row(x, src_off, t, gl);
-      store_key_row(x, r, pool_next + p, gl, act && (r % a.nc == crank));
+      const bool mine = act && (r % a.nc == crank);
+      store_key_row(x, r, pool_next + p, gl, mine);
+      if (mine && gl == 0 && a.born) a.born[(size_t)row * a.s_max + r] = u * a.L.C + t;
     }
     for (int i = tid; i < na; i += kWorkers) cur()[S0 + i] = pool_next + i;
     pool_next += na;
@@ -533,7 +536,7 @@ struct Workers {
         if (!wvote(ok)) return false;
         if (tid < C) list()[tid] = tid;
         wsync();
-        append_rows(0, na, (a.L.gate_initial && a.L.gate_keys) ? lay.G : lay.P);
+        append_rows(0, na, (a.L.gate_initial && a.L.gate_keys) ? lay.G : lay.P, 0);
         if (crank == 0)
           for (int i = tid; i < C; i += kWorkers) route_row[i] = i < na ? -(1 + i) : 0;
         wsync();
@@ -604,7 +607,7 @@ struct Workers {
           }
         }
         wsync();
-        append_rows(S0, na, (a.L.gate_appends && a.L.gate_keys) ? lay.G : lay.P);
+        append_rows(S0, na, (a.L.gate_appends && a.L.gate_keys) ? lay.G : lay.P, u);
         if (has_nov) signal_issuer();  // the appended rows are in the resident memory: the logits pass may start
       } else if (tid < C) {
         pos()[tid] = -1;
@@ -1122,10 +1125,15 @@ bool chain_tc_supported(int D, const LayerDev& L, int n_plan, int s_max, int row
 
 // The chain for one batch: routing + key side, then the value side.  pk_all / gk_all: [rows][n_plan*C][D] from the
 // pre-pass; route: [rows][n_plan][C].
-cudaError_t launch_chain_tc(const LayerDev& L, int batch, Tensor4 v, Tensor4 gate, const kvm_update_plan* plan_dev, int n_plan,
-                            int s_max, MemoryDev mem, bf16* pool_k, bf16* pool_v, long long pool_rows, int* ver_idx,
-                            long long ver_rows, const bf16* pk_all, const bf16* gk_all, int* route, int* status,
-                            uint32_t wait_limit, uint32_t test_flags, cudaStream_t stream) {
+cudaError_t launch_vside(const LayerDev& L, int batch, long long T, Tensor4 v, Tensor4 gate, const kvm_update_plan* plan_dev,
+                         int n_plan, int s_max, MemoryDev mem, bf16* pool_v, long long pool_rows, const int* ver_idx,
+                         long long ver_rows, const int* route, const int* born, unsigned* tbits, int* status,
+                         uint32_t wait_limit, cudaStream_t stream);
+
+cudaError_t launch_chain_tc(const LayerDev& L, int batch, long long T, Tensor4 v, Tensor4 gate, const kvm_update_plan* plan_dev,
+                            int n_plan, int s_max, MemoryDev mem, bf16* pool_k, bf16* pool_v, long long pool_rows, int* ver_idx,
+                            long long ver_rows, const bf16* pk_all, const bf16* gk_all, int* route, int* born, unsigned* tbits,
+                            int* status, uint32_t wait_limit, uint32_t test_flags, cudaStream_t stream) {
   using namespace chain;
   const int rows = batch * L.Hkv, C = L.C;
   const int nc = chain_tc_cluster_size(C, s_max, rows);
@@ -1144,7 +1152,7 @@ cudaError_t launch_chain_tc(const LayerDev& L, int batch, Tensor4 v, Tensor4 gat
   a.L = L; a.plan = plan_dev; a.n_plan = n_plan; a.nc = nc; a.s_max = s_max; a.n_tok = n_tok;
   a.k_sum = mem.k_sum; a.k_attn = mem.k_attn; a.capacity = mem.capacity;
   a.pool_k = ver_idx ? pool_k : nullptr; a.pool_rows = pool_rows; a.ver_idx = ver_idx; a.ver_rows = ver_rows;
-  a.route = route; a.status = status; a.wait_limit = wait_limit; a.test_flags = test_flags;
+  a.route = route; a.born = born; a.status = status; a.wait_limit = wait_limit; a.test_flags = test_flags;
   cudaError_t e = cudaFuncSetAttribute(kvm_chain_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxSmem);
   if (e != cudaSuccess) return e;
   cudaLaunchConfig_t cfg = {};
@@ -1161,7 +1169,12 @@ cudaError_t launch_chain_tc(const LayerDev& L, int batch, Tensor4 v, Tensor4 gat
   cfg.numAttrs = 1;
   e = cudaLaunchKernelEx(&cfg, kvm_chain_tc_kernel, a, maps);
   if (e != cudaSuccess) return e;
-  // value side: one warp per memory row, the routing decisions of as many updates as fit 64 KB per tile
+  // value side.  With versions: deltas of every (kv row, update) on the tensor cores, then one warp per memory row.
+  if (ver_idx && pool_v)
+    return launch_vside(L, batch, T, v, gate, plan_dev, n_plan, s_max, mem, pool_v, pool_rows, ver_idx, ver_rows, route, born,
+                        tbits, status, wait_limit, stream);
+  // Without (only the final memory is wanted): one warp per memory row walks the routing decisions itself, as many
+  // updates as fit 64 KB per tile
   const int tile_updates = std::max(1, std::min(n_plan, (64 * 1024) / (C * 2)));
   const size_t vsmem = (size_t)tile_updates * C * 2 + (size_t)((n_plan + 3) & ~3) * 4;
   e = cudaFuncSetAttribute(kvm_vpass_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)vsmem);

@@ -433,10 +433,10 @@ kvm_attn_prefill_kernel(LayerDev L, long long T, Tensor4 q, Tensor4 k, Tensor4 v
 
 // ------------------------------------------------------------------------------------- host side
 bool chain_tc_supported(int D, const LayerDev& L, int n_plan, int s_max, int rows);
-cudaError_t launch_chain_tc(const LayerDev& L, int batch, Tensor4 v, Tensor4 gate, const kvm_update_plan* plan_dev, int n_plan,
-                            int s_max, MemoryDev mem, bf16* pool_k, bf16* pool_v, long long pool_rows, int* ver_idx,
-                            long long ver_rows, const bf16* pk_all, const bf16* gk_all, int* route, int* status,
-                            uint32_t wait_limit, uint32_t test_flags, cudaStream_t stream);
+cudaError_t launch_chain_tc(const LayerDev& L, int batch, long long T, Tensor4 v, Tensor4 gate, const kvm_update_plan* plan_dev,
+                            int n_plan, int s_max, MemoryDev mem, bf16* pool_k, bf16* pool_v, long long pool_rows, int* ver_idx,
+                            long long ver_rows, const bf16* pk_all, const bf16* gk_all, int* route, int* born, unsigned* tbits,
+                            int* status, uint32_t wait_limit, uint32_t test_flags, cudaStream_t stream);
 cudaError_t launch_attn_tc(const LayerDev& L, int batch, long long T, Tensor4 q, Tensor4 k, Tensor4 v,
                            const kvm_update_plan* plan_dev, const bf16* pool_k, const bf16* pool_v, long long pool_rows,
                            const int* ver_idx, long long ver_rows, bf16* out, int* status, cudaStream_t stream);
@@ -445,8 +445,8 @@ template <int D>
 static cudaError_t launch_prefill(const LayerDev& L, int batch, long long T, Tensor4 q, Tensor4 k, Tensor4 v, Tensor4 gate,
                                   const kvm_update_plan* plan_dev, int n_plan, long long ver_rows, MemoryDev mem,
                                   bf16* out, int* route, bf16* pool_k, bf16* pool_v, long long pool_rows, int* ver_idx,
-                                  bf16* pk_scr, bf16* pk_all, bf16* gk_all, int* route_ws, int s_final, int* status,
-                                  unsigned phases, cudaStream_t stream) {
+                                  bf16* pk_scr, bf16* pk_all, bf16* gk_all, int* route_ws, int* born_ws, unsigned* tbits_ws,
+                                  int s_final, int* status, unsigned phases, cudaStream_t stream) {
   constexpr int NT = 512;
   const int rows = batch * L.Hkv;
   const int n_qblocks = (int)((T + L.C - 1) / L.C);
@@ -463,9 +463,9 @@ static cudaError_t launch_prefill(const LayerDev& L, int batch, long long T, Ten
   }
   if ((phases & KVM_PREFILL_CHAIN) && tc_chain) {
     const bool test = (phases & KVM_PREFILL_TEST_WITHHOLD_ARRIVAL) != 0;
-    e = launch_chain_tc(L, batch, v, gate, plan_dev, n_plan, s_final, mem, pool_k, pool_v, pool_rows, versions ? ver_idx : nullptr,
-                        ver_rows, pk_all, gk_all, route ? route : route_ws, status, test ? (1u << 11) : tc::kSpinLimit,
-                        test ? 1u : 0u, stream);
+    e = launch_chain_tc(L, batch, T, v, gate, plan_dev, n_plan, s_final, mem, pool_k, pool_v, pool_rows, versions ? ver_idx : nullptr,
+                        ver_rows, pk_all, gk_all, route ? route : route_ws, born_ws, tbits_ws, status,
+                        test ? (1u << 11) : tc::kSpinLimit, test ? 1u : 0u, stream);
     if (e != cudaSuccess) return e;
   } else if (phases & KVM_PREFILL_CHAIN) {
     const bool sb = update_block_fits_smem<D>(L.C, mem.capacity);
@@ -535,12 +535,12 @@ static cudaError_t launch_prefill(const LayerDev& L, int batch, long long T, Ten
 cudaError_t prefill_dispatch(int D, const LayerDev& L, int batch, long long T, Tensor4 q, Tensor4 k, Tensor4 v,
                              Tensor4 gate, const kvm_update_plan* plan_dev, int n_plan, long long ver_rows,
                              MemoryDev mem, bf16* out, int* route, bf16* pool_k, bf16* pool_v, long long pool_rows,
-                             int* ver_idx, bf16* pk_scr, bf16* pk_all, bf16* gk_all, int* route_ws, int s_final, int* status,
-                             unsigned phases, cudaStream_t stream) {
+                             int* ver_idx, bf16* pk_scr, bf16* pk_all, bf16* gk_all, int* route_ws, int* born_ws, unsigned* tbits_ws,
+                             int s_final, int* status, unsigned phases, cudaStream_t stream) {
   switch (D) {
-    case 32: return launch_prefill<32>(L, batch, T, q, k, v, gate, plan_dev, n_plan, ver_rows, mem, out, route, pool_k, pool_v, pool_rows, ver_idx, pk_scr, pk_all, gk_all, route_ws, s_final, status, phases, stream);
-    case 64: return launch_prefill<64>(L, batch, T, q, k, v, gate, plan_dev, n_plan, ver_rows, mem, out, route, pool_k, pool_v, pool_rows, ver_idx, pk_scr, pk_all, gk_all, route_ws, s_final, status, phases, stream);
-    case 128: return launch_prefill<128>(L, batch, T, q, k, v, gate, plan_dev, n_plan, ver_rows, mem, out, route, pool_k, pool_v, pool_rows, ver_idx, pk_scr, pk_all, gk_all, route_ws, s_final, status, phases, stream);
+    case 32: return launch_prefill<32>(L, batch, T, q, k, v, gate, plan_dev, n_plan, ver_rows, mem, out, route, pool_k, pool_v, pool_rows, ver_idx, pk_scr, pk_all, gk_all, route_ws, born_ws, tbits_ws, s_final, status, phases, stream);
+    case 64: return launch_prefill<64>(L, batch, T, q, k, v, gate, plan_dev, n_plan, ver_rows, mem, out, route, pool_k, pool_v, pool_rows, ver_idx, pk_scr, pk_all, gk_all, route_ws, born_ws, tbits_ws, s_final, status, phases, stream);
+    case 128: return launch_prefill<128>(L, batch, T, q, k, v, gate, plan_dev, n_plan, ver_rows, mem, out, route, pool_k, pool_v, pool_rows, ver_idx, pk_scr, pk_all, gk_all, route_ws, born_ws, tbits_ws, s_final, status, phases, stream);
   }
   return cudaErrorInvalidValue;
 }
