@@ -358,7 +358,8 @@ def run_b200(args):
                        "global_batch": B, "seq_len": T, "heads_per_gpu": h_loc,
                        "parallelism": f"heads/{world}" + (" + all-gather of outputs" if world > 1 else ""),
                        "l2": "inputs (1.6 GB) larger than L2, no flush needed"},
-            "e2e": e2e, "gpu_launches": 4 * args.steps,  # per step: prepared + gated keys, chain (routing and keys), value pass, block attention
+            # per step: prepared + gated keys, chain (routing and keys), value deltas, value rows, block attention
+            "e2e": e2e, "gpu_launches": 5 * args.steps,
             "roofline": roofline, "cpu_baseline": cpu,
             "clocks": clocks.summary(), "decode": decode, "power_law": power_law, "check": check,
         }

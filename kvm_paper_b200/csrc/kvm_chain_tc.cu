@@ -42,9 +42,13 @@ namespace chain {
 constexpr int HD = 128;
 constexpr int kWorkerWarps = 16;
 constexpr int kWorkers = kWorkerWarps * 32;   // threads that do everything but issuing copies and MMAs
-constexpr int kThreads = kWorkers + 32;       // + the issuing warp (one elected thread)
+constexpr int kIssuers = 2;                   // issuing threads (one warp each): issuing an MMA costs its thread about as much
+                                              // as the tensor core needs to execute it, so each token tile has its own
+constexpr int kThreads = kWorkers + kIssuers * 32;
 constexpr int kChunk = 256;                   // memory rows per MMA instruction and per tensor-memory chunk (the N limit)
 constexpr int kRowPad = 64;                   // granularity of the resident rows per CTA
+constexpr int kNewRows = 16;                  // up to this many appended rows per update take the logits-first order
+constexpr int kDirectNew = 2;                 // ... and up to this many are scored with plain dot products instead of an MMA pass
 constexpr uint32_t kTmemCols = 512;
 constexpr int kMaxSmem = 226 * 1024;          // dynamic part; the kernel also holds 1 KB of static shared memory
 
@@ -185,7 +189,8 @@ struct Issuer {
   int crank, row;
   const CUtensorMap* map_pk;
   const CUtensorMap* map_gk;
-  uint32_t g = 0;        // chunks issued so far (buffer g % 4, use g / 4)
+  int which;             // 0: token tile 0, all copies, the scatter; 1: token tile 1 of the routing passes only
+  uint32_t g = 0;        // chunks issued so far
   uint32_t n_w2i = 0, n_sc = 0, n_load = 0;
   volatile int* abort;
 
@@ -229,7 +234,7 @@ struct Issuer {
       const int n = min(kChunk, n_rows - c * kChunk);
       const uint32_t idesc = tc::make_idesc(128, (n + 15) & ~15, 0, 0);
       const uint64_t db0 = tc::make_desc(r_addr + (uint32_t)(c * kChunk * 128), 16, 1024);
-      for (int m = 0; m < n_mt; ++m) {
+      for (int m = which; m < n_mt; m += kIssuers) {
         if (g >= 1 && !wait(&bars->tm_empty[m], (g - 1) & 1, a.wait_limit, abort)) return false;
         tc::tc_fence_after_sync();
         const uint64_t da0 = tc::make_desc(a_addr + (uint32_t)(m * 128 * 128), 16, 1024);
@@ -242,6 +247,28 @@ struct Issuer {
         if (!(withhold_first_commit && c == 0 && m == 0)) tc::mma_commit_own_cta(&bars->tm_full[m]);
       }
     }
+    return true;
+  }
+  // Logits of every token against the rows that were just appended (at most kNewRows of them), which every CTA keeps
+  // as a small operand of its own: S[tokens x 16] = gk[tokens x D] * newk[16 x D]^T
+  __device__ __forceinline__ bool pass_new_rows() {
+    const int C = a.L.C, n_mt = C / 128;
+    constexpr uint32_t idesc = tc::make_idesc(128, kNewRows, 0, 0);
+    const uint32_t a_addr = tc::smem_u32(smem + lay.G);
+    const uint64_t db0 = tc::make_desc(tc::smem_u32(smem + lay.part), 16, 1024);
+    for (int m = which; m < n_mt; m += kIssuers) {
+      if (g >= 1 && !wait(&bars->tm_empty[m], (g - 1) & 1, a.wait_limit, abort)) return false;
+      tc::tc_fence_after_sync();
+      const uint64_t da0 = tc::make_desc(a_addr + (uint32_t)(m * 128 * 128), 16, 1024);
+#pragma unroll
+      for (int ks = 0; ks < HD / 16; ++ks) {
+        const uint64_t da = da0 + (uint64_t)(((uint32_t)(ks >> 2) * (uint32_t)(C * 128) + (uint32_t)(ks & 3) * 32u) >> 4);
+        const uint64_t db = db0 + (uint64_t)(((uint32_t)(ks >> 2) * (uint32_t)(kNewRows * 128) + (uint32_t)(ks & 3) * 32u) >> 4);
+        tc::mma_ss(tmem + (uint32_t)(m * kChunk), da, db, idesc, ks > 0);
+      }
+      tc::mma_commit_own_cta(&bars->tm_full[m]);
+    }
+    ++g;
     return true;
   }
   // delta[128 compacted rows x D] = onehot[rows x C tokens] * gk[C tokens x D]
@@ -260,8 +287,11 @@ struct Issuer {
 
   __device__ bool run() {
     const int C = a.L.C, nc = a.nc;
+    // The second issuer follows the same schedule and takes part in the same handshakes, but only issues the routing
+    // MMAs of its token tile.
+    const bool primary = which == 0;
     // block 0 (the initial memory) needs the prepared keys only; the gated keys travel with it to keep the barriers in step
-    load_block(0, true);
+    if (primary) load_block(0, true);
     for (int u = 0; u < a.n_plan; ++u) {
       const kvm_update_plan pl = a.plan[u];
       const int S0 = pl.state_before, na = pl.n_append, S1 = S0 + na, nm = C - na;
@@ -269,37 +299,56 @@ struct Issuer {
         // the workers build the initial memory from the prepared keys and report when the block buffers are free
         if (!wait_workers()) return false;
         n_load = 1;
-        if (a.n_plan > 1) load_block(1, true);
-        if (a.n_plan > 2 && crank == 0) prefetch_block(2);
+        if (primary && a.n_plan > 1) load_block(1, true);
+        if (primary && a.n_plan > 2 && crank == 0) prefetch_block(2);
         continue;
       }
       const bool has_nov = na > 0 && nm > 0;
-      if (u + 2 < a.n_plan && crank == (u & (nc - 1))) prefetch_block(u + 2);  // one CTA of the cluster asks, all profit
-      if (has_nov) {
-        if (!wait(&bars->full_p, n_load & 1, a.wait_limit, abort)) return false;
-        if (!pass(lay.P, n_local(S0, nc, crank), false)) return false;
-        if (!wait_workers()) return false;  // the appended rows are in the resident memory
-      }
-      if (nm > 0) {
+      if (primary && u + 2 < a.n_plan && crank == (u & (nc - 1))) prefetch_block(u + 2);  // one CTA of the cluster asks, all profit
+      const bool withhold = (a.test_flags & 1u) && u == 1;
+      if (nm > 0 && na <= kNewRows) {
+        // few appended rows: the logits against the OLD memory do not depend on them, so they go first and the
+        // novelty MMAs follow behind (the workers read one result while the tensor core produces the next); the
+        // logits against the new rows are a small third pass once the workers have chosen and stored them
         if (!wait(&bars->full_g, n_load & 1, a.wait_limit, abort)) return false;
-        if (!pass(lay.G, n_local(S1, nc, crank), (a.test_flags & 1u) && u == 1)) return false;
+        if (!pass(lay.G, n_local(S0, nc, crank), withhold)) return false;
+        if (has_nov) {
+          if (!wait(&bars->full_p, n_load & 1, a.wait_limit, abort)) return false;
+          if (!pass(lay.P, n_local(S0, nc, crank), false)) return false;
+          if (na > kDirectNew) {  // (one or two new rows are scored by the workers with plain dot products)
+            if (!wait_workers()) return false;  // the new rows are in every CTA's small operand
+            if (!pass_new_rows()) return false;
+          }
+        }
+      } else {
+        if (has_nov) {
+          if (!wait(&bars->full_p, n_load & 1, a.wait_limit, abort)) return false;
+          if (!pass(lay.P, n_local(S0, nc, crank), false)) return false;
+          if (!wait_workers()) return false;  // the appended rows are in the resident memory
+        }
+        if (nm > 0) {
+          if (!wait(&bars->full_g, n_load & 1, a.wait_limit, abort)) return false;
+          if (!pass(lay.G, n_local(S1, nc, crank), withhold)) return false;
+        }
       }
       // scatter passes (their number is decided by the workers once the routing is final)
       if (!wait_workers()) return false;
       const int n_pass = *reinterpret_cast<volatile int*>(&bars->n_pass);
       for (int p = 0; p < n_pass; ++p) {
         if (p > 0 && !wait_workers()) return false;
-        scatter();
+        if (primary) scatter();
         ++n_sc;
       }
       if (n_pass == 0) {  // nothing routed to this CTA's rows: the logits MMAs must still be complete before G is overwritten
-        tc::mma_commit_own_cta(&bars->sc_done);
+        if (primary) tc::mma_commit_own_cta(&bars->sc_done);
         ++n_sc;
       }
-      if (!wait(&bars->sc_done, (n_sc - 1) & 1, a.wait_limit, abort)) return false;
+      // (all routing MMAs were read back by the workers before they asked for the scatter, so the commit of the
+      // primary issuer covers what the block buffers are needed for)
+      if (primary && !wait(&bars->sc_done, (n_sc - 1) & 1, a.wait_limit, abort)) return false;
       ++n_load;  // the loads of this update have been consumed
       // both operands of every block are loaded (also where an update needs only one): the two barriers stay in step
-      if (u + 1 < a.n_plan) load_block(u + 1, true);
+      if (primary && u + 1 < a.n_plan) load_block(u + 1, true);
       // the next routing pass reads the resident memory the workers are refreshing now
       if (!wait_workers()) return false;
     }
@@ -350,10 +399,19 @@ struct Workers {
   // 32-column groups; leaves per token the CTA's partial result in part(half)[token].
   template <bool ARG>
   __device__ __forceinline__ bool read_pass(int n_rows, int protected_rows) {
+    float v;
+    int i;
+    const bool ok = read_regs<ARG>(n_rows, protected_rows, v, i);
+    const int half = warp >> 3, mt = (warp >> 2) & 1, quarter = warp & 3;
+    if (mt * 128 < a.L.C) part(half)[mt * 128 + quarter * 32 + lane] = make_float2(v, __int_as_float(i));
+    return wvote(ok);
+  }
+  // The same, the thread's result (value; global row or -1) left in registers, no vote.
+  template <bool ARG>
+  __device__ __forceinline__ bool read_regs(int n_rows, int protected_rows, float& v_out, int& i_out) {
     const int C = a.L.C, nc = a.nc;
     const int half = warp >> 3, mt = (warp >> 2) & 1, quarter = warp & 3;
     const bool active = mt * 128 < C;
-    const int token = mt * 128 + quarter * 32 + lane;
     const int n_chunks = ceil_div(n_rows, kChunk);
     // first local row that counts: global row l * nc + crank >= protected_rows
     const int l_min = ARG ? (protected_rows > crank ? (protected_rows - crank + nc - 1) / nc : 0) : 0;
@@ -406,20 +464,19 @@ struct Workers {
       __syncwarp();
       if (lane == 0) tc::mbar_arrive(&bars->tm_empty[mt]);
     }
-    if (active) {
-      float v = bv[0];
-      int i = bi[0];
-      if (!ARG) {
-        v = fmaxf(fmaxf(bv[0], bv[1]), fmaxf(bv[2], bv[3]));
-      } else {
+    float v = bv[0];
+    int i = bi[0];
+    if (!ARG) {
+      v = fmaxf(fmaxf(bv[0], bv[1]), fmaxf(bv[2], bv[3]));
+    } else {
 #pragma unroll
-        for (int j = 1; j < 4; ++j)  // first maximum in row order: larger value, or equal value at a lower row
-          if (bi[j] >= 0 && (i < 0 || bv[j] > v || (bv[j] == v && bi[j] < i))) { v = bv[j]; i = bi[j]; }
-        if (i >= 0) i = i * nc + crank;  // local -> global row
-      }
-      part(half)[token] = make_float2(v, __int_as_float(i));
+      for (int j = 1; j < 4; ++j)  // first maximum in row order: larger value, or equal value at a lower row
+        if (bi[j] >= 0 && (i < 0 || bv[j] > v || (bv[j] == v && bi[j] < i))) { v = bv[j]; i = bi[j]; }
+      if (i >= 0) i = i * nc + crank;  // local -> global row
     }
-    return wvote(ok);
+    v_out = v;
+    i_out = i;
+    return ok;
   }
 
   // Merge the two column halves, exchange the CTA's partial results with the peers, combine.
@@ -470,17 +527,61 @@ struct Workers {
     return wvote(ok);
   }
 
+  // Both routing results of the logits-first order in one exchange.  part(half)[token] holds {best logit over the
+  // old rows, row (16 bits, 0xffff = none) | novelty maximum as bf16 << 16}; the bf16 rounding of the novelty commutes
+  // with the maximum.  Leaves the novelty in nov()[token] and the best old row in the token thread's registers.
+  __device__ __forceinline__ bool exchange_both(float& best_v, int& best_i) {
+    const int C = a.L.C, nc = a.nc;
+    const int parity = n_x & 1;
+    float v = -INFINITY, nv = -INFINITY;
+    int i = -1;
+    auto take = [&](float2 p) {
+      const unsigned w = __float_as_uint(p.y);
+      const int pi = (w & 0xffffu) == 0xffffu ? -1 : (int)(w & 0xffffu);
+      nv = fmaxf(nv, __uint_as_float(w & 0xffff0000u));
+      if (pi >= 0 && (i < 0 || p.x > v || (p.x == v && pi < i))) { v = p.x; i = pi; }
+    };
+    if (tid < C) {
+      take(part(0)[tid]);
+      take(part(1)[tid]);
+    }
+    bool ok = true;
+    if (nc > 1) {
+      if (tid == 0) tc::mbar_arrive_expect_tx(&bars->xbar[parity], (uint32_t)((nc - 1) * C * 8));
+      if (tid < C) {
+        const float2* slot = &xb(parity, crank)[tid];
+        const int packed = (int)(((unsigned)i & 0xffffu) | (__float_as_uint(nv) & 0xffff0000u));
+        for (int p = 0; p < nc; ++p)
+          if (p != crank) st_async_v2(peer_addr(slot, p), v, packed, peer_addr(&bars->xbar[parity], p));
+      }
+      ok = tid < C ? wait<true>(&bars->xbar[parity], (n_x >> 1) & 1, a.wait_limit, abort) : true;
+      if (ok && tid < C)
+        for (int p = 0; p < nc; ++p)
+          if (p != crank) take(xb(parity, p)[tid]);
+    }
+    ++n_x;
+    if (tid < C) nov()[tid] = nv;
+    best_v = v;
+    best_i = i;
+    return wvote(ok);
+  }
+
   // LayerNorm view of one memory row (8 lanes per row): source `x`, written to the resident memory (if local) and
   // to a pool row / the carried sums.
-  __device__ __forceinline__ void store_key_row(RowVec<HD, 8>& x, int r, int slot, int gl, bool mine) {
+  // `new_row` >= 0: also row `new_row` of the small operand every CTA keeps of the rows appended in this update.
+  __device__ __forceinline__ void store_key_row(RowVec<HD, 8>& x, int r, int slot, int gl, bool mine, int new_row = -1) {
     const size_t grow = (size_t)row * a.capacity + r;
     if (mine) store_row<HD, 8>(x, a.k_sum + grow * HD, gl);
     layer_norm_row<HD, 8>(x, ln_w, ln_b, a.L.ln_eps, gl);
+    uint4 u0, u1;
+    u0.x = pack_bf16(x.x[0], x.x[1]); u0.y = pack_bf16(x.x[2], x.x[3]); u0.z = pack_bf16(x.x[4], x.x[5]); u0.w = pack_bf16(x.x[6], x.x[7]);
+    u1.x = pack_bf16(x.x[8], x.x[9]); u1.y = pack_bf16(x.x[10], x.x[11]); u1.z = pack_bf16(x.x[12], x.x[13]); u1.w = pack_bf16(x.x[14], x.x[15]);
+    if (new_row >= 0) {
+      *reinterpret_cast<uint4*>(smem + lay.part + piece(kNewRows, new_row, 2 * gl)) = u0;
+      *reinterpret_cast<uint4*>(smem + lay.part + piece(kNewRows, new_row, 2 * gl + 1)) = u1;
+    }
     if (mine) {
       const int l = r / a.nc;
-      uint4 u0, u1;
-      u0.x = pack_bf16(x.x[0], x.x[1]); u0.y = pack_bf16(x.x[2], x.x[3]); u0.z = pack_bf16(x.x[4], x.x[5]); u0.w = pack_bf16(x.x[6], x.x[7]);
-      u1.x = pack_bf16(x.x[8], x.x[9]); u1.y = pack_bf16(x.x[10], x.x[11]); u1.z = pack_bf16(x.x[12], x.x[13]); u1.w = pack_bf16(x.x[14], x.x[15]);
       *reinterpret_cast<uint4*>(smem + lay.R + piece(lay.Rcap, l, 2 * gl)) = u0;
       *reinterpret_cast<uint4*>(smem + lay.R + piece(lay.Rcap, l, 2 * gl + 1)) = u1;
       if (a.pool_k) {
@@ -491,8 +592,10 @@ struct Workers {
     }
   }
   // the 16 elements of lane gl of row t of a block operand (prepared or gated keys)
-  __device__ __forceinline__ void load_block_row(RowVec<HD, 8>& x, uint32_t off, int t, int gl) {
-    const int C = a.L.C;
+  __device__ __forceinline__ void load_block_row(RowVec<HD, 8>& x, uint32_t off, int t, int gl) { load_block_row_n(x, off, a.L.C, t, gl); }
+  // ... of an operand of `rows` rows
+  __device__ __forceinline__ void load_block_row_n(RowVec<HD, 8>& x, uint32_t off, int rows, int t, int gl) {
+    const int C = rows;
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
       const uint4 u = *reinterpret_cast<const uint4*>(smem + off + piece(C, t, 2 * gl + h));
@@ -503,18 +606,19 @@ struct Workers {
   }
 
   // rows [S0, S0 + na) from the tokens list()[0..na): `src_off` = operand holding what is stored (prepared or gated keys)
-  __device__ __forceinline__ void append_rows(int S0, int na, uint32_t src_off, int u) {
+  // `all_ctas`: every CTA also keeps the rows' view in its small operand of new rows (na <= kNewRows)
+  __device__ __forceinline__ void append_rows(int S0, int na, uint32_t src_off, int u, bool all_ctas = false) {
     const int gl = tid & 7, grp = tid >> 3;
     for (int base = 0; base < na; base += kWorkers / 8) {  // whole warps stay together: the LayerNorm uses group shuffles
       const int p = base + grp;
       const bool act = p < na;
-      if (!__any_sync(0xffffffffu, act && ((S0 + p) % a.nc == crank))) continue;  // nothing for this warp to store
+      if (!__any_sync(0xffffffffu, act && (all_ctas || (S0 + p) % a.nc == crank))) continue;  // nothing for this warp to store
       const int r = S0 + (act ? p : 0);
       const int t = list()[act ? p : 0];
       RowVec<HD, 8> x;
       load_block_row(x, src_off, t, gl);
       const bool mine = act && (r % a.nc == crank);
-      store_key_row(x, r, pool_next + p, gl, mine);
+      store_key_row(x, r, pool_next + p, gl, mine, (all_ctas && act) ? p : -1);
       if (mine && gl == 0 && a.born) a.born[(size_t)row * a.s_max + r] = u * a.L.C + t;
     }
     for (int i = tid; i < na; i += kWorkers) cur()[S0 + i] = pool_next + i;
@@ -548,8 +652,25 @@ struct Workers {
       }
       const bool has_nov = na > 0 && nm > 0;
       const int protected_rows = min(a.L.sink_len, S1);
+      // few appended rows: logits against the old memory first, the novelty behind them, both exchanged together,
+      // the logits against the new rows last (see the issuer)
+      const bool fast = nm > 0 && na <= kNewRows;
+      float best_v = -INFINITY;  // (fast) this token's best logit and row so far
+      int best_i = -1;
       // ---- 1. novelty of every token against the old memory; the n_append least similar tokens are appended
-      if (has_nov) {
+      if (fast) {
+        float vl_, vn_ = -INFINITY;
+        int il_, unused;
+        bool okr = read_regs<true>(n_local(S0, nc, crank), protected_rows, vl_, il_);
+        if (has_nov) okr = read_regs<false>(n_local(S0, nc, crank), 0, vn_, unused) && okr;
+        const int mt = (warp >> 2) & 1;
+        if (mt * 128 < C) {
+          const unsigned packed = ((unsigned)il_ & 0xffffu) | ((unsigned)__bfloat16_as_ushort(__float2bfloat16_rn(vn_)) << 16);
+          part(warp >> 3)[mt * 128 + (warp & 3) * 32 + lane] = make_float2(vl_, __uint_as_float(packed));
+        }
+        if (!wvote(okr)) return false;
+        if (!exchange_both(best_v, best_i)) return false;
+      } else if (has_nov) {
         if (!read_pass<false>(n_local(S0, nc, crank), 0)) return false;
         if (!exchange<false>()) return false;
       }
@@ -607,8 +728,8 @@ struct Workers {
           }
         }
         wsync();
-        append_rows(S0, na, (a.L.gate_appends && a.L.gate_keys) ? lay.G : lay.P, u);
-        if (has_nov) signal_issuer();  // the appended rows are in the resident memory: the logits pass may start
+        append_rows(S0, na, (a.L.gate_appends && a.L.gate_keys) ? lay.G : lay.P, u, fast);
+        if (has_nov && !(fast && na <= kDirectNew)) signal_issuer();  // the appended rows are in place: the pass against them may start
       } else if (tid < C) {
         pos()[tid] = -1;
       }
@@ -622,7 +743,62 @@ struct Workers {
         for (int i = tid; i < C * 16; i += kWorkers) o[i] = make_uint4(0, 0, 0, 0);
       }
       // ---- 2. merge target of every token: first argmax of the fp32 logits over the memory after the appends
-      if (nm > 0) {
+      if (fast) {
+        bool okm = true;
+        if (na > 0 && na <= kDirectNew) {
+          // one or two new rows: fp32 dot products of every token's gated key with them, eight lanes per token (fixed
+          // summation order); the rows are read from the small operand every CTA keeps of them
+          // (results in the novelty and append-list arrays, which nobody reads any more in this update)
+          float* dots_row[2] = {nov(), reinterpret_cast<float*>(list())};
+          static_assert(kDirectNew <= 2, "two scratch rows");
+          const int gl = tid & 7, grp = tid >> 3;
+          for (int j = 0; j < na; ++j) {
+            RowVec<HD, 8> nr;
+            load_block_row_n(nr, lay.part, kNewRows, j, gl);
+            for (int base = 0; base < C; base += kWorkers / 8) {
+              const int t = base + grp;
+              RowVec<HD, 8> kr;
+              load_block_row(kr, lay.G, t, gl);
+              float acc = 0.f;
+#pragma unroll
+              for (int e = 0; e < HD / 8; ++e) acc = fmaf(kr.x[e], nr.x[e], acc);
+              acc = group_sum<8>(acc);
+              if (gl == 0) dots_row[j][t] = acc;
+            }
+          }
+          wsync();
+          if (tid < C)
+            for (int j = 0; j < na; ++j) {
+              const float x = dots_row[j][tid];
+              if (S0 + j >= protected_rows && (x > best_v || best_i < 0)) { best_v = x; best_i = S0 + j; }
+            }
+        } else if (na > 0) {
+          // the new rows (columns 0 .. na-1 of the small pass) against this token's best old row: a new row has the
+          // higher index, it wins only with a strictly larger logit
+          const int mt = (warp >> 2) & 1;
+          if (mt * 128 < C) {
+            okm = wait(&bars->tm_full[mt], g & 1, a.wait_limit, abort);
+            okm = __all_sync(0xffffffffu, okm);
+            if (okm && warp * 32 < C) {
+              tc::tc_fence_after_sync();
+              uint32_t r16[16];
+              tc::tmem_ld16(tmem + ((uint32_t)((warp & 3) * 32) << 16) + (uint32_t)(mt * kChunk), r16);
+              tc::tmem_ld_wait();
+#pragma unroll
+              for (int j = 0; j < kNewRows; ++j) {
+                const float x = __uint_as_float(r16[j]);
+                if (j < na && S0 + j >= protected_rows && (x > best_v || best_i < 0)) { best_v = x; best_i = S0 + j; }
+              }
+              tc::tc_fence_before_sync();
+            }
+            __syncwarp();
+            if (lane == 0) tc::mbar_arrive(&bars->tm_empty[mt]);
+          }
+          ++g;
+        }
+        if (tid < C) idx()[tid] = best_i;
+        if (!wvote(okm)) return false;
+      } else if (nm > 0) {
         if (!read_pass<true>(n_local(S1, nc, crank), protected_rows)) return false;
         if (!exchange<true>()) return false;
       }
@@ -859,9 +1035,9 @@ kvm_chain_tc_kernel(const __grid_constant__ Args a, const __grid_constant__ Maps
   volatile int* abort = &bars->abort;
 
   bool ok = true;
-  if (warp == kWorkerWarps) {
+  if (warp >= kWorkerWarps) {
     if (lane == 0) {
-      Issuer is{a, smem, lay, bars, tmem, crank, row, &maps.pk, &maps.gk};
+      Issuer is{a, smem, lay, bars, tmem, crank, row, &maps.pk, &maps.gk, warp - kWorkerWarps};
       is.abort = abort;
       ok = is.run();
     }
