@@ -47,6 +47,7 @@ constexpr int kIssuers = 2;                   // issuing threads (one warp each)
 constexpr int kThreads = kWorkers + kIssuers * 32;
 constexpr int kChunk = 256;                   // memory rows per MMA instruction and per tensor-memory chunk (the N limit)
 constexpr int kRowPad = 64;                   // granularity of the resident rows per CTA
+constexpr int kLoaderThread = 15 * 32;        // the worker thread that issues the next block's copies
 constexpr int kNewRows = 16;                  // up to this many appended rows per update take the logits-first order
 constexpr int kDirectNew = 2;                 // ... and up to this many are scored with plain dot products instead of an MMA pass
 constexpr uint32_t kTmemCols = 512;
@@ -83,6 +84,7 @@ struct Bars {
   uint64_t w2i;                         // workers -> issuer: shared-memory operands are ready
   uint64_t sc_done;                     // scatter MMAs complete
   uint64_t xbar[2];                     // arrivals of the peers' partial results (two in flight)
+  uint64_t zero_done;                   // the copy engine has cleared the one-hot operand
   uint32_t tmem_base;
   int abort;                            // somebody in the cluster gave up
   int n_pass;                           // scatter passes of the current update (workers -> issuer)
@@ -90,6 +92,7 @@ struct Bars {
   int red_t[32];
 };
 
+static_assert(kNewRows <= kWorkerWarps, "one warp per appended row in the short path");
 static_assert(sizeof(Bars) <= 384, "the barrier block outgrew its shared-memory region");
 
 struct Args {
@@ -112,6 +115,9 @@ struct Args {
   uint32_t wait_limit;
   uint32_t test_flags;   // bit 0: the issuer withholds one commit (exercises the timeout path)
 };
+
+// Source of the copy that clears the one-hot operand of the scatter (64 KB of zeros, resident in L2).
+__device__ __align__(128) unsigned char g_zeros[256 * 256];
 
 // ------------------------------------------------------------------------------------------------ primitives
 __device__ __forceinline__ void wsync() { asm volatile("bar.sync 1, %0;" ::"n"(kWorkers) : "memory"); }
@@ -178,6 +184,19 @@ __device__ __forceinline__ uint32_t piece(int rows, int r, int c) {
 // rows r < S owned by CTA `rank` (r % nc == rank)
 __device__ __forceinline__ int n_local(int S, int nc, int rank) { return S > rank ? (S - rank + nc - 1) / nc : 0; }
 
+// One thread: tiled TMA copies of block u of a kv row (prepared and gated keys, two 64-element halves each) into the
+// block buffers.  The gated keys first: the logits pass, which opens an update, reads them.
+__device__ __forceinline__ void issue_block_loads(unsigned char* smem, const Layout& lay, Bars* bars, const CUtensorMap* map_pk,
+                                                  const CUtensorMap* map_gk, int row, long long n_tok, int C, int u) {
+  const int y = (int)((long long)row * n_tok + (long long)u * C);
+  tc::mbar_arrive_expect_tx(&bars->full_g, (uint32_t)C * 256u);
+  tc::tma_load_2d(smem + lay.G, map_gk, 0, y, &bars->full_g);
+  tc::tma_load_2d(smem + lay.G + C * 128, map_gk, 64, y, &bars->full_g);
+  tc::mbar_arrive_expect_tx(&bars->full_p, (uint32_t)C * 256u);
+  tc::tma_load_2d(smem + lay.P, map_pk, 0, y, &bars->full_p);
+  tc::tma_load_2d(smem + lay.P + C * 128, map_pk, 64, y, &bars->full_p);
+}
+
 // ------------------------------------------------------------------------------------------------ the issuer
 // One thread: TMA copies of the next block, the MMAs of the routing passes and of the scatter.
 struct Issuer {
@@ -191,7 +210,7 @@ struct Issuer {
   const CUtensorMap* map_gk;
   int which;             // 0: token tile 0, all copies, the scatter; 1: token tile 1 of the routing passes only
   uint32_t g = 0;        // chunks issued so far
-  uint32_t n_w2i = 0, n_sc = 0, n_load = 0;
+  uint32_t n_w2i = 0, n_sc = 0, n_load = 0, n_zero = 0;
   volatile int* abort;
 
   __device__ __forceinline__ bool wait_workers() {
@@ -210,39 +229,41 @@ struct Issuer {
       asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global.tile [%0, {%1, %2}];" ::"l"(map_gk), "r"(x), "r"(y) : "memory");
     }
   }
-  __device__ __forceinline__ void load_block(int u, bool want_p) {
+  __device__ __forceinline__ void load_block(int u) { issue_block_loads(smem, lay, bars, map_pk, map_gk, row, a.n_tok, a.L.C, u); }
+  // Operand descriptors and strides that never change, built once (the per-update code of this thread stays short: it
+  // runs alone, so every instruction-cache line it touches for the first time in an update is a wait of its own).
+  uint64_t d_p, d_g, d_r, d_new, d_gmn;  // prepared keys / one-hot (K-major), gated keys (K-major), resident rows, new rows, gated keys (MN-major)
+  uint32_t a_half, r_half;               // second 64-element half of an operand, in descriptor units (16 bytes)
+  __device__ __forceinline__ void setup() {
     const int C = a.L.C;
-    const int y = (int)((long long)row * a.n_tok + (long long)u * C);
-    if (want_p) {
-      tc::mbar_arrive_expect_tx(&bars->full_p, (uint32_t)C * 256u);
-      tc::tma_load_2d(smem + lay.P, map_pk, 0, y, &bars->full_p);
-      tc::tma_load_2d(smem + lay.P + C * 128, map_pk, 64, y, &bars->full_p);
-    }
-    tc::mbar_arrive_expect_tx(&bars->full_g, (uint32_t)C * 256u);
-    tc::tma_load_2d(smem + lay.G, map_gk, 0, y, &bars->full_g);
-    tc::tma_load_2d(smem + lay.G + C * 128, map_gk, 64, y, &bars->full_g);
+    d_p = tc::make_desc(tc::smem_u32(smem + lay.P), 16, 1024);
+    d_g = tc::make_desc(tc::smem_u32(smem + lay.G), 16, 1024);
+    d_r = tc::make_desc(tc::smem_u32(smem + lay.R), 16, 1024);
+    d_new = tc::make_desc(tc::smem_u32(smem + lay.part), 16, 1024);
+    d_gmn = tc::make_desc(tc::smem_u32(smem + lay.G), (uint32_t)C * 128u, 1024);
+    a_half = (uint32_t)(C * 128) >> 4;
+    r_half = (uint32_t)(lay.Rcap * 128) >> 4;
   }
   // S[tokens x rows] = A[tokens x D] * R[rows x D]^T over the first n_rows local rows, up to 256 rows per chunk: one
   // MMA per token tile and k-step covers the whole chunk (issuing an MMA costs about as much as executing a small
   // one), the accumulators of token tile m live in tensor-memory columns [256 m, 256 m + N).  One commit per token
-  // tile, so that the first tile is read back while the second is computed.
-  __device__ __forceinline__ bool pass(uint32_t a_off, int n_rows, bool withhold_first_commit) {
-    const int C = a.L.C, n_mt = C / 128;
-    const uint32_t a_addr = tc::smem_u32(smem + a_off), r_addr = tc::smem_u32(smem + lay.R);
+  // tile, so that the first tile is read back while the second is computed.  The loops are kept rolled on purpose.
+  __device__ __forceinline__ bool pass(uint64_t da_base, int n_rows, bool withhold_first_commit) {
+    const int n_mt = a.L.C / 128;
     const int n_chunks = ceil_div(n_rows, kChunk);
     for (int c = 0; c < n_chunks; ++c, ++g) {
       const int n = min(kChunk, n_rows - c * kChunk);
       const uint32_t idesc = tc::make_idesc(128, (n + 15) & ~15, 0, 0);
-      const uint64_t db0 = tc::make_desc(r_addr + (uint32_t)(c * kChunk * 128), 16, 1024);
+      const uint64_t db0 = d_r + (uint64_t)((uint32_t)(c * kChunk * 128) >> 4);
       for (int m = which; m < n_mt; m += kIssuers) {
         if (g >= 1 && !wait(&bars->tm_empty[m], (g - 1) & 1, a.wait_limit, abort)) return false;
         tc::tc_fence_after_sync();
-        const uint64_t da0 = tc::make_desc(a_addr + (uint32_t)(m * 128 * 128), 16, 1024);
-#pragma unroll
+        const uint64_t da0 = da_base + (uint64_t)((uint32_t)(m * 128 * 128) >> 4);
+        const uint32_t d = tmem + (uint32_t)(m * kChunk);
+#pragma unroll 1
         for (int ks = 0; ks < HD / 16; ++ks) {
-          const uint64_t da = da0 + (uint64_t)(((uint32_t)(ks >> 2) * (uint32_t)(C * 128) + (uint32_t)(ks & 3) * 32u) >> 4);
-          const uint64_t db = db0 + (uint64_t)(((uint32_t)(ks >> 2) * (uint32_t)(lay.Rcap * 128) + (uint32_t)(ks & 3) * 32u) >> 4);
-          tc::mma_ss(tmem + (uint32_t)(m * kChunk), da, db, idesc, ks > 0);
+          const uint32_t lo = (uint32_t)(ks & 3) * 2u;
+          tc::mma_ss(d, da0 + (uint64_t)(((ks >> 2) ? a_half : 0u) + lo), db0 + (uint64_t)(((ks >> 2) ? r_half : 0u) + lo), idesc, ks > 0);
         }
         if (!(withhold_first_commit && c == 0 && m == 0)) tc::mma_commit_own_cta(&bars->tm_full[m]);
       }
@@ -252,19 +273,18 @@ struct Issuer {
   // Logits of every token against the rows that were just appended (at most kNewRows of them), which every CTA keeps
   // as a small operand of its own: S[tokens x 16] = gk[tokens x D] * newk[16 x D]^T
   __device__ __forceinline__ bool pass_new_rows() {
-    const int C = a.L.C, n_mt = C / 128;
+    const int n_mt = a.L.C / 128;
     constexpr uint32_t idesc = tc::make_idesc(128, kNewRows, 0, 0);
-    const uint32_t a_addr = tc::smem_u32(smem + lay.G);
-    const uint64_t db0 = tc::make_desc(tc::smem_u32(smem + lay.part), 16, 1024);
+    constexpr uint32_t n_half = (uint32_t)(kNewRows * 128) >> 4;
     for (int m = which; m < n_mt; m += kIssuers) {
       if (g >= 1 && !wait(&bars->tm_empty[m], (g - 1) & 1, a.wait_limit, abort)) return false;
       tc::tc_fence_after_sync();
-      const uint64_t da0 = tc::make_desc(a_addr + (uint32_t)(m * 128 * 128), 16, 1024);
-#pragma unroll
+      const uint64_t da0 = d_g + (uint64_t)((uint32_t)(m * 128 * 128) >> 4);
+      const uint32_t d = tmem + (uint32_t)(m * kChunk);
+#pragma unroll 1
       for (int ks = 0; ks < HD / 16; ++ks) {
-        const uint64_t da = da0 + (uint64_t)(((uint32_t)(ks >> 2) * (uint32_t)(C * 128) + (uint32_t)(ks & 3) * 32u) >> 4);
-        const uint64_t db = db0 + (uint64_t)(((uint32_t)(ks >> 2) * (uint32_t)(kNewRows * 128) + (uint32_t)(ks & 3) * 32u) >> 4);
-        tc::mma_ss(tmem + (uint32_t)(m * kChunk), da, db, idesc, ks > 0);
+        const uint32_t lo = (uint32_t)(ks & 3) * 2u;
+        tc::mma_ss(d, da0 + (uint64_t)(((ks >> 2) ? a_half : 0u) + lo), d_new + (uint64_t)(((ks >> 2) ? n_half : 0u) + lo), idesc, ks > 0);
       }
       tc::mma_commit_own_cta(&bars->tm_full[m]);
     }
@@ -272,16 +292,13 @@ struct Issuer {
     return true;
   }
   // delta[128 compacted rows x D] = onehot[rows x C tokens] * gk[C tokens x D]
+  // (one-hot: K-major [C/64][128][64] in the buffer of the prepared keys; gated keys: MN-major)
   __device__ __forceinline__ void scatter() {
-    const int C = a.L.C;
     constexpr uint32_t idesc = tc::make_idesc(128, HD, 0, 1);
-    const uint64_t da0 = tc::make_desc(tc::smem_u32(smem + lay.P), 16, 1024);             // one-hot, K-major: [C/64][128][64]
-    const uint64_t db0 = tc::make_desc(tc::smem_u32(smem + lay.G), (uint32_t)C * 128u, 1024);  // gated keys, MN-major
-    for (int ks = 0; ks < C / 16; ++ks) {
-      const uint64_t da = da0 + (uint64_t)(((uint32_t)(ks >> 2) * (128u * 128u) + (uint32_t)(ks & 3) * 32u) >> 4);
-      const uint64_t db = db0 + (uint64_t)(((uint32_t)ks * 2048u) >> 4);
-      tc::mma_ss(tmem, da, db, idesc, ks > 0);
-    }
+    const int n_ks = a.L.C / 16;
+#pragma unroll 1
+    for (int ks = 0; ks < n_ks; ++ks)
+      tc::mma_ss(tmem, d_p + (uint64_t)((uint32_t)(ks >> 2) * (128u * 128u >> 4) + (uint32_t)(ks & 3) * 2u), d_gmn + (uint64_t)((uint32_t)ks * (2048u >> 4)), idesc, ks > 0);
     tc::mma_commit_own_cta(&bars->sc_done);
   }
 
@@ -290,16 +307,19 @@ struct Issuer {
     // The second issuer follows the same schedule and takes part in the same handshakes, but only issues the routing
     // MMAs of its token tile.
     const bool primary = which == 0;
+    setup();
     // block 0 (the initial memory) needs the prepared keys only; the gated keys travel with it to keep the barriers in step
-    if (primary) load_block(0, true);
+    if (primary) load_block(0);
+    kvm_update_plan pl_next = a.plan[0];  // fetched one update ahead: the table lives in global memory
     for (int u = 0; u < a.n_plan; ++u) {
-      const kvm_update_plan pl = a.plan[u];
+      const kvm_update_plan pl = pl_next;
+      if (u + 1 < a.n_plan) pl_next = a.plan[u + 1];
       const int S0 = pl.state_before, na = pl.n_append, S1 = S0 + na, nm = C - na;
       if (u == 0) {
         // the workers build the initial memory from the prepared keys and report when the block buffers are free
         if (!wait_workers()) return false;
         n_load = 1;
-        if (primary && a.n_plan > 1) load_block(1, true);
+        if (primary && a.n_plan > 1) load_block(1);
         if (primary && a.n_plan > 2 && crank == 0) prefetch_block(2);
         continue;
       }
@@ -311,24 +331,31 @@ struct Issuer {
         // novelty MMAs follow behind (the workers read one result while the tensor core produces the next); the
         // logits against the new rows are a small third pass once the workers have chosen and stored them
         if (!wait(&bars->full_g, n_load & 1, a.wait_limit, abort)) return false;
-        if (!pass(lay.G, n_local(S0, nc, crank), withhold)) return false;
+        if (!pass(d_g, n_local(S0, nc, crank), withhold)) return false;
         if (has_nov) {
           if (!wait(&bars->full_p, n_load & 1, a.wait_limit, abort)) return false;
-          if (!pass(lay.P, n_local(S0, nc, crank), false)) return false;
-          if (na > kDirectNew) {  // (one or two new rows are scored by the workers with plain dot products)
-            if (!wait_workers()) return false;  // the new rows are in every CTA's small operand
-            if (!pass_new_rows()) return false;
-          }
+          if (!pass(d_p, n_local(S0, nc, crank), false)) return false;
         }
+        // The workers report when nobody reads the prepared keys any more (novelty read back, appended rows stored, the
+        // new rows in every CTA's small operand): the copy engine clears their buffer, which becomes the one-hot operand
+        // of the scatter, while the workers score the new rows and build the routing table.
+        if (!wait_workers()) return false;
+        if (primary) {
+          // (an update without appends never looked at the prepared keys: their copy must have landed before the buffer is reused)
+          if (!has_nov && !wait(&bars->full_p, n_load & 1, a.wait_limit, abort)) return false;
+          tc::mbar_arrive_expect_tx(&bars->zero_done, (uint32_t)C * 256u);
+          tc::bulk_g2s(smem + lay.P, g_zeros, (uint32_t)C * 256u, &bars->zero_done);
+        }
+        if (has_nov && na > kDirectNew && !pass_new_rows()) return false;  // (one or two new rows are scored by the workers with plain dot products)
       } else {
         if (has_nov) {
           if (!wait(&bars->full_p, n_load & 1, a.wait_limit, abort)) return false;
-          if (!pass(lay.P, n_local(S0, nc, crank), false)) return false;
+          if (!pass(d_p, n_local(S0, nc, crank), false)) return false;
           if (!wait_workers()) return false;  // the appended rows are in the resident memory
         }
         if (nm > 0) {
           if (!wait(&bars->full_g, n_load & 1, a.wait_limit, abort)) return false;
-          if (!pass(lay.G, n_local(S1, nc, crank), withhold)) return false;
+          if (!pass(d_g, n_local(S1, nc, crank), withhold)) return false;
         }
       }
       // scatter passes (their number is decided by the workers once the routing is final)
@@ -346,9 +373,11 @@ struct Issuer {
       // (all routing MMAs were read back by the workers before they asked for the scatter, so the commit of the
       // primary issuer covers what the block buffers are needed for)
       if (primary && !wait(&bars->sc_done, (n_sc - 1) & 1, a.wait_limit, abort)) return false;
-      ++n_load;  // the loads of this update have been consumed
-      // both operands of every block are loaded (also where an update needs only one): the two barriers stay in step
-      if (primary && u + 1 < a.n_plan) load_block(u + 1, true);
+      if (nm > 0 && na <= kNewRows) {  // the clearing copy has landed, too (nobody may have waited for it: no row of this CTA touched)
+        if (primary && !wait(&bars->zero_done, n_zero & 1, a.wait_limit, abort)) return false;
+        ++n_zero;
+      }
+      ++n_load;  // the loads of this update have been consumed; a worker thread has issued the next block's (see there)
       // the next routing pass reads the resident memory the workers are refreshing now
       if (!wait_workers()) return false;
     }
@@ -368,10 +397,11 @@ struct Workers {
   const float* ln_b;
   volatile int* abort;
   int tid, warp, lane;
-  uint32_t g = 0, n_sc = 0, n_x = 0, n_load = 0;
+  const CUtensorMap* map_pk;
+  const CUtensorMap* map_gk;
+  uint32_t g = 0, n_sc = 0, n_x = 0, n_load = 0, n_zero = 0;
   int pool_next = 0;
   unsigned mine_mask = 0;  // lanes whose row (a multiple of 32 + lane) belongs to this CTA
-  bool pend_ok = true;     // result of a wait that the next vote still has to take into account
 
   __device__ __forceinline__ float* nov() const { return reinterpret_cast<float*>(smem + lay.tok); }
   __device__ __forceinline__ int* idx() const { return reinterpret_cast<int*>(smem + lay.tok) + a.L.C; }
@@ -417,8 +447,7 @@ struct Workers {
     const int l_min = ARG ? (protected_rows > crank ? (protected_rows - crank + nc - 1) / nc : 0) : 0;
     float bv[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
     int bi[4] = {-1, -1, -1, -1};
-    bool ok = pend_ok;
-    pend_ok = true;
+    bool ok = true;
     for (int c = 0; c < n_chunks; ++c, ++g) {
       if (!active) continue;
       ok = ok && wait(&bars->tm_full[mt], g & 1, a.wait_limit, abort);
@@ -625,12 +654,42 @@ struct Workers {
     pool_next += na;
   }
 
+  // The same for at most kWorkerWarps rows, one warp per row and four elements per lane, every CTA keeping the rows' view
+  // in its small operand of new rows: the few warps that store rows run alone, and what they wait for is mostly their
+  // own instructions, so the code is kept short.
+  __device__ __forceinline__ void append_rows_warp(int S0, int na, uint32_t src_off, int u) {
+    if (warp < na) {
+      const int p = warp, r = S0 + p, t = list()[p], pc = lane >> 1;
+      const uint32_t sub = (uint32_t)(lane & 1) * 8u;  // which half of a 16-byte piece
+      const uint2 raw = *reinterpret_cast<const uint2*>(smem + src_off + piece(a.L.C, t, pc) + sub);
+      RowVec<HD, 32> x;
+      const float2 e0 = unpack_bf16(raw.x), e1 = unpack_bf16(raw.y);
+      x.x[0] = e0.x; x.x[1] = e0.y; x.x[2] = e1.x; x.x[3] = e1.y;
+      const bool mine = r % a.nc == crank;
+      if (mine) *reinterpret_cast<uint2*>(a.k_sum + ((size_t)row * a.capacity + r) * HD + lane * 4) = raw;  // the carried sum is the token's row
+      layer_norm_row<HD, 32>(x, ln_w, ln_b, a.L.ln_eps, lane);
+      uint2 o;
+      o.x = pack_bf16(x.x[0], x.x[1]);
+      o.y = pack_bf16(x.x[2], x.x[3]);
+      *reinterpret_cast<uint2*>(smem + lay.part + piece(kNewRows, p, pc) + sub) = o;
+      if (mine) {
+        *reinterpret_cast<uint2*>(smem + lay.R + piece(lay.Rcap, r / a.nc, pc) + sub) = o;
+        if (a.pool_k) *reinterpret_cast<uint2*>(a.pool_k + ((size_t)row * a.pool_rows + pool_next + p) * HD + lane * 4) = o;
+        if (lane == 0 && a.born) a.born[(size_t)row * a.s_max + r] = u * a.L.C + t;
+      }
+    }
+    if (tid < na) cur()[S0 + tid] = pool_next + tid;
+    pool_next += na;
+  }
+
   __device__ bool run() {
     const int C = a.L.C, nc = a.nc;
     for (int l = crank; l < 32; l += nc) mine_mask |= 1u << l;
     int* route_row = a.route + (size_t)row * a.n_plan * C;
+    kvm_update_plan pl_next = a.plan[0];  // fetched one update ahead
     for (int u = 0; u < a.n_plan; ++u) {
-      const kvm_update_plan pl = a.plan[u];
+      const kvm_update_plan pl = pl_next;
+      if (u + 1 < a.n_plan) pl_next = a.plan[u + 1];
       const int S0 = pl.state_before, na = pl.n_append, S1 = S0 + na, nm = C - na;
       int* ver = (a.ver_idx && pl.version_row >= 0) ? a.ver_idx + (size_t)row * a.ver_rows + pl.version_row : nullptr;
       bool ok = true;
@@ -728,19 +787,19 @@ struct Workers {
           }
         }
         wsync();
-        append_rows(S0, na, (a.L.gate_appends && a.L.gate_keys) ? lay.G : lay.P, u, fast);
-        if (has_nov && !(fast && na <= kDirectNew)) signal_issuer();  // the appended rows are in place: the pass against them may start
+        if (fast) append_rows_warp(S0, na, (a.L.gate_appends && a.L.gate_keys) ? lay.G : lay.P, u);
+        else append_rows(S0, na, (a.L.gate_appends && a.L.gate_keys) ? lay.G : lay.P, u);
+        if (!fast && has_nov) signal_issuer();  // the appended rows are in place: the pass against them may start
       } else if (tid < C) {
         pos()[tid] = -1;
       }
-      if (nm > 0) {
-        // the prepared keys are dead from here on: their buffer becomes the one-hot operand of the scatter; it is
-        // cleared now, while the tensor core works on the logits
-        // (an update without appends never looked at them: their copy must have landed before the buffer is reused)
-        if (na == 0) pend_ok = wait(&bars->full_p, n_load & 1, a.wait_limit, abort);
-        else wsync();  // the warps that store appended rows have read their prepared keys
+      // The prepared keys are dead from here on: their buffer becomes the one-hot operand of the scatter.
+      if (fast) {
+        signal_issuer();  // the issuer has the copy engine clear it (and may start the pass against the new rows)
+      } else if (nm > 0) {
+        wsync();  // the warps that store appended rows have read their prepared keys
         uint4* o = reinterpret_cast<uint4*>(smem + lay.P);
-        for (int i = tid; i < C * 16; i += kWorkers) o[i] = make_uint4(0, 0, 0, 0);
+        for (int i = tid; i < C * 16; i += kWorkers) o[i] = make_uint4(0, 0, 0, 0);  // while the tensor core works on the logits
       }
       // ---- 2. merge target of every token: first argmax of the fp32 logits over the memory after the appends
       if (fast) {
@@ -749,6 +808,7 @@ struct Workers {
           // one or two new rows: fp32 dot products of every token's gated key with them, eight lanes per token (fixed
           // summation order); the rows are read from the small operand every CTA keeps of them
           // (results in the novelty and append-list arrays, which nobody reads any more in this update)
+          wsync();  // the new rows are in the small operand (stored by the warps that appended them)
           float* dots_row[2] = {nov(), reinterpret_cast<float*>(list())};
           static_assert(kDirectNew <= 2, "two scratch rows");
           const int gl = tid & 7, grp = tid >> 3;
@@ -857,8 +917,15 @@ struct Workers {
       if (tid == 0) bars->n_pass = n_pass;
       if (n_pass == 0) {
         signal_issuer();
-        ++n_sc;  // the issuer still commits once (it waits for the logits MMAs before the block buffers are reused)
+        ++n_sc;  // the issuer still commits once
+        // No row of this CTA was touched: every MMA that read the block buffers has been read back, only the clearing
+        // copy may still be on its way.
+        if (tid == kLoaderThread && u + 1 < a.n_plan) {
+          const bool okl = fast ? wait(&bars->zero_done, n_zero & 1, a.wait_limit, abort) : true;
+          if (okl) issue_block_loads(smem, lay, bars, map_pk, map_gk, row, a.n_tok, C, u + 1);  // (a wait that ran out shows up at the next one)
+        }
       }
+      bool okz = true;
       for (int p = 0; p < n_pass; ++p) {
         {  // one-hot operand [C/64][128 rows][64 tokens] (in the buffer of the prepared keys, which are dead by now)
           if (p > 0) {  // a further pass: clear what the previous one set
@@ -866,7 +933,8 @@ struct Workers {
             for (int i = tid; i < C * 16; i += kWorkers) o[i] = make_uint4(0, 0, 0, 0);
             wsync();
           }
-          if (my >= 0 && my % nc == crank) {
+          if (p == 0 && fast) okz = wait(&bars->zero_done, n_zero & 1, a.wait_limit, abort);  // the cleared buffer has landed
+          if (okz && my >= 0 && my % nc == crank) {
             const int ll = lci()[my / nc] - p * 128;
             if (ll >= 0 && ll < 128) {
               const uint32_t off = (uint32_t)(tid >> 6) * (128u * 128u) + tc::sw128_offset(ll, tid & 63);
@@ -886,8 +954,12 @@ struct Workers {
 #pragma unroll
           for (int j = 0; j < 4; ++j) old[j] = *reinterpret_cast<const uint4*>(a.k_sum + grow * HD + colq * 32 + j * 8);
         }
-        ok = wait(&bars->sc_done, n_sc & 1, a.wait_limit, abort);
+        ok = wait(&bars->sc_done, n_sc & 1, a.wait_limit, abort) && okz;
         ++n_sc;
+        // The scatter was the last reader of the block buffers: one thread has the next block copied in right away (both
+        // operands of every block, also where an update needs only one: the two barriers stay in step).
+        if (ok && p == n_pass - 1 && tid == kLoaderThread && u + 1 < a.n_plan)
+          issue_block_loads(smem, lay, bars, map_pk, map_gk, row, a.n_tok, C, u + 1);
         if (!wvote(ok)) return false;
         tc::tc_fence_after_sync();
         float x[32];
@@ -956,6 +1028,7 @@ struct Workers {
           }
         }
       }
+      if (fast) ++n_zero;
       // ---- 5. the version: every touched row moved to a fresh pool row
       for (int i = tid; i < S1; i += kWorkers)
         if (tf()[i] == (unsigned short)u) cur()[i] = pool_next + gci()[i];
@@ -1021,6 +1094,7 @@ kvm_chain_tc_kernel(const __grid_constant__ Args a, const __grid_constant__ Maps
     tc::mbar_init(&bars->sc_done, 1);
     tc::mbar_init(&bars->xbar[0], 1);  // one local arrival that states the bytes the peers will store
     tc::mbar_init(&bars->xbar[1], 1);
+    tc::mbar_init(&bars->zero_done, 1);
     bars->abort = 0;
     bars->n_pass = 0;
     tc::fence_barrier_init();
@@ -1042,7 +1116,7 @@ kvm_chain_tc_kernel(const __grid_constant__ Args a, const __grid_constant__ Maps
       ok = is.run();
     }
   } else {
-    Workers w{a, smem, lay, bars, tmem, crank, row, ln_s, ln_s + HD, abort, tid, warp, lane};
+    Workers w{a, smem, lay, bars, tmem, crank, row, ln_s, ln_s + HD, abort, tid, warp, lane, &maps.pk, &maps.gk};
     ok = w.run();
   }
   if (!ok) {
