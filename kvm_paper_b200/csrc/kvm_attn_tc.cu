@@ -56,7 +56,7 @@ struct Cfg {
 };
 
 struct Bars {
-  uint64_t q_full[2], kv_full[kStages], kv_empty[kStages], s_full[2][2], p_full[2], pv_done[2], o_final[2], o_ready[2];
+  uint64_t q_full[2], kv_full[kStages], kv_empty[kStages], s_full[2][2], p_full[2][2], pv_done[2], o_final[2], o_ready[2];
   uint32_t tmem_base;
 };
 
@@ -210,7 +210,9 @@ __device__ __forceinline__ bool mma_role(const Slice<NQ>& sl, unsigned char* sme
   for (int t = 0; t < sl.n_max; ++t) {
     const int stage = t % kStages;
     if (t < nt) {
-      if (!tc::mbar_wait(&bars->p_full[qi], t & 1)) return false;
+      // (one barrier per score buffer: a softmax warp that is a tile ahead of its neighbours arrives on the other one
+      // and cannot complete this tile's phase in their place)
+      if (!tc::mbar_wait(&bars->p_full[qi][t & 1], (t >> 1) & 1)) return false;
       tc::tc_fence_after_sync();
       const uint64_t db0 = dV + (uint64_t)((stage * 16384) >> 4);
       // P (bf16) lies in the first 32 columns of the score buffer it was computed from: 8 columns per k-step
@@ -325,7 +327,7 @@ __device__ __forceinline__ bool softmax_role(const Slice<NQ>& sl, const LayerDev
     tc::tmem_st_wait();
     tc::tc_fence_before_sync();
     __syncwarp();
-    if (lane == 0) tc::mbar_arrive(&bars->p_full[qi]);
+    if (lane == 0) tc::mbar_arrive(&bars->p_full[qi][sbuf]);
   }
   // epilogue: O / l -> bf16 -> the query tile's operand buffer (all QK of this tile have completed), in the
   // 128-byte-swizzled layout of a [128 tokens][64] box per half of the head dimension -> two TMA stores into
@@ -415,7 +417,8 @@ kvm_attn_prefill_tc_kernel(LayerDev L, long long T, Tensor4 q, Tensor4 k, Tensor
       tc::mbar_init(&bars->q_full[i], 1);
       tc::mbar_init(&bars->s_full[i][0], 1);
       tc::mbar_init(&bars->s_full[i][1], 1);
-      tc::mbar_init(&bars->p_full[i], 4);
+      tc::mbar_init(&bars->p_full[i][0], 4);
+      tc::mbar_init(&bars->p_full[i][1], 4);
       tc::mbar_init(&bars->pv_done[i], 1);
       tc::mbar_init(&bars->o_final[i], 1);
       tc::mbar_init(&bars->o_ready[i], 4);
