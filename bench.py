@@ -530,7 +530,7 @@ def run_decode(args, dev, rank, world, peaks):
     nbytes = host_walk()
 
     def run_all():
-        out = cache.run(q, k, v, g)       # one C call: two kernel launches per token
+        out = cache.run(q, k, v, g)       # one C call per 32 tokens: two kernel launches per token
         return sharding.gather_sequences(out, world, seq_dim=1)  # [steps, all sequences, H*D]
 
     run_all()  # warm-up pass over the whole trajectory

@@ -34,15 +34,26 @@ __device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.lau
 template <int D, int NT, bool UPDATE, bool SB>
 __global__ void __launch_bounds__(NT, 1)
 kvm_decode_pre_kernel(LayerDev L, DecodeCacheDev cache, Tensor4 k, Tensor4 v, Tensor4 gate,
-                      const int* __restrict__ n_append_arr, bf16* pk_scr, int* route, int scope) {
+                      const int* __restrict__ n_append_arr, bf16* pk_scr, int* route, int scope, int batch) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
-  const int row = blockIdx.x;
+  int row = blockIdx.x;
+  if (scope == 2) {
+    // Only the sequences with a memory update at this token, on a grid of just their rows (a CTA of this variant
+    // takes a whole SM: a grid over all rows would queue hundreds of CTAs that return at once behind the few SMs
+    // the attention of the other sequences leaves free): CTA j * Hkv + h belongs to the j-th updating sequence.
+    const int j = blockIdx.x / L.Hkv;
+    int found = -1, cnt = 0;
+    for (int i = 0; i < batch && found < 0; ++i)
+      if (n_append_arr[i] >= 0 && cnt++ == j) found = i;
+    if (found < 0) return;
+    row = found * L.Hkv + (int)(blockIdx.x % L.Hkv);
+  }
   const int b = row / L.Hkv, h = row % L.Hkv;
   pdl_wait();     // the previous token's attention kernel has advanced the lengths
   pdl_trigger();  // this token's attention kernel may set itself up meanwhile
-  if (scope) {  // 1: only sequences without a memory update at this token, 2: only those with one
+  if (scope == 1) {  // only sequences without a memory update at this token
     const int na = n_append_arr ? n_append_arr[b] : -1;
-    if ((scope == 1 && na >= 0) || (scope == 2 && na < 0)) return;
+    if (na >= 0) return;
   }
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int C = L.C, WC = L.W * L.C;
@@ -838,7 +849,7 @@ static cudaError_t launch_decode(const LayerDev& L, int batch, const DecodeCache
     // plain token: the two kernels are chained with programmatic dependent launches (`overlap` callers only)
     const bool pdl = overlap != 0;
     e = launch_pdl(kvm_decode_pre_kernel<D, 32, false, false>, dim3(rows), dim3(32), 0, stream, pdl, L, cache, k, v, gate,
-                   (const int*)nullptr, pk_scr, route, 0);
+                   (const int*)nullptr, pk_scr, route, 0, batch);
     if (e != cudaSuccess) return e;
     return attn(0, n_sm, nullptr, pdl);
   }
@@ -850,7 +861,7 @@ static cudaError_t launch_decode(const LayerDev& L, int batch, const DecodeCache
   const int upd_sms = any_update * L.Hkv;  // SMs the updating rows occupy (one CTA each)
   DecodeSide* side = (overlap && any_update < batch && upd_sms * 2 <= n_sm) ? decode_side() : nullptr;
   if (!side) {  // one stream: update + ring write for every row, then attention over everything
-    upd<<<rows, NT, smem_u, stream>>>(L, cache, k, v, gate, n_append, pk_scr, route, 0);
+    upd<<<rows, NT, smem_u, stream>>>(L, cache, k, v, gate, n_append, pk_scr, route, 0, batch);
     e = cudaGetLastError();
     if (e != cudaSuccess) return e;
     return attn(0, n_sm, n_append);
@@ -858,14 +869,14 @@ static cudaError_t launch_decode(const LayerDev& L, int batch, const DecodeCache
   // fork: the updating sequences' rows on the side stream ...
   if ((e = cudaEventRecord(side->fork, stream)) != cudaSuccess) return e;
   if ((e = cudaStreamWaitEvent(side->stream, side->fork, 0)) != cudaSuccess) return e;
-  upd<<<rows, NT, smem_u, side->stream>>>(L, cache, k, v, gate, n_append, pk_scr, route, 2);
+  upd<<<any_update * L.Hkv, NT, smem_u, side->stream>>>(L, cache, k, v, gate, n_append, pk_scr, route, 2, batch);
   if ((e = cudaGetLastError()) != cudaSuccess) return e;
   // ... followed there by their attention, on the SMs the update leaves (second launch counter of the workspace;
   // the two attention launches touch disjoint sequences, rows, partial slots and outputs)
   if ((e = attn(2, upd_sms, n_append, false, 1, side->stream)) != cudaSuccess) return e;
   if ((e = cudaEventRecord(side->join, side->stream)) != cudaSuccess) return e;
   // ... next to the ring write and the attention of all others, which leave those SMs free
-  kvm_decode_pre_kernel<D, 32, false, false><<<rows, 32, 0, stream>>>(L, cache, k, v, gate, n_append, pk_scr, route, 1);
+  kvm_decode_pre_kernel<D, 32, false, false><<<rows, 32, 0, stream>>>(L, cache, k, v, gate, n_append, pk_scr, route, 1, batch);
   if ((e = cudaGetLastError()) != cudaSuccess) return e;
   if ((e = attn(1, n_sm - upd_sms, n_append)) != cudaSuccess) return e;
   // join

@@ -513,37 +513,46 @@ class KvmDecodeCache:
     def run(self, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, gate: torch.Tensor) -> torch.Tensor:
         """``n`` consecutive decode tokens with inputs already on the device (teacher-forced / synthetic
         decoding): q [n,B,Hq,1,D], k/v [n,B,Hkv,1,D], gate [n,B,Hkv,1,1], contiguous.  Returns [n,B,Hq*D].
-        The host walks the per-sequence schedule for all n tokens first, then issues one C call."""
+        The host walks the per-sequence schedule a piece of 32 tokens at a time and issues one C call per piece, so
+        that the device works on one piece while the next is planned."""
         lib = _lib.load()
         cfg, B = self.cfg, self.batch
         n = q.size(0)
         if q.shape != (n, B, cfg.n_q_heads, 1, cfg.head_dim) or k.shape != (n, B, cfg.n_kv_heads, 1, cfg.head_dim):
             raise ValueError(f"run expects [n,B,H,1,D] inputs, got q {tuple(q.shape)} k {tuple(k.shape)}")
         q, k, v, gate = (t.to(torch.bfloat16).contiguous() for t in (q, k, v, gate))
-        n_app_all = np.full((n, B), -1, dtype=np.int32)
-        any_upd = (C.c_int32 * n)()
-        max_rows = (C.c_int32 * n)()
-        for i in range(n):
-            na, mr = self._plan_step()
-            if na is not None:
-                n_app_all[i] = na
-                any_upd[i] = int((na >= 0).sum())
-            max_rows[i] = min(mr, self.memory.capacity + self.ring_capacity)
-        if int(self.state_len_h.max()) > self.memory.capacity:
-            self._reserve(int(self.state_len_h.max()))
-            max_rows_bound = self.memory.capacity + self.ring_capacity
-            for i in range(n):
-                max_rows[i] = min(max_rows[i], max_rows_bound)
-        n_app_dev = torch.from_numpy(n_app_all).to(self.device)
         out = torch.empty(n, B, cfg.n_q_heads * cfg.head_dim, device=self.device, dtype=torch.bfloat16)
-        ccache = _CCache(self.memory.c(), self.ring_k.data_ptr(), self.ring_v.data_ptr(), self.ring_gate.data_ptr(),
-                         self.total_len.data_ptr(), self.state_len.data_ptr())
-        rc = lib.kvm_decode_run(
-            C.byref(self.params.c), B, ccache, n, _tensor4(q[0], "q"), _tensor4(k[0], "k"), _tensor4(v[0], "v"),
-            _tensor4(gate[0], "gate"), q.stride(0), k.stride(0), gate.stride(0), n_app_dev.data_ptr(), any_upd, max_rows,
-            out.data_ptr(), self._ws.data_ptr(), self._ws_bytes, _stream_ptr(self.device))
-        _lib.check(rc)
-        self._keepalive = (q, k, v, gate, n_app_dev)
+        keep = [q, k, v, gate]
+        # The schedule is walked and issued in pieces: while the device works on one piece the host plans the next
+        # (a walk of all n tokens up front would leave the device idle for its whole duration).
+        piece = 32
+        for lo in range(0, n, piece):
+            m = min(piece, n - lo)
+            n_app = np.full((m, B), -1, dtype=np.int32)
+            any_upd = (C.c_int32 * m)()
+            max_rows = (C.c_int32 * m)()
+            for i in range(m):
+                na, mr = self._plan_step()
+                if na is not None:
+                    n_app[i] = na
+                    any_upd[i] = int((na >= 0).sum())
+                max_rows[i] = min(mr, self.memory.capacity + self.ring_capacity)
+            if int(self.state_len_h.max()) > self.memory.capacity:
+                self._reserve(int(self.state_len_h.max()))
+                bound = self.memory.capacity + self.ring_capacity
+                for i in range(m):
+                    max_rows[i] = min(max_rows[i], bound)
+            n_app_dev = torch.from_numpy(n_app).to(self.device, non_blocking=True) if any(any_upd) else None
+            ccache = _CCache(self.memory.c(), self.ring_k.data_ptr(), self.ring_v.data_ptr(), self.ring_gate.data_ptr(),
+                             self.total_len.data_ptr(), self.state_len.data_ptr())
+            rc = lib.kvm_decode_run(
+                C.byref(self.params.c), B, ccache, m, _tensor4(q[lo], "q"), _tensor4(k[lo], "k"), _tensor4(v[lo], "v"),
+                _tensor4(gate[lo], "gate"), q.stride(0), k.stride(0), gate.stride(0),
+                n_app_dev.data_ptr() if n_app_dev is not None else None, any_upd, max_rows,
+                out[lo].data_ptr(), self._ws.data_ptr(), self._ws_bytes, _stream_ptr(self.device))
+            _lib.check(rc)
+            keep.append(n_app_dev)
+        self._keepalive = tuple(keep)
         return out
 
     def check_status(self) -> None:
