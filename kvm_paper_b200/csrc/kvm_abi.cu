@@ -134,7 +134,9 @@ PrefillWs prefill_ws(const kvm_layer* l, int batch, long long seq_len, long long
   // for the value side: the token that created each memory row (at most C * n_plan rows), one bit per (update, row)
   const size_t max_rows = (size_t)C * n_plan;
   w.born = off; off = align_up(off + (tc ? rows * max_rows * 4 : 0), 256);
-  w.tbits = off; off = align_up(off + (tc ? rows * (size_t)n_plan * ((max_rows + 31) / 32) * 4 : 0), 256);
+  // (behind the bit table: control words of the value side, one progress flag per CTA of the routing kernel and a list
+  // of up to 1024 jobs that spare CTAs of the routing's launch gave back)
+  w.tbits = off; off = align_up(off + (tc ? rows * (size_t)n_plan * ((max_rows + 31) / 32) * 4 + (4 + rows * 8 + 1024) * 4 : 0), 256);
   w.total = off;
   return w;
 }

@@ -35,6 +35,7 @@
 #include "kvm_common.cuh"
 #include "kvm_tc.cuh"
 #include "kvm_tma_host.cuh"
+#include "kvm_vdelta.cuh"
 
 namespace kvm {
 namespace chain {
@@ -111,6 +112,10 @@ struct Args {
   long long ver_rows;
   int* route;            // [rows][n_plan][C]
   int* born;             // [rows][s_max] token that created each memory row, or null
+  int* progress;         // [rows][nc] last update whose routes and version table are published (for the value-delta jobs
+                         // that spare CTAs of this launch work on meanwhile), or null
+  int* chain_done;       // CTAs of the routing that have finished
+  int chain_ctas;        // CTAs of the routing (the CTAs behind them take value-delta jobs)
   int* status;
   uint32_t wait_limit;
   uint32_t test_flags;   // bit 0: the issuer withholds one commit (exercises the timeout path)
@@ -213,6 +218,13 @@ struct Issuer {
   uint32_t n_w2i = 0, n_sc = 0, n_load = 0, n_zero = 0;
   volatile int* abort;
 
+  // Update u of this CTA's rows is complete in global memory (routes, version table): tell the CTAs that work on the
+  // value side.  Called behind a wait for all worker warps, whose writes this thread's fence makes visible with the flag.
+  __device__ __forceinline__ void publish(int u) {
+    if (a.progress == nullptr) return;
+    __threadfence();
+    *reinterpret_cast<volatile int*>(a.progress + (size_t)row * a.nc + crank) = u;
+  }
   __device__ __forceinline__ bool wait_workers() {
     const bool ok = wait(&bars->w2i, n_w2i & 1, a.wait_limit, abort);
     ++n_w2i;
@@ -318,6 +330,7 @@ struct Issuer {
       if (u == 0) {
         // the workers build the initial memory from the prepared keys and report when the block buffers are free
         if (!wait_workers()) return false;
+        if (primary) publish(0);
         n_load = 1;
         if (primary && a.n_plan > 1) load_block(1);
         if (primary && a.n_plan > 2 && crank == 0) prefetch_block(2);
@@ -380,6 +393,7 @@ struct Issuer {
       ++n_load;  // the loads of this update have been consumed; a worker thread has issued the next block's (see there)
       // the next routing pass reads the resident memory the workers are refreshing now
       if (!wait_workers()) return false;
+      if (primary) publish(u);
     }
     return true;
   }
@@ -1059,17 +1073,27 @@ struct Maps {
 };
 
 __global__ void __launch_bounds__(kThreads, 1)
-kvm_chain_tc_kernel(const __grid_constant__ Args a, const __grid_constant__ Maps maps) {
+kvm_chain_tc_kernel(const __grid_constant__ Args a, const __grid_constant__ Maps maps, const __grid_constant__ vside::DeltaArgs va,
+                    const __grid_constant__ vside::Maps vmaps) {
   extern __shared__ __align__(1024) unsigned char smem[];
   __shared__ __align__(16) float ln_s[2 * HD];
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  if ((int)blockIdx.x >= a.chain_ctas) {
+    // A spare CTA of the launch (whole clusters of them): it works on the value side of the updates the routing has
+    // published so far, until the routing is over; what is left then is taken by the kernel behind this one.
+    if (tid < vside::kThreads) vside::delta_jobs(va, vmaps, smem, tid);
+    return;
+  }
   const int nc = a.nc;
   const int row = blockIdx.x / nc, crank = blockIdx.x % nc;
   const Layout lay(a.L.C, a.s_max, nc);
   Bars* bars = reinterpret_cast<Bars*>(smem + lay.bars);
   const bool aligned = (tc::smem_u32(smem) & 1023u) == 0;  // operand tiles need 1024-byte alignment (uniform over the grid)
   if (!aligned) {
-    if (tid == 0) atomicExch(a.status, KVM_ERR_UNSUPPORTED);
+    if (tid == 0) {
+      atomicExch(a.status, KVM_ERR_UNSUPPORTED);
+      if (a.chain_done) atomicAdd(a.chain_done, 1);
+    }
     return;
   }
   for (int i = tid; i < HD; i += kThreads) {
@@ -1136,6 +1160,10 @@ kvm_chain_tc_kernel(const __grid_constant__ Args a, const __grid_constant__ Maps
   tc::tc_fence_before_sync();
   __syncthreads();
   if (warp == kWorkerWarps) tc::tmem_dealloc(tmem, kTmemCols);
+  if (tid == 0 && a.chain_done) {  // (the spare CTAs stop taking value-delta jobs when every routing CTA has got here)
+    __threadfence();
+    atomicAdd(a.chain_done, 1);
+  }
   if (nc > 1) cluster_barrier();  // nobody leaves while a peer may still write into its shared memory
 }
 
@@ -1375,10 +1403,11 @@ bool chain_tc_supported(int D, const LayerDev& L, int n_plan, int s_max, int row
 
 // The chain for one batch: routing + key side, then the value side.  pk_all / gk_all: [rows][n_plan*C][D] from the
 // pre-pass; route: [rows][n_plan][C].
-cudaError_t launch_vside(const LayerDev& L, int batch, long long T, Tensor4 v, Tensor4 gate, const kvm_update_plan* plan_dev,
-                         int n_plan, int s_max, MemoryDev mem, bf16* pool_v, long long pool_rows, const int* ver_idx,
-                         long long ver_rows, const int* route, const int* born, unsigned* tbits, int* status,
-                         uint32_t wait_limit, cudaStream_t stream);
+bool vside_setup(const LayerDev& L, int batch, long long T, Tensor4 v, Tensor4 gate, const kvm_update_plan* plan_dev, int n_plan,
+                 int s_max, bf16* pool_v, long long pool_rows, const int* ver_idx, long long ver_rows, const int* route,
+                 unsigned* tbits, int* status, uint32_t wait_limit, vside::DeltaArgs* a, vside::Maps* maps);
+size_t vside_smem_bytes(int C, int s_max);
+cudaError_t launch_vside(vside::DeltaArgs a, const vside::Maps& maps, Tensor4 v, MemoryDev mem, const int* born, cudaStream_t stream);
 
 cudaError_t launch_chain_tc(const LayerDev& L, int batch, long long T, Tensor4 v, Tensor4 gate, const kvm_update_plan* plan_dev,
                             int n_plan, int s_max, MemoryDev mem, bf16* pool_k, bf16* pool_v, long long pool_rows, int* ver_idx,
@@ -1403,12 +1432,49 @@ cudaError_t launch_chain_tc(const LayerDev& L, int batch, long long T, Tensor4 v
   a.k_sum = mem.k_sum; a.k_attn = mem.k_attn; a.capacity = mem.capacity;
   a.pool_k = ver_idx ? pool_k : nullptr; a.pool_rows = pool_rows; a.ver_idx = ver_idx; a.ver_rows = ver_rows;
   a.route = route; a.born = born; a.status = status; a.wait_limit = wait_limit; a.test_flags = test_flags;
-  cudaError_t e = cudaFuncSetAttribute(kvm_chain_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxSmem);
+  a.progress = nullptr; a.chain_done = nullptr; a.chain_ctas = rows * nc;
+  // The value side (with versions): deltas of every (kv row, update) on the tensor cores, then one warp per memory row.
+  // SMs the routing leaves free take value-delta jobs inside the same launch, as whole clusters behind the routing's,
+  // following the routing through a flag per (kv row, CTA); three control words and the flags live behind the bit table.
+  const bool vside_on = ver_idx && pool_v;
+  vside::DeltaArgs va = {};
+  vside::Maps vmaps = {};
+  int spare = 0;
+  size_t smem_bytes = lay.total;
+  cudaError_t e;
+  if (vside_on) {
+    if (!vside_setup(L, batch, T, v, gate, plan_dev, n_plan, s_max, pool_v, pool_rows, ver_idx, ver_rows, route, tbits, status,
+                     wait_limit, &va, &vmaps))
+      return cudaErrorInvalidValue;
+    // control words: job counter, finished routing CTAs, given-back jobs (count, taken), then the progress flags and
+    // the list of given-back jobs (one per spare CTA at most)
+    int* ctrl = reinterpret_cast<int*>(tbits + (size_t)rows * n_plan * va.words);
+    e = cudaMemsetAsync(ctrl, 0, (size_t)(4 + rows * nc) * sizeof(int), stream);
+    if (e != cudaSuccess) return e;
+    va.queue = ctrl;
+    int dev = 0, n_sm = 0;
+    if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, dev);
+    spare = std::max(0, (n_sm - rows * nc) / nc) * nc;
+    if (vside_smem_bytes(C, s_max) > (size_t)kMaxSmem) spare = 0;
+    if (spare > 0) {
+      a.chain_done = ctrl + 1;
+      a.progress = ctrl + 4;
+      va.n_given_back = ctrl + 2;
+      va.given_back_taken = ctrl + 3;
+      va.given_back = ctrl + 4 + rows * nc;
+      va.chain_done = a.chain_done;
+      va.progress = a.progress;
+      va.nc = nc;
+      va.chain_ctas = rows * nc;
+      smem_bytes = std::max(smem_bytes, vside_smem_bytes(C, s_max));
+    }
+  }
+  e = cudaFuncSetAttribute(kvm_chain_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxSmem);
   if (e != cudaSuccess) return e;
   cudaLaunchConfig_t cfg = {};
   cfg.blockDim = dim3(kThreads);
-  cfg.gridDim = dim3(rows * nc);
-  cfg.dynamicSmemBytes = lay.total;
+  cfg.gridDim = dim3(rows * nc + spare);
+  cfg.dynamicSmemBytes = smem_bytes;
   cfg.stream = stream;
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeClusterDimension;
@@ -1417,12 +1483,9 @@ cudaError_t launch_chain_tc(const LayerDev& L, int batch, long long T, Tensor4 v
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  e = cudaLaunchKernelEx(&cfg, kvm_chain_tc_kernel, a, maps);
+  e = cudaLaunchKernelEx(&cfg, kvm_chain_tc_kernel, a, maps, va, vmaps);
   if (e != cudaSuccess) return e;
-  // value side.  With versions: deltas of every (kv row, update) on the tensor cores, then one warp per memory row.
-  if (ver_idx && pool_v)
-    return launch_vside(L, batch, T, v, gate, plan_dev, n_plan, s_max, mem, pool_v, pool_rows, ver_idx, ver_rows, route, born,
-                        tbits, status, wait_limit, stream);
+  if (vside_on) return launch_vside(va, vmaps, v, mem, born, stream);
   // Without (only the final memory is wanted): one warp per memory row walks the routing decisions itself, as many
   // updates as fit 64 KB per tile
   const int tile_updates = std::max(1, std::min(n_plan, (64 * 1024) / (C * 2)));
