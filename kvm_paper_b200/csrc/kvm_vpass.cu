@@ -33,7 +33,7 @@ kvm_vdelta_kernel(const __grid_constant__ DeltaArgs a, const __grid_constant__ M
 constexpr int kApWarps = 8;
 
 // One warp per memory row.  born[row * s_final + r]: the token that created memory row r.
-__global__ void __launch_bounds__(kApWarps * 32, 4)
+__global__ void __launch_bounds__(kApWarps * 32, 8)
 kvm_vapply_kernel(LayerDev L, Tensor4 v, Tensor4 gate, const kvm_update_plan* __restrict__ plan, int n_plan,
                   const int* __restrict__ born, MemoryDev mem, bf16* __restrict__ pool_v, long long pool_rows,
                   const int* __restrict__ ver_idx, long long ver_rows, const unsigned* __restrict__ tbits, int words,
@@ -88,9 +88,10 @@ kvm_vapply_kernel(LayerDev L, Tensor4 v, Tensor4 gate, const kvm_update_plan* __
     }
     unsigned todo = __ballot_sync(0xffffffffu, touched || u == u_b);
     const unsigned tmask = __ballot_sync(0xffffffffu, touched);
-    // the deltas of up to eight touched updates are fetched together
+    // the deltas of two touched updates are fetched together (more in flight per warp costs registers, and with them
+    // resident warps: a full SM of warps with two loads each hides the latency better than half of one with eight)
     while (todo) {
-      constexpr int NB = 8;
+      constexpr int NB = 2;
       int src[NB], sl[NB];
       uint2 dl[NB];
       int n = 0;
