@@ -214,6 +214,9 @@ def run_b200(args):
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
     if world > 1:
+        # the output gather runs alone (nothing to overlap it with): let NCCL use more of the GPU than its default
+        os.environ.setdefault("NCCL_MIN_NCHANNELS", "64")
+        os.environ.setdefault("NCCL_NTHREADS", "512")
         dist.init_process_group("nccl", device_id=dev)
     _lib.load()
     cfg = CFG2
@@ -237,7 +240,7 @@ def run_b200(args):
 
     def step():
         out = runner.run(q, k, v, gate)
-        return sharding.gather_heads(out, world)  # [B,T,H*D] on every rank (NCCL all-gather + head-order permute)
+        return sharding.gather_heads(out, world)  # [B,T,H*D] on every rank (NCCL all-gather + the library's head-order copy)
 
     def barrier():
         if world > 1:

@@ -246,6 +246,12 @@ int kvm_decode_step_static(const kvm_layer* layer, int32_t batch, kvm_decode_cac
 int kvm_memory_refresh(const kvm_layer* layer, int32_t batch, kvm_memory memory,
                        const int32_t* state_len_dev, void* stream);
 
+/* Head order after an all-gather of head-sharded mixer outputs: src [n_shards][n_tokens][shard_bytes] (what
+ * an all-gather of the ranks' [B*T, h_loc*D] outputs leaves) -> dst [n_tokens][n_shards][shard_bytes], i.e.
+ * [B, T, H*D] with the heads in rank order.  shard_bytes a multiple of 16, both buffers 16-byte aligned.
+ * No counterpart in the reference (its mixers run on one device); replaces a strided tensor copy in the host code. */
+int kvm_interleave_shards(void* dst, const void* src, int32_t n_shards, int64_t n_tokens, int64_t shard_bytes, void* stream);
+
 /* Description of the last error of the calling thread ("" if none). */
 const char* kvm_last_error_string(void);
 

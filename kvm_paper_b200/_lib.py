@@ -57,7 +57,7 @@ class KvmDecodeCache(C.Structure):
 EXPORTS = [
     "kvm_prefill_workspace_bytes", "kvm_prefill_forward", "kvm_decode_workspace_bytes", "kvm_decode_step",
     "kvm_memory_refresh", "kvm_last_error_string", "kvm_abi_version", "kvm_decode_step_static", "kvm_prefill_status", "kvm_decode_run",
-    "kvm_decode_status", "kvm_prefill_workspace_layout",
+    "kvm_decode_status", "kvm_prefill_workspace_layout", "kvm_interleave_shards",
 ]
 STATIC_SCRATCH_BYTES = 32 << 20
 
@@ -106,6 +106,8 @@ def load():
         C.c_void_p, C.c_int32, C.c_int32, C.c_void_p, C.c_void_p, C.c_void_p]
     lib.kvm_memory_refresh.restype = C.c_int
     lib.kvm_memory_refresh.argtypes = [LP(KvmLayer), C.c_int32, KvmMemory, C.c_void_p, C.c_void_p]
+    lib.kvm_interleave_shards.restype = C.c_int
+    lib.kvm_interleave_shards.argtypes = [C.c_void_p, C.c_void_p, C.c_int32, C.c_int64, C.c_int64, C.c_void_p]
     lib.kvm_last_error_string.restype = C.c_char_p
     lib.kvm_last_error_string.argtypes = []
     lib.kvm_abi_version.restype = C.c_int

@@ -186,6 +186,11 @@ int static_scratch_for_current_device(void** out) {
 
 }  // namespace
 
+namespace kvm {
+cudaError_t launch_interleave_shards(void* dst, const void* src, int n_shards, long long n_tokens, long long shard_bytes, cudaStream_t stream);
+}
+using kvm::launch_interleave_shards;
+
 extern "C" {
 
 const char* kvm_last_error_string(void) { return g_err; }
@@ -421,6 +426,16 @@ int kvm_memory_refresh(const kvm_layer* layer, int32_t batch, kvm_memory memory,
     return fail(KVM_ERR_BAD_ARGUMENT, "memory arrays must not be NULL");
   cudaError_t e = refresh_dispatch(layer->head_dim, to_dev(layer), batch, to_dev(memory), state_len_dev, static_cast<cudaStream_t>(stream));
   if (e != cudaSuccess) return cuda_fail(e, "kvm_memory_refresh");
+  return KVM_OK;
+}
+
+int kvm_interleave_shards(void* dst, const void* src, int32_t n_shards, int64_t n_tokens, int64_t shard_bytes, void* stream) {
+  g_err[0] = 0;
+  if (!dst || !src || n_shards <= 0 || n_tokens <= 0 || shard_bytes <= 0 || shard_bytes % 16 || ((uintptr_t)dst) % 16 || ((uintptr_t)src) % 16)
+    return fail(KVM_ERR_BAD_ARGUMENT, "kvm_interleave_shards: buffers must be 16-byte aligned and shard_bytes (%lld) a positive multiple of 16",
+                (long long)shard_bytes);
+  cudaError_t e = launch_interleave_shards(dst, src, n_shards, n_tokens, shard_bytes, static_cast<cudaStream_t>(stream));
+  if (e != cudaSuccess) return cuda_fail(e, "kvm_interleave_shards");
   return KVM_OK;
 }
 

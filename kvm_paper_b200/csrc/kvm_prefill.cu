@@ -1,3 +1,4 @@
+#include <algorithm>
 // Prefill kernels: (1) the memory chain -- initial memory, then one block-recurrent update per
 // token block, each leaving a "version" of the attention view of the memory (an index table into a row pool);
 // (2) block attention -- every query tile attends jointly to [memory version ; sliding window]
@@ -553,6 +554,31 @@ size_t update_smem_bytes(int D, int C, int capacity) {  // of the variant withou
     case 128: return UpdateSmem<128>::bytes(C, capacity, false);
   }
   return 0;
+}
+
+// ------------------------------------------------------------------------------------ head order after a gather
+// src [n_shards][n_tokens][pieces] -> dst [n_tokens][n_shards][pieces], 16-byte pieces: consecutive threads copy
+// consecutive pieces of the destination, so both sides move whole runs of `pieces` x 16 bytes.
+__global__ void __launch_bounds__(256)
+kvm_interleave_shards_kernel(uint4* __restrict__ dst, const uint4* __restrict__ src, int n_shards, long long n_tokens, int pieces) {
+  const long long total = n_tokens * n_shards * pieces;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+    const int p = (int)(i % pieces);
+    const long long ts = i / pieces;
+    const int sh = (int)(ts % n_shards);
+    const long long t = ts / n_shards;
+    dst[i] = src[((long long)sh * n_tokens + t) * pieces + p];
+  }
+}
+
+cudaError_t launch_interleave_shards(void* dst, const void* src, int n_shards, long long n_tokens, long long shard_bytes, cudaStream_t stream) {
+  const int pieces = (int)(shard_bytes / 16);
+  const long long total = n_tokens * n_shards * pieces;
+  int dev = 0, n_sm = 148;
+  if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, dev);
+  const int grid = (int)std::min<long long>((total + 255) / 256, (long long)n_sm * 16);
+  kvm_interleave_shards_kernel<<<grid, 256, 0, stream>>>(static_cast<uint4*>(dst), static_cast<const uint4*>(src), n_shards, n_tokens, pieces);
+  return cudaGetLastError();
 }
 
 }  // namespace kvm

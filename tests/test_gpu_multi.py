@@ -39,3 +39,19 @@ def test_two_gpu_results_equal_single_gpu():
             break
     assert res.returncode == 0, res.stdout[-2000:] + res.stderr[-2000:]
     assert "MULTI_GPU_OK" in res.stdout, res.stdout[-2000:] + res.stderr[-2000:]
+
+
+def test_interleave_shards_equals_the_strided_copy():
+    """The copy kernel behind ``gather_heads`` (one GPU is enough): [shards, tokens, shard] -> [tokens, shards * shard]."""
+    from kvm_paper_b200 import _lib
+
+    torch.manual_seed(0)
+    for world, tokens, hd in ((2, 1000, 1024), (8, 333, 256), (4, 7, 8)):
+        buf = torch.randn(world, tokens, hd, device="cuda").bfloat16()
+        full = torch.empty(tokens, world * hd, device="cuda", dtype=torch.bfloat16)
+        rc = _lib.load().kvm_interleave_shards(full.data_ptr(), buf.data_ptr(), world, tokens, hd * 2,
+                                               torch.cuda.current_stream().cuda_stream)
+        _lib.check(rc)
+        assert torch.equal(full, buf.permute(1, 0, 2).reshape(tokens, world * hd))
+    with pytest.raises(ValueError):  # argument errors are ValueErrors, as in the reference
+        _lib.check(_lib.load().kvm_interleave_shards(full.data_ptr(), buf.data_ptr(), 2, 4, 10, None))  # not a multiple of 16
