@@ -9,24 +9,33 @@
 //   kvm_chain_tc_kernel   routing and the KEY side of the memory: a cluster of 1..8 CTAs per kv row walks all
 //                         updates.  Memory row r belongs to CTA r % nc, which keeps the attention view of its
 //                         rows (k_attn) RESIDENT in shared memory in the tensor-core operand layout, so a routing
-//                         pass loads nothing: per update
-//                           1. novelty pass   S = pk x k_attn^T (tcgen05, accumulators in tensor memory), running
-//                                             maximum per token, partial maxima exchanged through distributed
-//                                             shared memory, rounded to bf16; the n_append lowest are appended
-//                           2. logits pass    S = gk x k_attn^T against the memory after the appends, running fp32
-//                                             first-argmax per token (sink rows excluded), partial results
-//                                             exchanged, lowest row wins ties
-//                           3. scatter        delta[rows x D] = onehot[rows x tokens] x gk[tokens x D] on the
+//                         pass loads nothing.  Per update, in the common case of few appended rows:
+//                           1. logits pass    S = gk x k_attn^T against the memory as it is (tcgen05, accumulators
+//                                             in tensor memory), running fp32 first-argmax per token (sink rows
+//                                             excluded), then the novelty pass S = pk x k_attn^T, running maximum
+//                                             per token; both partial results exchanged between the CTAs in one
+//                                             go (st.async into the peers' shared memory); the n_append tokens of
+//                                             lowest bf16-rounded novelty are appended (LayerNorm by one warp per
+//                                             row) and scored against every token (dot products, or a small third
+//                                             MMA pass); a new row wins a token only with a strictly larger logit
+//                                             (with many appended rows: novelty pass, appends, then one logits pass
+//                                             against the memory after the appends)
+//                           2. scatter        delta[rows x D] = onehot[rows x tokens] x gk[tokens x D] on the
 //                                             tensor cores (touched rows compacted onto the 128 accumulator
-//                                             lanes; products are exact, the accumulation order is the hardware's
-//                                             and fixed), then row = bf16(row + bf16(delta)), LayerNorm refresh of
-//                                             the touched rows into shared memory and into the row pool
+//                                             lanes; the one-hot operand lives in the buffer of the prepared keys,
+//                                             cleared by the copy engine; products are exact, the accumulation order
+//                                             is the hardware's and fixed), then row = bf16(row + bf16(delta)),
+//                                             LayerNorm refresh of the touched rows into shared memory and into the
+//                                             row pool
 //                         Prepared keys pk and gated keys gk = bf16(pk * gate) of every token come from a parallel
-//                         pre-pass and arrive by tiled TMA one update ahead.
-//   kvm_vpass_kernel      the VALUE side, which no later update reads: one warp per memory row walks the routing
-//                         decisions of all updates and accumulates the gated values routed to its row in token
-//                         order (fixed-order, warp-parallel over the head dimension), writing the row's value view
-//                         for every version it changes.  Fully parallel over rows and kv rows.
+//                         pre-pass and arrive by tiled TMA, issued as soon as the scatter has read the buffers.
+//                         CTAs of the launch beyond the routing's (whole clusters on the SMs it leaves free) work on
+//                         the value side meanwhile: see kvm_vdelta.cuh.
+//   value side            which no later update reads: value deltas per (kv row, update) on the tensor cores
+//                         (kvm_vdelta.cuh), then one warp per memory row (kvm_vpass.cu); kvm_vpass_kernel below is
+//                         the variant for a chain of which only the final memory is wanted (no versions): one warp
+//                         per memory row walks the routing decisions of all updates and accumulates the gated
+//                         values routed to its row in token order.
 // Every wait is bounded; a wait that runs out sets the status word, all roles and all CTAs of the cluster leave
 // through the common exit, tensor memory is freed.
 #include <algorithm>
