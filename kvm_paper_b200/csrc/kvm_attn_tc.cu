@@ -239,6 +239,12 @@ __device__ __forceinline__ bool mma_role(const Slice<NQ>& sl, unsigned char* sme
   return true;
 }
 
+__device__ __forceinline__ float max3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
+
 // ------------------------------------------------------------------------------------------ softmax
 // One query row per thread of warpgroup qi.  Returns false if a bounded wait expired.
 template <int NQ>
@@ -277,9 +283,9 @@ __device__ __forceinline__ bool softmax_role(const Slice<NQ>& sl, const LayerDev
     }
     float tm0 = -INFINITY, tm1 = -INFINITY;
 #pragma unroll
-    for (int i = 0; i < 32; ++i) {
-      tm0 = fmaxf(tm0, __uint_as_float(sr[0][i]));
-      tm1 = fmaxf(tm1, __uint_as_float(sr[1][i]));
+    for (int i = 0; i < 32; i += 2) {
+      tm0 = max3(tm0, __uint_as_float(sr[0][i]), __uint_as_float(sr[0][i + 1]));
+      tm1 = max3(tm1, __uint_as_float(sr[1][i]), __uint_as_float(sr[1][i + 1]));
     }
     const float tmax = fmaxf(tm0, tm1) * sc;  // sc > 0
     const bool need = tmax > m_run + kRescaleThreshold || (m_run == -INFINITY && tmax > -INFINITY);
@@ -299,7 +305,11 @@ __device__ __forceinline__ bool softmax_role(const Slice<NQ>& sl, const LayerDev
           tc::tmem_ld16(lane_addr + col_o + cb * 16, o);
           tc::tmem_ld_wait();
 #pragma unroll
-          for (int i = 0; i < 16; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+          for (int i = 0; i < 16; i += 2) {
+            const float2 r = __fmul2_rn(make_float2(__uint_as_float(o[i]), __uint_as_float(o[i + 1])), make_float2(alpha, alpha));
+            o[i] = __float_as_uint(r.x);
+            o[i + 1] = __float_as_uint(r.y);
+          }
           tc::tmem_st16(lane_addr + col_o + cb * 16, o);
         }
         tc::tmem_st_wait();
@@ -307,7 +317,8 @@ __device__ __forceinline__ bool softmax_role(const Slice<NQ>& sl, const LayerDev
       m_run = m_new;
     }
     const float neg_m = (m_run == -INFINITY) ? 0.f : -m_run;
-    float ls0 = 0.f, ls1 = 0.f;
+    float2 ls = make_float2(0.f, 0.f);
+    const float2 sc2 = make_float2(sc, sc), nm2 = make_float2(neg_m, neg_m);
     // P replaces the scores it came from (all 64 columns of this row are in registers): the A operand of P V,
     // written in two halves of 16 columns (32 keys) each
 #pragma unroll
@@ -315,15 +326,15 @@ __device__ __forceinline__ bool softmax_role(const Slice<NQ>& sl, const LayerDev
       uint32_t pk[16];
 #pragma unroll
       for (int e = 0; e < 16; ++e) {
-        const float p0 = ex2(fmaf(__uint_as_float(sr[half][e * 2]), sc, neg_m));
-        const float p1 = ex2(fmaf(__uint_as_float(sr[half][e * 2 + 1]), sc, neg_m));
-        ls0 += p0;
-        ls1 += p1;
-        pk[e] = pack_bf16(p0, p1);
+        // two keys per instruction: the packed fp32 forms of the multiply-add and of the add
+        const float2 x = __ffma2_rn(make_float2(__uint_as_float(sr[half][e * 2]), __uint_as_float(sr[half][e * 2 + 1])), sc2, nm2);
+        const float2 p = make_float2(ex2(x.x), ex2(x.y));
+        ls = __fadd2_rn(ls, p);
+        pk[e] = pack_bf16(p.x, p.y);
       }
       tc::tmem_st16(lane_addr + (uint32_t)((qi * 2 + sbuf) * BN + half * 16), pk);
     }
-    l_run += ls0 + ls1;
+    l_run += ls.x + ls.y;
     tc::tmem_st_wait();
     tc::tc_fence_before_sync();
     __syncwarp();
