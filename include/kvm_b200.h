@@ -154,6 +154,53 @@ typedef struct kvm_prefill_layout {
 int kvm_prefill_workspace_layout(const kvm_layer* layer, int32_t batch, int64_t seq_len,
                                  int64_t total_version_rows, kvm_prefill_layout* out);
 
+/* The mixer's prologue in one pass over the projection outputs: token shift, per-head LayerNorm of q and k, rotary
+ * embedding, merge gate, and the prepared / gated keys of the tokens the memory updates will consume.
+ * Replaces the elementwise part of calc_qkv (model/value_residual_mixin.py:219-235: apply_token_shift of
+ * model/tokenshift.py:11-37, ln_q, ln_k) and of forward's prefix (model/kvm_mixer.py:381-399:
+ * apply_rotary_embeddings of model/rwkv7_backbone.py:76-88, merge gate 1 + elu(key_weighting(x)), head-major views);
+ * the projections themselves (c_q, c_k, c_v, key_weighting: plain GEMMs) and the value residual stay with the caller.
+ * All tensors bf16 and contiguous unless said; every operation rounds to bf16 where the reference's bf16 module does.
+ *   q_lin [B,T,Hq*D], k_lin, v_lin [B,T,Hkv*D]   projection outputs (v after a pre-shift value residual)
+ *   gate_lin [B,T,Hkv]                            key_weighting output, NULL: gate of ones
+ *   shift_q [Hq*D], shift_k, shift_v [Hkv*D]      token-shift scales, all three NULL: no token shift
+ *   prev_q [B,Hq*D], prev_k, prev_v [B,Hkv*D]     last token of the previous call (cached decode), NULL: the first
+ *                                                 token is shifted against itself
+ *   ln_q_w, ln_q_b, ln_k_w, ln_k_b [D] fp32       per-head LayerNorm of q and k, all four NULL: none
+ *   cos, sin [B or 1, T, D]                       rotary tables as RotaryEmbedding returns them (the sign of the
+ *                                                 odd sin entries folded in); rope_stride_b = T*D or 0; NULL: none */
+typedef struct kvm_prologue {
+  const void* q_lin;
+  const void* k_lin;
+  const void* v_lin;
+  const void* gate_lin;
+  const void* shift_q;
+  const void* shift_k;
+  const void* shift_v;
+  const void* prev_q;
+  const void* prev_k;
+  const void* prev_v;
+  const float* ln_q_w;
+  const float* ln_q_b;
+  const float* ln_k_w;
+  const float* ln_k_b;
+  float ln_qk_eps;
+  const void* cos;
+  const void* sin;
+  int64_t rope_stride_b;
+} kvm_prologue;
+/*   q_out [B,T,Hq,D], k_out, v_out [B,T,Hkv,D]   the operator's inputs (pass them on as [B,H,T,D] views)
+ *   gate_out [B,Hkv,T]                           merge gate
+ *   workspace  a prefill workspace for this shape (kvm_prefill_workspace_bytes) or NULL.  When given and the
+ *              prompt has memory updates, the prepared keys (and, for the tensor-core chain, the gated keys) of
+ *              the consumed tokens are written where kvm_prefill_forward keeps them, and a following
+ *              kvm_prefill_forward on the same workspace may be given KVM_PREFILL_KEYS_PREPARED to skip its own
+ *              pass over the keys (same bits either way). */
+#define KVM_PREFILL_KEYS_PREPARED 32u /* with CHAIN: the workspace already holds the prepared keys (kvm_prologue_forward) */
+int kvm_prologue_forward(const kvm_layer* layer, int32_t batch, int64_t seq_len, const kvm_prologue* in,
+                         void* q_out, void* k_out, void* v_out, void* gate_out, int64_t total_version_rows,
+                         void* workspace, size_t workspace_bytes, void* stream);
+
 /* The decode-time cache of one layer for `batch` sequences with ragged lengths (all device memory,
  * caller-owned).  Replaces TritonKVMDecodeCache (model/kvm_triton_decode.py:34-400); unlike the
  * reference's cache, lengths are per sequence. */

@@ -15,6 +15,7 @@ LIB_PATH = os.path.join(_HERE, "libkvm_b200.so")
 KVM_OK = 0
 PREFILL_CHAIN, PREFILL_ATTENTION, PREFILL_LEGACY_ATTENTION, PREFILL_LEGACY_CHAIN = 1, 2, 4, 8
 PREFILL_TEST_WITHHOLD_ARRIVAL = 16
+PREFILL_KEYS_PREPARED = 32
 ERROR_NAMES = {1: "bad argument", 2: "capacity", 3: "device timeout", 4: "CUDA error", 5: "unsupported"}
 
 
@@ -49,6 +50,12 @@ class KvmPrefillLayout(C.Structure):
                 ("gated_keys_offset", C.c_size_t), ("pool_rows", C.c_int64), ("total_bytes", C.c_size_t)]
 
 
+class KvmPrologue(C.Structure):
+    _fields_ = [(n, C.c_void_p) for n in ("q_lin", "k_lin", "v_lin", "gate_lin", "shift_q", "shift_k", "shift_v",
+                                          "prev_q", "prev_k", "prev_v", "ln_q_w", "ln_q_b", "ln_k_w", "ln_k_b")] + [
+        ("ln_qk_eps", C.c_float), ("cos", C.c_void_p), ("sin", C.c_void_p), ("rope_stride_b", C.c_int64)]
+
+
 class KvmDecodeCache(C.Structure):
     _fields_ = [("memory", KvmMemory), ("ring_k", C.c_void_p), ("ring_v", C.c_void_p),
                 ("ring_gate", C.c_void_p), ("total_len", C.c_void_p), ("state_len", C.c_void_p)]
@@ -57,7 +64,7 @@ class KvmDecodeCache(C.Structure):
 EXPORTS = [
     "kvm_prefill_workspace_bytes", "kvm_prefill_forward", "kvm_decode_workspace_bytes", "kvm_decode_step",
     "kvm_memory_refresh", "kvm_last_error_string", "kvm_abi_version", "kvm_decode_step_static", "kvm_prefill_status", "kvm_decode_run",
-    "kvm_decode_status", "kvm_prefill_workspace_layout", "kvm_interleave_shards",
+    "kvm_decode_status", "kvm_prefill_workspace_layout", "kvm_interleave_shards", "kvm_prologue_forward",
 ]
 STATIC_SCRATCH_BYTES = 32 << 20
 
@@ -106,6 +113,9 @@ def load():
         C.c_void_p, C.c_int32, C.c_int32, C.c_void_p, C.c_void_p, C.c_void_p]
     lib.kvm_memory_refresh.restype = C.c_int
     lib.kvm_memory_refresh.argtypes = [LP(KvmLayer), C.c_int32, KvmMemory, C.c_void_p, C.c_void_p]
+    lib.kvm_prologue_forward.restype = C.c_int
+    lib.kvm_prologue_forward.argtypes = [LP(KvmLayer), C.c_int32, C.c_int64, LP(KvmPrologue), C.c_void_p, C.c_void_p, C.c_void_p,
+                                         C.c_void_p, C.c_int64, C.c_void_p, C.c_size_t, C.c_void_p]
     lib.kvm_interleave_shards.restype = C.c_int
     lib.kvm_interleave_shards.argtypes = [C.c_void_p, C.c_void_p, C.c_int32, C.c_int64, C.c_int64, C.c_void_p]
     lib.kvm_last_error_string.restype = C.c_char_p

@@ -15,7 +15,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libkvm_b200.so")
-SOURCES = ["kvm_abi.cu", "kvm_prefill.cu", "kvm_chain_tc.cu", "kvm_vpass.cu", "kvm_attn_tc.cu", "kvm_decode.cu"]
+SOURCES = ["kvm_abi.cu", "kvm_prefill.cu", "kvm_chain_tc.cu", "kvm_vpass.cu", "kvm_attn_tc.cu", "kvm_decode.cu", "kvm_prologue.cu"]
 HEADERS = ["kvm_common.cuh", "kvm_update.cuh", "kvm_tc.cuh", "kvm_tma_host.cuh", "kvm_vdelta.cuh", os.path.join("..", "..", "include", "kvm_b200.h")]
 
 

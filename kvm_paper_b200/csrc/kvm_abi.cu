@@ -187,6 +187,7 @@ int static_scratch_for_current_device(void** out) {
 }  // namespace
 
 namespace kvm {
+cudaError_t launch_prologue(int D, const LayerDev& L, const PrologueDev& p, int batch, long long T, cudaStream_t stream);
 cudaError_t launch_interleave_shards(void* dst, const void* src, int n_shards, long long n_tokens, long long shard_bytes, cudaStream_t stream);
 }
 using kvm::launch_interleave_shards;
@@ -210,7 +211,7 @@ int kvm_prefill_forward(const kvm_layer* layer, int32_t batch, int64_t seq_len, 
   g_err[0] = 0;
   if (int rc = check_layer(layer)) return rc;
   if (batch <= 0 || seq_len <= 0) return fail(KVM_ERR_BAD_ARGUMENT, "batch %d and seq_len %lld must be positive", batch, (long long)seq_len);
-  if ((phases & 3u) == 0 || (phases & ~31u)) return fail(KVM_ERR_BAD_ARGUMENT, "phases %u must be a combination of KVM_PREFILL_CHAIN and KVM_PREFILL_ATTENTION", phases);
+  if ((phases & 3u) == 0 || (phases & ~63u)) return fail(KVM_ERR_BAD_ARGUMENT, "phases %u must be a combination of KVM_PREFILL_CHAIN and KVM_PREFILL_ATTENTION", phases);
   const int D = layer->head_dim, C = layer->chunk_len, W = layer->n_bswa_chunks;
   if (int rc = check_tensor(q, "q", D)) return rc;
   if (int rc = check_tensor(k, "k", D)) return rc;
@@ -261,6 +262,67 @@ int kvm_prefill_forward(const kvm_layer* layer, int32_t batch, int64_t seq_len, 
                                    reinterpret_cast<int*>(wsb + ws.status), phases,
                                    static_cast<cudaStream_t>(stream));
   if (e != cudaSuccess) return cuda_fail(e, "kvm_prefill_forward");
+  return KVM_OK;
+}
+
+int kvm_prologue_forward(const kvm_layer* layer, int32_t batch, int64_t seq_len, const kvm_prologue* in, void* q_out,
+                         void* k_out, void* v_out, void* gate_out, int64_t total_version_rows, void* workspace,
+                         size_t workspace_bytes, void* stream) {
+  g_err[0] = 0;
+  if (int rc = check_layer(layer)) return rc;
+  if (batch <= 0 || seq_len <= 0) return fail(KVM_ERR_BAD_ARGUMENT, "batch %d and seq_len %lld must be positive", batch, (long long)seq_len);
+  if (!in || !in->q_lin || !in->k_lin || !in->v_lin || !q_out || !k_out || !v_out || !gate_out)
+    return fail(KVM_ERR_BAD_ARGUMENT, "kvm_prologue_forward: projections and outputs must not be NULL");
+  const int D = layer->head_dim;
+  if (D != 32 && D != 64 && D != 128) return fail(KVM_ERR_UNSUPPORTED, "kvm_prologue_forward: head_dim %d (supported: 32, 64, 128)", D);
+  const int n_shift = (in->shift_q != nullptr) + (in->shift_k != nullptr) + (in->shift_v != nullptr);
+  if (n_shift != 0 && n_shift != 3) return fail(KVM_ERR_BAD_ARGUMENT, "token-shift scales must be given for q, k and v or for none");
+  const int n_ln = (in->ln_q_w != nullptr) + (in->ln_q_b != nullptr) + (in->ln_k_w != nullptr) + (in->ln_k_b != nullptr);
+  if (n_ln != 0 && n_ln != 4) return fail(KVM_ERR_BAD_ARGUMENT, "LayerNorm weights and biases must be given for q and k or for neither");
+  if ((in->cos == nullptr) != (in->sin == nullptr)) return fail(KVM_ERR_BAD_ARGUMENT, "cos and sin must both be given or both be NULL");
+  if (in->cos && in->rope_stride_b != 0 && in->rope_stride_b != seq_len * D)
+    return fail(KVM_ERR_BAD_ARGUMENT, "rope_stride_b %lld must be 0 or seq_len*head_dim", (long long)in->rope_stride_b);
+  const void* aligned[] = {in->q_lin, in->k_lin, in->v_lin, in->shift_q, in->shift_k, in->shift_v, in->prev_q, in->prev_k, in->prev_v,
+                           in->cos, in->sin, q_out, k_out, v_out};
+  for (const void* a : aligned)
+    if (((uintptr_t)a) % 16) return fail(KVM_ERR_BAD_ARGUMENT, "kvm_prologue_forward: tensors must be 16-byte aligned");
+  kvm::PrologueDev p = {};
+  p.q_lin = static_cast<const bf16*>(in->q_lin);
+  p.k_lin = static_cast<const bf16*>(in->k_lin);
+  p.v_lin = static_cast<const bf16*>(in->v_lin);
+  p.gate_lin = static_cast<const bf16*>(in->gate_lin);
+  p.shift_q = static_cast<const bf16*>(in->shift_q);
+  p.shift_k = static_cast<const bf16*>(in->shift_k);
+  p.shift_v = static_cast<const bf16*>(in->shift_v);
+  p.prev_q = static_cast<const bf16*>(in->prev_q);
+  p.prev_k = static_cast<const bf16*>(in->prev_k);
+  p.prev_v = static_cast<const bf16*>(in->prev_v);
+  p.ln_q_w = in->ln_q_w;
+  p.ln_q_b = in->ln_q_b;
+  p.ln_k_w = in->ln_k_w;
+  p.ln_k_b = in->ln_k_b;
+  p.ln_qk_eps = in->ln_qk_eps;
+  p.cos = static_cast<const bf16*>(in->cos);
+  p.sin = static_cast<const bf16*>(in->sin);
+  p.rope_stride_b = in->rope_stride_b;
+  p.q_out = static_cast<bf16*>(q_out);
+  p.k_out = static_cast<bf16*>(k_out);
+  p.v_out = static_cast<bf16*>(v_out);
+  p.gate_out = static_cast<bf16*>(gate_out);
+  const long long C = layer->chunk_len;
+  const long long n_qblocks = (seq_len + C - 1) / C;
+  const long long n_plan = n_qblocks > layer->n_bswa_chunks ? n_qblocks - layer->n_bswa_chunks : 1;
+  if (workspace && n_plan > 1) {
+    const PrefillWs ws = prefill_ws(layer, batch, seq_len, total_version_rows);
+    if (workspace_bytes < ws.total) return fail(KVM_ERR_CAPACITY, "workspace of %zu bytes given, %zu needed", workspace_bytes, ws.total);
+    if (((uintptr_t)workspace) % 256) return fail(KVM_ERR_BAD_ARGUMENT, "workspace must be 256-byte aligned");
+    unsigned char* wsb = static_cast<unsigned char*>(workspace);
+    p.pk_all = reinterpret_cast<bf16*>(wsb + ws.pk_all);
+    p.gk_all = ws.route > ws.gk_all ? reinterpret_cast<bf16*>(wsb + ws.gk_all) : nullptr;  // present for the tensor-core chain's shapes
+    p.n_tok = n_plan * C;
+  }
+  const cudaError_t e = kvm::launch_prologue(D, to_dev(layer), p, batch, seq_len, static_cast<cudaStream_t>(stream));
+  if (e != cudaSuccess) return cuda_fail(e, "kvm_prologue_forward");
   return KVM_OK;
 }
 

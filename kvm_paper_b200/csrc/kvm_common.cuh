@@ -34,6 +34,35 @@ struct Tensor4 {
   }
 };
 
+// Arguments of the fused prologue kernel (the projections' outputs, the module's parameters, the outputs).
+struct PrologueDev {
+  const bf16* q_lin;
+  const bf16* k_lin;
+  const bf16* v_lin;
+  const bf16* gate_lin;
+  const bf16* shift_q;
+  const bf16* shift_k;
+  const bf16* shift_v;
+  const bf16* prev_q;
+  const bf16* prev_k;
+  const bf16* prev_v;
+  const float* ln_q_w;
+  const float* ln_q_b;
+  const float* ln_k_w;
+  const float* ln_k_b;
+  float ln_qk_eps;
+  const bf16* cos;
+  const bf16* sin;
+  long long rope_stride_b;
+  bf16* q_out;
+  bf16* k_out;
+  bf16* v_out;
+  bf16* gate_out;
+  bf16* pk_all;
+  bf16* gk_all;
+  long long n_tok;  // tokens per kv row in pk_all / gk_all
+};
+
 struct MemoryDev {
   bf16* k_sum;
   bf16* v_sum;

@@ -455,7 +455,7 @@ static cudaError_t launch_prefill(const LayerDev& L, int batch, long long T, Ten
   cudaError_t e;
   // head_dim 128 and blocks of 128 / 256 tokens: the chain with the resident memory on the tensor cores
   const bool tc_chain = !(phases & KVM_PREFILL_LEGACY_CHAIN) && chain_tc_supported(D, L, n_plan, s_final, rows);
-  if ((phases & KVM_PREFILL_CHAIN) && n_plan > 1) {
+  if ((phases & KVM_PREFILL_CHAIN) && n_plan > 1 && !(phases & KVM_PREFILL_KEYS_PREPARED)) {
     const long long n_tok = (long long)n_plan * L.C;
     dim3 pgrid((unsigned)((n_tok + 32 * kPrepUnroll - 1) / (32 * kPrepUnroll)), rows);
     kvm_prepare_keys_kernel<D><<<pgrid, 256, 0, stream>>>(L, k, gate, pk_all, tc_chain ? gk_all : nullptr, n_tok);

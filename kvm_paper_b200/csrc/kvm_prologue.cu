@@ -1,0 +1,147 @@
+// Fused prologue of the mixer: everything between the q/k/v/gate projections and the operator's inputs in one pass.
+//
+// Per token and head: token shift against the previous token, per-head LayerNorm of q and k, rotary embedding,
+// the merge gate 1 + elu(.), and (for the keys that a memory update will consume) the prepared key
+// bf16(LayerNorm(key with its rotary dims zeroed)) and the gated key bf16(prepared * gate) in the layout the chain
+// kernels read, so that the prefill can skip its own pass over the keys.
+// Follows model/tokenshift.py:11-37, model/value_residual_mixin.py:219-235 (token shift, ln_q / ln_k),
+// model/rwkv7_backbone.py:76-88 (rotary on interleaved pairs), model/kvm_mixer.py:381-399 (merge gate, head-major
+// views), model/kvm_mixer.py:120-129 (prepared key).  Every operation of the reference's bf16 module rounds its result
+// to bf16; the kernel rounds at the same points.
+//
+// One group of 8 lanes per (token, head) row, D/8 contiguous elements per lane (16-byte accesses; a rotary pair never
+// straddles lanes).  The kernel is a single streaming pass: q, k, v are read once (plus the previous token's
+// row, which the neighbouring group has just read: an L1/L2 hit) and written once.
+#include "kvm_common.cuh"
+
+namespace kvm {
+
+namespace {
+
+// Lane groups of 8 lanes per row, as in the prefill's own pass over the keys: the prepared keys come out with the same
+// bits whichever of the two wrote them.
+constexpr int GL = 8;
+
+// LayerNorm as the reference's module evaluates it on bf16 rows: moments in fp32, y = (x*rstd - mean*rstd)*w + b with
+// every product and sum rounded on its own, one rounding to bf16 at the end.
+template <int D>
+__device__ __forceinline__ void qk_layer_norm(RowVec<D, GL>& r, const float* __restrict__ w, const float* __restrict__ b, float eps,
+                                              int gl) {
+  constexpr int EPL = D / GL;
+  float s = 0.f;
+#pragma unroll
+  for (int i = 0; i < EPL; ++i) s += r.x[i];
+  const float mean = group_sum<GL>(s) * (1.0f / D);
+  float q = 0.f;
+#pragma unroll
+  for (int i = 0; i < EPL; ++i) {
+    const float d = r.x[i] - mean;
+    q += d * d;
+  }
+  const float var = group_sum<GL>(q) * (1.0f / D);
+  const float rstd = 1.0f / sqrtf(fmaxf(var, 0.f) + eps);
+  const float bias = __fmul_rn(-mean, rstd);
+#pragma unroll
+  for (int i = 0; i < EPL; ++i) {
+    const int d = gl * EPL + i;
+    r.x[i] = bf16_round(__fadd_rn(__fmul_rn(__fadd_rn(__fmul_rn(r.x[i], rstd), bias), w[d]), b[d]));
+  }
+}
+
+template <int D>
+__global__ void __launch_bounds__(256)
+kvm_prologue_kernel(LayerDev L, PrologueDev p, long long T) {
+  constexpr int EPL = D / GL;
+  const int gl = threadIdx.x % GL;
+  const int HS = L.Hq + 2 * L.Hkv;  // rows per token: query heads, key heads, value heads
+  // (the lane groups of a warp reduce with full-warp shuffles: every group runs the same sequence of reductions, on
+  // a valid row, and only the stores are predicated)
+  const long long unit_raw = (long long)blockIdx.x * (256 / GL) + threadIdx.x / GL;
+  const bool valid = unit_raw < T * HS;
+  const long long unit = valid ? unit_raw : T * HS - 1;
+  const int b = blockIdx.y;
+  const long long t = unit / HS;
+  const int slot = (int)(unit % HS);
+  const int kind = slot < L.Hq ? 0 : (slot < L.Hq + L.Hkv ? 1 : 2);  // q, k, v
+  const int h = kind == 0 ? slot : (kind == 1 ? slot - L.Hq : slot - L.Hq - L.Hkv);
+  const int H = kind == 0 ? L.Hq : L.Hkv;
+  const bf16* lin = kind == 0 ? p.q_lin : (kind == 1 ? p.k_lin : p.v_lin);
+  const bf16* shift = kind == 0 ? p.shift_q : (kind == 1 ? p.shift_k : p.shift_v);
+  const bf16* prev = kind == 0 ? p.prev_q : (kind == 1 ? p.prev_k : p.prev_v);
+  bf16* out = kind == 0 ? p.q_out : (kind == 1 ? p.k_out : p.v_out);
+  const size_t row_off = ((size_t)b * T + t) * H * D + (size_t)h * D;
+
+  RowVec<D, GL> x;
+  load_row<D, GL>(x, lin + row_off, gl);
+  if (shift) {
+    // x + scale * (previous token - x); the first token of a call uses the cached token, or itself
+    RowVec<D, GL> xp, sc;
+    const bf16* pr = t > 0 ? lin + row_off - (size_t)H * D : (prev ? prev + (size_t)b * H * D + (size_t)h * D : lin + row_off);
+    load_row<D, GL>(xp, pr, gl);
+    load_row<D, GL>(sc, shift + (size_t)h * D, gl);
+#pragma unroll
+    for (int i = 0; i < EPL; ++i) x.x[i] = bf16_round(x.x[i] + bf16_round(sc.x[i] * bf16_round(xp.x[i] - x.x[i])));
+  }
+  if (p.ln_q_w) {  // (uniform: q and k are normalised or neither is; value rows go through the motions)
+    RowVec<D, GL> y = x;
+    qk_layer_norm<D>(y, kind == 0 ? p.ln_q_w : p.ln_k_w, kind == 0 ? p.ln_q_b : p.ln_k_b, p.ln_qk_eps, gl);
+    if (kind < 2) x = y;
+  }
+  if (kind < 2) {
+    if (p.cos) {
+      RowVec<D, GL> c, s;
+      const size_t ro = (size_t)b * p.rope_stride_b + (size_t)t * D;
+      load_row<D, GL>(c, p.cos + ro, gl);
+      load_row<D, GL>(s, p.sin + ro, gl);
+#pragma unroll
+      for (int i = 0; i < EPL; i += 2) {  // cos * x + sin * (pair swapped), the sign of sin folded into the table
+        const float a0 = x.x[i], a1 = x.x[i + 1];
+        x.x[i] = bf16_round(bf16_round(c.x[i] * a0) + bf16_round(s.x[i] * a1));
+        x.x[i + 1] = bf16_round(bf16_round(c.x[i + 1] * a1) + bf16_round(s.x[i + 1] * a0));
+      }
+    }
+  }
+  if (valid) store_row<D, GL>(x, out + row_off, gl);
+  const bool is_key = valid && kind == 1;
+
+  // merge gate 1 + elu(g) of this (token, kv head), in the head-major layout [B, Hkv, T]
+  float g = 1.0f;
+  if (p.gate_lin && is_key) {
+    const float gl_in = __bfloat162float(p.gate_lin[((size_t)b * T + t) * L.Hkv + h]);
+    const float e = bf16_round(gl_in > 0.f ? gl_in : expf(gl_in) - 1.0f);
+    g = bf16_round(1.0f + e);
+  }
+  if (is_key && gl == 0) p.gate_out[((size_t)b * L.Hkv + h) * T + t] = __float2bfloat16_rn(g);
+  if (!p.pk_all) return;  // (uniform)
+  const bool consumed = is_key && t < p.n_tok;
+  // prepared key and gated key of a token that a memory update consumes
+#pragma unroll
+  for (int i = 0; i < EPL; ++i)
+    if (gl * EPL + i < L.rope_dim) x.x[i] = 0.f;
+  layer_norm_row<D, GL>(x, L.ln_w, L.ln_b, L.ln_eps, gl);
+  const size_t po = (((size_t)b * L.Hkv + h) * p.n_tok + t) * D;
+  if (consumed) store_row<D, GL>(x, p.pk_all + po, gl);
+  if (p.gk_all && consumed) {
+    if (L.gate_keys) {
+#pragma unroll
+      for (int i = 0; i < EPL; ++i) x.x[i] = bf16_round(x.x[i] * g);
+    }
+    store_row<D, GL>(x, p.gk_all + po, gl);
+  }
+}
+
+}  // namespace
+
+cudaError_t launch_prologue(int D, const LayerDev& L, const PrologueDev& p, int batch, long long T, cudaStream_t stream) {
+  const long long units = T * (L.Hq + 2 * L.Hkv);
+  const dim3 grid((unsigned)((units + 256 / GL - 1) / (256 / GL)), (unsigned)batch);
+  switch (D) {
+    case 32: kvm_prologue_kernel<32><<<grid, 256, 0, stream>>>(L, p, T); break;
+    case 64: kvm_prologue_kernel<64><<<grid, 256, 0, stream>>>(L, p, T); break;
+    case 128: kvm_prologue_kernel<128><<<grid, 256, 0, stream>>>(L, p, T); break;
+    default: return cudaErrorInvalidValue;
+  }
+  return cudaGetLastError();
+}
+
+}  // namespace kvm

@@ -304,6 +304,47 @@ class SequenceMixer(nn.Module):
             gate = torch.ones((B, self.num_key_value_heads, T, 1), device=x.device, dtype=torch.float)
         return q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2), gate
 
+    def prologue_params(self, device) -> ops.PrologueParams:
+        ln = isinstance(self.ln_q, nn.LayerNorm)
+        shift = self.tokenshift_mode == "rwkv"
+        return ops.PrologueParams(device, shift_q=self.x_q if shift else None, shift_k=self.x_k if shift else None,
+                                  shift_v=self.x_v if shift else None, ln_q=self.ln_q if ln else None,
+                                  ln_k=self.ln_k if ln else None, ln_eps=self.ln_q.eps if ln else 1e-5)
+
+    def fused_prologue_applies(self, x: torch.Tensor) -> bool:
+        """The one-kernel prologue covers bf16 modules on CUDA with head dims the kernel is built for and a value
+        path without the post-shift residual (that variant mixes values after the token shift)."""
+        return (x.is_cuda and x.dtype == torch.bfloat16 and self.c_q.weight.dtype == torch.bfloat16
+                and self.d_qk_head in (32, 64, 128) and self.value_projection_size == self.num_key_value_heads * self.d_qk_head
+                and self.value_residual_mode != "rwkv_post_tokenshift")
+
+    def forward_prefix_fused(self, x, v_first, position_embeddings, past_key_values=None, runner=None):
+        """``forward_prefix`` with everything behind the projections in one kernel (``kvm_prologue_forward``): the
+        projections and the value residual are torch GEMMs / elementwise ops as in ``calc_qkv``; token shift, q/k
+        LayerNorm, rotary embedding and merge gate run fused, and with ``runner`` the prepared keys of the prompt are
+        written into its workspace (reference: model/value_residual_mixin.py:173-237, model/kvm_mixer.py:367-401)."""
+        B, T, _ = x.size()
+        states = past_key_values.get_states(self.layer_idx) if past_key_values is not None else {}
+        past_len = past_key_values.get_seq_length(self.layer_idx) if past_key_values is not None else 0
+        if past_len > 0 and T != 1:
+            raise AssertionError("cached decode expects single-token inputs.")
+        q, k, v = self.c_q(x), self.c_k(x), self.c_v(x)
+        if self.value_residual_mode == "linear":
+            v = (1 - self.lamb) * v + self.lamb * v_first.view_as(v)
+        elif self.value_residual_mode == "rwkv":
+            v = v + (v_first.to(v.dtype) - v) * self._value_gate(x).to(v.dtype)
+        prev = None
+        if past_key_values is not None:
+            prev = (states.get(self._CACHE_Q_FINAL), states.get(self._CACHE_K_FINAL), states.get(self._CACHE_V_FINAL))
+            past_key_values.update(self.layer_idx, offset=0, states_dict={
+                self._CACHE_Q_FINAL: q[:, -1:].detach(), self._CACHE_K_FINAL: k[:, -1:].detach(),
+                self._CACHE_V_FINAL: v[:, -1:].detach(), self._CACHE_X_FINAL: x[:, -1:].detach()})
+        gated = self.config.kvm_use_merge_gate_keys or self.config.kvm_use_merge_gate_values
+        gate_lin = self.key_weighting(x) if gated else None
+        dev = x.device
+        return ops.prologue_forward(self.layer_params(dev), self.prologue_params(dev), q.contiguous(), k.contiguous(),
+                                    v.contiguous(), gate_lin, position_embeddings, prev=prev, runner=runner)
+
     # ------------------------------------------------------------------ module entry points
     def forward(self, x, v_first, position_embeddings, attention_mask, past_key_values=None, **kwargs):
         q, k, v, gate = self.forward_prefix(x, v_first, position_embeddings, attention_mask, past_key_values, **kwargs)

@@ -199,6 +199,79 @@ class PrefillResult:
     runner: Any = None                # the PrefillRunner that produced it (workspace inspection)
 
 
+class PrologueParams:
+    """Device copies of what the fused prologue reads besides the projections: token-shift scales (bf16),
+    per-head LayerNorm of q and k (fp32), all optional as in the reference module
+    (model/value_residual_mixin.py:60-98)."""
+
+    def __init__(self, device, *, shift_q=None, shift_k=None, shift_v=None, ln_q=None, ln_k=None, ln_eps: float = 1e-5):
+        dev = torch.device(device)
+        shifts = [None if t is None else t.detach().to(dev, torch.bfloat16).reshape(-1).contiguous() for t in (shift_q, shift_k, shift_v)]
+        if any(t is None for t in shifts) and not all(t is None for t in shifts):
+            raise ValueError("token-shift scales must be given for q, k and v or for none")
+        self.shift_q, self.shift_k, self.shift_v = shifts
+        if (ln_q is None) != (ln_k is None):
+            raise ValueError("LayerNorm must be given for q and k or for neither")
+        self.ln = None
+        if ln_q is not None:
+            self.ln = tuple(t.detach().to(dev, torch.float32).contiguous() for t in (ln_q.weight, ln_q.bias, ln_k.weight, ln_k.bias))
+        self.ln_eps = float(ln_eps)
+
+
+def prologue_forward(params: LayerParams, pro: PrologueParams, q_lin: torch.Tensor, k_lin: torch.Tensor, v_lin: torch.Tensor,
+                     gate_lin: torch.Tensor | None, position_embeddings, *, prev=None, runner: "PrefillRunner | None" = None):
+    """Token shift, q/k LayerNorm, rotary embedding and merge gate in one kernel over the projection outputs
+    ([B,T,H*D] bf16).  Returns q [B,Hq,T,D], k, v [B,Hkv,T,D], gate [B,Hkv,T,1] as views of [B,T,H,D] / [B,Hkv,T]
+    buffers, the layouts the reference hands its mixer (model/kvm_mixer.py:397-399).  With ``runner`` the prepared
+    keys of the tokens that memory updates consume are written into that runner's workspace, and its ``run`` may
+    be called with ``keys_prepared=True``.  ``prev`` = (q, k, v) rows [B,1,H*D] of the previous call's last token."""
+    cfg = params.cfg
+    B, T, _ = q_lin.shape
+    D, Hq, Hkv = cfg.head_dim, cfg.n_q_heads, cfg.n_kv_heads
+    for name, t, h in (("q", q_lin, Hq), ("k", k_lin, Hkv), ("v", v_lin, Hkv)):
+        if t.dtype != torch.bfloat16 or not t.is_cuda or not t.is_contiguous() or t.shape != (B, T, h * D):
+            raise ValueError(f"{name} projection must be a contiguous bf16 CUDA tensor [B,T,{h * D}], got {tuple(t.shape)} {t.dtype}")
+    keep = []
+    arg = _lib.KvmPrologue()
+    arg.q_lin, arg.k_lin, arg.v_lin = q_lin.data_ptr(), k_lin.data_ptr(), v_lin.data_ptr()
+    if gate_lin is not None:
+        gate_lin = gate_lin.to(torch.bfloat16).reshape(B, T, Hkv).contiguous()
+        keep.append(gate_lin)
+        arg.gate_lin = gate_lin.data_ptr()
+    if pro.shift_q is not None:
+        arg.shift_q, arg.shift_k, arg.shift_v = pro.shift_q.data_ptr(), pro.shift_k.data_ptr(), pro.shift_v.data_ptr()
+        if prev is not None and all(t is not None for t in prev):
+            pv = [t.to(q_lin.device, torch.bfloat16).reshape(B, -1).contiguous() for t in prev]
+            keep += pv
+            arg.prev_q, arg.prev_k, arg.prev_v = (t.data_ptr() for t in pv)
+    if pro.ln is not None:
+        arg.ln_q_w, arg.ln_q_b, arg.ln_k_w, arg.ln_k_b = (t.data_ptr() for t in pro.ln)
+        arg.ln_qk_eps = pro.ln_eps
+    if position_embeddings is not None:
+        cos, sin = position_embeddings
+        cs = [t.to(q_lin.device, torch.bfloat16).reshape(-1, T, D).contiguous() for t in (cos, sin)]
+        if cs[0].size(0) not in (1, B):
+            raise ValueError(f"rotary tables must have batch 1 or {B}, got {cs[0].size(0)}")
+        keep += cs
+        arg.cos, arg.sin = cs[0].data_ptr(), cs[1].data_ptr()
+        arg.rope_stride_b = 0 if cs[0].size(0) == 1 else T * D
+    dev = q_lin.device
+    q = torch.empty(B, T, Hq, D, device=dev, dtype=torch.bfloat16)
+    k = torch.empty(B, T, Hkv, D, device=dev, dtype=torch.bfloat16)
+    v = torch.empty(B, T, Hkv, D, device=dev, dtype=torch.bfloat16)
+    gate = torch.empty(B, Hkv, T, device=dev, dtype=torch.bfloat16)
+    ws_ptr, ws_bytes, ver_rows = None, 0, 0
+    if runner is not None:
+        if runner.batch != B or runner.plan.seq_len != T:
+            raise ValueError("runner was built for another batch or sequence length")
+        ws_ptr, ws_bytes, ver_rows = runner.ws.data_ptr(), runner.ws_bytes, runner.plan.total_version_rows
+    rc = _lib.load().kvm_prologue_forward(C.byref(params.c), B, T, C.byref(arg), q.data_ptr(), k.data_ptr(), v.data_ptr(),
+                                          gate.data_ptr(), ver_rows, ws_ptr, ws_bytes, _stream_ptr(dev))
+    _lib.check(rc)
+    del keep  # (the kernel is enqueued on the current stream: torch's allocator keeps the blocks until it has run)
+    return q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2), gate.unsqueeze(-1)
+
+
 class PrefillRunner:
     """Preallocated buffers for repeated prefills of one shape (memory, workspace with the row pool and version tables, output).
 
@@ -222,8 +295,12 @@ class PrefillRunner:
         self.plan_host = plan.to_ctypes()
 
     def run(self, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, gate: torch.Tensor,
-            phases: int = _lib.PREFILL_CHAIN | _lib.PREFILL_ATTENTION) -> torch.Tensor:
+            phases: int = _lib.PREFILL_CHAIN | _lib.PREFILL_ATTENTION, *, keys_prepared: bool = False) -> torch.Tensor:
+        """``keys_prepared``: ``prologue_forward(..., runner=self)`` has written the prepared keys of this prompt into
+        the workspace; the chain phase skips its own pass over the keys."""
         cfg, plan = self.params.cfg, self.plan
+        if keys_prepared:
+            phases |= _lib.PREFILL_KEYS_PREPARED
         B, Hq, T, D = q.shape
         if (B, Hq, D) != (self.batch, cfg.n_q_heads, cfg.head_dim) or k.shape != (B, cfg.n_kv_heads, T, D) or v.shape != k.shape:
             raise ValueError(f"shape mismatch: q {tuple(q.shape)}, k {tuple(k.shape)}, v {tuple(v.shape)} for {cfg}")
