@@ -22,6 +22,30 @@ namespace {
 // bits whichever of the two wrote them.
 constexpr int GL = 8;
 
+// Both values rounded to bf16 with one conversion instruction (the kernel is bound by its instruction count).
+__device__ __forceinline__ void round2(float& a, float& b) {
+  const float2 r = unpack_bf16(pack_bf16(a, b));
+  a = r.x;
+  b = r.y;
+}
+
+// A lane's share of a row as packed bf16 pairs: fetched early, unpacked where it is used (the rotary tables are
+// requested together with the row itself, so that their latency is not paid again behind the LayerNorm).
+template <int EPL>
+__device__ __forceinline__ void load_raw(uint32_t (&w)[EPL / 2], const bf16* p) {
+  if constexpr (EPL % 8 == 0) {
+#pragma unroll
+    for (int c = 0; c < EPL / 8; ++c) {
+      const uint4 u = *reinterpret_cast<const uint4*>(p + c * 8);
+      w[c * 4] = u.x; w[c * 4 + 1] = u.y; w[c * 4 + 2] = u.z; w[c * 4 + 3] = u.w;
+    }
+  } else {
+    static_assert(EPL == 4, "lane share of 4 or a multiple of 8 elements");
+    const uint2 u = *reinterpret_cast<const uint2*>(p);
+    w[0] = u.x; w[1] = u.y;
+  }
+}
+
 // LayerNorm as the reference's module evaluates it on bf16 rows: moments in fp32, y = (x*rstd - mean*rstd)*w + b with
 // every product and sum rounded on its own, one rounding to bf16 at the end.
 template <int D>
@@ -42,12 +66,31 @@ __device__ __forceinline__ void qk_layer_norm(RowVec<D, GL>& r, const float* __r
   const float rstd = 1.0f / sqrtf(fmaxf(var, 0.f) + eps);
   const float bias = __fmul_rn(-mean, rstd);
 #pragma unroll
-  for (int i = 0; i < EPL; ++i) {
+  for (int i = 0; i < EPL; i += 2) {
     const int d = gl * EPL + i;
-    r.x[i] = bf16_round(__fadd_rn(__fmul_rn(__fadd_rn(__fmul_rn(r.x[i], rstd), bias), w[d]), b[d]));
+    r.x[i] = __fadd_rn(__fmul_rn(__fadd_rn(__fmul_rn(r.x[i], rstd), bias), w[d]), b[d]);
+    r.x[i + 1] = __fadd_rn(__fmul_rn(__fadd_rn(__fmul_rn(r.x[i + 1], rstd), bias), w[d + 1]), b[d + 1]);
+    round2(r.x[i], r.x[i + 1]);
   }
 }
 
+template <int EPL>
+__device__ __forceinline__ void store_raw(const uint32_t (&w)[EPL / 2], bf16* p) {
+  if constexpr (EPL % 8 == 0) {
+#pragma unroll
+    for (int c = 0; c < EPL / 8; ++c)
+      *reinterpret_cast<uint4*>(p + c * 8) = make_uint4(w[c * 4], w[c * 4 + 1], w[c * 4 + 2], w[c * 4 + 3]);
+  } else {
+    *reinterpret_cast<uint2*>(p) = make_uint2(w[0], w[1]);
+  }
+}
+__device__ __forceinline__ __nv_bfloat162 as_bf162(uint32_t u) { return *reinterpret_cast<__nv_bfloat162*>(&u); }
+__device__ __forceinline__ uint32_t as_u32(__nv_bfloat162 v) { return *reinterpret_cast<uint32_t*>(&v); }
+
+// Token shift and rotary embedding are bf16 arithmetic in the reference (every product, difference and sum rounded
+// to bf16): they run on packed pairs with the hardware's bf16 instructions (exact result rounded once, which is what
+// "compute in fp32, round to bf16" gives for one operation on bf16 operands; the _rn forms are never contracted into
+// a fused multiply-add).  Only the LayerNorms unpack to fp32.
 template <int D>
 __global__ void __launch_bounds__(256)
 kvm_prologue_kernel(LayerDev L, PrologueDev p, long long T) {
@@ -69,39 +112,50 @@ kvm_prologue_kernel(LayerDev L, PrologueDev p, long long T) {
   const bf16* shift = kind == 0 ? p.shift_q : (kind == 1 ? p.shift_k : p.shift_v);
   const bf16* prev = kind == 0 ? p.prev_q : (kind == 1 ? p.prev_k : p.prev_v);
   bf16* out = kind == 0 ? p.q_out : (kind == 1 ? p.k_out : p.v_out);
-  const size_t row_off = ((size_t)b * T + t) * H * D + (size_t)h * D;
+  const size_t row_off = ((size_t)b * T + t) * H * D + (size_t)h * D + gl * EPL;  // this lane's share of the row
 
-  RowVec<D, GL> x;
-  load_row<D, GL>(x, lin + row_off, gl);
+  uint32_t x[EPL / 2];
+  load_raw<EPL>(x, lin + row_off);
   if (shift) {
     // x + scale * (previous token - x); the first token of a call uses the cached token, or itself
-    RowVec<D, GL> xp, sc;
-    const bf16* pr = t > 0 ? lin + row_off - (size_t)H * D : (prev ? prev + (size_t)b * H * D + (size_t)h * D : lin + row_off);
-    load_row<D, GL>(xp, pr, gl);
-    load_row<D, GL>(sc, shift + (size_t)h * D, gl);
+    uint32_t xp[EPL / 2], sc[EPL / 2];
+    const bf16* pr = t > 0 ? lin + row_off - (size_t)H * D : (prev ? prev + (size_t)b * H * D + (size_t)h * D + gl * EPL : lin + row_off);
+    load_raw<EPL>(xp, pr);
+    load_raw<EPL>(sc, shift + (size_t)h * D + gl * EPL);
 #pragma unroll
-    for (int i = 0; i < EPL; ++i) x.x[i] = bf16_round(x.x[i] + bf16_round(sc.x[i] * bf16_round(xp.x[i] - x.x[i])));
-  }
-  if (p.ln_q_w) {  // (uniform: q and k are normalised or neither is; value rows go through the motions)
-    RowVec<D, GL> y = x;
-    qk_layer_norm<D>(y, kind == 0 ? p.ln_q_w : p.ln_k_w, kind == 0 ? p.ln_q_b : p.ln_k_b, p.ln_qk_eps, gl);
-    if (kind < 2) x = y;
-  }
-  if (kind < 2) {
-    if (p.cos) {
-      RowVec<D, GL> c, s;
-      const size_t ro = (size_t)b * p.rope_stride_b + (size_t)t * D;
-      load_row<D, GL>(c, p.cos + ro, gl);
-      load_row<D, GL>(s, p.sin + ro, gl);
-#pragma unroll
-      for (int i = 0; i < EPL; i += 2) {  // cos * x + sin * (pair swapped), the sign of sin folded into the table
-        const float a0 = x.x[i], a1 = x.x[i + 1];
-        x.x[i] = bf16_round(bf16_round(c.x[i] * a0) + bf16_round(s.x[i] * a1));
-        x.x[i + 1] = bf16_round(bf16_round(c.x[i + 1] * a1) + bf16_round(s.x[i + 1] * a0));
-      }
+    for (int i = 0; i < EPL / 2; ++i) {
+      const __nv_bfloat162 xi = as_bf162(x[i]);
+      x[i] = as_u32(__hadd2_rn(xi, __hmul2_rn(as_bf162(sc[i]), __hsub2_rn(as_bf162(xp[i]), xi))));
     }
   }
-  if (valid) store_row<D, GL>(x, out + row_off, gl);
+  // (warp-uniform: the reductions inside use full-warp shuffles.  With four or more heads of a kind in a row a warp
+  // holds rows of one kind and value rows skip this; in a mixed warp they go through the motions)
+  if (p.ln_q_w && __any_sync(0xffffffffu, kind < 2)) {
+    RowVec<D, GL> y;
+#pragma unroll
+    for (int i = 0; i < EPL / 2; ++i) {
+      const float2 f = unpack_bf16(x[i]);
+      y.x[2 * i] = f.x;
+      y.x[2 * i + 1] = f.y;
+    }
+    qk_layer_norm<D>(y, kind == 0 ? p.ln_q_w : p.ln_k_w, kind == 0 ? p.ln_q_b : p.ln_k_b, p.ln_qk_eps, gl);
+    if (kind < 2) {
+#pragma unroll
+      for (int i = 0; i < EPL / 2; ++i) x[i] = pack_bf16(y.x[2 * i], y.x[2 * i + 1]);
+    }
+  }
+  if (p.cos != nullptr && kind < 2) {
+    uint32_t c[EPL / 2], s[EPL / 2];
+    const size_t ro = (size_t)b * p.rope_stride_b + (size_t)t * D + gl * EPL;
+    load_raw<EPL>(c, p.cos + ro);
+    load_raw<EPL>(s, p.sin + ro);
+#pragma unroll
+    for (int i = 0; i < EPL / 2; ++i) {  // cos * x + sin * (pair swapped), the sign of sin folded into the table
+      const __nv_bfloat162 xi = as_bf162(x[i]);
+      x[i] = as_u32(__hadd2_rn(__hmul2_rn(as_bf162(c[i]), xi), __hmul2_rn(as_bf162(s[i]), __lowhigh2highlow(xi))));
+    }
+  }
+  if (valid) store_raw<EPL>(x, out + row_off);
   const bool is_key = valid && kind == 1;
 
   // merge gate 1 + elu(g) of this (token, kv head), in the head-major layout [B, Hkv, T]
@@ -112,21 +166,29 @@ kvm_prologue_kernel(LayerDev L, PrologueDev p, long long T) {
     g = bf16_round(1.0f + e);
   }
   if (is_key && gl == 0) p.gate_out[((size_t)b * L.Hkv + h) * T + t] = __float2bfloat16_rn(g);
-  if (!p.pk_all) return;  // (uniform)
-  const bool consumed = is_key && t < p.n_tok;
+  const bool consumed = p.pk_all && is_key && t < p.n_tok;
+  if (!__any_sync(0xffffffffu, consumed)) return;  // (warp-uniform, as above)
   // prepared key and gated key of a token that a memory update consumes
+  RowVec<D, GL> r;
 #pragma unroll
-  for (int i = 0; i < EPL; ++i)
-    if (gl * EPL + i < L.rope_dim) x.x[i] = 0.f;
-  layer_norm_row<D, GL>(x, L.ln_w, L.ln_b, L.ln_eps, gl);
+  for (int i = 0; i < EPL / 2; ++i) {
+    const float2 f = unpack_bf16(x[i]);
+    r.x[2 * i] = (gl * EPL + 2 * i < L.rope_dim) ? 0.f : f.x;
+    r.x[2 * i + 1] = (gl * EPL + 2 * i + 1 < L.rope_dim) ? 0.f : f.y;
+  }
+  layer_norm_row<D, GL>(r, L.ln_w, L.ln_b, L.ln_eps, gl);
   const size_t po = (((size_t)b * L.Hkv + h) * p.n_tok + t) * D;
-  if (consumed) store_row<D, GL>(x, p.pk_all + po, gl);
+  if (consumed) store_row<D, GL>(r, p.pk_all + po, gl);
   if (p.gk_all && consumed) {
     if (L.gate_keys) {
 #pragma unroll
-      for (int i = 0; i < EPL; ++i) x.x[i] = bf16_round(x.x[i] * g);
+      for (int i = 0; i < EPL; i += 2) {
+        r.x[i] *= g;
+        r.x[i + 1] *= g;
+        round2(r.x[i], r.x[i + 1]);
+      }
     }
-    store_row<D, GL>(x, p.gk_all + po, gl);
+    store_row<D, GL>(r, p.gk_all + po, gl);
   }
 }
 

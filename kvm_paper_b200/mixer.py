@@ -94,6 +94,8 @@ class SequenceMixer(nn.Module):
     # ``last_route`` ([B*Hkv, n_updates+1, C] after a prefill, [B*Hkv, C] or None after a decode step;
     # >= 0: memory row merged into, -(1+row): appended as that row).
     capture_routes = False
+    # prompts of bf16 modules go through the one-kernel prologue (kvm_prologue_forward); False keeps the PyTorch prefix
+    use_fused_prologue = True
     last_route = None
 
     _CACHE_DECODE = "kvm_b200_decode_cache"
@@ -346,12 +348,24 @@ class SequenceMixer(nn.Module):
                                     v.contiguous(), gate_lin, position_embeddings, prev=prev, runner=runner)
 
     # ------------------------------------------------------------------ module entry points
+    def _prompt_fused(self, x, v_first, position_embeddings, attention_mask, past_key_values, **kwargs):
+        """A prompt through the one-kernel prologue, which also leaves the prepared keys in the prefill's workspace."""
+        params = self.layer_params(x.device)
+        runner = ops.PrefillRunner(params, x.size(0), self.make_prefill_plan(int(x.size(1))), want_route=self.capture_routes)
+        q, k, v, gate = self.forward_prefix_fused(x, v_first, position_embeddings, past_key_values, runner=runner)
+        return self.forward_prefill(q, k, v, gate, v_first, position_embeddings, attention_mask, past_key_values,
+                                    _prefill_runner=runner, **kwargs)
+
     def forward(self, x, v_first, position_embeddings, attention_mask, past_key_values=None, **kwargs):
+        if self.use_fused_prologue and attention_mask is None and self.fused_prologue_applies(x):
+            return self._prompt_fused(x, v_first, position_embeddings, attention_mask, past_key_values, **kwargs)
         q, k, v, gate = self.forward_prefix(x, v_first, position_embeddings, attention_mask, past_key_values, **kwargs)
         return self.forward_prefill(q, k, v, gate, v_first, position_embeddings, attention_mask, past_key_values, **kwargs)
 
     def forward_inference(self, x, v_first, position_embeddings, attention_mask, past_key_values=None, **kwargs):
         past_len = past_key_values.get_seq_length(self.layer_idx) if past_key_values is not None else 0
+        if past_len == 0 and self.use_fused_prologue and attention_mask is None and self.fused_prologue_applies(x):
+            return self._prompt_fused(x, v_first, position_embeddings, attention_mask, past_key_values, **kwargs)
         q, k, v, gate = self.forward_prefix(x, v_first, position_embeddings, attention_mask, past_key_values, **kwargs)
         fn = self.forward_single if past_len > 0 else self.forward_prefill
         return fn(q, k, v, gate, v_first, position_embeddings, attention_mask, past_key_values, **kwargs)
@@ -362,22 +376,24 @@ class SequenceMixer(nn.Module):
         if torch.is_grad_enabled() and t.requires_grad:
             raise ValueError("kvm_b200 mixer implements inference (prefill/decode) only; call it under torch.no_grad()")
 
-    def prefill_raw(self, q, k, v, merge_gate, *, want_route: bool = False, memory_capacity: int | None = None):
-        """Operator-boundary prefill: returns ops.PrefillResult (pre-``c_proj`` activations, final memory)."""
+    def prefill_raw(self, q, k, v, merge_gate, *, want_route: bool = False, memory_capacity: int | None = None, runner=None):
+        """Operator-boundary prefill: returns ops.PrefillResult (pre-``c_proj`` activations, final memory).
+        ``runner``: the runner whose workspace the fused prologue filled with this prompt's prepared keys."""
         self._require_cuda(q)
-        plan = self.make_prefill_plan(int(q.size(2)))
+        plan = self.make_prefill_plan(int(q.size(2))) if runner is None else runner.plan
         params = self.layer_params(q.device)
         return ops.prefill_forward(params, q, k, v, merge_gate, plan, want_route=want_route,
-                                   memory_capacity=memory_capacity, check=self.check_device_status)
+                                   memory_capacity=memory_capacity, check=self.check_device_status,
+                                   runner=runner, keys_prepared=runner is not None)
 
     def forward_prefill(self, q, k, v, merge_gate, v_first, position_embeddings, attention_mask,
                         past_key_values=None, **kwargs):
         """Reference: model/kvm_mixer.py:403-516, model/kvm_triton_mixer.py:560-664."""
-        del v_first, position_embeddings, kwargs
+        del v_first, position_embeddings
         if attention_mask is not None:
             raise ValueError("kvm_b200 mixer does not support attention_mask")
         T = int(q.size(2))
-        res = self.prefill_raw(q, k, v, merge_gate, want_route=self.capture_routes)
+        res = self.prefill_raw(q, k, v, merge_gate, want_route=self.capture_routes, runner=kwargs.pop("_prefill_runner", None))
         if self.capture_routes:
             self.last_route = res.route
         y = self.c_proj(res.out.to(q.dtype))

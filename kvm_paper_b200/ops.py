@@ -410,7 +410,8 @@ class HostPrefill:
 
 def prefill_forward(params: LayerParams, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, gate: torch.Tensor,
                     plan: PrefillPlan, *, memory_capacity: int | None = None, want_route: bool = False,
-                    phases: int = _lib.PREFILL_CHAIN | _lib.PREFILL_ATTENTION, check: bool = False) -> PrefillResult:
+                    phases: int = _lib.PREFILL_CHAIN | _lib.PREFILL_ATTENTION, check: bool = False,
+                    runner: "PrefillRunner | None" = None, keys_prepared: bool = False) -> PrefillResult:
     """Whole-prompt prefill through ``kvm_prefill_forward``.
 
     q [B,Hq,T,D], k/v [B,Hkv,T,D], gate [B,Hkv,T,1]; strided views are passed as they are."""
@@ -418,8 +419,9 @@ def prefill_forward(params: LayerParams, q: torch.Tensor, k: torch.Tensor, v: to
         raise ValueError(f"q must be [B,Hq,T,D], got {tuple(q.shape)}")
     if not q.is_cuda:
         raise RuntimeError("kvm_b200 runs on CUDA tensors only (there is no CPU path)")
-    runner = PrefillRunner(params, q.size(0), plan, memory_capacity=memory_capacity, want_route=want_route)
-    out = runner.run(q, k, v, gate, phases=phases)
+    if runner is None:  # (a caller that ran the fused prologue brings the runner whose workspace holds the prepared keys)
+        runner = PrefillRunner(params, q.size(0), plan, memory_capacity=memory_capacity, want_route=want_route)
+    out = runner.run(q, k, v, gate, phases=phases, keys_prepared=keys_prepared)
     if check:
         runner.check_status()
     # buffers are released by the caching allocator in stream order

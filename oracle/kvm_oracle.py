@@ -12,6 +12,7 @@ the CPU it reproduces the reference bit for bit (pinned by the golden fixtures u
 Reference files followed (paths inside the reference project):
   model/kvm_mixer.py                      eager mixer ("historical golden")
   model/kvm_fp32_routing_reference.py     same, merge-routing logits in fp32 (the routing oracle)
+  model/tokenshift.py, model/value_residual_mixin.py, model/rwkv7_backbone.py   the prologue behind the projections
 
 Tensor layouts: q [B,Hq,T,D], k [B,Hkv,T,D], v [B,Hkv,T,Dv], merge_gate [B,Hkv,T,1];
 outputs are the pre-``c_proj`` activations [B,T,Hq*Dv].
@@ -519,3 +520,50 @@ def slot_histogram(best_idx: torch.Tensor, n_slots: int) -> torch.Tensor:
     out = torch.zeros(B, H, n_slots, dtype=torch.long)
     out.scatter_add_(2, best_idx.long().cpu(), torch.ones_like(best_idx, dtype=torch.long).cpu())
     return out
+
+
+# ------------------------------------------------------------------------------------------------ prologue
+def prologue(q_lin, k_lin, v_lin, gate_lin, *, n_q_heads: int, n_kv_heads: int, shift=None, prev=None, ln_q=None, ln_k=None,
+             ln_eps: float = 1e-5, position_embeddings=None):
+    """What the reference does between its projections and the mixer's post-QKV tensors, on the projections' outputs
+    ([B,T,H*D]; v after a pre-shift value residual): token shift ``x + scale * (previous token - x)`` with the cached
+    last token of the previous call or the first token itself (model/tokenshift.py:11-37,
+    model/value_residual_mixin.py:219-224), per-head LayerNorm of q and k (model/value_residual_mixin.py:230-235),
+    rotary embedding on interleaved pairs with the sign folded into the sine table (model/rwkv7_backbone.py:76-88),
+    merge gate ``1 + elu(.)`` and the head-major views (model/kvm_mixer.py:381-399).  The same tensor operations in the
+    same order as the reference, so every intermediate is rounded where the reference rounds it.
+
+    shift = (x_q, x_k, x_v) or None; prev = (q, k, v) rows [B,1,H*D] or None; ln_q / ln_k = (weight, bias) or None.
+    Returns q [B,Hq,T,D], k, v [B,Hkv,T,D], merge_gate [B,Hkv,T,1]."""
+    B, T, _ = q_lin.shape
+
+    def shifted(x, scale, prev_token):
+        if prev_token is None:
+            prev_token = x[:, :1]
+        elif prev_token.dtype != x.dtype:
+            prev_token = prev_token.to(x.dtype)
+        return x + scale * (torch.cat([prev_token, x[:, :-1]], dim=1) - x)
+
+    q, k, v = q_lin, k_lin, v_lin
+    if shift is not None:
+        pv = prev if prev is not None else (None, None, None)
+        q, k, v = shifted(q, shift[0], pv[0]), shifted(k, shift[1], pv[1]), shifted(v, shift[2], pv[2])
+    q = q.reshape(B, T, n_q_heads, -1)
+    k = k.reshape(B, T, n_kv_heads, -1)
+    v = v.reshape(B, T, n_kv_heads, -1)
+    if ln_q is not None:
+        q = F.layer_norm(q, (q.size(-1),), ln_q[0], ln_q[1], ln_eps)
+        k = F.layer_norm(k, (k.size(-1),), ln_k[0], ln_k[1], ln_eps)
+    if position_embeddings is not None:
+        cos, sin = position_embeddings
+
+        def rotary(x):
+            flipped = x.view(*x.shape[:-1], x.shape[-1] // 2, 2).flip(-1).view(x.shape)
+            return cos * x + sin * flipped
+
+        q, k = rotary(q), rotary(k)
+    if gate_lin is not None:
+        gate = 1.0 + F.elu(gate_lin.view(B, T, n_kv_heads, 1)).transpose(1, 2)
+    else:
+        gate = torch.ones((B, n_kv_heads, T, 1), dtype=torch.float)
+    return q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2), gate

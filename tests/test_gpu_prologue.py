@@ -147,3 +147,40 @@ def test_class_fused_prefix_equals_its_pytorch_prefix(name):
         got = m.forward_prefix_fused(x, vf, rot, StatesCache())
     for a, b, what in zip(got, want, ("q", "k", "v", "gate")):
         _assert_bf16_equal_up_to_ties(a, b.to(torch.bfloat16), f"{name} {what}")
+
+
+@pytest.mark.parametrize("D,Hq,Hkv,T,with_prev,with_shift", [(128, 4, 2, 777, False, True), (128, 2, 2, 1, True, True), (64, 4, 2, 333, True, True),
+                                                               (32, 2, 1, 100, False, False)])
+def test_prologue_kernel_matches_the_oracle_on_random_inputs(D, Hq, Hkv, T, with_prev, with_shift):
+    """Kernel against ``oracle.prologue`` (the reference's own tensor operations on the CPU) on seeded inputs: ragged
+    lengths (the last lane groups of the grid run past the end), a cached previous token, per-batch rotary tables."""
+    from oracle import kvm_oracle as ko
+    dev = torch.device("cuda")
+    B = 3
+    g = torch.Generator().manual_seed(100 + T)
+    rnd = lambda *s: torch.randn(*s, generator=g).to(torch.bfloat16)  # noqa: E731
+    q_lin, k_lin, v_lin, g_lin = rnd(B, T, Hq * D), rnd(B, T, Hkv * D), rnd(B, T, Hkv * D), rnd(B, T, Hkv)
+    shift = tuple((0.5 * torch.rand(n, generator=g)).to(torch.bfloat16) for n in (Hq * D, Hkv * D, Hkv * D)) if with_shift else None
+    prev = (rnd(B, 1, Hq * D), rnd(B, 1, Hkv * D), rnd(B, 1, Hkv * D)) if with_prev else None
+    ln = [(1.0 + 0.1 * torch.randn(D, generator=g)).to(torch.bfloat16) if i % 2 == 0 else (0.05 * torch.randn(D, generator=g)).to(torch.bfloat16)
+          for i in range(4)]
+    pos = torch.stack([torch.arange(T) + 17 * b for b in range(B)])  # a different offset per sequence
+    cfg = type("Cfg", (), {"rope_partial_dim": D // 2})
+    rot = rotary_tables(cfg, D, pos)
+    with torch.no_grad():
+        want = ko.prologue(q_lin, k_lin, v_lin, g_lin, n_q_heads=Hq, n_kv_heads=Hkv, shift=shift, prev=prev,
+                           ln_q=(ln[0], ln[1]), ln_k=(ln[2], ln[3]), position_embeddings=rot)
+    spec = ko.KvmSpec(num_attention_heads=Hq, num_key_value_heads=Hkv, d_qk_head=D, d_v_head=D, rope_partial_dim=D // 2, chunk_len=32)
+    params = gh.layer_params(spec, dev)
+
+    class _LN:
+        def __init__(self, w, b):
+            self.weight, self.bias = w, b
+
+    pro = ops.PrologueParams(dev, shift_q=None if shift is None else shift[0], shift_k=None if shift is None else shift[1],
+                             shift_v=None if shift is None else shift[2], ln_q=_LN(ln[0], ln[1]), ln_k=_LN(ln[2], ln[3]))
+    got = ops.prologue_forward(params, pro, q_lin.to(dev), k_lin.to(dev), v_lin.to(dev), g_lin.to(dev), tuple(t.to(dev) for t in rot),
+                               prev=None if prev is None else tuple(t.to(dev) for t in prev))
+    for a, b, what in zip(got, want, ("q", "k", "v", "gate")):
+        _assert_bf16_equal_up_to_ties(a, b, f"D{D} T{T} {what}")
+    assert torch.equal(got[2].cpu(), want[2])  # token shift alone: the same bits

@@ -98,3 +98,49 @@ def test_oracle_prefill_then_decode_equals_longer_prefill():
             assert max_abs(yi, y_full[:, i:i + 1]) < 1e-5
     assert max_abs(st["kvm_s_k"], st_full["kvm_s_k"]) < 1e-4
     assert st["kvm_s_k"].shape == st_full["kvm_s_k"].shape
+
+
+def _projections(m, x, vf):
+    """The reference's projections and pre-shift value residual (plain GEMMs and elementwise ops on the CPU)."""
+    q, k, v = m.c_q(x), m.c_k(x), m.c_v(x)
+    if m.value_residual_mode == "linear":
+        v = (1 - m.lamb) * v + m.lamb * vf.view_as(v)
+    elif m.value_residual_mode == "rwkv":
+        v = v + (vf.to(v.dtype) - v) * m._value_gate(x).to(v.dtype)
+    gated = m.config.kvm_use_merge_gate_keys or m.config.kvm_use_merge_gate_values
+    return q, k, v, (m.key_weighting(x) if gated else None)
+
+
+@pytest.mark.parametrize("name", SMALL_FIXTURES)
+def test_oracle_prologue_matches_reference_fixture(name):
+    """``oracle.prologue`` on the projections of the fixture's hidden inputs gives the post-QKV tensors the reference
+    recorded, bit for bit, for the prompt and for cached single-token calls."""
+    from tests.helpers import mixer_from_fixture, rotary_tables
+    fix = load_fixture(name)
+    cfg, m = mixer_from_fixture(fix)
+    if m.value_residual_mode == "rwkv_post_tokenshift":
+        pytest.skip("post-shift value residual: not part of the fused prologue")
+    T, B = fix["case"]["T"], fix["case"]["B"]
+    x, vf = fix["x"], fix["v_first"]
+    shift = (m.x_q, m.x_k, m.x_v) if m.tokenshift_mode == "rwkv" else None
+    has_ln = isinstance(m.ln_q, torch.nn.LayerNorm)
+    kw = dict(n_q_heads=m.num_attention_heads, n_kv_heads=m.num_key_value_heads, shift=shift,
+              ln_q=(m.ln_q.weight, m.ln_q.bias) if has_ln else None, ln_k=(m.ln_k.weight, m.ln_k.bias) if has_ln else None,
+              ln_eps=m.ln_q.eps if has_ln else 1e-5)
+    with torch.no_grad():
+        lin = _projections(m, x[:, :T], None if vf is None else vf[:, :T])
+        pos = torch.arange(T).view(1, T).expand(B, T)
+        got = ko.prologue(*lin, position_embeddings=rotary_tables(cfg, m.d_qk_head, pos), **kw)
+        pq = fix["post_qkv"]
+        for g, w in zip(got, (pq["q"], pq["k"], pq["v"], pq["merge_gate"])):
+            assert g.shape == w.shape and torch.equal(g, w)
+        if fix["decode_qkv"] is not None:
+            dq, dk, dv, dg = fix["decode_qkv"]
+            prev = tuple(t[:, -1:] for t in lin[:3])
+            for i in range(min(5, dq.size(2))):
+                lin = _projections(m, x[:, T + i:T + i + 1], None if vf is None else vf[:, T + i:T + i + 1])
+                pos = torch.full((B, 1), T + i, dtype=torch.long)
+                got = ko.prologue(*lin, position_embeddings=rotary_tables(cfg, m.d_qk_head, pos), prev=prev, **kw)
+                for g, w in zip(got, (dq, dk, dv, dg)):
+                    assert torch.equal(g, w[:, :, i:i + 1])
+                prev = tuple(lin[:3])
