@@ -501,6 +501,105 @@ def run_power_law(mixer, params, q, k, v, gate, B, T, C, W, D, h_loc, peaks, rep
             "algorithmic_flops": flops, "status": status}
 
 
+def run_long_context(args):
+    """`--long-context`: BASELINE configs[4] (not the default line): batch 1, T = 262144, 32 heads x 128, blocks of 512
+    tokens, power-law memory 16*sqrt(context) capped at 4096 means, keys from a seeded mixture of 64 Gaussian clusters;
+    heads sharded over the ranks, outputs gathered.  Blocks of 512 tokens take the general chain kernel."""
+    import math as _m
+
+    import torch.distributed as dist
+
+    from kvm_paper_b200 import _lib, ops, sharding
+    rank, world, local = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1)), int(os.environ.get("LOCAL_RANK", 0))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        os.environ.setdefault("NCCL_MIN_NCHANNELS", "64")
+        os.environ.setdefault("NCCL_NTHREADS", "512")
+        dist.init_process_group("nccl", device_id=dev)
+    H, D, C, W, T, cap = 32, 128, 512, 2, 262144 if args.seq_len is None else args.seq_len, 4096
+    h_loc = H // world
+    cfg = ops.LayerConfig(n_q_heads=h_loc, n_kv_heads=h_loc, head_dim=D, chunk_len=C, n_bswa_chunks=W, rope_dim=64, sink_len=1)
+    g0 = torch.Generator().manual_seed(4)
+    params = ops.LayerParams(cfg, 1.0 + 0.1 * torch.randn(D, generator=g0), 0.05 * torch.randn(D, generator=g0), None, None, dev)
+
+    def desired(ctx_len, available_context, current):
+        target = max(int(_m.floor(16.0 * (float(max(int(ctx_len), 0)) ** 0.5))), C)
+        return max(min(target, max(int(available_context), 0), cap), max(int(current), 0))
+
+    plan = ops.build_prefill_plan(T, C, W, desired)
+    g = torch.Generator(device=dev).manual_seed(40)          # the same cluster centres on every rank,
+    centers = torch.randn(64, D, generator=g, device=dev)
+    g = torch.Generator(device=dev).manual_seed(41 + rank)   # this rank's heads
+    ln = torch.nn.functional.layer_norm
+    which = torch.randint(0, 64, (1, T, h_loc), generator=g, device=dev)
+    k = ln(centers[which] + 0.5 * torch.randn(1, T, h_loc, D, generator=g, device=dev), (D,)).bfloat16().transpose(1, 2)
+    del which
+    q = ln(torch.randn(1, T, h_loc, D, generator=g, device=dev), (D,)).bfloat16().transpose(1, 2)
+    v = torch.randn(1, T, h_loc, D, generator=g, device=dev).bfloat16().transpose(1, 2)
+    gate = (1 + torch.nn.functional.elu(0.5 * torch.randn(1, T, h_loc, 1, generator=g, device=dev))).bfloat16().transpose(1, 2)
+    runner = ops.PrefillRunner(params, 1, plan)
+
+    def step():
+        return sharding.gather_heads(runner.run(q, k, v, gate), world)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    barrier()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with ClockSampler(local) as clocks:
+        barrier()
+        a.record()
+        for _ in range(args.steps):
+            step()
+        b.record()
+        barrier()
+    t = torch.tensor([a.elapsed_time(b) / args.steps], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms = float(t.item())
+
+    def timed(phases):
+        runner.run(q, k, v, gate, phases=phases)
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        runner.run(q, k, v, gate, phases=phases)
+        b.record()
+        torch.cuda.synchronize()
+        return a.elapsed_time(b)
+
+    chain_ms, attn_ms = timed(_lib.PREFILL_CHAIN), timed(_lib.PREFILL_ATTENTION)
+    runner.run(q, k, v, gate)
+    status = "ok"
+    try:
+        runner.check_status()
+    except Exception as exc:
+        status = str(exc)
+    peaks = _peaks()
+    flops = 4.0 * D * attention_pairs(T, C, W, plan) * h_loc
+    tf = flops / (attn_ms * 1e-3) / 1e12
+    if rank == 0:
+        print(json.dumps({
+            "metric": f"kvm_prefill_tokens_per_s_T{T}", "value": round(T / (ms * 1e-3), 1), "unit": UNIT, "n_gpus": world,
+            "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": round(ms, 3), "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": "BASELINE configs[4]: long-context KVM layer, B1 x T262144, 32 heads x 128, block 512, power-law "
+                                   "memory capped at 4096 means, keys from 64 Gaussian clusters, post-QKV operator boundary",
+                       "seq_len": T, "heads_per_gpu": h_loc, "parallelism": f"heads/{world}" + (" + all-gather of outputs" if world > 1 else ""),
+                       "final_means": plan.final_state_len, "updates": plan.n_updates,
+                       "chain_kernel": "general chain kernel (blocks of 512 tokens)"},
+            "chain_ms": round(chain_ms, 3), "attention_ms": round(attn_ms, 3), "attention_tflops": round(tf, 1),
+            "attention_frac": round(tf / peaks["bf16_tflops"], 4), "status": status, "clocks": clocks.summary()}))
+    if world > 1:
+        dist.destroy_process_group()
+
+
 # DRAM traffic of the dominant kernels from ncu captures (dram__bytes_read.sum + dram__bytes_write.sum of one
 # launch), scaled to this run's launch by the units it processes; the captures and their commands are the
 # summaries under profiles/ named after these kernels.
@@ -711,6 +810,7 @@ def main():
     ap.add_argument("--seq-len", type=int, default=None)
     ap.add_argument("--prefill-only", action="store_true", help="skip e2e, decode and the CPU baseline")
     ap.add_argument("--decode-only", action="store_true", help="run only the decode workload")
+    ap.add_argument("--long-context", action="store_true", help="BASELINE configs[4] (T=262144, 32 heads, block 512, 4096 means) instead of the default line")
     ap.add_argument("--decode-seqs", type=int, default=None)
     args = ap.parse_args()
     if args.batch is not None:
@@ -723,6 +823,8 @@ def main():
         args.no_decode = args.no_cpu = True
     if args.impl == "reference":
         run_reference(args)
+    elif args.long_context:
+        run_long_context(args)
     else:
         run_b200(args)
 

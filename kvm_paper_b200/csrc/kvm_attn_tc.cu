@@ -347,20 +347,22 @@ __device__ __forceinline__ bool softmax_role(const Slice<NQ>& sl, const LayerDev
   tc::tc_fence_after_sync();
   const float inv = l_run > 0.f ? 1.0f / l_run : 0.f;
   unsigned char* dO = smem + CF::kOffQ + qi * 32768;
+  // (64 columns per round trip to tensor memory: the score registers of the loop are free by now)
 #pragma unroll
-  for (int cb = 0; cb < HD / 16; ++cb) {
-    uint32_t o[16];
-    tc::tmem_ld16(lane_addr + col_o + cb * 16, o);
+  for (int hb = 0; hb < HD / 64; ++hb) {
+    uint32_t o[2][32];
+    tc::tmem_ld32(lane_addr + col_o + hb * 64, o[0]);
+    tc::tmem_ld32(lane_addr + col_o + hb * 64 + 32, o[1]);
     tc::tmem_ld_wait();
 #pragma unroll
-    for (int i = 0; i < 2; ++i) {
+    for (int c8 = 0; c8 < 8; ++c8) {  // 16-byte chunk c8 of this half's 128-byte row
+      const uint32_t* oo = &o[c8 >> 2][(c8 & 3) * 8];
       uint4 o8;
-      o8.x = pack_bf16(__uint_as_float(o[i * 8 + 0]) * inv, __uint_as_float(o[i * 8 + 1]) * inv);
-      o8.y = pack_bf16(__uint_as_float(o[i * 8 + 2]) * inv, __uint_as_float(o[i * 8 + 3]) * inv);
-      o8.z = pack_bf16(__uint_as_float(o[i * 8 + 4]) * inv, __uint_as_float(o[i * 8 + 5]) * inv);
-      o8.w = pack_bf16(__uint_as_float(o[i * 8 + 6]) * inv, __uint_as_float(o[i * 8 + 7]) * inv);
-      const int c = cb * 2 + i;  // 16-byte chunk of the 256-byte row: half c >> 3, chunk c & 7 within the half
-      *reinterpret_cast<uint4*>(dO + (c >> 3) * 16384 + row * 128 + ((((c & 7) ^ (row & 7)) & 7) << 4)) = o8;
+      o8.x = pack_bf16(__uint_as_float(oo[0]) * inv, __uint_as_float(oo[1]) * inv);
+      o8.y = pack_bf16(__uint_as_float(oo[2]) * inv, __uint_as_float(oo[3]) * inv);
+      o8.z = pack_bf16(__uint_as_float(oo[4]) * inv, __uint_as_float(oo[5]) * inv);
+      o8.w = pack_bf16(__uint_as_float(oo[6]) * inv, __uint_as_float(oo[7]) * inv);
+      *reinterpret_cast<uint4*>(dO + hb * 16384 + row * 128 + (((c8 ^ (row & 7)) & 7) << 4)) = o8;
     }
   }
   tc::fence_proxy_async();  // generic-proxy writes -> visible to the TMA store
