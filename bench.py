@@ -353,7 +353,7 @@ def run_b200(args):
 
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu:
-        cpu = cpu_baseline(cfg, seconds_hint=20)
+        cpu = cpu_baseline(cfg, seconds_hint=20, eager_gpu_too=True)
 
     if rank == 0:
         line = {
@@ -436,9 +436,11 @@ def run_prologue(runner, params, q, k, v, gate, B, T, C, D, h_loc, peaks, dev, r
         return a.elapsed_time(b) / reps
 
     res = {}
+    bufs = (torch.empty(B, T, h_loc, D, device=dev, dtype=torch.bfloat16), torch.empty(B, T, h_loc, D, device=dev, dtype=torch.bfloat16),
+            torch.empty(B, T, h_loc, D, device=dev, dtype=torch.bfloat16), torch.empty(B, h_loc, T, device=dev, dtype=torch.bfloat16))
 
     def pro_only():
-        res["t"] = ops.prologue_forward(params, pro, q_lin, k_lin, v_lin, g_lin, rot, runner=runner)
+        res["t"] = ops.prologue_forward(params, pro, q_lin, k_lin, v_lin, g_lin, rot, runner=runner, out=bufs)
 
     ms = timed(pro_only)
     pq, pk_, pv, pg = res["t"]
@@ -743,7 +745,7 @@ def run_decode(args, dev, rank, world, peaks):
 
 # ------------------------------------------------------------------------------------ CPU oracle
 
-def cpu_baseline(cfg, seconds_hint=20, heads=4, T=None):
+def cpu_baseline(cfg, seconds_hint=20, heads=4, T=None, eager_gpu_too=False):
     """The CPU oracle (port of the reference's eager mixer) on a bounded sample of the prefill workload:
     batch 1, `heads` of the 16 heads, full length; throughput scaled by heads/16 (work is linear in heads)."""
     from oracle import kvm_oracle as ko
@@ -771,7 +773,35 @@ def cpu_baseline(cfg, seconds_hint=20, heads=4, T=None):
             times.append(time.perf_counter() - t0)
     best = sorted(times)[len(times) // 2] if times else first
     value = T * (heads / cfg["H"]) / cfg["B"] * cfg["B"] / best  # layer-equivalent tokens/s for one batch row stream
-    return {"value": round(value, 1), "unit": UNIT, "cores": threads, "kind": "port",
+    eager_gpu = None
+    if eager_gpu_too and torch.cuda.is_available():
+        # the same port with its tensors on the GPU: what the reference's eager (non-Triton) mixer costs on this B200
+        # (one PyTorch launch per operation of every block), on the whole workload
+        dev = torch.device("cuda", torch.cuda.current_device())
+        spec_f = ko.KvmSpec(cfg["H"], cfg["H"], D, D, cfg["rope"], cfg["C"], cfg["W"], cfg["cap_chunks"], cfg["sink"], "plus_one",
+                            state_min_len=cfg["C"])
+        gg = torch.Generator(device=dev).manual_seed(1)
+        mk = lambda *shape: torch.randn(*shape, generator=gg, device=dev)  # noqa: E731
+        Bf, Hf = cfg["B"], cfg["H"]
+        qg = torch.nn.functional.layer_norm(mk(Bf, T, Hf, D), (D,)).bfloat16().transpose(1, 2)
+        kg = torch.nn.functional.layer_norm(mk(Bf, T, Hf, D), (D,)).bfloat16().transpose(1, 2)
+        vg = mk(Bf, T, Hf, D).bfloat16().transpose(1, 2)
+        gateg = (1 + torch.nn.functional.elu(mk(Bf, T, Hf, 1))).bfloat16().transpose(1, 2)
+        tg = []
+        with torch.no_grad():
+            ko.prefill(spec_f, qg, kg, vg, gateg)
+            for _ in range(3):
+                torch.cuda.synchronize()
+                t0 = time.perf_counter()
+                ko.prefill(spec_f, qg, kg, vg, gateg)
+                torch.cuda.synchronize()
+                tg.append(time.perf_counter() - t0)
+        tgm = sorted(tg)[1]
+        eager_gpu = {"value": round(Bf * T / tgm, 1), "unit": UNIT, "ms_per_step": round(tgm * 1e3, 2),
+                     "sample": f"oracle/kvm_oracle.py prefill with CUDA tensors, the whole workload (B{Bf} x {Hf} heads x T={T}), median of 3"}
+        del qg, kg, vg, gateg
+        torch.cuda.empty_cache()
+    return {"value": round(value, 1), "unit": UNIT, "cores": threads, "kind": "port", "eager_port_on_this_gpu": eager_gpu,
             "sample": f"oracle/kvm_oracle.py prefill, bf16, batch 1 x {heads} of {cfg['H']} heads x T={T}, median of {len(times) or 1} runs "
                       f"({best:.2f} s each); value = T * ({heads}/{cfg['H']}) / time (work is linear in heads and batch)",
             "torch": torch.__version__}

@@ -283,7 +283,8 @@ int kvm_prologue_forward(const kvm_layer* layer, int32_t batch, int64_t seq_len,
   if (in->cos && in->rope_stride_b != 0 && in->rope_stride_b != seq_len * D)
     return fail(KVM_ERR_BAD_ARGUMENT, "rope_stride_b %lld must be 0 or seq_len*head_dim", (long long)in->rope_stride_b);
   const void* aligned[] = {in->q_lin, in->k_lin, in->v_lin, in->shift_q, in->shift_k, in->shift_v, in->prev_q, in->prev_k, in->prev_v,
-                           in->cos, in->sin, q_out, k_out, v_out};
+                           in->cos, in->sin, q_out, k_out, v_out, in->ln_q_w, in->ln_q_b, in->ln_k_w, in->ln_k_b,
+                           layer->ln_weight_dev, layer->ln_bias_dev};
   for (const void* a : aligned)
     if (((uintptr_t)a) % 16) return fail(KVM_ERR_BAD_ARGUMENT, "kvm_prologue_forward: tensors must be 16-byte aligned");
   kvm::PrologueDev p = {};

@@ -219,12 +219,14 @@ class PrologueParams:
 
 
 def prologue_forward(params: LayerParams, pro: PrologueParams, q_lin: torch.Tensor, k_lin: torch.Tensor, v_lin: torch.Tensor,
-                     gate_lin: torch.Tensor | None, position_embeddings, *, prev=None, runner: "PrefillRunner | None" = None):
+                     gate_lin: torch.Tensor | None, position_embeddings, *, prev=None, runner: "PrefillRunner | None" = None,
+                     out: tuple | None = None):
     """Token shift, q/k LayerNorm, rotary embedding and merge gate in one kernel over the projection outputs
     ([B,T,H*D] bf16).  Returns q [B,Hq,T,D], k, v [B,Hkv,T,D], gate [B,Hkv,T,1] as views of [B,T,H,D] / [B,Hkv,T]
     buffers, the layouts the reference hands its mixer (model/kvm_mixer.py:397-399).  With ``runner`` the prepared
     keys of the tokens that memory updates consume are written into that runner's workspace, and its ``run`` may
-    be called with ``keys_prepared=True``.  ``prev`` = (q, k, v) rows [B,1,H*D] of the previous call's last token."""
+    be called with ``keys_prepared=True``.  ``prev`` = (q, k, v) rows [B,1,H*D] of the previous call's last token.
+    ``out`` = preallocated (q [B,T,Hq,D], k, v [B,T,Hkv,D], gate [B,Hkv,T]) bf16 buffers to write into."""
     cfg = params.cfg
     B, T, _ = q_lin.shape
     D, Hq, Hkv = cfg.head_dim, cfg.n_q_heads, cfg.n_kv_heads
@@ -256,10 +258,16 @@ def prologue_forward(params: LayerParams, pro: PrologueParams, q_lin: torch.Tens
         arg.cos, arg.sin = cs[0].data_ptr(), cs[1].data_ptr()
         arg.rope_stride_b = 0 if cs[0].size(0) == 1 else T * D
     dev = q_lin.device
-    q = torch.empty(B, T, Hq, D, device=dev, dtype=torch.bfloat16)
-    k = torch.empty(B, T, Hkv, D, device=dev, dtype=torch.bfloat16)
-    v = torch.empty(B, T, Hkv, D, device=dev, dtype=torch.bfloat16)
-    gate = torch.empty(B, Hkv, T, device=dev, dtype=torch.bfloat16)
+    if out is not None:
+        q, k, v, gate = out
+        for t, shape in ((q, (B, T, Hq, D)), (k, (B, T, Hkv, D)), (v, (B, T, Hkv, D)), (gate, (B, Hkv, T))):
+            if tuple(t.shape) != shape or t.dtype != torch.bfloat16 or not t.is_contiguous() or t.device != dev:
+                raise ValueError(f"out buffer must be a contiguous bf16 tensor {shape} on {dev}, got {tuple(t.shape)} {t.dtype}")
+    else:
+        q = torch.empty(B, T, Hq, D, device=dev, dtype=torch.bfloat16)
+        k = torch.empty(B, T, Hkv, D, device=dev, dtype=torch.bfloat16)
+        v = torch.empty(B, T, Hkv, D, device=dev, dtype=torch.bfloat16)
+        gate = torch.empty(B, Hkv, T, device=dev, dtype=torch.bfloat16)
     ws_ptr, ws_bytes, ver_rows = None, 0, 0
     if runner is not None:
         if runner.batch != B or runner.plan.seq_len != T:
