@@ -34,19 +34,22 @@ __device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.lau
 template <int D, int NT, bool UPDATE, bool SB>
 __global__ void __launch_bounds__(NT, 1)
 kvm_decode_pre_kernel(LayerDev L, DecodeCacheDev cache, Tensor4 k, Tensor4 v, Tensor4 gate,
-                      const int* __restrict__ n_append_arr, bf16* pk_scr, int* route, int scope, int batch) {
+                      const int* __restrict__ n_append_arr, bf16* pk_scr, int* route, int scope, int batch, int nc) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
-  int row = blockIdx.x;
+  // `nc` CTAs (a thread-block cluster) share one kv row of a memory update: each scans its part of the memory and
+  // refreshes its share of the touched rows; rank 0 alone writes the new token
+  const int cta = (int)blockIdx.x / nc, crank = (int)blockIdx.x % nc;
+  int row = cta;
   if (scope == 2) {
     // Only the sequences with a memory update at this token, on a grid of just their rows (a CTA of this variant
     // takes a whole SM: a grid over all rows would queue hundreds of CTAs that return at once behind the few SMs
     // the attention of the other sequences leaves free): CTA j * Hkv + h belongs to the j-th updating sequence.
-    const int j = blockIdx.x / L.Hkv;
+    const int j = cta / L.Hkv;
     int found = -1, cnt = 0;
     for (int i = 0; i < batch && found < 0; ++i)
       if (n_append_arr[i] >= 0 && cnt++ == j) found = i;
     if (found < 0) return;
-    row = found * L.Hkv + (int)(blockIdx.x % L.Hkv);
+    row = found * L.Hkv + cta % L.Hkv;
   }
   const int b = row / L.Hkv, h = row % L.Hkv;
   pdl_wait();     // the previous token's attention kernel has advanced the lengths
@@ -87,11 +90,12 @@ kvm_decode_pre_kernel(LayerDev L, DecodeCacheDev cache, Tensor4 k, Tensor4 v, Te
       ViewStore view;  // decode keeps one live copy of the attention view: rows are refreshed in place
       view.k = m.k_attn; view.v = m.v_attn; view.cur = nullptr; view.ver_idx = nullptr; view.pool_next = 0;
       memory_update<D, NT, SB>(L, src, m, view, cap, S, n_app, pk_scr + (size_t)row * C * D,
-                               route ? route + (size_t)row * C : nullptr, s);
+                               route ? route + (size_t)row * C : nullptr, s, nc, crank);
     }
   }
-  // the new token
-  if (warp == 0) {
+  // the new token (behind the update: its ring slot may be one the leaving block has just been read from; with a
+  // cluster the update ends with a cluster-wide barrier, so every CTA has read the block by now)
+  if (warp == 0 && crank == 0) {
     const bf16* kp = k.row(b, h, 0);
     const bf16* vp = v.row(b, h, 0);
     const bf16 gt = *gate.row(b, h, 0);
@@ -117,6 +121,7 @@ kvm_decode_pre_kernel(LayerDev L, DecodeCacheDev cache, Tensor4 k, Tensor4 v, Te
 }
 
 // ------------------------------------------------------------------------------------- attention
+constexpr int kDecUpdateCluster = 2;                       // CTAs per kv row of a boundary update on the side stream
 constexpr int kDecConsumers = 8;                           // math warps (16 keys of every chunk each)
 constexpr int kDecThreads = (kDecConsumers + 1) * 32;      // + one producer warp
 constexpr int kDecChunk = kDecConsumers * 16;              // rows per pipeline stage
@@ -849,7 +854,7 @@ static cudaError_t launch_decode(const LayerDev& L, int batch, const DecodeCache
     // plain token: the two kernels are chained with programmatic dependent launches (`overlap` callers only)
     const bool pdl = overlap != 0;
     e = launch_pdl(kvm_decode_pre_kernel<D, 32, false, false>, dim3(rows), dim3(32), 0, stream, pdl, L, cache, k, v, gate,
-                   (const int*)nullptr, pk_scr, route, 0, batch);
+                   (const int*)nullptr, pk_scr, route, 0, batch, 1);
     if (e != cudaSuccess) return e;
     return attn(0, n_sm, nullptr, pdl);
   }
@@ -858,10 +863,15 @@ static cudaError_t launch_decode(const LayerDev& L, int batch, const DecodeCache
   auto upd = sb ? kvm_decode_pre_kernel<D, NT, true, true> : kvm_decode_pre_kernel<D, NT, true, false>;
   e = cudaFuncSetAttribute(upd, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_u);
   if (e != cudaSuccess) return e;
-  const int upd_sms = any_update * L.Hkv;  // SMs the updating rows occupy (one CTA each)
+  // A cluster of CTAs per updating kv row while the updating rows are few (the update is a chain of short phases:
+  // more CTAs per row shorten it, and the updated sequences' attention behind it gets their SMs)
+  int nc = 1;
+  for (int c = kDecUpdateCluster; c > 1; c >>= 1)
+    if (any_update * L.Hkv * c * 4 <= n_sm) { nc = c; break; }
+  const int upd_sms = any_update * L.Hkv * nc;  // SMs the updating rows occupy (one CTA each)
   DecodeSide* side = (overlap && any_update < batch && upd_sms * 2 <= n_sm) ? decode_side() : nullptr;
   if (!side) {  // one stream: update + ring write for every row, then attention over everything
-    upd<<<rows, NT, smem_u, stream>>>(L, cache, k, v, gate, n_append, pk_scr, route, 0, batch);
+    upd<<<rows, NT, smem_u, stream>>>(L, cache, k, v, gate, n_append, pk_scr, route, 0, batch, 1);
     e = cudaGetLastError();
     if (e != cudaSuccess) return e;
     return attn(0, n_sm, n_append);
@@ -869,14 +879,27 @@ static cudaError_t launch_decode(const LayerDev& L, int batch, const DecodeCache
   // fork: the updating sequences' rows on the side stream ...
   if ((e = cudaEventRecord(side->fork, stream)) != cudaSuccess) return e;
   if ((e = cudaStreamWaitEvent(side->stream, side->fork, 0)) != cudaSuccess) return e;
-  upd<<<any_update * L.Hkv, NT, smem_u, side->stream>>>(L, cache, k, v, gate, n_append, pk_scr, route, 2, batch);
-  if ((e = cudaGetLastError()) != cudaSuccess) return e;
+  {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(upd_sms);
+    cfg.blockDim = dim3(NT);
+    cfg.dynamicSmemBytes = smem_u;
+    cfg.stream = side->stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = nc;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    if ((e = cudaLaunchKernelEx(&cfg, upd, L, cache, k, v, gate, n_append, pk_scr, route, 2, batch, nc)) != cudaSuccess) return e;
+  }
   // ... followed there by their attention, on the SMs the update leaves (second launch counter of the workspace;
   // the two attention launches touch disjoint sequences, rows, partial slots and outputs)
   if ((e = attn(2, upd_sms, n_append, false, 1, side->stream)) != cudaSuccess) return e;
   if ((e = cudaEventRecord(side->join, side->stream)) != cudaSuccess) return e;
   // ... next to the ring write and the attention of all others, which leave those SMs free
-  kvm_decode_pre_kernel<D, 32, false, false><<<rows, 32, 0, stream>>>(L, cache, k, v, gate, n_append, pk_scr, route, 1, batch);
+  kvm_decode_pre_kernel<D, 32, false, false><<<rows, 32, 0, stream>>>(L, cache, k, v, gate, n_append, pk_scr, route, 1, batch, 1);
   if ((e = cudaGetLastError()) != cudaSuccess) return e;
   if ((e = attn(1, n_sm - upd_sms, n_append)) != cudaSuccess) return e;
   // join
