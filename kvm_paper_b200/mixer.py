@@ -366,7 +366,11 @@ class SequenceMixer(nn.Module):
         past_len = past_key_values.get_seq_length(self.layer_idx) if past_key_values is not None else 0
         if past_len == 0 and self.use_fused_prologue and attention_mask is None and self.fused_prologue_applies(x):
             return self._prompt_fused(x, v_first, position_embeddings, attention_mask, past_key_values, **kwargs)
-        q, k, v, gate = self.forward_prefix(x, v_first, position_embeddings, attention_mask, past_key_values, **kwargs)
+        if past_len > 0 and self.use_fused_prologue and attention_mask is None and self.fused_prologue_applies(x):
+            # cached single-token step: the same kernel, shifting against the previous call's last token
+            q, k, v, gate = self.forward_prefix_fused(x, v_first, position_embeddings, past_key_values)
+        else:
+            q, k, v, gate = self.forward_prefix(x, v_first, position_embeddings, attention_mask, past_key_values, **kwargs)
         fn = self.forward_single if past_len > 0 else self.forward_prefill
         return fn(q, k, v, gate, v_first, position_embeddings, attention_mask, past_key_values, **kwargs)
 
