@@ -238,7 +238,15 @@ def run_b200(args):
     runner = ops.PrefillRunner(params, B, plan)
     from kvm_paper_b200 import sharding
 
+    # N > 1: the attention kernel stores every tile of this rank's heads into all ranks' [B,T,H*D] buffers itself (peer
+    # stores over NVLink while other tiles are computed); `--nccl-gather` takes the all-gather + head-order copy instead
+    gathered = None
+    if world > 1 and not args.nccl_gather:
+        gathered = sharding.GatheredPrefillOutput(B, T, cfg["H"], D, dev)
+
     def step():
+        if gathered is not None:
+            return gathered.run(runner, q, k, v, gate)  # [B,T,H*D] on every rank, complete behind a one-word all-reduce
         out = runner.run(q, k, v, gate)
         return sharding.gather_heads(out, world)  # [B,T,H*D] on every rank (NCCL all-gather + the library's head-order copy)
 
@@ -283,6 +291,13 @@ def run_b200(args):
     chain_ms = time_phase(_lib.PREFILL_CHAIN, n_rep)
     attn_ms = time_phase(_lib.PREFILL_ATTENTION, n_rep)
     runner.run(q, k, v, gate)  # leave a whole prefill in the buffers (the status word belongs to a whole prefill)
+    gathered_ok = None
+    if gathered is not None:  # the self-gathered output holds this rank's heads exactly as the plain call computes them
+        full = step()
+        torch.cuda.synchronize()
+        gathered_ok = bool(torch.equal(full[:, :, rank * h_loc * D:(rank + 1) * h_loc * D], runner.out))
+        if world > 1:
+            dist.barrier()
     peaks = _peaks()
     pairs = attention_pairs(T, C, W, plan)
     attn_flops = 4.0 * D * pairs * B * h_loc          # QK^T and PV of this rank's heads
@@ -295,6 +310,8 @@ def run_b200(args):
 
     # ---- the timed kernels reported nothing, and what they computed is what the oracle computes (one head)
     check = {"prefill_status": "ok"}
+    if gathered_ok is not None:
+        check["self_gathered_output_equals_local"] = gathered_ok
     try:
         runner.check_status()
     except Exception as exc:  # a bounded device-side wait ran out: the number above is not a measurement
@@ -364,7 +381,8 @@ def run_b200(args):
                                     "block 256, +1 mean per block (cap 1024), post-QKV operator boundary")
                        if (B, T) == (4, 32768) else f"REDUCED profiling case of configs[1]: B{B} x T{T}",
                        "global_batch": B, "seq_len": T, "heads_per_gpu": h_loc,
-                       "parallelism": f"heads/{world}" + (" + all-gather of outputs" if world > 1 else ""),
+                       "parallelism": f"heads/{world}" + ("" if world == 1 else (" + all-gather of outputs" if gathered is None else
+                                                                                 " + outputs stored into every rank's buffer by the attention kernel (peer stores)")),
                        "l2": "inputs (1.6 GB) larger than L2, no flush needed"},
             # per step: prepared + gated keys, chain (routing and keys), value deltas, value rows, block attention
             "e2e": e2e, "gpu_launches": 5 * args.steps,
@@ -840,6 +858,7 @@ def main():
     ap.add_argument("--seq-len", type=int, default=None)
     ap.add_argument("--prefill-only", action="store_true", help="skip e2e, decode and the CPU baseline")
     ap.add_argument("--decode-only", action="store_true", help="run only the decode workload")
+    ap.add_argument("--nccl-gather", action="store_true", help="N > 1: gather the outputs with an NCCL all-gather instead of the attention kernel's peer stores")
     ap.add_argument("--long-context", action="store_true", help="BASELINE configs[4] (T=262144, 32 heads, block 512, 4096 means) instead of the default line")
     ap.add_argument("--decode-seqs", type=int, default=None)
     args = ap.parse_args()

@@ -126,6 +126,21 @@ int kvm_prefill_forward(const kvm_layer* layer, int32_t batch, int64_t seq_len,
                         kvm_memory memory, void* out, int32_t* route_dev,
                         void* workspace, size_t workspace_bytes, uint32_t phases, void* stream);
 
+/* kvm_prefill_forward for one rank of a head-sharded prefill whose block attention gathers the outputs by itself:
+ * `layer` describes this rank's heads, `out_bases[r]` is rank r's whole output [B, T, n_ranks * Hq * D] bf16 (addresses
+ * this process can write: its own buffer and peer mappings of the others'), and the attention kernel stores every
+ * tile of this rank's heads into columns [rank * Hq * D, (rank + 1) * Hq * D) of ALL of them (peer stores over NVLink,
+ * issued by the copy engine while other tiles are computed), so no collective follows.  A rank's buffer is complete
+ * once every rank's call has finished: the caller synchronises the ranks behind the call (and before the buffers are
+ * written again).  Needs the tensor-core attention kernel (head_dim 128, blocks of a multiple of 128 tokens).
+ * No counterpart in the reference (it is data-parallel only). */
+int kvm_prefill_forward_gathered(const kvm_layer* layer, int32_t batch, int64_t seq_len,
+                                 kvm_tensor4 q, kvm_tensor4 k, kvm_tensor4 v, kvm_tensor4 gate,
+                                 const kvm_update_plan* plan_dev, const kvm_update_plan* plan_host,
+                                 int32_t n_updates, int64_t total_version_rows, kvm_memory memory,
+                                 int32_t n_ranks, int32_t rank, void* const* out_bases, int32_t* route_dev,
+                                 void* workspace, size_t workspace_bytes, uint32_t phases, void* stream);
+
 /* Waits for `stream` and returns what the kernels of the last prefill on this workspace reported (the
  * status word is opened by a call that includes KVM_PREFILL_CHAIN and collects what that call and later
  * attention-only calls report): KVM_OK, or KVM_ERR_DEVICE_TIMEOUT if a bounded device-side wait

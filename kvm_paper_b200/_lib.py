@@ -65,6 +65,7 @@ EXPORTS = [
     "kvm_prefill_workspace_bytes", "kvm_prefill_forward", "kvm_decode_workspace_bytes", "kvm_decode_step",
     "kvm_memory_refresh", "kvm_last_error_string", "kvm_abi_version", "kvm_decode_step_static", "kvm_prefill_status", "kvm_decode_run",
     "kvm_decode_status", "kvm_prefill_workspace_layout", "kvm_interleave_shards", "kvm_prologue_forward",
+    "kvm_prefill_forward_gathered",
 ]
 STATIC_SCRATCH_BYTES = 32 << 20
 
@@ -88,6 +89,11 @@ def load():
     lib.kvm_prefill_forward.argtypes = [
         LP(KvmLayer), C.c_int32, C.c_int64, KvmTensor4, KvmTensor4, KvmTensor4, KvmTensor4,
         C.c_void_p, LP(KvmUpdatePlan), C.c_int32, C.c_int64, KvmMemory, C.c_void_p, C.c_void_p,
+        C.c_void_p, C.c_size_t, C.c_uint32, C.c_void_p]
+    lib.kvm_prefill_forward_gathered.restype = C.c_int
+    lib.kvm_prefill_forward_gathered.argtypes = [
+        LP(KvmLayer), C.c_int32, C.c_int64, KvmTensor4, KvmTensor4, KvmTensor4, KvmTensor4,
+        C.c_void_p, LP(KvmUpdatePlan), C.c_int32, C.c_int64, KvmMemory, C.c_int32, C.c_int32, LP(C.c_void_p), C.c_void_p,
         C.c_void_p, C.c_size_t, C.c_uint32, C.c_void_p]
     lib.kvm_prefill_status.restype = C.c_int
     lib.kvm_prefill_status.argtypes = [C.c_void_p, C.c_void_p]

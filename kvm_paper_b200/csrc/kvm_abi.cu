@@ -12,7 +12,7 @@ cudaError_t prefill_dispatch(int D, const LayerDev& L, int batch, long long T, T
                              Tensor4 gate, const kvm_update_plan* plan_dev, int n_plan, long long ver_rows,
                              MemoryDev mem, bf16* out, int* route, bf16* pool_k, bf16* pool_v, long long pool_rows,
                              int* ver_idx, bf16* pk_scr, bf16* pk_all, bf16* gk_all, int* route_ws, int* born_ws, unsigned* tbits_ws,
-                             int s_final, int* status, unsigned phases, cudaStream_t stream);
+                             int s_final, int* status, unsigned phases, cudaStream_t stream, const kvm::GatherDst* gd);
 size_t update_smem_bytes(int D, int C, int capacity);
 cudaError_t decode_dispatch(int D, const LayerDev& L, int batch, const DecodeCacheDev& cache, Tensor4 q, Tensor4 k,
                             Tensor4 v, Tensor4 gate, const int* n_append, int any_update, int max_rows, bf16* out,
@@ -203,11 +203,11 @@ size_t kvm_prefill_workspace_bytes(const kvm_layer* layer, int32_t batch, int64_
   return prefill_ws(layer, batch, seq_len, total_version_rows).total;
 }
 
-int kvm_prefill_forward(const kvm_layer* layer, int32_t batch, int64_t seq_len, kvm_tensor4 q, kvm_tensor4 k,
-                        kvm_tensor4 v, kvm_tensor4 gate, const kvm_update_plan* plan_dev,
-                        const kvm_update_plan* plan_host, int32_t n_updates, int64_t total_version_rows,
-                        kvm_memory memory, void* out, int32_t* route_dev, void* workspace, size_t workspace_bytes,
-                        uint32_t phases, void* stream) {
+static int prefill_forward_impl(const kvm_layer* layer, int32_t batch, int64_t seq_len, kvm_tensor4 q, kvm_tensor4 k,
+                                kvm_tensor4 v, kvm_tensor4 gate, const kvm_update_plan* plan_dev,
+                                const kvm_update_plan* plan_host, int32_t n_updates, int64_t total_version_rows,
+                                kvm_memory memory, void* out, int32_t* route_dev, void* workspace, size_t workspace_bytes,
+                                uint32_t phases, void* stream, const kvm::GatherDst* gd) {
   g_err[0] = 0;
   if (int rc = check_layer(layer)) return rc;
   if (batch <= 0 || seq_len <= 0) return fail(KVM_ERR_BAD_ARGUMENT, "batch %d and seq_len %lld must be positive", batch, (long long)seq_len);
@@ -260,9 +260,42 @@ int kvm_prefill_forward(const kvm_layer* layer, int32_t batch, int64_t seq_len, 
                                    reinterpret_cast<bf16*>(wsb + ws.gk_all), reinterpret_cast<int*>(wsb + ws.route),
                                    reinterpret_cast<int*>(wsb + ws.born), reinterpret_cast<unsigned*>(wsb + ws.tbits), (int)S,
                                    reinterpret_cast<int*>(wsb + ws.status), phases,
-                                   static_cast<cudaStream_t>(stream));
+                                   static_cast<cudaStream_t>(stream), gd);
+  if (e == cudaErrorNotSupported && gd)
+    return fail(KVM_ERR_UNSUPPORTED, "kvm_prefill_forward_gathered needs the tensor-core attention kernel (head_dim 128, blocks of a multiple of 128 tokens)");
   if (e != cudaSuccess) return cuda_fail(e, "kvm_prefill_forward");
   return KVM_OK;
+}
+
+int kvm_prefill_forward(const kvm_layer* layer, int32_t batch, int64_t seq_len, kvm_tensor4 q, kvm_tensor4 k,
+                        kvm_tensor4 v, kvm_tensor4 gate, const kvm_update_plan* plan_dev,
+                        const kvm_update_plan* plan_host, int32_t n_updates, int64_t total_version_rows,
+                        kvm_memory memory, void* out, int32_t* route_dev, void* workspace, size_t workspace_bytes,
+                        uint32_t phases, void* stream) {
+  return prefill_forward_impl(layer, batch, seq_len, q, k, v, gate, plan_dev, plan_host, n_updates, total_version_rows, memory, out,
+                              route_dev, workspace, workspace_bytes, phases, stream, nullptr);
+}
+
+int kvm_prefill_forward_gathered(const kvm_layer* layer, int32_t batch, int64_t seq_len, kvm_tensor4 q, kvm_tensor4 k,
+                                 kvm_tensor4 v, kvm_tensor4 gate, const kvm_update_plan* plan_dev,
+                                 const kvm_update_plan* plan_host, int32_t n_updates, int64_t total_version_rows,
+                                 kvm_memory memory, int32_t n_ranks, int32_t rank, void* const* out_bases,
+                                 int32_t* route_dev, void* workspace, size_t workspace_bytes, uint32_t phases, void* stream) {
+  g_err[0] = 0;
+  if (n_ranks < 2 || n_ranks > 8 || rank < 0 || rank >= n_ranks || !out_bases)
+    return fail(KVM_ERR_BAD_ARGUMENT, "kvm_prefill_forward_gathered: n_ranks %d must be 2..8, rank %d inside it, out_bases not NULL", n_ranks, rank);
+  kvm::GatherDst gd = {};
+  gd.n_ranks = n_ranks;
+  gd.rank = rank;
+  for (int r = 0; r < n_ranks; ++r) {
+    if (!out_bases[r] || ((uintptr_t)out_bases[r]) % 16)
+      return fail(KVM_ERR_BAD_ARGUMENT, "kvm_prefill_forward_gathered: output buffer of rank %d is NULL or not 16-byte aligned", r);
+    gd.base[r] = out_bases[r];
+  }
+  if (layer && (layer->head_dim != 128 || layer->chunk_len % 128 != 0 || (phases & KVM_PREFILL_LEGACY_ATTENTION)))
+    return fail(KVM_ERR_UNSUPPORTED, "kvm_prefill_forward_gathered needs the tensor-core attention kernel (head_dim 128, blocks of a multiple of 128 tokens)");
+  return prefill_forward_impl(layer, batch, seq_len, q, k, v, gate, plan_dev, plan_host, n_updates, total_version_rows, memory,
+                              out_bases[rank], route_dev, workspace, workspace_bytes, phases, stream, &gd);
 }
 
 int kvm_prologue_forward(const kvm_layer* layer, int32_t batch, int64_t seq_len, const kvm_prologue* in, void* q_out,

@@ -93,6 +93,10 @@ struct Slice {
 struct AttnMaps {
   CUtensorMap q, k, v, o;  // o: the output [B, T, Hq, D] with boxes of 64 elements x 128 tokens
   int q_head_inner, kv_head_inner;  // the head dimension has the smaller stride ([B,T,H,D] storage): it comes second
+  // head-sharded prefill that gathers by itself: `o` and `o_peer` describe every rank's [B, T, n_ranks*Hq, D] buffer
+  // (this rank's first), the CTA stores its tile into each at head `h_off + hq`
+  CUtensorMap o_peer[7];
+  int n_peer, h_off;
 };
 // box at (element x, token t, head h, batch b) of a tensor whose dimensions are ordered by stride
 __device__ __forceinline__ void attn_tma(void* dst, const CUtensorMap* m, bool head_inner, int x, int t, int h, int b,
@@ -372,8 +376,15 @@ __device__ __forceinline__ bool softmax_role(const Slice<NQ>& sl, const LayerDev
     if (!warp_wait(&bars->o_ready[qi], 0)) return false;
     if (lane == 0) {
       const int qs = (int)(sl.q0 + (long long)qi * BM);
-      tc::tma_store_4d(&maps->o, dO, 0, sl.hq, qs, sl.b);
-      tc::tma_store_4d(&maps->o, dO + 16384, 64, sl.hq, qs, sl.b);
+      const int hh = sl.hq + maps->h_off;
+      tc::tma_store_4d(&maps->o, dO, 0, hh, qs, sl.b);
+      tc::tma_store_4d(&maps->o, dO + 16384, 64, hh, qs, sl.b);
+      // the same tile into the other ranks' buffers (peer memory over NVLink: the gather of the outputs rides on the
+      // copy engine while the other CTAs compute)
+      for (int pr = 0; pr < maps->n_peer; ++pr) {
+        tc::tma_store_4d(&maps->o_peer[pr], dO, 0, hh, qs, sl.b);
+        tc::tma_store_4d(&maps->o_peer[pr], dO + 16384, 64, hh, qs, sl.b);
+      }
       tc::bulk_commit_group();
       tc::bulk_wait_group_read0();  // shared memory must outlive the copy
     }
@@ -491,7 +502,8 @@ kvm_attn_prefill_tc_kernel(LayerDev L, long long T, Tensor4 q, Tensor4 k, Tensor
 template <int NQ>
 static cudaError_t launch_nq(const LayerDev& L, int batch, long long T, Tensor4 q, Tensor4 k, Tensor4 v,
                              const kvm_update_plan* plan_dev, const bf16* pool_k, const bf16* pool_v, long long pool_rows,
-                             const int* ver_idx, long long ver_rows, bf16* out, int* status, cudaStream_t stream) {
+                             const int* ver_idx, long long ver_rows, bf16* out, int* status, cudaStream_t stream,
+                             const GatherDst* gd) {
   using CF = Cfg<NQ>;
   const int n_qblocks = (int)((T + L.C - 1) / L.C);
   const int ctas_per_block = L.C / (BM * NQ);
@@ -515,14 +527,24 @@ static cudaError_t launch_nq(const LayerDev& L, int batch, long long T, Tensor4 
   maps.q_head_inner = q.sh < q.st ? 1 : 0;
   maps.kv_head_inner = k.sh < k.st ? 1 : 0;
   if ((v.sh < v.st) != (k.sh < k.st)) return cudaErrorInvalidValue;  // keys and values share one layout
-  Tensor4 o4;  // the output [B, T, Hq*D] seen as [batch][head][token][D]
-  o4.ptr = out;
-  o4.sb = T * (long long)L.Hq * HD;
-  o4.st = (long long)L.Hq * HD;
+  const int out_heads = gd ? L.Hq * gd->n_ranks : L.Hq;
+  Tensor4 o4;  // the output [B, T, heads*D] seen as [batch][head][token][D]
+  o4.ptr = gd ? static_cast<const bf16*>(gd->base[gd->rank]) : out;
+  o4.sb = T * (long long)out_heads * HD;
+  o4.st = (long long)out_heads * HD;
   o4.sh = HD;
   if (!encode(&maps.q, q, L.Hq, BM, maps.q_head_inner != 0) || !encode(&maps.k, k, L.Hkv, BN, maps.kv_head_inner != 0) ||
-      !encode(&maps.v, v, L.Hkv, BN, maps.kv_head_inner != 0) || !encode(&maps.o, o4, L.Hq, BM, true))
+      !encode(&maps.v, v, L.Hkv, BN, maps.kv_head_inner != 0) || !encode(&maps.o, o4, out_heads, BM, true))
     return cudaErrorInvalidValue;
+  maps.n_peer = 0;
+  maps.h_off = gd ? gd->rank * L.Hq : 0;
+  if (gd) {
+    for (int r = 0; r < gd->n_ranks; ++r) {
+      if (r == gd->rank) continue;
+      o4.ptr = static_cast<const bf16*>(gd->base[r]);
+      if (!encode(&maps.o_peer[maps.n_peer++], o4, out_heads, BM, true)) return cudaErrorInvalidValue;
+    }
+  }
   dim3 grid(n_qblocks * ctas_per_block, batch * L.Hq);
   kvm_attn_prefill_tc_kernel<NQ><<<grid, CF::kThreads, CF::kSmemBytes, stream>>>(
       L, T, q, k, v, plan_dev, pool_k, pool_v, pool_rows, ver_idx, ver_rows, out, ctas_per_block,
@@ -533,10 +555,12 @@ static cudaError_t launch_nq(const LayerDev& L, int batch, long long T, Tensor4 
 
 cudaError_t launch_attn_tc(const LayerDev& L, int batch, long long T, Tensor4 q, Tensor4 k, Tensor4 v,
                            const kvm_update_plan* plan_dev, const bf16* pool_k, const bf16* pool_v, long long pool_rows,
-                           const int* ver_idx, long long ver_rows, bf16* out, int* status, cudaStream_t stream) {
+                           const int* ver_idx, long long ver_rows, bf16* out, int* status, cudaStream_t stream,
+                           const GatherDst* gd) {
+  if (gd && (gd->n_ranks < 2 || gd->n_ranks > 8 || gd->rank < 0 || gd->rank >= gd->n_ranks)) return cudaErrorInvalidValue;
   if (L.C % 256 == 0)
-    return launch_nq<2>(L, batch, T, q, k, v, plan_dev, pool_k, pool_v, pool_rows, ver_idx, ver_rows, out, status, stream);
-  return launch_nq<1>(L, batch, T, q, k, v, plan_dev, pool_k, pool_v, pool_rows, ver_idx, ver_rows, out, status, stream);
+    return launch_nq<2>(L, batch, T, q, k, v, plan_dev, pool_k, pool_v, pool_rows, ver_idx, ver_rows, out, status, stream, gd);
+  return launch_nq<1>(L, batch, T, q, k, v, plan_dev, pool_k, pool_v, pool_rows, ver_idx, ver_rows, out, status, stream, gd);
 }
 
 }  // namespace kvm

@@ -34,6 +34,14 @@ struct Tensor4 {
   }
 };
 
+// Where the block attention of a head-sharded prefill puts its output when it gathers by itself: every rank's
+// [B, T, n_ranks * Hq * D] buffer (peer-mapped addresses); this rank's heads go to columns [rank * Hq * D, (rank + 1) * Hq * D)
+// of all of them.
+struct GatherDst {
+  int n_ranks, rank;
+  void* base[8];
+};
+
 // Arguments of the fused prologue kernel (the projections' outputs, the module's parameters, the outputs).
 struct PrologueDev {
   const bf16* q_lin;

@@ -440,14 +440,15 @@ cudaError_t launch_chain_tc(const LayerDev& L, int batch, long long T, Tensor4 v
                             int* status, uint32_t wait_limit, uint32_t test_flags, cudaStream_t stream);
 cudaError_t launch_attn_tc(const LayerDev& L, int batch, long long T, Tensor4 q, Tensor4 k, Tensor4 v,
                            const kvm_update_plan* plan_dev, const bf16* pool_k, const bf16* pool_v, long long pool_rows,
-                           const int* ver_idx, long long ver_rows, bf16* out, int* status, cudaStream_t stream);
+                           const int* ver_idx, long long ver_rows, bf16* out, int* status, cudaStream_t stream,
+                           const GatherDst* gd);
 
 template <int D>
 static cudaError_t launch_prefill(const LayerDev& L, int batch, long long T, Tensor4 q, Tensor4 k, Tensor4 v, Tensor4 gate,
                                   const kvm_update_plan* plan_dev, int n_plan, long long ver_rows, MemoryDev mem,
                                   bf16* out, int* route, bf16* pool_k, bf16* pool_v, long long pool_rows, int* ver_idx,
                                   bf16* pk_scr, bf16* pk_all, bf16* gk_all, int* route_ws, int* born_ws, unsigned* tbits_ws,
-                                  int s_final, int* status, unsigned phases, cudaStream_t stream) {
+                                  int s_final, int* status, unsigned phases, cudaStream_t stream, const GatherDst* gd) {
   constexpr int NT = 512;
   const int rows = batch * L.Hkv;
   const int n_qblocks = (int)((T + L.C - 1) / L.C);
@@ -519,9 +520,10 @@ static cudaError_t launch_prefill(const LayerDev& L, int batch, long long T, Ten
   if constexpr (D == 128) {
     // tcgen05 / tensor-memory kernel: head_dim 128 and blocks that are whole 128-row query tiles
     if (L.C % 128 == 0 && !(phases & KVM_PREFILL_LEGACY_ATTENTION))
-      return launch_attn_tc(L, batch, T, q, k, v, plan_dev, pool_k, pool_v, pool_rows, ver_idx, ver_rows, out, status, stream);
+      return launch_attn_tc(L, batch, T, q, k, v, plan_dev, pool_k, pool_v, pool_rows, ver_idx, ver_rows, out, status, stream, gd);
   }
 
+  if (gd) return cudaErrorNotSupported;  // only the tcgen05 attention kernel stores into the other ranks' buffers
   constexpr int BM = 64;
   const int tiles_per_block = (L.C + BM - 1) / BM;
   const size_t smem_a = attn_smem_bytes<D>();
@@ -537,11 +539,11 @@ cudaError_t prefill_dispatch(int D, const LayerDev& L, int batch, long long T, T
                              Tensor4 gate, const kvm_update_plan* plan_dev, int n_plan, long long ver_rows,
                              MemoryDev mem, bf16* out, int* route, bf16* pool_k, bf16* pool_v, long long pool_rows,
                              int* ver_idx, bf16* pk_scr, bf16* pk_all, bf16* gk_all, int* route_ws, int* born_ws, unsigned* tbits_ws,
-                             int s_final, int* status, unsigned phases, cudaStream_t stream) {
+                             int s_final, int* status, unsigned phases, cudaStream_t stream, const GatherDst* gd) {
   switch (D) {
-    case 32: return launch_prefill<32>(L, batch, T, q, k, v, gate, plan_dev, n_plan, ver_rows, mem, out, route, pool_k, pool_v, pool_rows, ver_idx, pk_scr, pk_all, gk_all, route_ws, born_ws, tbits_ws, s_final, status, phases, stream);
-    case 64: return launch_prefill<64>(L, batch, T, q, k, v, gate, plan_dev, n_plan, ver_rows, mem, out, route, pool_k, pool_v, pool_rows, ver_idx, pk_scr, pk_all, gk_all, route_ws, born_ws, tbits_ws, s_final, status, phases, stream);
-    case 128: return launch_prefill<128>(L, batch, T, q, k, v, gate, plan_dev, n_plan, ver_rows, mem, out, route, pool_k, pool_v, pool_rows, ver_idx, pk_scr, pk_all, gk_all, route_ws, born_ws, tbits_ws, s_final, status, phases, stream);
+    case 32: return launch_prefill<32>(L, batch, T, q, k, v, gate, plan_dev, n_plan, ver_rows, mem, out, route, pool_k, pool_v, pool_rows, ver_idx, pk_scr, pk_all, gk_all, route_ws, born_ws, tbits_ws, s_final, status, phases, stream, gd);
+    case 64: return launch_prefill<64>(L, batch, T, q, k, v, gate, plan_dev, n_plan, ver_rows, mem, out, route, pool_k, pool_v, pool_rows, ver_idx, pk_scr, pk_all, gk_all, route_ws, born_ws, tbits_ws, s_final, status, phases, stream, gd);
+    case 128: return launch_prefill<128>(L, batch, T, q, k, v, gate, plan_dev, n_plan, ver_rows, mem, out, route, pool_k, pool_v, pool_rows, ver_idx, pk_scr, pk_all, gk_all, route_ws, born_ws, tbits_ws, s_final, status, phases, stream, gd);
   }
   return cudaErrorInvalidValue;
 }

@@ -325,6 +325,29 @@ class PrefillRunner:
         _lib.check(rc)
         return self.out
 
+    def run_gathered(self, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, gate: torch.Tensor, rank: int, out_ptrs: list[int],
+                     phases: int = _lib.PREFILL_CHAIN | _lib.PREFILL_ATTENTION, *, keys_prepared: bool = False) -> None:
+        """One rank of a head-sharded prefill whose attention kernel writes this rank's heads into every rank's
+        [B,T,world*Hq*D] output (``out_ptrs``: addresses of all ranks' buffers as this process sees them, see
+        ``sharding.GatheredPrefillOutput``).  Nothing is returned: a buffer is complete once every rank's call has
+        finished (the caller synchronises the ranks)."""
+        cfg, plan = self.params.cfg, self.plan
+        B, Hq, T, D = q.shape
+        if (B, Hq, D) != (self.batch, cfg.n_q_heads, cfg.head_dim) or k.shape != (B, cfg.n_kv_heads, T, D) or v.shape != k.shape:
+            raise ValueError(f"shape mismatch: q {tuple(q.shape)}, k {tuple(k.shape)}, v {tuple(v.shape)} for {cfg}")
+        if gate.shape != (B, cfg.n_kv_heads, T, 1) or T != plan.seq_len:
+            raise ValueError("merge gate must be [B,Hkv,T,1] and the plan built for this sequence length")
+        if keys_prepared:
+            phases |= _lib.PREFILL_KEYS_PREPARED
+        q, k, v, gate = (_as_bf16_view(t) for t in (q, k, v, gate))
+        bases = (C.c_void_p * len(out_ptrs))(*out_ptrs)
+        rc = _lib.load().kvm_prefill_forward_gathered(
+            C.byref(self.params.c), B, T, _tensor4(q, "q"), _tensor4(k, "k"), _tensor4(v, "v"), _tensor4(gate, "gate"),
+            self.plan_dev.data_ptr(), self.plan_host, plan.n_updates, plan.total_version_rows, self.memory.c(),
+            len(out_ptrs), int(rank), bases, _ptr(self.route), self.ws.data_ptr(), self.ws_bytes, phases,
+            _stream_ptr(self.params.device))
+        _lib.check(rc)
+
     def check_status(self) -> None:
         """Synchronise and raise if a kernel of the last run reported a device-side timeout."""
         rc = _lib.load().kvm_prefill_status(self.ws.data_ptr(), _stream_ptr(self.params.device))

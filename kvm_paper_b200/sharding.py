@@ -2,7 +2,8 @@
 
 Every (batch, kv-head) pair owns an independent memory and window, so no term of the mixer crosses heads
 or sequences: each rank runs the kernels on its slice and the only collective is one all-gather of the
-mixer outputs (NCCL over NVLink on GPUs, gloo on CPU ranks in the tests).  The reference has no
+mixer outputs (NCCL over NVLink on GPUs, gloo on CPU ranks in the tests), or no collective at all where the block
+attention kernel stores its tiles into every rank's output itself (``GatheredPrefillOutput``).  The reference has no
 counterpart (it is data-parallel only).
 """
 
@@ -49,6 +50,35 @@ def gather_heads(out_local: torch.Tensor, world: int, group=None) -> torch.Tenso
         _lib.check(rc)
         return full
     return buf.view(world, B, T, hd).permute(1, 2, 0, 3).reshape(B, T, world * hd)
+
+
+class GatheredPrefillOutput:
+    """Output buffers of a head-sharded prefill that every rank's attention kernel writes into directly (peer stores
+    over NVLink), so that no collective follows the kernels: each rank holds ``n_buffers`` tensors [B, T, H*D] in
+    symmetric memory and knows its peers' addresses of them.  ``run`` enqueues this rank's prefill and returns the
+    buffer that holds all heads once every rank has finished, which a small all-reduce behind the kernels establishes
+    (stream-ordered on every rank).  The buffers alternate, so that a rank that is already in its next call does not
+    write into a buffer a slower rank's consumer is still reading."""
+
+    def __init__(self, batch: int, seq_len: int, n_q_heads_total: int, head_dim: int, device, group=None, n_buffers: int = 2):
+        import torch.distributed._symmetric_memory as symm_mem
+        self.group = group if group is not None else dist.group.WORLD
+        self.rank, self.world = dist.get_rank(self.group), dist.get_world_size(self.group)
+        self.buffers, self.ptrs = [], []
+        for _ in range(n_buffers):
+            t = symm_mem.empty((batch, seq_len, n_q_heads_total * head_dim), dtype=torch.bfloat16, device=device)
+            hdl = symm_mem.rendezvous(t, self.group)
+            self.buffers.append(t)
+            self.ptrs.append([int(p) for p in hdl.buffer_ptrs])
+        self._flag = torch.zeros(1, device=device, dtype=torch.int32)
+        self._turn = 0
+
+    def run(self, runner, q, k, v, gate, **kwargs) -> torch.Tensor:
+        i = self._turn
+        self._turn = (i + 1) % len(self.buffers)
+        runner.run_gathered(q, k, v, gate, self.rank, self.ptrs[i], **kwargs)
+        dist.all_reduce(self._flag, group=self.group)  # behind every rank's kernels: all tiles have been stored everywhere
+        return self.buffers[i]
 
 
 def sequence_shard(n_seq: int, rank: int, world: int) -> slice:

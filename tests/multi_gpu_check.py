@@ -1,5 +1,6 @@
 """Run under torchrun on N GPUs: head-sharded prefill and sequence-sharded decode, gathered over NCCL, must
-equal the single-GPU result bit for bit (sharding changes no arithmetic).  Prints MULTI_GPU_OK on rank 0."""
+equal the single-GPU result bit for bit (sharding changes no arithmetic); so must the prefill whose attention kernel
+gathers by itself (peer stores).  Prints MULTI_GPU_OK on rank 0."""
 
 import os
 import sys
@@ -35,6 +36,18 @@ def main():
     _, _, res = gh.device_prefill(local, ql, kl, vl, gl, want_route=False)
     y = sharding.gather_heads(res.out, world)
     ok = True
+    # the same prefill with the attention kernel storing its tiles into every rank's output itself (no collective):
+    # every rank's buffer must equal the NCCL-gathered output, on both of the alternating buffers
+    gathered = sharding.GatheredPrefillOutput(B, T, Hq, D, torch.device("cuda"))
+    dev_in = [t.to("cuda", torch.bfloat16) for t in (ql, kl, vl, gl)]
+    for turn in range(3):
+        y2 = gathered.run(res.runner, *dev_in)
+        torch.cuda.synchronize()
+        if not torch.equal(y2, y):
+            d = (y2.float() - y.float()).abs()
+            print(f"rank {rank}: gathered prefill (call {turn}) differs from the all-gathered one: max abs", float(d.max()), flush=True)
+            ok = False
+        dist.barrier()  # nobody writes into a buffer that a peer is still comparing
     if rank == 0:
         _, _, ref = gh.device_prefill(full, q, k, v, gate, want_route=False)
         ok = torch.equal(y, ref.out)
