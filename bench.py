@@ -559,8 +559,11 @@ def run_long_context(args):
     v = torch.randn(1, T, h_loc, D, generator=g, device=dev).bfloat16().transpose(1, 2)
     gate = (1 + torch.nn.functional.elu(0.5 * torch.randn(1, T, h_loc, 1, generator=g, device=dev))).bfloat16().transpose(1, 2)
     runner = ops.PrefillRunner(params, 1, plan)
+    gathered = sharding.GatheredPrefillOutput(1, T, H, D, dev) if world > 1 and not args.nccl_gather else None
 
     def step():
+        if gathered is not None:
+            return gathered.run(runner, q, k, v, gate)
         return sharding.gather_heads(runner.run(q, k, v, gate), world)
 
     def barrier():
@@ -611,7 +614,8 @@ def run_long_context(args):
             "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
             "config": {"workload": "BASELINE configs[4]: long-context KVM layer, B1 x T262144, 32 heads x 128, block 512, power-law "
                                    "memory capped at 4096 means, keys from 64 Gaussian clusters, post-QKV operator boundary",
-                       "seq_len": T, "heads_per_gpu": h_loc, "parallelism": f"heads/{world}" + (" + all-gather of outputs" if world > 1 else ""),
+                       "seq_len": T, "heads_per_gpu": h_loc, "parallelism": f"heads/{world}" + ("" if world == 1 else (" + all-gather of outputs" if gathered is None else
+                                                                                 " + outputs stored into every rank's buffer by the attention kernel (peer stores)")),
                        "final_means": plan.final_state_len, "updates": plan.n_updates,
                        "chain_kernel": "general chain kernel (blocks of 512 tokens)"},
             "chain_ms": round(chain_ms, 3), "attention_ms": round(attn_ms, 3), "attention_tflops": round(tf, 1),
