@@ -242,7 +242,14 @@ def run_b200(args):
     # stores over NVLink while other tiles are computed); `--nccl-gather` takes the all-gather + head-order copy instead
     gathered = None
     if world > 1 and not args.nccl_gather:
-        gathered = sharding.GatheredPrefillOutput(B, T, cfg["H"], D, dev)
+        try:
+            gathered = sharding.GatheredPrefillOutput(B, T, cfg["H"], D, dev)
+        except Exception as exc:  # no peer access between these GPUs: the collective instead (the line says which ran)
+            print(f"[bench] symmetric memory unavailable ({exc}); gathering with NCCL", file=sys.stderr)
+        ok_all = torch.tensor([1 if gathered is not None else 0], device=dev)
+        dist.all_reduce(ok_all, op=dist.ReduceOp.MIN)  # every rank takes the same route
+        if int(ok_all.item()) == 0:
+            gathered = None
 
     def step():
         if gathered is not None:
