@@ -151,6 +151,21 @@ def test_abi_argument_errors_are_reported_without_a_device():
     assert rc == 2 and b"capacity" in lib.kvm_last_error_string()
     with pytest.raises(_lib.KvmError):
         _lib.check(rc)
+    # the self-gathering prefill: rank count, rank, buffer addresses and kernel shape are checked before anything else
+    bases = (ctypes.c_void_p * 2)(4096, 8192)
+    args = (ctypes.byref(layer), 1, 40, t4, t4, t4, t4, 8, plan, 0, 0, mem)
+    tail = (None, 256, 1 << 20, 3, None)
+    assert lib.kvm_prefill_forward_gathered(*args, 1, 0, bases, *tail) == 1 and b"n_ranks" in lib.kvm_last_error_string()
+    assert lib.kvm_prefill_forward_gathered(*args, 2, 2, bases, *tail) == 1
+    bad = (ctypes.c_void_p * 2)(4096, 8200)
+    assert lib.kvm_prefill_forward_gathered(*args, 2, 0, bad, *tail) == 1 and b"aligned" in lib.kvm_last_error_string()
+    assert lib.kvm_prefill_forward_gathered(*args, 2, 0, bases, *tail) == 5 and b"head_dim 128" in lib.kvm_last_error_string()
+    # the prologue: token-shift scales for all of q, k, v or for none
+    pro = _lib.KvmPrologue()
+    pro.q_lin = pro.k_lin = pro.v_lin = 4096
+    pro.shift_q = 4096
+    rc = lib.kvm_prologue_forward(ctypes.byref(layer), 1, 40, ctypes.byref(pro), 4096, 4096, 4096, 4096, 0, None, 0, None)
+    assert rc == 1 and b"token-shift" in lib.kvm_last_error_string()
 
 
 def test_mixer_error_conventions():
