@@ -82,15 +82,18 @@ struct Layout {
     rowi = off; off += sp * 4u + sp * 2u + ((2u * Rcap + 15u) & ~15u);  // cur[sp] i32, gci[sp] i16, lci[Rcap] i16 (by local row)
     tloc = off; off += ((2u * C + 15u) & ~15u) + 2u * sp;  // touched_local[C] u16, stamps[sp] u16 (update that last touched the row)
     stat = part;                                         // LayerNorm partial sums of the scatter epilogue (the routing partials are dead by then)
-    bars = off; off += 384u;
+    bars = off; off += 448u;
     total = (off + 15u) & ~15u;
   }
 };
 
 struct Bars {
   uint64_t full_p, full_g;              // TMA arrivals of the block's prepared / gated keys
-  uint64_t tm_full[2];                  // MMAs of a chunk complete, per tile of 128 tokens
-  uint64_t tm_empty[2];                 // ... and read back
+  // MMAs of a chunk complete, per tile of 128 tokens / ... and read back.  With at most 128 resident rows per CTA the
+  // 256 accumulator columns of a token tile hold two chunks: consecutive passes alternate between the halves (first
+  // index), so that a pass is issued while the workers still read the one before it
+  uint64_t tm_full[2][2];
+  uint64_t tm_empty[2][2];
   uint64_t w2i;                         // workers -> issuer: shared-memory operands are ready
   uint64_t sc_done;                     // scatter MMAs complete
   uint64_t xbar[2];                     // arrivals of the peers' partial results (two in flight)
@@ -103,7 +106,7 @@ struct Bars {
 };
 
 static_assert(kNewRows <= kWorkerWarps, "one warp per appended row in the short path");
-static_assert(sizeof(Bars) <= 384, "the barrier block outgrew its shared-memory region");
+static_assert(sizeof(Bars) <= 448, "the barrier block outgrew its shared-memory region");
 
 struct Args {
   LayerDev L;
@@ -226,6 +229,10 @@ struct Issuer {
   uint32_t g = 0;        // chunks issued so far
   uint32_t n_w2i = 0, n_sc = 0, n_load = 0, n_zero = 0;
   volatile int* abort;
+  // accumulator half and per-barrier phase of chunk number gg (see Bars::tm_full): with at most 128 resident rows per
+  // CTA consecutive chunks alternate between the halves of a token tile's 256 columns
+  __device__ __forceinline__ int acc_half(uint32_t gg) const { return lay.Rcap <= 128 ? (int)(gg & 1u) : 0; }
+  __device__ __forceinline__ int acc_phase(uint32_t gg) const { return lay.Rcap <= 128 ? (int)(gg >> 1) : (int)gg; }
 
   // Update u of this CTA's rows is complete in global memory (routes, version table): tell the CTAs that work on the
   // value side.  Called behind a wait for all worker warps, whose writes this thread's fence makes visible with the flag.
@@ -277,16 +284,17 @@ struct Issuer {
       const uint32_t idesc = tc::make_idesc(128, (n + 15) & ~15, 0, 0);
       const uint64_t db0 = d_r + (uint64_t)((uint32_t)(c * kChunk * 128) >> 4);
       for (int m = which; m < n_mt; m += kIssuers) {
-        if (g >= 1 && !wait(&bars->tm_empty[m], (g - 1) & 1, a.wait_limit, abort)) return false;
+        const int hb = acc_half(g), ph = acc_phase(g);
+        if (ph >= 1 && !wait(&bars->tm_empty[hb][m], (ph - 1) & 1, a.wait_limit, abort)) return false;
         tc::tc_fence_after_sync();
         const uint64_t da0 = da_base + (uint64_t)((uint32_t)(m * 128 * 128) >> 4);
-        const uint32_t d = tmem + (uint32_t)(m * kChunk);
+        const uint32_t d = tmem + (uint32_t)(m * kChunk + hb * 128);
 #pragma unroll 1
         for (int ks = 0; ks < HD / 16; ++ks) {
           const uint32_t lo = (uint32_t)(ks & 3) * 2u;
           tc::mma_ss(d, da0 + (uint64_t)(((ks >> 2) ? a_half : 0u) + lo), db0 + (uint64_t)(((ks >> 2) ? r_half : 0u) + lo), idesc, ks > 0);
         }
-        if (!(withhold_first_commit && c == 0 && m == 0)) tc::mma_commit_own_cta(&bars->tm_full[m]);
+        if (!(withhold_first_commit && c == 0 && m == 0)) tc::mma_commit_own_cta(&bars->tm_full[hb][m]);
       }
     }
     return true;
@@ -298,16 +306,17 @@ struct Issuer {
     constexpr uint32_t idesc = tc::make_idesc(128, kNewRows, 0, 0);
     constexpr uint32_t n_half = (uint32_t)(kNewRows * 128) >> 4;
     for (int m = which; m < n_mt; m += kIssuers) {
-      if (g >= 1 && !wait(&bars->tm_empty[m], (g - 1) & 1, a.wait_limit, abort)) return false;
+      const int hb = acc_half(g), ph = acc_phase(g);
+      if (ph >= 1 && !wait(&bars->tm_empty[hb][m], (ph - 1) & 1, a.wait_limit, abort)) return false;
       tc::tc_fence_after_sync();
       const uint64_t da0 = d_g + (uint64_t)((uint32_t)(m * 128 * 128) >> 4);
-      const uint32_t d = tmem + (uint32_t)(m * kChunk);
+      const uint32_t d = tmem + (uint32_t)(m * kChunk + hb * 128);
 #pragma unroll 1
       for (int ks = 0; ks < HD / 16; ++ks) {
         const uint32_t lo = (uint32_t)(ks & 3) * 2u;
         tc::mma_ss(d, da0 + (uint64_t)(((ks >> 2) ? a_half : 0u) + lo), d_new + (uint64_t)(((ks >> 2) ? n_half : 0u) + lo), idesc, ks > 0);
       }
-      tc::mma_commit_own_cta(&bars->tm_full[m]);
+      tc::mma_commit_own_cta(&bars->tm_full[hb][m]);
     }
     ++g;
     return true;
@@ -425,6 +434,10 @@ struct Workers {
   uint32_t g = 0, n_sc = 0, n_x = 0, n_load = 0, n_zero = 0;
   int pool_next = 0;
   unsigned mine_mask = 0;  // lanes whose row (a multiple of 32 + lane) belongs to this CTA
+  // accumulator half and per-barrier phase of chunk number gg (see Bars::tm_full): with at most 128 resident rows per
+  // CTA consecutive chunks alternate between the halves of a token tile's 256 columns
+  __device__ __forceinline__ int acc_half(uint32_t gg) const { return lay.Rcap <= 128 ? (int)(gg & 1u) : 0; }
+  __device__ __forceinline__ int acc_phase(uint32_t gg) const { return lay.Rcap <= 128 ? (int)(gg >> 1) : (int)gg; }
 
   __device__ __forceinline__ float* nov() const { return reinterpret_cast<float*>(smem + lay.tok); }
   __device__ __forceinline__ int* idx() const { return reinterpret_cast<int*>(smem + lay.tok) + a.L.C; }
@@ -473,7 +486,8 @@ struct Workers {
     bool ok = true;
     for (int c = 0; c < n_chunks; ++c, ++g) {
       if (!active) continue;
-      ok = ok && wait(&bars->tm_full[mt], g & 1, a.wait_limit, abort);
+      const int hb = acc_half(g), ph = acc_phase(g);
+      ok = ok && wait(&bars->tm_full[hb][mt], ph & 1, a.wait_limit, abort);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;  // the caller aborts
       tc::tc_fence_after_sync();
@@ -482,7 +496,7 @@ struct Workers {
       const int g_begin = half ? g_half : 0, g_end = half ? n_groups : g_half;
       for (int gi = g_begin; gi < g_end; ++gi) {
         uint32_t r[32];
-        tc::tmem_ld32(tmem + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(mt * kChunk + gi * 32), r);
+        tc::tmem_ld32(tmem + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(mt * kChunk + hb * 128 + gi * 32), r);
         tc::tmem_ld_wait();
         const int l0 = c * kChunk + gi * 32;  // local row of column 0
         const bool full = l0 + 32 <= n_rows && l0 >= l_min;
@@ -514,7 +528,7 @@ struct Workers {
       }
       tc::tc_fence_before_sync();
       __syncwarp();
-      if (lane == 0) tc::mbar_arrive(&bars->tm_empty[mt]);
+      if (lane == 0) tc::mbar_arrive(&bars->tm_empty[hb][mt]);
     }
     float v = bv[0];
     int i = bi[0];
@@ -860,12 +874,13 @@ struct Workers {
           // higher index, it wins only with a strictly larger logit
           const int mt = (warp >> 2) & 1;
           if (mt * 128 < C) {
-            okm = wait(&bars->tm_full[mt], g & 1, a.wait_limit, abort);
+            const int hb = acc_half(g), ph = acc_phase(g);
+            okm = wait(&bars->tm_full[hb][mt], ph & 1, a.wait_limit, abort);
             okm = __all_sync(0xffffffffu, okm);
             if (okm && warp * 32 < C) {
               tc::tc_fence_after_sync();
               uint32_t r16[16];
-              tc::tmem_ld16(tmem + ((uint32_t)((warp & 3) * 32) << 16) + (uint32_t)(mt * kChunk), r16);
+              tc::tmem_ld16(tmem + ((uint32_t)((warp & 3) * 32) << 16) + (uint32_t)(mt * kChunk + hb * 128), r16);
               tc::tmem_ld_wait();
 #pragma unroll
               for (int j = 0; j < kNewRows; ++j) {
@@ -875,7 +890,7 @@ struct Workers {
               tc::tc_fence_before_sync();
             }
             __syncwarp();
-            if (lane == 0) tc::mbar_arrive(&bars->tm_empty[mt]);
+            if (lane == 0) tc::mbar_arrive(&bars->tm_empty[hb][mt]);
           }
           ++g;
         }
@@ -1120,8 +1135,10 @@ kvm_chain_tc_kernel(const __grid_constant__ Args a, const __grid_constant__ Maps
     tc::mbar_init(&bars->full_p, 1);
     tc::mbar_init(&bars->full_g, 1);
     for (int i = 0; i < 2; ++i) {
-      tc::mbar_init(&bars->tm_full[i], 1);
-      tc::mbar_init(&bars->tm_empty[i], 8);  // the eight warps that read a token tile
+      for (int hb = 0; hb < 2; ++hb) {
+        tc::mbar_init(&bars->tm_full[hb][i], 1);
+        tc::mbar_init(&bars->tm_empty[hb][i], 8);  // the eight warps that read a token tile
+      }
     }
     tc::mbar_init(&bars->w2i, kWorkerWarps);
     tc::mbar_init(&bars->sc_done, 1);
