@@ -245,6 +245,40 @@ __device__ __forceinline__ void layer_norm_row(RowVec<D, GL>& r, const float* __
   }
 }
 
+// The same LayerNorm for weights in GLOBAL memory at a 16-byte aligned address (the streaming passes over all keys: the
+// prefill's prepared-key pass and the fused prologue, which must give the same bits): weights by 16-byte loads, two
+// results rounded per conversion instruction.  The arithmetic per element is that of layer_norm_row.
+template <int D, int GL>
+__device__ __forceinline__ void layer_norm_row_g(RowVec<D, GL>& r, const float* __restrict__ w, const float* __restrict__ b,
+                                                 float eps, int gl) {
+  constexpr int EPL = D / GL;
+  static_assert(EPL % 4 == 0, "a lane's share starts at a multiple of four elements");
+  float s = 0.f;
+#pragma unroll
+  for (int i = 0; i < EPL; ++i) s += r.x[i];
+  float mean = group_sum<GL>(s) * (1.0f / D);
+  float q = 0.f;
+#pragma unroll
+  for (int i = 0; i < EPL; ++i) {
+    float d = r.x[i] - mean;
+    q += d * d;
+  }
+  float var = group_sum<GL>(q) * (1.0f / D);
+  float rstd = 1.0f / sqrtf(var + eps);
+  const float4* w4 = reinterpret_cast<const float4*>(w + gl * EPL);
+  const float4* b4 = reinterpret_cast<const float4*>(b + gl * EPL);
+#pragma unroll
+  for (int i = 0; i < EPL; i += 4) {
+    const float4 wv = __ldg(w4 + i / 4), bv = __ldg(b4 + i / 4);
+    r.x[i] = (r.x[i] - mean) * rstd * wv.x + bv.x;
+    r.x[i + 1] = (r.x[i + 1] - mean) * rstd * wv.y + bv.y;
+    r.x[i + 2] = (r.x[i + 2] - mean) * rstd * wv.z + bv.z;
+    r.x[i + 3] = (r.x[i + 3] - mean) * rstd * wv.w + bv.w;
+    const float2 r01 = unpack_bf16(pack_bf16(r.x[i], r.x[i + 1])), r23 = unpack_bf16(pack_bf16(r.x[i + 2], r.x[i + 3]));
+    r.x[i] = r01.x; r.x[i + 1] = r01.y; r.x[i + 2] = r23.x; r.x[i + 3] = r23.y;
+  }
+}
+
 // L2 norm of a row held by a lane group.
 template <int D, int GL = 32>
 __device__ __forceinline__ float row_norm(const RowVec<D, GL>& r) {

@@ -80,38 +80,6 @@ __device__ __forceinline__ void qk_layer_norm(RowVec<D, GL>& r, const float* __r
   }
 }
 
-// The prepared key's LayerNorm: the arithmetic of layer_norm_row (the prefill's own pass uses that one, and both must
-// give the same bits), with the weights fetched by 16-byte loads.
-template <int D>
-__device__ __forceinline__ void prepared_key_layer_norm(RowVec<D, GL>& r, const float* __restrict__ w, const float* __restrict__ b,
-                                                        float eps, int gl) {
-  constexpr int EPL = D / GL;
-  float s = 0.f;
-#pragma unroll
-  for (int i = 0; i < EPL; ++i) s += r.x[i];
-  float mean = group_sum<GL>(s) * (1.0f / D);
-  float q = 0.f;
-#pragma unroll
-  for (int i = 0; i < EPL; ++i) {
-    float d = r.x[i] - mean;
-    q += d * d;
-  }
-  float var = group_sum<GL>(q) * (1.0f / D);
-  float rstd = 1.0f / sqrtf(var + eps);
-  const float4* w4 = reinterpret_cast<const float4*>(w + gl * EPL);
-  const float4* b4 = reinterpret_cast<const float4*>(b + gl * EPL);
-#pragma unroll
-  for (int i = 0; i < EPL; i += 4) {
-    const float4 wv = __ldg(w4 + i / 4), bv = __ldg(b4 + i / 4);
-    r.x[i] = (r.x[i] - mean) * rstd * wv.x + bv.x;
-    r.x[i + 1] = (r.x[i + 1] - mean) * rstd * wv.y + bv.y;
-    r.x[i + 2] = (r.x[i + 2] - mean) * rstd * wv.z + bv.z;
-    r.x[i + 3] = (r.x[i + 3] - mean) * rstd * wv.w + bv.w;
-    round2(r.x[i], r.x[i + 1]);
-    round2(r.x[i + 2], r.x[i + 3]);
-  }
-}
-
 template <int EPL>
 __device__ __forceinline__ void store_raw(const uint32_t (&w)[EPL / 2], bf16* p) {
   if constexpr (EPL % 8 == 0) {
@@ -214,7 +182,7 @@ kvm_prologue_kernel(LayerDev L, PrologueDev p, long long T) {
     r.x[2 * i] = (gl * EPL + 2 * i < L.rope_dim) ? 0.f : f.x;
     r.x[2 * i + 1] = (gl * EPL + 2 * i + 1 < L.rope_dim) ? 0.f : f.y;
   }
-  prepared_key_layer_norm<D>(r, L.ln_w, L.ln_b, L.ln_eps, gl);
+  layer_norm_row_g<D, GL>(r, L.ln_w, L.ln_b, L.ln_eps, gl);
   const size_t po = (((size_t)b * L.Hkv + h) * p.n_tok + t) * D;
   if (consumed) store_row<D, GL>(r, p.pk_all + po, gl);
   if (p.gk_all && consumed) {
